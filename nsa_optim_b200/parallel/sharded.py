@@ -1,0 +1,471 @@
+"""Sharded-parameter data-parallel runtime (the framework's replacement for PyTorch FSDP).
+
+What the reference does with FSDP1 (nngabe/nsa_optim train.py:171-208): one flat parameter
+per block class instance plus a root unit for embedding / final norm / head, bf16
+all-gather before use, fp32 reduce-scatter of gradients, ``FULL_SHARD`` for Adam-family
+optimizers and ``SHARD_GRAD_OP`` for SOAP / Shampoo.
+
+Design here
+-----------
+* **Unit** = one block (or the root).  Its parameters live in one flat buffer in the compute
+  dtype; every parameter starts on a 256-element boundary (so 8-bit optimizer blocks and
+  16-byte TMA alignment never straddle parameters) and the buffer is padded to
+  ``world * 256`` elements.  Rank r owns elements ``[r*S, (r+1)*S)``.
+* **Execution** goes through one ``autograd.Function`` per block call.  With activation
+  checkpointing the function saves only the block input and recomputes in backward;
+  without it the block's local graph is kept and replayed.  Either way the function is the
+  single place where gathers, reshards and gradient reduction are ordered, on explicit
+  streams, with no module hooks.
+* **Strategies**: ``FULL_SHARD`` frees the gathered buffer after forward and re-gathers in
+  backward; ``SHARD_GRAD_OP`` keeps it between forward and backward; ``NO_SHARD`` (world 1)
+  touches nothing.  On 180 GB parts ``SHARD_GRAD_OP`` is the default whenever the gathered
+  model fits comfortably: one all-gather and one reduce-scatter per unit per optimizer step.
+* **Gradients**: after a unit's backward its parameter gradients are packed into an fp32
+  flat buffer, reduce-scattered (sum, then 1/world), and accumulated into the rank's fp32
+  gradient shard.  Optimizers see per-parameter *pieces*: 1-D views of the owned shard with
+  ``.grad`` views of the gradient shard, named like the original parameters.
+* **Clipping** uses the true global norm (sum of squares over disjoint shards, one
+  all-reduce) and hands the coefficient to the optimizer as a device scalar: no host sync.
+* **Communication back ends**: ``nccl``/``gloo`` collectives through ``torch.distributed``
+  (the measured baseline and the oracle) or ``fused`` peer-memory kernels from
+  ``parallel/symm.py`` when available.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from enum import Enum
+from typing import Any, Callable, Dict, Iterable, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+from torch import Tensor
+
+from . import dist as pdist
+
+ALIGN = 256
+
+
+class ShardingStrategy(str, Enum):
+    FULL_SHARD = "full_shard"
+    SHARD_GRAD_OP = "shard_grad_op"
+    NO_SHARD = "no_shard"
+
+
+@dataclass
+class ParamSlot:
+    name: str
+    shape: Tuple[int, ...]
+    offset: int
+    numel: int
+    param: nn.Parameter
+
+
+def _round_up(x: int, m: int) -> int:
+    return -(-x // m) * m
+
+
+class FlatUnit:
+    """One communication unit: layout, owned shard, gathered buffer, gradient shard."""
+
+    def __init__(self, name: str, module: Optional[nn.Module], named_params: List[Tuple[str, nn.Parameter]],
+                 world: int, rank: int, device: torch.device, dtype: torch.dtype,
+                 reduce_dtype: torch.dtype = torch.float32):
+        self.name, self.module = name, module
+        self.world, self.rank, self.device, self.dtype, self.reduce_dtype = world, rank, device, dtype, reduce_dtype
+        self.slots: List[ParamSlot] = []
+        off = 0
+        for n, p in named_params:
+            self.slots.append(ParamSlot(n, tuple(p.shape), off, p.numel(), p))
+            off = _round_up(off + p.numel(), ALIGN)
+        self.total = _round_up(max(off, ALIGN), world * ALIGN)
+        self.shard_size = self.total // world
+        # gathered buffer; parameters become views of an alias with its own version counter
+        self.full = torch.zeros(self.total, dtype=dtype, device=device)
+        for s in self.slots:
+            self.full[s.offset:s.offset + s.numel].copy_(s.param.detach().reshape(-1).to(dtype))
+        self._point_params()
+        lo = rank * self.shard_size
+        self.shard = self.full[lo:lo + self.shard_size].clone() if world > 1 else self.full
+        self.grad_shard = torch.zeros(self.shard_size, dtype=torch.float32, device=device)
+        self.gathered = True
+        self.ready_event = None          # CUDA event: gathered buffer is valid
+        self.reduce_event = None         # CUDA event: gradient shard holds this step's reduction
+        self.pieces: List[Tuple[str, nn.Parameter]] = []
+        self._build_pieces()
+
+    # ---- parameter views
+    def _point_params(self) -> None:
+        alias = self.full.data
+        for s in self.slots:
+            s.param.data = alias[s.offset:s.offset + s.numel].view(s.shape)
+
+    def _build_pieces(self) -> None:
+        """Per-parameter views of the owned shard, exposed to optimizers."""
+        lo, hi = self.rank * self.shard_size, (self.rank + 1) * self.shard_size
+        self.pieces = []
+        for s in self.slots:
+            a, b = max(lo, s.offset), min(hi, _round_up(s.offset + s.numel, ALIGN))
+            if b <= a or a >= s.offset + s.numel:
+                continue
+            whole = (a == s.offset and b >= s.offset + s.numel)
+            if whole and self.world == 1:
+                piece = s.param                       # NO_SHARD: the parameter itself
+                piece._logical_numel = s.numel
+                self.pieces.append((s.name, piece))
+                continue
+            # padded end: pieces of quantised states must cover whole 256-blocks
+            b_eff = min(b, hi)
+            view = self.shard[a - lo:b_eff - lo]
+            piece = nn.Parameter(view, requires_grad=True)
+            gview = self.grad_shard[a - lo:b_eff - lo]
+            if view.dtype == gview.dtype:
+                piece.grad = gview
+            else:
+                piece._fp32_grad = gview
+            piece._logical_numel = s.numel
+            piece._is_matrix = len(s.shape) >= 2
+            piece._no_weight_decay = getattr(s.param, "_no_weight_decay", False) or len(s.shape) == 1
+            if whole and len(s.shape) == 2 and (b_eff - a) == s.numel:
+                piece._orig_2d_shape = s.shape
+            self.pieces.append((s.name, piece))
+
+    # ---- memory
+    def free_full(self) -> None:
+        if self.world > 1 and self.gathered:
+            self.full.untyped_storage().resize_(0)
+            self.gathered = False
+
+    def alloc_full(self) -> None:
+        if not self.gathered:
+            self.full.untyped_storage().resize_(self.total * self.full.element_size())
+
+    def nbytes_full(self) -> int:
+        return self.total * self.full.element_size()
+
+
+class _UnitFunction(torch.autograd.Function):
+    """Runs one block as one autograd node; owns gather / recompute / gradient reduction."""
+
+    @staticmethod
+    def forward(ctx, runtime: "ShardedModel", unit: FlatUnit, hidden: Tensor, *args):
+        ctx.runtime, ctx.unit, ctx.args = runtime, unit, args
+        runtime._pre_forward(unit)
+        if runtime.activation_checkpointing:
+            with torch.no_grad():
+                out = unit.module(hidden, *args)
+            ctx.save_for_backward(hidden)
+            ctx.local = None
+        else:
+            with torch.enable_grad():
+                h = hidden.detach().requires_grad_(True)
+                out_g = unit.module(h, *args)
+            ctx.local = (h, out_g)
+            out = out_g.detach()
+        runtime._post_forward(unit)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out: Tensor):
+        runtime, unit = ctx.runtime, ctx.unit
+        runtime._pre_backward(unit)
+        if ctx.local is None:
+            (hidden,) = ctx.saved_tensors
+            with torch.enable_grad():
+                h = hidden.detach().requires_grad_(True)
+                out_g = unit.module(h, *ctx.args)
+        else:
+            h, out_g = ctx.local
+            ctx.local = None
+        torch.autograd.backward(out_g, grad_out)
+        runtime._post_backward(unit)
+        return (None, None, h.grad) + (None,) * len(ctx.args)
+
+
+class ShardedModel(nn.Module):
+    """Wraps a model from ``nsa_optim_b200.models`` for sharded data-parallel training."""
+
+    def __init__(self, model: nn.Module, info: Optional[pdist.DistInfo] = None,
+                 strategy: "ShardingStrategy | str | None" = None,
+                 param_dtype: Optional[torch.dtype] = None, reduce_dtype: torch.dtype = torch.float32,
+                 activation_checkpointing: Optional[bool] = None, comm: str = "auto",
+                 process_group=None):
+        super().__init__()
+        self.module = model
+        self.info = info or pdist.DistInfo(device=next(model.parameters()).device)
+        self.world, self.rank = self.info.world_size, self.info.rank
+        self.group = process_group
+        device = self.info.device
+        dtype = param_dtype or next(model.parameters()).dtype
+        model.to(device=device)
+        if self.world == 1:
+            strategy = ShardingStrategy.NO_SHARD
+        elif strategy is None:
+            strategy = ShardingStrategy.SHARD_GRAD_OP
+        self.strategy = ShardingStrategy(strategy)
+        if activation_checkpointing is None:
+            activation_checkpointing = bool(getattr(model, "gradient_checkpointing", False))
+        self.activation_checkpointing = activation_checkpointing
+        self.comm_mode = self._resolve_comm(comm)
+        # ---- units: root first (gathered for the whole step), then one per block
+        blocks = model.block_modules()
+        root_named = model.root_parameters()
+        self.root = FlatUnit("root", None, root_named, self.world, self.rank, device, dtype, reduce_dtype)
+        self.units: List[FlatUnit] = []
+        prefix = "layers."
+        for i, blk in enumerate(blocks):
+            named = [(f"{prefix}{i}.{n}", p) for n, p in blk.named_parameters()]
+            self.units.append(FlatUnit(f"{prefix}{i}", blk, named, self.world, self.rank, device, dtype, reduce_dtype))
+        self._unit_of = {id(u.module): u for u in self.units}
+        # buffers (rotary caches etc.) just move with the module
+        for b in model.buffers():
+            if b.is_floating_point() and b.dtype != torch.float32 and b.dtype != dtype:
+                b.data = b.data.to(dtype)
+        model.set_layer_runner(self._run_layer)
+        self._cuda = device.type == "cuda"
+        self.comm_stream = torch.cuda.Stream(device=device) if (self._cuda and self.world > 1) else None
+        self._order: List[FlatUnit] = []
+        self._micro_steps = 0
+        self.launch_counter = 0
+        if self.world > 1 and self.strategy == ShardingStrategy.FULL_SHARD:
+            for u in self.units:
+                u.free_full()
+
+    # ------------------------------------------------------------------ comm selection
+    def _resolve_comm(self, comm: str) -> str:
+        if self.world == 1:
+            return "none"
+        if comm in ("nccl", "gloo", "torch"):
+            return "torch"
+        if comm == "fused":
+            return "fused"
+        return "torch"
+
+    # ------------------------------------------------------------------ gather / reduce
+    def all_units(self) -> List[FlatUnit]:
+        return [self.root] + self.units
+
+    def _gather(self, unit: FlatUnit, async_: bool = True) -> None:
+        if self.world == 1 or unit.gathered:
+            return
+        unit.alloc_full()
+        if self.comm_stream is not None:
+            self.comm_stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self.comm_stream):
+                pdist.all_gather_flat(unit.full, unit.shard, self.group)
+                unit.ready_event = torch.cuda.Event()
+                unit.ready_event.record(self.comm_stream)
+            unit.full.record_stream(self.comm_stream)
+        else:
+            pdist.all_gather_flat(unit.full, unit.shard, self.group)
+        unit.gathered = True
+
+    def _wait_ready(self, unit: FlatUnit) -> None:
+        if unit.ready_event is not None:
+            torch.cuda.current_stream().wait_event(unit.ready_event)
+            unit.ready_event = None
+
+    def _reduce_grads(self, unit: FlatUnit) -> None:
+        """Pack parameter gradients, reduce-scatter, accumulate 1/world of the sum."""
+        if self.world == 1:
+            return
+        flat = torch.zeros(unit.total, dtype=unit.reduce_dtype, device=unit.device)
+        for s in unit.slots:
+            g = s.param.grad
+            if g is not None:
+                flat[s.offset:s.offset + s.numel].copy_(g.reshape(-1))
+                s.param.grad = None
+        out = torch.empty(unit.shard_size, dtype=unit.reduce_dtype, device=unit.device)
+        if self.comm_stream is not None:
+            self.comm_stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self.comm_stream):
+                pdist.reduce_scatter_flat(out, flat, self.group)
+                unit.grad_shard.add_(out, alpha=1.0 / self.world)
+                unit.reduce_event = torch.cuda.Event()
+                unit.reduce_event.record(self.comm_stream)
+            flat.record_stream(self.comm_stream)
+            out.record_stream(self.comm_stream)
+        else:
+            pdist.reduce_scatter_flat(out, flat, self.group)
+            unit.grad_shard.add_(out.float(), alpha=1.0 / self.world)
+
+    # ------------------------------------------------------------------ unit lifecycle
+    def _neighbour(self, unit: FlatUnit, step: int) -> Optional[FlatUnit]:
+        i = self.units.index(unit) + step
+        return self.units[i] if 0 <= i < len(self.units) else None
+
+    def _pre_forward(self, unit: FlatUnit) -> None:
+        self._gather(unit)
+        nxt = self._neighbour(unit, +1)
+        if nxt is not None:
+            self._gather(nxt)
+        self._wait_ready(unit)
+
+    def _post_forward(self, unit: FlatUnit) -> None:
+        if self.strategy == ShardingStrategy.FULL_SHARD:
+            unit.free_full()
+
+    def _pre_backward(self, unit: FlatUnit) -> None:
+        self._gather(unit)
+        prv = self._neighbour(unit, -1)
+        if prv is not None and self.strategy == ShardingStrategy.FULL_SHARD:
+            self._gather(prv)
+        self._wait_ready(unit)
+
+    def _post_backward(self, unit: FlatUnit) -> None:
+        self._reduce_grads(unit)
+        if self.strategy == ShardingStrategy.FULL_SHARD:
+            unit.free_full()
+
+    def _run_layer(self, layer: nn.Module, hidden: Tensor, *args) -> Tensor:
+        unit = self._unit_of[id(layer)]
+        if not (torch.is_grad_enabled() and self.module.training):
+            self._pre_forward(unit)
+            out = layer(hidden, *args)
+            if self.strategy == ShardingStrategy.FULL_SHARD:
+                unit.free_full()
+            return out
+        if self.world == 1 and not self.activation_checkpointing:
+            return layer(hidden, *args)
+        return _UnitFunction.apply(self, unit, hidden, *args)
+
+    # ------------------------------------------------------------------ public step API
+    def forward(self, *args, **kwargs):
+        self._gather(self.root)
+        self._wait_ready(self.root)
+        if self.units:
+            self._gather(self.units[0])
+        return self.module(*args, **kwargs)
+
+    def backward(self, loss: Tensor) -> None:
+        """``loss.backward()`` followed by the root unit's gradient reduction."""
+        loss.backward()
+        self._reduce_grads(self.root)
+        self._micro_steps += 1
+
+    def regather_all(self) -> None:
+        """After an optimizer step the gathered copies are stale: mark and (for the keeping
+        strategies) re-issue every all-gather on the communication stream."""
+        if self.world == 1:
+            return
+        for u in self.all_units():
+            u.gathered = False
+            if self.strategy != ShardingStrategy.FULL_SHARD or u is self.root:
+                self._gather(u)
+            else:
+                u.full.untyped_storage().resize_(0)
+
+    def wait_reductions(self) -> None:
+        if self.comm_stream is not None:
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        if self.world == 1:
+            for p in self.module.parameters():
+                p.grad = None
+            return
+        for u in self.all_units():
+            u.grad_shard.zero_()
+            for s in u.slots:
+                s.param.grad = None
+
+    # ------------------------------------------------------------------ optimizer view
+    def named_optimizer_parameters(self) -> List[Tuple[str, nn.Parameter]]:
+        out = []
+        for u in self.all_units():
+            out.extend(u.pieces)
+        return out
+
+    def local_grads(self) -> List[Tensor]:
+        if self.world == 1:
+            return [p.grad for p in self.module.parameters() if p.grad is not None]
+        return [u.grad_shard for u in self.all_units()]
+
+    def clip_grad_norm(self, max_norm: float, local_only: bool = False) -> Tuple[Tensor, Optional[Tensor]]:
+        """-> (global gradient norm, clip coefficient or None).  Both stay on the device; the
+        coefficient is meant for ``optimizer.step(grad_scale=coef)``.  ``local_only`` reproduces
+        the reference's behaviour of clipping by the local shard's norm (train.py:268-277)."""
+        self.wait_reductions()
+        grads = self.local_grads()
+        if not grads:
+            z = torch.zeros((), device=self.info.device)
+            return z, None
+        sq = torch.stack([g.float().pow(2).sum() for g in grads]).sum()
+        if self.world > 1 and not local_only:
+            pdist.all_reduce_sum(sq, self.group)
+        norm = sq.sqrt()
+        if max_norm is None or max_norm <= 0:
+            return norm, None
+        coef = (max_norm / (norm + 1e-6)).clamp(max=1.0)
+        return norm, coef
+
+    # ------------------------------------------------------------------ state dicts
+    def _full_unit_tensor(self, u: FlatUnit) -> Tensor:
+        if self.world == 1:
+            return u.full
+        out = torch.empty(u.total, dtype=u.dtype, device=u.device)
+        self.wait_reductions()
+        pdist.all_gather_flat(out, u.shard, self.group)
+        return out
+
+    def state_dict(self, rank0_only: bool = True, *args, **kwargs) -> Dict[str, Tensor]:
+        """Full (unsharded) CPU state dict with the wrapped model's key names."""
+        sd: Dict[str, Tensor] = {}
+        keep = (not rank0_only) or self.rank == 0
+        for u in self.all_units():
+            full = self._full_unit_tensor(u)
+            if keep:
+                for s in u.slots:
+                    sd[s.name] = full[s.offset:s.offset + s.numel].view(s.shape).detach().cpu().clone()
+        if keep:
+            params = {n for n, _ in self.module.named_parameters()}
+            for k, v in self.module.state_dict().items():
+                if k not in params:
+                    sd[k] = v.detach().cpu().clone()
+            order = list(self.module.state_dict().keys())
+            sd = {k: sd[k] for k in order if k in sd}
+        return sd
+
+    def load_state_dict(self, state_dict: Dict[str, Tensor], strict: bool = True):
+        missing = []
+        for u in self.all_units():
+            u.alloc_full()
+            for s in u.slots:
+                if s.name in state_dict:
+                    u.full[s.offset:s.offset + s.numel].copy_(state_dict[s.name].reshape(-1).to(u.dtype))
+                else:
+                    missing.append(s.name)
+            u.gathered = True
+            if self.world > 1:
+                lo = self.rank * u.shard_size
+                u.shard.copy_(u.full[lo:lo + u.shard_size])
+        bufs = {n for n, _ in self.module.named_buffers()}
+        for k, v in state_dict.items():
+            if k in bufs:
+                self.module.get_buffer(k).copy_(v)
+        if strict and missing:
+            raise KeyError(f"missing keys in state_dict: {missing[:5]}{'...' if len(missing) > 5 else ''}")
+        if self.world > 1 and self.strategy == ShardingStrategy.FULL_SHARD:
+            for u in self.units:
+                u.free_full()
+        return missing
+
+    def piece_map(self) -> Dict[int, Tuple[FlatUnit, ParamSlot, int, int]]:
+        """id(piece) -> (unit, slot, start offset of the piece inside the parameter, length)."""
+        out = {}
+        for u in self.all_units():
+            lo = u.rank * u.shard_size
+            by_name = {s.name: s for s in u.slots}
+            for name, piece in u.pieces:
+                s = by_name[name]
+                if piece is s.param:
+                    out[id(piece)] = (u, s, 0, s.numel)
+                else:
+                    a = max(lo, s.offset)
+                    out[id(piece)] = (u, s, a - s.offset, piece.numel())
+        return out
+
+
+def wrap_model(model: nn.Module, info: Optional[pdist.DistInfo] = None, **kwargs) -> ShardedModel:
+    return ShardedModel(model, info, **kwargs)
