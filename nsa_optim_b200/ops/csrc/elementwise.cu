@@ -1,0 +1,692 @@
+// Bandwidth-bound kernels: RMSNorm / gated RMSNorm / L2 norm (forward + backward),
+// SwiGLU, rotary embedding, causal depthwise conv1d (+SiLU), embedding gather and its
+// deterministic scatter-add backward.  bf16 storage, fp32 arithmetic, 16-byte accesses.
+//
+// Row kernels keep a whole row in registers (one global read per element).  Rows up to 512
+// elements use one warp per row, longer rows (up to 8192) use one 256-thread CTA per row.
+// Weight gradients of the norms and the convolution are reduced deterministically:
+// a persistent grid accumulates per-CTA partial sums into a scratch buffer
+// [grid, width] (fp32) that a second kernel adds up in a fixed order.
+#include "host.cuh"
+#include <cuda_bf16.h>
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ void load8(const bf16* p, float (&v)[8]) {
+  uint4 u = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f = __bfloat1622float2(h[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void store8(bf16* p, const float (&v)[8]) {
+  uint4 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf(-x)); }
+// d/dx silu(x)
+__device__ __forceinline__ float dsilu_f(float x) {
+  float s = sigmoid_f(x);
+  return s * (1.f + x * (1.f - s));
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+// Sum over the TPR threads that share a row.  TPR == 32: warp; TPR == 256: whole CTA.
+template <int TPR>
+__device__ __forceinline__ float row_sum(float v, float* red) {
+  v = warp_sum(v);
+  if (TPR == 32) return v;
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int i = 0; i < TPR / 32; ++i) t += red[i];
+  return t;
+}
+
+// ------------------------------------------------------------------------------------
+// (gated) RMSNorm.  MODE 0: y = x*rstd*w.   MODE 1: y = x*rstd*w * silu(g)   (norm, then gate)
+//                   MODE 2: u = x*silu(g); y = u*rstd(u)*w                    (gate, then norm)
+// ------------------------------------------------------------------------------------
+template <int TPR, int NV, int MODE>
+__global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ g,
+                                                          const bf16* __restrict__ w, bf16* __restrict__ y,
+                                                          float* __restrict__ rstd_out, long rows, int d, float eps) {
+  __shared__ float red[8];
+  const int rows_per_cta = 256 / TPR;
+  const long row = static_cast<long>(blockIdx.x) * rows_per_cta + threadIdx.x / TPR;
+  const int t = threadIdx.x % TPR;
+  const bool active = row < rows;
+  float xv[NV][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (t + i * TPR) * 8;
+    if (active && c < d) {
+      load8(x + row * d + c, xv[i]);
+      if (MODE == 2) {
+        float gv[8];
+        load8(g + row * d + c, gv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) xv[i][j] *= silu_f(gv[j]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += xv[i][j] * xv[i][j];
+    }
+  }
+  ss = row_sum<TPR>(ss, red);
+  const float rstd = rsqrtf(ss / d + eps);
+  if (active && t == 0 && rstd_out) rstd_out[row] = rstd;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (t + i * TPR) * 8;
+    if (active && c < d) {
+      float wv[8], o[8];
+      load8(w + c, wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = xv[i][j] * rstd * wv[j];
+      if (MODE == 1) {
+        float gv[8];
+        load8(g + row * d + c, gv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] *= silu_f(gv[j]);
+      }
+      store8(y + row * d + c, o);
+    }
+  }
+}
+
+// Backward.  Persistent over rows; writes dx (and dg for gated modes) and per-CTA partial
+// dw into `partial[gridDim.x][d]`.
+template <int TPR, int NV, int MODE>
+__global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ g,
+                                                          const bf16* __restrict__ w, const bf16* __restrict__ dy,
+                                                          const float* __restrict__ rstd_in, bf16* __restrict__ dx,
+                                                          bf16* __restrict__ dg, float* __restrict__ partial,
+                                                          long rows, int d) {
+  __shared__ float red[8];
+  __shared__ float dw_sh[(TPR == 32) ? 512 : 1];
+  const int rows_per_cta = 256 / TPR;
+  const int sub = threadIdx.x / TPR;
+  const int t = threadIdx.x % TPR;
+  float dwacc[NV][8];
+  float wv[NV][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (t + i * TPR) * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
+    if (c < d) load8(w + c, wv[i]);
+  }
+  for (long base = static_cast<long>(blockIdx.x) * rows_per_cta; base < rows; base += static_cast<long>(gridDim.x) * rows_per_cta) {
+    const long row = base + sub;
+    const bool active = row < rows;
+    const float rstd = active ? rstd_in[row] : 0.f;
+    float xn[NV][8], wdy[NV][8], gv[NV][8], sg[NV][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = (t + i * TPR) * 8;
+      if (active && c < d) {
+        float xv[8], dv[8];
+        load8(x + row * d + c, xv);
+        load8(dy + row * d + c, dv);
+        if (MODE != 0) load8(g + row * d + c, gv[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float xin = xv[j];
+          float dout = dv[j];
+          if (MODE == 2) { sg[i][j] = silu_f(gv[i][j]); xin *= sg[i][j]; }
+          xn[i][j] = xin * rstd;
+          if (MODE == 1) {
+            // y = n*w*silu(g): dg = dy*n*w*dsilu(g); upstream for the norm is dy*silu(g)
+            const float s = silu_f(gv[i][j]);
+            sg[i][j] = dout * xn[i][j] * wv[i][j] * dsilu_f(gv[i][j]);   // dg
+            dout *= s;
+          }
+          dwacc[i][j] += dout * xn[i][j];
+          wdy[i][j] = dout * wv[i][j];
+          dot += wdy[i][j] * xn[i][j];
+        }
+      }
+    }
+    dot = row_sum<TPR>(dot, red) / d;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = (t + i * TPR) * 8;
+      if (active && c < d) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (wdy[i][j] - xn[i][j] * dot);   // d/d(norm input)
+        if (MODE == 2) {
+          // norm input u = x*silu(g): dx = du*silu(g), dg = du*x*dsilu(g)
+          float xv[8], og[8];
+          load8(x + row * d + c, xv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            og[j] = o[j] * xv[j] * dsilu_f(gv[i][j]);
+            o[j] *= sg[i][j];
+          }
+          store8(dg + row * d + c, og);
+        } else if (MODE == 1) {
+          store8(dg + row * d + c, sg[i]);
+        }
+        store8(dx + row * d + c, o);
+      }
+    }
+  }
+  // per-CTA partial dw
+  if (TPR == 32) {
+    // 8 sub-rows share columns: combine through shared memory in a fixed order
+    for (int i = 0; i < NV; ++i) {
+      const int c = (t + i * TPR) * 8;
+      for (int s = 0; s < rows_per_cta; ++s) {
+        __syncthreads();
+        if (sub == s && c < d) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) dw_sh[c + j] = (s == 0 ? 0.f : dw_sh[c + j]) + dwacc[i][j];
+        }
+      }
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < d; c += 256) partial[static_cast<long>(blockIdx.x) * d + c] = dw_sh[c];
+  } else {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = (t + i * TPR) * 8;
+      if (c < d) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) partial[static_cast<long>(blockIdx.x) * d + c + j] = dwacc[i][j];
+      }
+    }
+  }
+}
+
+// out[c] = sum_p partial[p][c], p ascending (deterministic); bf16 or fp32 output.
+__global__ void reduce_partials_kernel(const float* __restrict__ partial, int parts, int width,
+                                       bf16* __restrict__ out_bf16, float* __restrict__ out_f32) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= width) return;
+  float s = 0.f;
+  for (int p = 0; p < parts; ++p) s += partial[static_cast<long>(p) * width + c];
+  if (out_bf16) out_bf16[c] = __float2bfloat16(s);
+  if (out_f32) out_f32[c] = s;
+}
+
+// ------------------------------------------------------------------------------------
+// L2 norm over the last dimension (d <= 512, warp per row)
+// ------------------------------------------------------------------------------------
+template <int NV>
+__global__ void __launch_bounds__(256) l2norm_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y,
+                                                         float* __restrict__ rinv_out, long rows, int d, float eps) {
+  const long row = static_cast<long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const int t = threadIdx.x & 31;
+  if (row >= rows) return;
+  float xv[NV][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (t + i * 32) * 8;
+    if (c < d) {
+      load8(x + row * d + c, xv[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += xv[i][j] * xv[i][j];
+    }
+  }
+  ss = warp_sum(ss);
+  const float rinv = rsqrtf(ss + eps);
+  if (t == 0) rinv_out[row] = rinv;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (t + i * 32) * 8;
+    if (c < d) {
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = xv[i][j] * rinv;
+      store8(y + row * d + c, o);
+    }
+  }
+}
+template <int NV>
+__global__ void __launch_bounds__(256) l2norm_bwd_kernel(const bf16* __restrict__ y, const bf16* __restrict__ dy,
+                                                         const float* __restrict__ rinv_in, bf16* __restrict__ dx,
+                                                         long rows, int d) {
+  const long row = static_cast<long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const int t = threadIdx.x & 31;
+  if (row >= rows) return;
+  float yv[NV][8], dv[NV][8];
+  float dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (t + i * 32) * 8;
+    if (c < d) {
+      load8(y + row * d + c, yv[i]);
+      load8(dy + row * d + c, dv[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dot += yv[i][j] * dv[i][j];
+    }
+  }
+  dot = warp_sum(dot);
+  const float rinv = rinv_in[row];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (t + i * 32) * 8;
+    if (c < d) {
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = rinv * (dv[i][j] - yv[i][j] * dot);
+      store8(dx + row * d + c, o);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// SwiGLU
+// ------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) swiglu_fwd_kernel(const bf16* __restrict__ g, const bf16* __restrict__ u,
+                                                         bf16* __restrict__ y, long n8, int cols8, long ldg8, long ldu8) {
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long r = i / cols8, c = i - r * cols8;
+    float gv[8], uv[8], o[8];
+    load8(g + (r * ldg8 + c) * 8, gv);
+    load8(u + (r * ldu8 + c) * 8, uv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = silu_f(gv[j]) * uv[j];
+    store8(y + i * 8, o);
+  }
+}
+__global__ void __launch_bounds__(256) swiglu_bwd_kernel(const bf16* __restrict__ g, const bf16* __restrict__ u,
+                                                         const bf16* __restrict__ dy, bf16* __restrict__ dg,
+                                                         bf16* __restrict__ du, long n8, int cols8, long ldg8, long ldu8,
+                                                         long ldo8) {
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long r = i / cols8, c = i - r * cols8;
+    float gv[8], uv[8], dv[8], o1[8], o2[8];
+    load8(g + (r * ldg8 + c) * 8, gv);
+    load8(u + (r * ldu8 + c) * 8, uv);
+    load8(dy + i * 8, dv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      o1[j] = dv[j] * uv[j] * dsilu_f(gv[j]);
+      o2[j] = dv[j] * silu_f(gv[j]);
+    }
+    store8(dg + (r * ldo8 + c) * 8, o1);
+    store8(du + (r * ldo8 + c) * 8, o2);
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// Rotary embedding, halves layout.  x (tokens T per batch, H heads, D); cos/sin (T, D/2).
+// sign = +1 forward, -1 backward (rotation by the opposite angle).  In-place safe.
+// ------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) rope_kernel(const bf16* __restrict__ x, const float* __restrict__ cs,
+                                                   const float* __restrict__ sn, bf16* __restrict__ y, long n_items,
+                                                   int T, int H, int D, float sign) {
+  const int d2v = D / 16;   // 8-wide vectors per half
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_items; i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const int v = static_cast<int>(i % d2v);
+    const long bh = i / d2v;            // (b*T + t)*H + h
+    const long bt = bh / H;
+    const int t = static_cast<int>(bt % T);
+    const bf16* px = x + bh * D + v * 8;
+    float a[8], b[8], o1[8], o2[8];
+    load8(px, a);
+    load8(px + D / 2, b);
+    const float* pc = cs + static_cast<long>(t) * (D / 2) + v * 8;
+    const float* ps = sn + static_cast<long>(t) * (D / 2) + v * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float c = pc[j], s = ps[j] * sign;
+      o1[j] = a[j] * c - b[j] * s;
+      o2[j] = b[j] * c + a[j] * s;
+    }
+    bf16* py = y + bh * D + v * 8;
+    store8(py, o1);
+    store8(py + D / 2, o2);
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// Causal depthwise conv1d, width W <= 4, channel-last (B, T, C), optional bias and SiLU.
+// Each thread owns 8 channels and walks TCHUNK consecutive time steps with a register window.
+// ------------------------------------------------------------------------------------
+constexpr int CONV_TCHUNK = 32;
+template <int W>
+__global__ void __launch_bounds__(128) conv1d_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
+                                                         const bf16* __restrict__ bias, bf16* __restrict__ y,
+                                                         int T, int C, long ldx, int act) {
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c >= C) return;
+  const int t0 = blockIdx.y * CONV_TCHUNK;
+  const long b = blockIdx.z;
+  float wv[W][8], bv[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    bv[k] = bias ? __bfloat162float(bias[c + k]) : 0.f;
+#pragma unroll
+    for (int j = 0; j < W; ++j) wv[j][k] = __bfloat162float(w[(c + k) * W + j]);
+  }
+  float win[W][8];
+#pragma unroll
+  for (int j = 0; j < W - 1; ++j) {
+    const int t = t0 - (W - 1) + j;
+    if (t >= 0) load8(x + (b * T + t) * ldx + c, win[j + 1]);
+    else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) win[j + 1][k] = 0.f;
+    }
+  }
+  for (int tt = 0; tt < CONV_TCHUNK; ++tt) {
+    const int t = t0 + tt;
+    if (t >= T) break;
+#pragma unroll
+    for (int j = 0; j < W - 1; ++j)
+#pragma unroll
+      for (int k = 0; k < 8; ++k) win[j][k] = win[j + 1][k];
+    load8(x + (b * T + t) * ldx + c, win[W - 1]);
+    float o[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float acc = bv[k];
+#pragma unroll
+      for (int j = 0; j < W; ++j) acc += wv[j][k] * win[j][k];
+      o[k] = act ? silu_f(acc) : acc;
+    }
+    store8(y + (b * T + t) * C + c, o);
+  }
+}
+
+// Backward: dx[t] = sum_j w[j] * dpre[t + (W-1) - j];  partial dw[j], db per (time chunk, batch).
+// partial layout: [chunk][ (W+1) ][C]   (row W = bias gradient), chunk = blockIdx.z*gridDim.y + blockIdx.y
+template <int W>
+__global__ void __launch_bounds__(128) conv1d_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
+                                                         const bf16* __restrict__ bias, const bf16* __restrict__ dy,
+                                                         bf16* __restrict__ dx, float* __restrict__ partial,
+                                                         int T, int C, long ldx, int act) {
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c >= C) return;
+  const int t0 = blockIdx.y * CONV_TCHUNK;
+  const long b = blockIdx.z;
+  float wv[W][8], bv[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    bv[k] = bias ? __bfloat162float(bias[c + k]) : 0.f;
+#pragma unroll
+    for (int j = 0; j < W; ++j) wv[j][k] = __bfloat162float(w[(c + k) * W + j]);
+  }
+  // dpre over [t0, t0 + TCHUNK + W - 1) is needed for dx on [t0, t0+TCHUNK); recompute pre-activations.
+  float xw[W][8];       // x window ending at the current time step
+  float dq[W][8];       // dpre[t], dpre[t-1], ... ring: dq[0] = newest
+  float dwacc[W][8], dbacc[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    dbacc[k] = 0.f;
+#pragma unroll
+    for (int j = 0; j < W; ++j) { dwacc[j][k] = 0.f; dq[j][k] = 0.f; }
+  }
+#pragma unroll
+  for (int j = 0; j < W - 1; ++j) {
+    const int t = t0 - (W - 1) + j;
+    if (t >= 0 && t < T) load8(x + (b * T + t) * ldx + c, xw[j + 1]);
+    else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) xw[j + 1][k] = 0.f;
+    }
+  }
+  for (int tt = 0; tt < CONV_TCHUNK + W - 1; ++tt) {
+    const int t = t0 + tt;
+#pragma unroll
+    for (int j = 0; j < W - 1; ++j)
+#pragma unroll
+      for (int k = 0; k < 8; ++k) xw[j][k] = xw[j + 1][k];
+#pragma unroll
+    for (int j = W - 1; j > 0; --j)
+#pragma unroll
+      for (int k = 0; k < 8; ++k) dq[j][k] = dq[j - 1][k];
+    if (t < T) {
+      load8(x + (b * T + t) * ldx + c, xw[W - 1]);
+      float dv[8];
+      load8(dy + (b * T + t) * C + c, dv);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        float pre = bv[k];
+#pragma unroll
+        for (int j = 0; j < W; ++j) pre += wv[j][k] * xw[j][k];
+        const float dp = act ? dv[k] * dsilu_f(pre) : dv[k];
+        dq[0][k] = dp;
+        if (tt < CONV_TCHUNK) {          // each time step's weight gradient is counted by one chunk only
+          dbacc[k] += dp;
+#pragma unroll
+          for (int j = 0; j < W; ++j) dwacc[j][k] += dp * xw[j][k];
+        }
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) { dq[0][k] = 0.f; xw[W - 1][k] = 0.f; }
+    }
+    // dx at time s = t - (W-1): sum_j w[j] * dpre[s + (W-1) - j] = sum_j w[j] * dq[j]
+    const int s = t - (W - 1);
+    if (s >= t0 && s < t0 + CONV_TCHUNK && s < T) {
+      float o[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < W; ++j) acc += wv[j][k] * dq[j][k];
+        o[k] = acc;
+      }
+      store8(dx + (b * T + s) * C + c, o);
+    }
+  }
+  const long chunk = static_cast<long>(blockIdx.z) * gridDim.y + blockIdx.y;
+  float* pp = partial + chunk * (W + 1) * C;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+#pragma unroll
+    for (int j = 0; j < W; ++j) pp[static_cast<long>(j) * C + c + k] = dwacc[j][k];
+    pp[static_cast<long>(W) * C + c + k] = dbacc[k];
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// Embedding
+// ------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) embedding_fwd_kernel(const long* __restrict__ ids, const bf16* __restrict__ w,
+                                                            bf16* __restrict__ y, long n, int d, long vocab) {
+  const int d8 = d / 8;
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n * d8; i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long tok = i / d8;
+    const int v = static_cast<int>(i - tok * d8);
+    long id = ids[tok];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    *reinterpret_cast<uint4*>(y + tok * d + v * 8) = *reinterpret_cast<const uint4*>(w + id * d + v * 8);
+  }
+}
+// ids sorted ascending with `perm` giving the original token position of each sorted entry.
+// One CTA column per run start: sums the run's gradient rows in sorted order (deterministic).
+__global__ void __launch_bounds__(256) embedding_bwd_kernel(const long* __restrict__ sorted_ids,
+                                                            const long* __restrict__ perm, const bf16* __restrict__ dy,
+                                                            float* __restrict__ dw, long n, int d) {
+  const long i = blockIdx.x;
+  const long id = sorted_ids[i];
+  if (i > 0 && sorted_ids[i - 1] == id) return;   // not a run start
+  for (int c = threadIdx.x * 8; c < d; c += blockDim.x * 8) {
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+    for (long j = i; j < n && sorted_ids[j] == id; ++j) {
+      float v[8];
+      load8(dy + perm[j] * d + c, v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += v[k];
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) dw[id * d + c + k] += acc[k];
+  }
+}
+
+inline int grid_for(long n, int block, int per_sm = 8) {
+  long g = (n + block - 1) / block;
+  long cap = static_cast<long>(nsa::sm_count()) * per_sm;
+  return static_cast<int>(g < cap ? (g < 1 ? 1 : g) : cap);
+}
+
+template <int MODE>
+int launch_rms_fwd(const void* x, const void* g, const void* w, void* y, float* rstd, long rows, int d, float eps, cudaStream_t st) {
+  const bf16 *X = (const bf16*)x, *G = (const bf16*)g, *Wt = (const bf16*)w;
+  bf16* Y = (bf16*)y;
+  if (d % 8) return nsa::fail(NSA_ERR_SHAPE, "rmsnorm: width must be a multiple of 8");
+  if (d <= 256) rmsnorm_fwd_kernel<32, 1, MODE><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(X, G, Wt, Y, rstd, rows, d, eps);
+  else if (d <= 512) rmsnorm_fwd_kernel<32, 2, MODE><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(X, G, Wt, Y, rstd, rows, d, eps);
+  else if (d <= 2048) rmsnorm_fwd_kernel<256, 1, MODE><<<(unsigned)rows, 256, 0, st>>>(X, G, Wt, Y, rstd, rows, d, eps);
+  else if (d <= 4096) rmsnorm_fwd_kernel<256, 2, MODE><<<(unsigned)rows, 256, 0, st>>>(X, G, Wt, Y, rstd, rows, d, eps);
+  else if (d <= 8192) rmsnorm_fwd_kernel<256, 4, MODE><<<(unsigned)rows, 256, 0, st>>>(X, G, Wt, Y, rstd, rows, d, eps);
+  else return nsa::fail(NSA_ERR_SHAPE, "rmsnorm: width above 8192 is not supported");
+  nsa::count_launch();
+  return 0;
+}
+
+template <int MODE>
+int launch_rms_bwd(const void* x, const void* g, const void* w, const void* dy, const float* rstd, void* dx, void* dg,
+                   float* partial, int grid, long rows, int d, cudaStream_t st) {
+  const bf16 *X = (const bf16*)x, *G = (const bf16*)g, *Wt = (const bf16*)w, *DY = (const bf16*)dy;
+  bf16 *DX = (bf16*)dx, *DG = (bf16*)dg;
+  if (d <= 256) rmsnorm_bwd_kernel<32, 1, MODE><<<grid, 256, 0, st>>>(X, G, Wt, DY, rstd, DX, DG, partial, rows, d);
+  else if (d <= 512) rmsnorm_bwd_kernel<32, 2, MODE><<<grid, 256, 0, st>>>(X, G, Wt, DY, rstd, DX, DG, partial, rows, d);
+  else if (d <= 2048) rmsnorm_bwd_kernel<256, 1, MODE><<<grid, 256, 0, st>>>(X, G, Wt, DY, rstd, DX, DG, partial, rows, d);
+  else if (d <= 4096) rmsnorm_bwd_kernel<256, 2, MODE><<<grid, 256, 0, st>>>(X, G, Wt, DY, rstd, DX, DG, partial, rows, d);
+  else if (d <= 8192) rmsnorm_bwd_kernel<256, 4, MODE><<<grid, 256, 0, st>>>(X, G, Wt, DY, rstd, DX, DG, partial, rows, d);
+  else return nsa::fail(NSA_ERR_SHAPE, "rmsnorm: width above 8192 is not supported");
+  nsa::count_launch();
+  return 0;
+}
+
+}  // namespace
+
+// mode: 0 plain, 1 norm-then-gate, 2 gate-then-norm.  rstd (rows) fp32 is written for backward.
+extern "C" int nsa_rmsnorm_fwd(const void* x, const void* gate, const void* w, void* y, float* rstd, long rows, int d,
+                               float eps, int mode, cudaStream_t st) {
+  if (mode == 0) return launch_rms_fwd<0>(x, gate, w, y, rstd, rows, d, eps, st);
+  if (mode == 1) return launch_rms_fwd<1>(x, gate, w, y, rstd, rows, d, eps, st);
+  return launch_rms_fwd<2>(x, gate, w, y, rstd, rows, d, eps, st);
+}
+
+// Number of per-CTA partial rows the backward needs in `partial` (fp32 [parts, d]).
+extern "C" int nsa_rmsnorm_bwd_parts(long rows, int d) {
+  const int rows_per_cta = d <= 512 ? 8 : 1;
+  long want = (rows + rows_per_cta - 1) / rows_per_cta;
+  long cap = static_cast<long>(nsa::sm_count()) * 4;
+  return static_cast<int>(want < cap ? want : cap);
+}
+
+// dw_bf16 / dw_f32: either may be null.  `partial` is caller-provided scratch of
+// nsa_rmsnorm_bwd_parts(rows, d) * d floats.
+extern "C" int nsa_rmsnorm_bwd(const void* x, const void* gate, const void* w, const void* dy, const float* rstd,
+                               void* dx, void* dgate, void* dw_bf16, float* dw_f32, float* partial, long rows, int d,
+                               int mode, cudaStream_t st) {
+  if (d % 8) return nsa::fail(NSA_ERR_SHAPE, "rmsnorm: width must be a multiple of 8");
+  const int parts = nsa_rmsnorm_bwd_parts(rows, d);
+  int rc;
+  if (mode == 0) rc = launch_rms_bwd<0>(x, gate, w, dy, rstd, dx, dgate, partial, parts, rows, d, st);
+  else if (mode == 1) rc = launch_rms_bwd<1>(x, gate, w, dy, rstd, dx, dgate, partial, parts, rows, d, st);
+  else rc = launch_rms_bwd<2>(x, gate, w, dy, rstd, dx, dgate, partial, parts, rows, d, st);
+  if (rc) return rc;
+  reduce_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(partial, parts, d, (bf16*)dw_bf16, dw_f32);
+  nsa::count_launch();
+  return 0;
+}
+
+extern "C" int nsa_l2norm_fwd(const void* x, void* y, float* rinv, long rows, int d, float eps, cudaStream_t st) {
+  if (d % 8 || d > 512) return nsa::fail(NSA_ERR_SHAPE, "l2norm: width must be a multiple of 8, at most 512");
+  const unsigned grid = (unsigned)((rows + 7) / 8);
+  if (d <= 256) l2norm_fwd_kernel<1><<<grid, 256, 0, st>>>((const bf16*)x, (bf16*)y, rinv, rows, d, eps);
+  else l2norm_fwd_kernel<2><<<grid, 256, 0, st>>>((const bf16*)x, (bf16*)y, rinv, rows, d, eps);
+  nsa::count_launch();
+  return 0;
+}
+extern "C" int nsa_l2norm_bwd(const void* y, const void* dy, const float* rinv, void* dx, long rows, int d, cudaStream_t st) {
+  if (d % 8 || d > 512) return nsa::fail(NSA_ERR_SHAPE, "l2norm: width must be a multiple of 8, at most 512");
+  const unsigned grid = (unsigned)((rows + 7) / 8);
+  if (d <= 256) l2norm_bwd_kernel<1><<<grid, 256, 0, st>>>((const bf16*)y, (const bf16*)dy, rinv, (bf16*)dx, rows, d);
+  else l2norm_bwd_kernel<2><<<grid, 256, 0, st>>>((const bf16*)y, (const bf16*)dy, rinv, (bf16*)dx, rows, d);
+  nsa::count_launch();
+  return 0;
+}
+
+// gate / up: [rows, cols] with row pitches ldg / ldu (elements, multiples of 8); y contiguous.
+extern "C" int nsa_swiglu_fwd(const void* g, const void* u, void* y, long rows, int cols, long ldg, long ldu, cudaStream_t st) {
+  if ((cols % 8) || (ldg % 8) || (ldu % 8)) return nsa::fail(NSA_ERR_SHAPE, "swiglu: sizes must be multiples of 8");
+  const long n8 = rows * (cols / 8);
+  swiglu_fwd_kernel<<<grid_for(n8, 256), 256, 0, st>>>((const bf16*)g, (const bf16*)u, (bf16*)y, n8, cols / 8, ldg / 8, ldu / 8);
+  nsa::count_launch();
+  return 0;
+}
+extern "C" int nsa_swiglu_bwd(const void* g, const void* u, const void* dy, void* dg, void* du, long rows, int cols,
+                              long ldg, long ldu, long ldo, cudaStream_t st) {
+  if ((cols % 8) || (ldg % 8) || (ldu % 8) || (ldo % 8)) return nsa::fail(NSA_ERR_SHAPE, "swiglu: sizes must be multiples of 8");
+  const long n8 = rows * (cols / 8);
+  swiglu_bwd_kernel<<<grid_for(n8, 256), 256, 0, st>>>((const bf16*)g, (const bf16*)u, (const bf16*)dy, (bf16*)dg, (bf16*)du,
+                                                        n8, cols / 8, ldg / 8, ldu / 8, ldo / 8);
+  nsa::count_launch();
+  return 0;
+}
+
+extern "C" int nsa_rope(const void* x, const float* cos_t, const float* sin_t, void* y, long batch, int T, int H, int D,
+                        int backward, cudaStream_t st) {
+  if (D % 16) return nsa::fail(NSA_ERR_SHAPE, "rope: head_dim must be a multiple of 16");
+  const long n = batch * T * H * (D / 16);
+  rope_kernel<<<grid_for(n, 256), 256, 0, st>>>((const bf16*)x, cos_t, sin_t, (bf16*)y, n, T, H, D, backward ? -1.f : 1.f);
+  nsa::count_launch();
+  return 0;
+}
+
+extern "C" int nsa_conv1d_fwd(const void* x, const void* w, const void* bias, void* y, int B, int T, int C, long ldx,
+                              int width, int act, cudaStream_t st) {
+  if (C % 8 || ldx % 8 || width != 4) return nsa::fail(NSA_ERR_SHAPE, "conv1d: channels multiple of 8 and width 4 required");
+  dim3 grid((C / 8 + 127) / 128, (T + CONV_TCHUNK - 1) / CONV_TCHUNK, B);
+  conv1d_fwd_kernel<4><<<grid, 128, 0, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)bias, (bf16*)y, T, C, ldx, act);
+  nsa::count_launch();
+  return 0;
+}
+extern "C" long nsa_conv1d_bwd_parts(int B, int T) { return static_cast<long>(B) * ((T + CONV_TCHUNK - 1) / CONV_TCHUNK); }
+// partial: scratch of parts * 5 * C floats.  dw_f32: [4*C] laid out [j][c]; db_f32: [C].
+extern "C" int nsa_conv1d_bwd(const void* x, const void* w, const void* bias, const void* dy, void* dx, float* partial,
+                              float* dwdb_f32, int B, int T, int C, long ldx, int width, int act, cudaStream_t st) {
+  if (C % 8 || ldx % 8 || width != 4) return nsa::fail(NSA_ERR_SHAPE, "conv1d: channels multiple of 8 and width 4 required");
+  dim3 grid((C / 8 + 127) / 128, (T + CONV_TCHUNK - 1) / CONV_TCHUNK, B);
+  conv1d_bwd_kernel<4><<<grid, 128, 0, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)bias, (const bf16*)dy, (bf16*)dx,
+                                             partial, T, C, ldx, act);
+  const int parts = static_cast<int>(nsa_conv1d_bwd_parts(B, T));
+  reduce_partials_kernel<<<(5 * C + 255) / 256, 256, 0, st>>>(partial, parts, 5 * C, nullptr, dwdb_f32);
+  nsa::count_launch(2);
+  return 0;
+}
+
+extern "C" int nsa_embedding_fwd(const long* ids, const void* w, void* y, long n, int d, long vocab, cudaStream_t st) {
+  if (d % 8) return nsa::fail(NSA_ERR_SHAPE, "embedding: width must be a multiple of 8");
+  embedding_fwd_kernel<<<grid_for(n * (d / 8), 256), 256, 0, st>>>(ids, (const bf16*)w, (bf16*)y, n, d, vocab);
+  nsa::count_launch();
+  return 0;
+}
+// dw (fp32 [vocab, d]) must be zero-initialised by the caller; rows of absent ids stay zero.
+extern "C" int nsa_embedding_bwd(const long* sorted_ids, const long* perm, const void* dy, float* dw, long n, int d, cudaStream_t st) {
+  if (d % 8) return nsa::fail(NSA_ERR_SHAPE, "embedding: width must be a multiple of 8");
+  embedding_bwd_kernel<<<(unsigned)n, 256, 0, st>>>(sorted_ids, perm, (const bf16*)dy, dw, n, d);
+  nsa::count_launch();
+  return 0;
+}

@@ -1,0 +1,261 @@
+// Optimizer and loss kernels.
+//   * fused AdamW (decoupled weight decay, bias correction, optional fp32 master copy);
+//   * 8-bit AdamW: moments stored as uint8 codes of a 256-entry dynamic-tree code book with
+//     one fp32 absmax per 256-element block (signed map for the first moment, unsigned for
+//     the second); one CTA per block: dequantise, update, block absmax, requantise;
+//   * sum of squares for the global gradient norm (deterministic two-stage reduction);
+//   * softmax cross-entropy over a (rows, vocab) bf16 logits block: per-row loss and the
+//     logits overwritten in place by d(loss)/d(logits).
+// Gradients may be bf16 or fp32; an optional device scalar `grad_scale` multiplies them
+// (clip coefficient), so no host synchronisation is needed between norm and update.
+#include "host.cuh"
+#include <cuda_bf16.h>
+
+namespace {
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+struct AdamArgs {
+  float lr, beta1, beta2, eps, wd, bc1, bc2_sqrt;   // bc1 = 1-beta1^t, bc2_sqrt = sqrt(1-beta2^t)
+};
+
+template <typename PT, typename GT>
+__global__ void __launch_bounds__(256) adamw_kernel(PT* __restrict__ p, const GT* __restrict__ g, float* __restrict__ m,
+                                                    float* __restrict__ v, float* __restrict__ master,
+                                                    const float* __restrict__ grad_scale, long n, AdamArgs a) {
+  const float gs = grad_scale ? *grad_scale : 1.f;
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const float gr = static_cast<float>(g[i]) * gs;
+    float w = master ? master[i] : static_cast<float>(p[i]);
+    w *= (1.f - a.lr * a.wd);
+    const float mm = a.beta1 * m[i] + (1.f - a.beta1) * gr;
+    const float vv = a.beta2 * v[i] + (1.f - a.beta2) * gr * gr;
+    m[i] = mm;
+    v[i] = vv;
+    w -= (a.lr / a.bc1) * mm / (sqrtf(vv) / a.bc2_sqrt + a.eps);
+    if (master) master[i] = w;
+    p[i] = static_cast<PT>(w);
+  }
+}
+
+// Index of the code-book entry nearest to x; `cb` sorted ascending, 256 entries, in shared memory.
+__device__ __forceinline__ int nearest_code(const float* cb, float x) {
+  int lo = 0, hi = 255;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (cb[mid] <= x) lo = mid; else hi = mid;
+  }
+  return (x - cb[lo] <= cb[hi] - x) ? lo : hi;
+}
+
+// One CTA (256 threads) per 256-element block.
+template <typename PT, typename GT>
+__global__ void __launch_bounds__(256) adamw8bit_kernel(PT* __restrict__ p, const GT* __restrict__ g,
+                                                        uint8_t* __restrict__ mq, float* __restrict__ mabs,
+                                                        uint8_t* __restrict__ vq, float* __restrict__ vabs,
+                                                        const float* __restrict__ cb_signed,
+                                                        const float* __restrict__ cb_unsigned,
+                                                        const float* __restrict__ grad_scale, long nblocks, AdamArgs a) {
+  __shared__ float cs[256], cu[256];
+  __shared__ float red_m[8], red_v[8];
+  cs[threadIdx.x] = cb_signed[threadIdx.x];
+  cu[threadIdx.x] = cb_unsigned[threadIdx.x];
+  __syncthreads();
+  const float gs = grad_scale ? *grad_scale : 1.f;
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  for (long b = blockIdx.x; b < nblocks; b += gridDim.x) {
+    const long i = b * 256 + threadIdx.x;
+    const float gr = static_cast<float>(g[i]) * gs;
+    const float mm = a.beta1 * (cs[mq[i]] * mabs[b]) + (1.f - a.beta1) * gr;
+    const float vv = a.beta2 * (cu[vq[i]] * vabs[b]) + (1.f - a.beta2) * gr * gr;
+    float wt = static_cast<float>(p[i]);
+    wt *= (1.f - a.lr * a.wd);
+    wt -= (a.lr / a.bc1) * mm / (sqrtf(vv) / a.bc2_sqrt + a.eps);
+    p[i] = static_cast<PT>(wt);
+    float am = warp_max(fabsf(mm)), av = warp_max(vv);
+    __syncthreads();               // previous iteration's readers of red_* are done
+    if (l == 0) { red_m[w] = am; red_v[w] = av; }
+    __syncthreads();
+    am = red_m[0]; av = red_v[0];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) { am = fmaxf(am, red_m[k]); av = fmaxf(av, red_v[k]); }
+    mq[i] = static_cast<uint8_t>(nearest_code(cs, mm / fmaxf(am, 1e-30f)));
+    vq[i] = static_cast<uint8_t>(nearest_code(cu, vv / fmaxf(av, 1e-30f)));
+    if (threadIdx.x == 0) { mabs[b] = am; vabs[b] = av; }
+  }
+}
+
+template <typename GT>
+__global__ void __launch_bounds__(256) sumsq_partial_kernel(const GT* __restrict__ g, long n, float* __restrict__ partial) {
+  __shared__ float red[8];
+  float s = 0.f;
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const float x = static_cast<float>(g[i]);
+    s += x * x;
+  }
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int k = 0; k < 8; ++k) t += red[k];
+    partial[blockIdx.x] = t;
+  }
+}
+__global__ void sumsq_final_kernel(const float* __restrict__ partial, int parts, float* __restrict__ out, int accumulate) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    float t = accumulate ? *out : 0.f;
+    for (int k = 0; k < parts; ++k) t += partial[k];
+    *out = t;
+  }
+}
+
+// One CTA per row.  loss_out[row] = lse - logit[label] (0 for ignored rows); the row is then
+// overwritten with (softmax - onehot) * (*inv_count) (zeros for ignored rows).
+__global__ void __launch_bounds__(256) cross_entropy_kernel(bf16* __restrict__ logits, const long* __restrict__ labels,
+                                                            float* __restrict__ loss_out, const float* __restrict__ inv_count,
+                                                            int V, long ld, long ignore_index, int write_grad) {
+  __shared__ float red[8], red2[8];
+  const long row = blockIdx.x;
+  bf16* lp = logits + row * ld;
+  const long label = labels[row];
+  const bool ignored = (label == ignore_index) || label < 0 || label >= V;
+  const int V8 = V / 8;
+  // pass 1: online max / sum-exp
+  float mx = -INFINITY, sum = 0.f;
+  for (int i = threadIdx.x; i < V8; i += blockDim.x) {
+    uint4 u = *reinterpret_cast<const uint4*>(lp + i * 8);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+    float x[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { float2 f = __bfloat1622float2(h[k]); x[2 * k] = f.x; x[2 * k + 1] = f.y; }
+    float lm = x[0];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) lm = fmaxf(lm, x[k]);
+    const float nm = fmaxf(mx, lm);
+    float ls = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) ls += __expf(x[k] - nm);
+    sum = sum * __expf(mx - nm) + ls;
+    mx = nm;
+  }
+  for (int i = V8 * 8 + threadIdx.x; i < V; i += blockDim.x) {
+    const float x = __bfloat162float(lp[i]);
+    const float nm = fmaxf(mx, x);
+    sum = sum * __expf(mx - nm) + __expf(x - nm);
+    mx = nm;
+  }
+  // combine across the CTA
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  float gm = warp_max(mx);
+  if (l == 0) red[w] = gm;
+  __syncthreads();
+  gm = red[0];
+#pragma unroll
+  for (int k = 1; k < 8; ++k) gm = fmaxf(gm, red[k]);
+  float s = (mx == -INFINITY) ? 0.f : sum * __expf(mx - gm);
+  s = warp_sum(s);
+  if (l == 0) red2[w] = s;
+  __syncthreads();
+  s = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) s += red2[k];
+  const float lse = gm + __logf(s);
+  if (threadIdx.x == 0) loss_out[row] = ignored ? 0.f : lse - __bfloat162float(lp[label]);
+  if (!write_grad) return;
+  __syncthreads();      // the label logit has been read before anyone overwrites it
+  const float scale = ignored ? 0.f : *inv_count;
+  for (int i = threadIdx.x; i < V8; i += blockDim.x) {
+    uint4 u = *reinterpret_cast<const uint4*>(lp + i * 8);
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float2 f = __bfloat1622float2(h[k]);
+      const int c = i * 8 + 2 * k;
+      f.x = (__expf(f.x - lse) - (c == label ? 1.f : 0.f)) * scale;
+      f.y = (__expf(f.y - lse) - (c + 1 == label ? 1.f : 0.f)) * scale;
+      h[k] = __floats2bfloat162_rn(f.x, f.y);
+    }
+    *reinterpret_cast<uint4*>(lp + i * 8) = u;
+  }
+  for (int i = V8 * 8 + threadIdx.x; i < V; i += blockDim.x) {
+    const float x = __bfloat162float(lp[i]);
+    lp[i] = __float2bfloat16((__expf(x - lse) - (i == label ? 1.f : 0.f)) * scale);
+  }
+}
+
+inline int grid_cap(long want, int per_sm) {
+  long cap = static_cast<long>(nsa::sm_count()) * per_sm;
+  return static_cast<int>(want < cap ? (want < 1 ? 1 : want) : cap);
+}
+AdamArgs make_args(int step, float lr, float b1, float b2, float eps, float wd) {
+  AdamArgs a;
+  a.lr = lr; a.beta1 = b1; a.beta2 = b2; a.eps = eps; a.wd = wd;
+  a.bc1 = 1.f - powf(b1, (float)step);
+  a.bc2_sqrt = sqrtf(1.f - powf(b2, (float)step));
+  return a;
+}
+}  // namespace
+
+// p: bf16 (p_fp32 = 0) or fp32; g: bf16 (g_fp32 = 0) or fp32; m, v fp32; master fp32 or null.
+extern "C" int nsa_adamw_step(void* p, const void* g, float* m, float* v, float* master, const float* grad_scale,
+                              long n, int p_fp32, int g_fp32, int step, float lr, float b1, float b2, float eps, float wd,
+                              cudaStream_t st) {
+  if (n <= 0) return 0;
+  const AdamArgs a = make_args(step, lr, b1, b2, eps, wd);
+  const int grid = grid_cap((n + 255) / 256, 16);
+  if (p_fp32 && g_fp32) adamw_kernel<float, float><<<grid, 256, 0, st>>>((float*)p, (const float*)g, m, v, master, grad_scale, n, a);
+  else if (p_fp32) adamw_kernel<float, bf16><<<grid, 256, 0, st>>>((float*)p, (const bf16*)g, m, v, master, grad_scale, n, a);
+  else if (g_fp32) adamw_kernel<bf16, float><<<grid, 256, 0, st>>>((bf16*)p, (const float*)g, m, v, master, grad_scale, n, a);
+  else adamw_kernel<bf16, bf16><<<grid, 256, 0, st>>>((bf16*)p, (const bf16*)g, m, v, master, grad_scale, n, a);
+  nsa::count_launch();
+  return 0;
+}
+
+// n must be a multiple of 256.  cb_signed / cb_unsigned: device pointers to 256 fp32 entries.
+extern "C" int nsa_adamw8bit_step(void* p, const void* g, uint8_t* mq, float* mabs, uint8_t* vq, float* vabs,
+                                  const float* cb_signed, const float* cb_unsigned, const float* grad_scale, long n,
+                                  int p_fp32, int g_fp32, int step, float lr, float b1, float b2, float eps, float wd,
+                                  cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (n % 256) return nsa::fail(NSA_ERR_SHAPE, "adamw8bit: element count must be a multiple of 256");
+  const AdamArgs a = make_args(step, lr, b1, b2, eps, wd);
+  const long nb = n / 256;
+  const int grid = grid_cap(nb, 16);
+  if (p_fp32 && g_fp32) adamw8bit_kernel<float, float><<<grid, 256, 0, st>>>((float*)p, (const float*)g, mq, mabs, vq, vabs, cb_signed, cb_unsigned, grad_scale, nb, a);
+  else if (p_fp32) adamw8bit_kernel<float, bf16><<<grid, 256, 0, st>>>((float*)p, (const bf16*)g, mq, mabs, vq, vabs, cb_signed, cb_unsigned, grad_scale, nb, a);
+  else if (g_fp32) adamw8bit_kernel<bf16, float><<<grid, 256, 0, st>>>((bf16*)p, (const float*)g, mq, mabs, vq, vabs, cb_signed, cb_unsigned, grad_scale, nb, a);
+  else adamw8bit_kernel<bf16, bf16><<<grid, 256, 0, st>>>((bf16*)p, (const bf16*)g, mq, mabs, vq, vabs, cb_signed, cb_unsigned, grad_scale, nb, a);
+  nsa::count_launch();
+  return 0;
+}
+
+// out (device scalar) = [out +] sum(g^2).  partial: scratch of nsa_sumsq_parts() floats.
+extern "C" int nsa_sumsq_parts() { return nsa::sm_count() * 4; }
+extern "C" int nsa_sumsq(const void* g, long n, int g_fp32, float* partial, float* out, int accumulate, cudaStream_t st) {
+  const int parts = grid_cap((n + 255) / 256, 4);
+  if (g_fp32) sumsq_partial_kernel<float><<<parts, 256, 0, st>>>((const float*)g, n, partial);
+  else sumsq_partial_kernel<bf16><<<parts, 256, 0, st>>>((const bf16*)g, n, partial);
+  sumsq_final_kernel<<<1, 32, 0, st>>>(partial, parts, out, accumulate);
+  nsa::count_launch(2);
+  return 0;
+}
+
+extern "C" int nsa_cross_entropy(void* logits, const long* labels, float* loss_rows, const float* inv_count, long rows,
+                                 int V, long ld, long ignore_index, int write_grad, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (ld % 8) return nsa::fail(NSA_ERR_SHAPE, "cross_entropy: row pitch must be a multiple of 8");
+  cross_entropy_kernel<<<(unsigned)rows, 256, 0, st>>>((bf16*)logits, labels, loss_rows, inv_count, V, ld, ignore_index, write_grad);
+  nsa::count_launch();
+  return 0;
+}

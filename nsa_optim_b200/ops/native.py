@@ -1,0 +1,470 @@
+"""ctypes bindings and autograd wrappers for the sm_100a kernels in ``ops/csrc``.
+
+The shared library ``libnsa_b200.so`` lives beside this file (built by ``ops/build.py``) and
+exports plain C entry points that take device pointers, sizes and a stream; output tensors
+are allocated here with PyTorch.  Each differentiable op is one ``autograd.Function`` whose
+forward and backward both call native kernels.  ``SUPPORTED`` lists the ops that have a
+native implementation; ``ops/__init__.py`` consults :func:`supports`.
+
+Kernel failures do not raise from the device: kernels record a status block in pinned host
+memory (bounded waits, argument checks); :func:`check_status` turns it into an exception.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_float, c_int, c_long, c_longlong, c_void_p
+from typing import Optional, Tuple
+
+import torch
+from torch import Tensor
+
+from . import quant, torch_impl
+
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libnsa_b200.so")
+_lib: Optional[ctypes.CDLL] = None
+
+SUPPORTED = {
+    "linear", "rms_norm", "gated_rms_norm", "swiglu", "l2_norm", "rope", "embedding",
+    "causal_conv1d", "linear_cross_entropy", "adamw", "adamw_lowbit",
+}
+
+STATUS_NAMES = {
+    101: "timeout waiting for a TMA stage (smem full barrier)",
+    102: "timeout waiting for a free smem stage (smem empty barrier)",
+    103: "timeout waiting for an accumulator (tmem full barrier)",
+    104: "timeout waiting for a free accumulator (tmem empty barrier)",
+    201: "timeout waiting for a flag written by a peer GPU",
+    202: "timeout waiting for a flag written by another CTA",
+    301: "bad argument",
+}
+
+
+def lib_path() -> str:
+    return _LIB_PATH
+
+
+def load() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            raise FileNotFoundError(f"{_LIB_PATH} is missing; run `python -m nsa_optim_b200.ops.build`")
+        _lib = ctypes.CDLL(_LIB_PATH)
+        _lib.nsa_last_error.restype = ctypes.c_char_p
+        _lib.nsa_launch_count.restype = c_longlong
+        _lib.nsa_conv1d_bwd_parts.restype = c_long
+    return _lib
+
+
+def supports(op: str, t: Tensor) -> bool:
+    if op not in SUPPORTED or not t.is_cuda:
+        return False
+    if op in ("adamw", "adamw_lowbit"):
+        return t.dtype in (torch.bfloat16, torch.float32)
+    if op == "embedding":
+        return t.dtype == torch.bfloat16
+    return t.dtype == torch.bfloat16
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise RuntimeError(f"nsa_optim_b200 native call failed ({rc}): {load().nsa_last_error().decode()}")
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t: Optional[Tensor]) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def launch_count() -> int:
+    return int(load().nsa_launch_count())
+
+
+def reset_launch_count() -> None:
+    load().nsa_launch_count_reset()
+
+
+def read_status(reset: bool = True) -> Tuple[int, int, int, int]:
+    out = (c_int * 4)()
+    _check(load().nsa_status_read(out, c_int(1 if reset else 0)))
+    return tuple(int(v) for v in out)
+
+
+def check_status(sync: bool = True) -> None:
+    """Raise if any kernel since the last check reported a failure."""
+    if sync:
+        torch.cuda.synchronize()
+    code, block, info, count = read_status(reset=True)
+    if code != 0:
+        raise RuntimeError(f"native kernel reported status {code} ({STATUS_NAMES.get(code, 'unknown')}); "
+                           f"block {block}, detail {info}, {count} report(s)")
+
+
+# --------------------------------------------------------------------------------------
+# GEMM
+# --------------------------------------------------------------------------------------
+def _as_2d(x: Tensor) -> Tensor:
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1 or (x2.stride(0) % 8) or (x2.data_ptr() % 16):
+        x2 = x2.contiguous()
+    return x2
+
+
+def gemm(a: Tensor, b: Tensor, a_mn: bool, b_mn: bool, out: Optional[Tensor] = None,
+         out_dtype: torch.dtype = torch.bfloat16, accumulate: bool = False, max_ctas: int = 0) -> Tensor:
+    """C = op(A) op(B): a_mn False -> A is (M, K), True -> A is (K, M); b_mn False -> B is (N, K),
+    True -> B is (K, N).  Row pitches may exceed the logical width (sliced views)."""
+    a, b = _as_2d(a), _as_2d(b)
+    M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
+    N, Kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
+    if K != Kb:
+        raise ValueError(f"gemm: reduction sizes differ ({K} vs {Kb})")
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    _check(load().nsa_gemm_bf16(_p(a), _p(b), _p(out), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)),
+                                c_int(b.stride(0)), c_int(out.stride(0)), c_int(int(a_mn)), c_int(int(b_mn)),
+                                c_int(int(out.dtype == torch.float32)), c_int(int(accumulate)), c_int(max_ctas),
+                                _stream()))
+    return out
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x: Tensor, w: Tensor):
+        x2 = _as_2d(x)
+        ctx.save_for_backward(x2, w)
+        ctx.xshape = x.shape
+        y = gemm(x2, w, False, False)
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):
+        x2, w = ctx.saved_tensors
+        dy2 = _as_2d(dy)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w, False, True).view(ctx.xshape)          # dy (M,N) @ w (N,K)
+        if ctx.needs_input_grad[1]:
+            dw = gemm(dy2, x2, True, True)                            # dy^T (N,M) @ x (M,K)
+        return dx, dw
+
+
+def linear(x: Tensor, w: Tensor) -> Tensor:
+    if (x.shape[-1] % 8) or (w.shape[0] % 8):
+        return torch_impl.linear(x, w)
+    return _Linear.apply(x, w)
+
+
+# --------------------------------------------------------------------------------------
+# norms
+# --------------------------------------------------------------------------------------
+def _rms_fwd(x2, gate2, w, eps, mode):
+    rows, d = x2.shape
+    y = torch.empty_like(x2)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x2.device)
+    _check(load().nsa_rmsnorm_fwd(_p(x2), _p(gate2), _p(w), _p(y), _p(rstd), c_long(rows), c_int(d),
+                                  c_float(eps), c_int(mode), _stream()))
+    return y, rstd
+
+
+def _rms_bwd(x2, gate2, w, dy2, rstd, mode):
+    rows, d = x2.shape
+    dx = torch.empty_like(x2)
+    dg = torch.empty_like(x2) if mode != 0 else None
+    dw = torch.empty(d, dtype=torch.bfloat16, device=x2.device)
+    parts = int(load().nsa_rmsnorm_bwd_parts(c_long(rows), c_int(d)))
+    partial = torch.empty(parts * d, dtype=torch.float32, device=x2.device)
+    _check(load().nsa_rmsnorm_bwd(_p(x2), _p(gate2), _p(w), _p(dy2), _p(rstd), _p(dx), _p(dg), _p(dw), c_void_p(0),
+                                  _p(partial), c_long(rows), c_int(d), c_int(mode), _stream()))
+    return dx, dg, dw
+
+
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps):
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        wb = w.to(torch.bfloat16)
+        y, rstd = _rms_fwd(x2, None, wb, eps, 0)
+        ctx.save_for_backward(x2, wb, rstd)
+        ctx.wdtype = w.dtype
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, wb, rstd = ctx.saved_tensors
+        dx, _, dw = _rms_bwd(x2, None, wb, dy.reshape(x2.shape).contiguous(), rstd, 0)
+        return dx.view(dy.shape), dw.to(ctx.wdtype), None
+
+
+class _GatedRMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gate, w, eps, norm_before_gate):
+        mode = 1 if norm_before_gate else 2
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        g2 = gate.reshape(-1, gate.shape[-1]).contiguous()
+        wb = w.to(torch.bfloat16)
+        y, rstd = _rms_fwd(x2, g2, wb, eps, mode)
+        ctx.save_for_backward(x2, g2, wb, rstd)
+        ctx.mode, ctx.wdtype, ctx.gshape = mode, w.dtype, gate.shape
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, g2, wb, rstd = ctx.saved_tensors
+        dx, dg, dw = _rms_bwd(x2, g2, wb, dy.reshape(x2.shape).contiguous(), rstd, ctx.mode)
+        return dx.view(dy.shape), dg.view(ctx.gshape), dw.to(ctx.wdtype), None, None
+
+
+def rms_norm(x, w, eps=1e-6):
+    d = x.shape[-1]
+    if d % 8 or d > 8192:
+        return torch_impl.rms_norm(x, w, eps)
+    return _RMSNorm.apply(x, w, eps)
+
+
+def gated_rms_norm(x, gate, w, eps=1e-6, norm_before_gate=True):
+    d = x.shape[-1]
+    if d % 8 or d > 8192:
+        return torch_impl.gated_rms_norm(x, gate, w, eps, norm_before_gate)
+    return _GatedRMSNorm.apply(x, gate, w, eps, norm_before_gate)
+
+
+class _L2Norm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, eps):
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        rows, d = x2.shape
+        y = torch.empty_like(x2)
+        rinv = torch.empty(rows, dtype=torch.float32, device=x.device)
+        _check(load().nsa_l2norm_fwd(_p(x2), _p(y), _p(rinv), c_long(rows), c_int(d), c_float(eps), _stream()))
+        ctx.save_for_backward(y, rinv)
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        y, rinv = ctx.saved_tensors
+        dy2 = dy.reshape(y.shape).contiguous()
+        dx = torch.empty_like(y)
+        _check(load().nsa_l2norm_bwd(_p(y), _p(dy2), _p(rinv), _p(dx), c_long(y.shape[0]), c_int(y.shape[1]), _stream()))
+        return dx.view(dy.shape), None
+
+
+def l2_norm(x, eps=1e-6):
+    d = x.shape[-1]
+    if d % 8 or d > 512:
+        return torch_impl.l2_norm(x, eps)
+    return _L2Norm.apply(x, eps)
+
+
+# --------------------------------------------------------------------------------------
+# SwiGLU, RoPE
+# --------------------------------------------------------------------------------------
+def _rows_view(t: Tensor) -> Tensor:
+    t2 = t.reshape(-1, t.shape[-1])
+    if t2.stride(-1) != 1 or t2.stride(0) % 8 or t2.data_ptr() % 16:
+        t2 = t2.contiguous()
+    return t2
+
+
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate, up):
+        g2, u2 = _rows_view(gate), _rows_view(up)
+        rows, cols = g2.shape
+        y = torch.empty(rows, cols, dtype=gate.dtype, device=gate.device)
+        _check(load().nsa_swiglu_fwd(_p(g2), _p(u2), _p(y), c_long(rows), c_int(cols), c_long(g2.stride(0)),
+                                     c_long(u2.stride(0)), _stream()))
+        ctx.save_for_backward(g2, u2)
+        return y.view(gate.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        g2, u2 = ctx.saved_tensors
+        rows, cols = g2.shape
+        dy2 = dy.reshape(rows, cols).contiguous()
+        dg = torch.empty(rows, cols, dtype=dy.dtype, device=dy.device)
+        du = torch.empty(rows, cols, dtype=dy.dtype, device=dy.device)
+        _check(load().nsa_swiglu_bwd(_p(g2), _p(u2), _p(dy2), _p(dg), _p(du), c_long(rows), c_int(cols),
+                                     c_long(g2.stride(0)), c_long(u2.stride(0)), c_long(cols), _stream()))
+        return dg.view(dy.shape), du.view(dy.shape)
+
+
+def swiglu(gate, up):
+    if gate.shape[-1] % 8:
+        return torch_impl.swiglu(gate, up)
+    return _SwiGLU.apply(gate, up)
+
+
+def _rope_call(x: Tensor, cos: Tensor, sin: Tensor, backward: bool) -> Tensor:
+    B, T, H, D = x.shape
+    xc = x.contiguous()
+    y = torch.empty_like(xc)
+    _check(load().nsa_rope(_p(xc), _p(cos), _p(sin), _p(y), c_long(B), c_int(T), c_int(H), c_int(D),
+                           c_int(int(backward)), _stream()))
+    return y
+
+
+class _RoPE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin):
+        cos = cos.float().contiguous()
+        sin = sin.float().contiguous()
+        ctx.save_for_backward(cos, sin)
+        return _rope_call(x, cos, sin, False)
+
+    @staticmethod
+    def backward(ctx, dy):
+        cos, sin = ctx.saved_tensors
+        return _rope_call(dy, cos, sin, True), None, None
+
+
+def rope(x, cos, sin):
+    if x.shape[-1] % 16 or cos.shape[0] != x.shape[1]:
+        return torch_impl.rope(x, cos, sin)
+    return _RoPE.apply(x, cos, sin)
+
+
+# --------------------------------------------------------------------------------------
+# causal conv1d
+# --------------------------------------------------------------------------------------
+class _Conv1d(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, activation):
+        B, T, C = x.shape
+        xv = x if (x.stride(2) == 1 and x.stride(1) % 8 == 0 and x.stride(0) == T * x.stride(1)
+                   and x.data_ptr() % 16 == 0) else x.contiguous()
+        wb = weight.to(torch.bfloat16).contiguous()
+        bb = None if bias is None else bias.to(torch.bfloat16).contiguous()
+        y = torch.empty(B, T, C, dtype=x.dtype, device=x.device)
+        _check(load().nsa_conv1d_fwd(_p(xv), _p(wb), _p(bb), _p(y), c_int(B), c_int(T), c_int(C),
+                                     c_long(xv.stride(1)), c_int(weight.shape[-1]), c_int(int(activation)), _stream()))
+        ctx.save_for_backward(xv, wb, bb)
+        ctx.activation, ctx.wdtype = activation, weight.dtype
+        ctx.has_bias = bias is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xv, wb, bb = ctx.saved_tensors
+        B, T, C = xv.shape
+        W = wb.shape[-1]
+        dyc = dy.contiguous()
+        dx = torch.empty(B, T, C, dtype=dy.dtype, device=dy.device)
+        parts = int(load().nsa_conv1d_bwd_parts(c_int(B), c_int(T)))
+        partial = torch.empty(parts * (W + 1) * C, dtype=torch.float32, device=dy.device)
+        dwdb = torch.empty((W + 1) * C, dtype=torch.float32, device=dy.device)
+        _check(load().nsa_conv1d_bwd(_p(xv), _p(wb), _p(bb), _p(dyc), _p(dx), _p(partial), _p(dwdb), c_int(B), c_int(T),
+                                     c_int(C), c_long(xv.stride(1)), c_int(W), c_int(int(ctx.activation)), _stream()))
+        dw = dwdb[: W * C].view(W, C).t().contiguous().to(ctx.wdtype)
+        db = dwdb[W * C:].to(ctx.wdtype) if ctx.has_bias else None
+        return dx, dw, db, None
+
+
+def causal_conv1d(x, weight, bias, activation=True):
+    if x.shape[-1] % 8 or weight.shape[-1] != 4:
+        return torch_impl.causal_conv1d(x, weight, bias, activation)
+    return _Conv1d.apply(x, weight, bias, activation)
+
+
+# --------------------------------------------------------------------------------------
+# embedding
+# --------------------------------------------------------------------------------------
+class _Embedding(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, weight):
+        flat = ids.reshape(-1).contiguous()
+        n, d = flat.numel(), weight.shape[1]
+        y = torch.empty(n, d, dtype=weight.dtype, device=weight.device)
+        _check(load().nsa_embedding_fwd(_p(flat), _p(weight), _p(y), c_long(n), c_int(d), c_long(weight.shape[0]), _stream()))
+        ctx.save_for_backward(flat)
+        ctx.wshape, ctx.wdtype = weight.shape, weight.dtype
+        return y.view(*ids.shape, d)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (flat,) = ctx.saved_tensors
+        n, d = flat.numel(), ctx.wshape[1]
+        sorted_ids, perm = torch.sort(flat, stable=True)
+        dw = torch.zeros(ctx.wshape, dtype=torch.float32, device=dy.device)
+        dy2 = dy.reshape(n, d).contiguous()
+        _check(load().nsa_embedding_bwd(_p(sorted_ids), _p(perm), _p(dy2), _p(dw), c_long(n), c_int(d), _stream()))
+        return None, dw.to(ctx.wdtype)
+
+
+def embedding(ids, weight):
+    if weight.shape[1] % 8 or ids.dtype != torch.long:
+        return torch_impl.embedding(ids, weight)
+    return _Embedding.apply(ids, weight)
+
+
+# --------------------------------------------------------------------------------------
+# fused linear + cross entropy
+# --------------------------------------------------------------------------------------
+class _LinearCE(torch.autograd.Function):
+    """Per token chunk: logits GEMM (tcgen05) -> softmax-CE kernel that overwrites the logits
+    with their gradient -> two gradient GEMMs.  The (chunk, V) block is the largest temporary."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, labels, ignore_index, chunk):
+        N, d = hidden.shape
+        V = weight.shape[0]
+        h = _as_2d(hidden)
+        labels = labels.contiguous()
+        need_h, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        n_valid = (labels != ignore_index).sum().clamp_min(1).float()
+        inv = (1.0 / n_valid).reshape(1)
+        loss_rows = torch.empty(N, dtype=torch.float32, device=hidden.device)
+        dh = torch.empty_like(h) if need_h else None
+        dw = torch.zeros(V, d, dtype=torch.float32, device=hidden.device) if need_w else None
+        logits = torch.empty(min(chunk, N), V, dtype=torch.bfloat16, device=hidden.device)
+        for s0 in range(0, N, chunk):
+            s1 = min(N, s0 + chunk)
+            lg = logits[: s1 - s0]
+            gemm(h[s0:s1], weight, False, False, out=lg)
+            _check(load().nsa_cross_entropy(_p(lg), _p(labels[s0:s1]), _p(loss_rows[s0:s1]), _p(inv), c_long(s1 - s0),
+                                            c_int(V), c_long(lg.stride(0)), c_long(ignore_index),
+                                            c_int(int(need_h or need_w)), _stream()))
+            if need_h:
+                gemm(lg, weight, False, True, out=dh[s0:s1])                   # dlogits (n,V) @ W (V,d)
+            if need_w:
+                gemm(lg, h[s0:s1], True, True, out=dw, accumulate=(s0 > 0))    # dlogits^T (V,n) @ h (n,d)
+        ctx.save_for_backward(dh, dw)
+        ctx.wdtype = weight.dtype
+        return loss_rows.sum() * inv[0]
+
+    @staticmethod
+    def backward(ctx, gout):
+        dh, dw = ctx.saved_tensors
+        return (None if dh is None else dh * gout.to(dh.dtype),
+                None if dw is None else (dw * gout).to(ctx.wdtype), None, None, None)
+
+
+def linear_cross_entropy(hidden, weight, labels, ignore_index=-100, chunk=4096):
+    if hidden.shape[-1] % 8 or weight.shape[0] % 8:
+        return torch_impl.linear_cross_entropy(hidden, weight, labels, ignore_index, chunk)
+    return _LinearCE.apply(hidden, weight, labels, ignore_index, chunk)
+
+
+# --------------------------------------------------------------------------------------
+# optimizer steps
+# --------------------------------------------------------------------------------------
+def adamw_step(p, g, m, v, master, step, lr, b1, b2, eps, wd, grad_scale):
+    gs = None if grad_scale is None else grad_scale.reshape(1).float()
+    _check(load().nsa_adamw_step(_p(p), _p(g), _p(m), _p(v), _p(master), _p(gs), c_long(p.numel()),
+                                 c_int(int(p.dtype == torch.float32)), c_int(int(g.dtype == torch.float32)),
+                                 c_int(step), c_float(lr), c_float(b1), c_float(b2), c_float(eps), c_float(wd), _stream()))
+
+
+def adamw8bit_step(p, g, mq, mabs, vq, vabs, step, lr, b1, b2, eps, wd, grad_scale, block):
+    if block != 256:
+        raise ValueError("the native 8-bit AdamW kernel uses 256-element blocks")
+    gs = None if grad_scale is None else grad_scale.reshape(1).float()
+    cs = quant.codebook(8, True, p.device)
+    cu = quant.codebook(8, False, p.device)
+    _check(load().nsa_adamw8bit_step(_p(p), _p(g), _p(mq), _p(mabs), _p(vq), _p(vabs), _p(cs), _p(cu), _p(gs),
+                                     c_long(p.numel()), c_int(int(p.dtype == torch.float32)),
+                                     c_int(int(g.dtype == torch.float32)), c_int(step), c_float(lr), c_float(b1),
+                                     c_float(b2), c_float(eps), c_float(wd), _stream()))

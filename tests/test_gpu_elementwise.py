@@ -1,0 +1,170 @@
+"""Bandwidth-bound kernels, loss and optimizer kernels against the fp32 PyTorch oracles."""
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from nsa_optim_b200.ops import oracle, quant, torch_impl
+
+pytestmark = pytest.mark.gpu
+
+
+def close(got, ref, rtol=2e-2, atol=2e-2):
+    err = (got.float() - ref.float()).abs().max().item()
+    scale = ref.float().abs().max().item()
+    assert err <= rtol * scale + atol, (err, scale)
+
+
+def bf(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).bfloat16()
+
+
+@pytest.mark.parametrize("rows,d", [(37, 256), (9, 512), (5, 2048), (3, 4096), (2, 5632)])
+def test_rmsnorm(native, rows, d):
+    x, w = bf(rows, d).requires_grad_(), (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16().requires_grad_()
+    y = native.rms_norm(x, w, 1e-6)
+    g = bf(rows, d)
+    y.backward(g)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = oracle.rms_norm(xr, wr, 1e-6)
+    yr.backward(g.float())
+    close(y, yr); close(x.grad, xr.grad); close(w.grad, wr.grad, atol=5e-2)
+
+
+@pytest.mark.parametrize("nbg", [True, False])
+@pytest.mark.parametrize("rows,d", [(40, 256), (6, 4096)])
+def test_gated_rmsnorm(native, rows, d, nbg):
+    x, gt = bf(rows, d).requires_grad_(), bf(rows, d).requires_grad_()
+    w = (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16().requires_grad_()
+    y = native.gated_rms_norm(x, gt, w, 1e-5, nbg)
+    g = bf(rows, d)
+    y.backward(g)
+    xr, gr, wr = (t.detach().float().requires_grad_() for t in (x, gt, w))
+    yr = oracle.gated_rms_norm(xr, gr, wr, 1e-5, nbg)
+    yr.backward(g.float())
+    close(y, yr); close(x.grad, xr.grad); close(gt.grad, gr.grad); close(w.grad, wr.grad, atol=5e-2)
+
+
+def test_l2norm(native):
+    x = bf(2, 33, 4, 128).requires_grad_()
+    y = native.l2_norm(x)
+    g = bf(2, 33, 4, 128)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    yr = oracle.l2_norm(xr)
+    yr.backward(g.float())
+    close(y, yr); close(x.grad, xr.grad)
+
+
+def test_swiglu(native):
+    a, b = bf(70, 1536).requires_grad_(), bf(70, 1536).requires_grad_()
+    y = native.swiglu(a, b)
+    g = bf(70, 1536)
+    y.backward(g)
+    ar, br = a.detach().float().requires_grad_(), b.detach().float().requires_grad_()
+    yr = oracle.swiglu(ar, br)
+    yr.backward(g.float())
+    close(y, yr); close(a.grad, ar.grad); close(b.grad, br.grad)
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_rope(native, D):
+    x = bf(2, 50, 3, D).requires_grad_()
+    cos, sin = oracle.rope_tables(D, 50, 1e4, device="cuda")
+    y = native.rope(x, cos, sin)
+    g = bf(2, 50, 3, D)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    yr = oracle.rope(xr, cos, sin)
+    yr.backward(g.float())
+    close(y, yr); close(x.grad, xr.grad)
+
+
+@pytest.mark.parametrize("bias", [True, False])
+def test_causal_conv1d(native, bias):
+    B, T, C = 2, 75, 136
+    x = bf(B, T, C).requires_grad_()
+    w = bf(C, 4, scale=0.5).requires_grad_()
+    b = bf(C, scale=0.5).requires_grad_() if bias else None
+    y = native.causal_conv1d(x, w, b, True)
+    g = bf(B, T, C)
+    y.backward(g)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    brr = b.detach().float().requires_grad_() if bias else None
+    yr = oracle.causal_conv1d(xr, wr, brr, True)
+    yr.backward(g.float())
+    close(y, yr); close(x.grad, xr.grad); close(w.grad, wr.grad, atol=8e-2)
+    if bias:
+        close(b.grad, brr.grad, atol=8e-2)
+
+
+def test_embedding(native):
+    w = bf(500, 64).requires_grad_()
+    ids = torch.randint(0, 500, (3, 40), device="cuda")
+    y = native.embedding(ids, w)
+    g = bf(3, 40, 64)
+    y.backward(g)
+    wr = w.detach().float().requires_grad_()
+    yr = F.embedding(ids, wr)
+    yr.backward(g.float())
+    assert torch.equal(y.float(), yr)
+    close(w.grad, wr.grad)
+
+
+def test_linear_cross_entropy(native):
+    N, d, V = 300, 128, 1000
+    h = bf(N, d, scale=0.5).requires_grad_()
+    w = bf(V, d, scale=0.1).requires_grad_()
+    y = torch.randint(0, V, (N,), device="cuda")
+    y[::7] = -100
+    loss = native.linear_cross_entropy(h, w, y, -100, 128)
+    loss.backward()
+    hr, wr = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    lr = oracle.linear_cross_entropy(hr, wr, y)
+    lr.backward()
+    assert abs(loss.item() - lr.item()) < 2e-2
+    close(h.grad, hr.grad, atol=1e-4, rtol=5e-2); close(w.grad, wr.grad, atol=1e-4, rtol=5e-2)
+
+
+@pytest.mark.parametrize("pdt", [torch.bfloat16, torch.float32])
+def test_adamw_kernel(native, pdt):
+    n = 5000
+    p = torch.randn(n, device="cuda").to(pdt)
+    g = torch.randn(n, device="cuda")
+    m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    pr, mr, vr = p.float().clone(), m.clone(), v.clone()
+    scale = torch.tensor(0.5, device="cuda")
+    for t in (1, 2, 3):
+        native.adamw_step(p, g, m, v, None, t, 1e-2, 0.9, 0.95, 1e-8, 0.1, scale)
+        oracle.adamw_step(pr, g * 0.5, mr, vr, t, 1e-2, 0.9, 0.95, 1e-8, 0.1)
+        if pdt == torch.bfloat16:
+            pr = pr.bfloat16().float()
+    close(m, mr, 1e-5, 1e-6); close(v, vr, 1e-5, 1e-6); close(p, pr, 1e-2 if pdt == torch.bfloat16 else 1e-5, 1e-5)
+
+
+def test_adamw8bit_kernel_matches_torch_codec(native):
+    n = 256 * 40
+    p = torch.randn(n, device="cuda").bfloat16()
+    pr = p.clone()
+    mq = torch.full((n,), 127, dtype=torch.uint8, device="cuda"); vq = torch.zeros(n, dtype=torch.uint8, device="cuda")
+    zero_m = quant.quantize_blockwise(torch.zeros(256), 8, True, 256)[0][0].item()
+    mq.fill_(zero_m)
+    mabs, vabs = torch.zeros(n // 256, device="cuda"), torch.zeros(n // 256, device="cuda")
+    mr, vr = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    for t in (1, 2, 3, 4):
+        g = torch.randn(n, device="cuda")
+        native.adamw8bit_step(p, g, mq, mabs, vq, vabs, t, 1e-2, 0.9, 0.95, 1e-8, 0.1, None, 256)
+        # reference: dequantise the previous reference state through the same codec
+        mr = mr * 0.9 + 0.1 * g
+        vr = vr * 0.95 + 0.05 * g * g
+        w = pr.float() * (1 - 1e-2 * 0.1)
+        w = w - (1e-2 / (1 - 0.9 ** t)) * mr / (vr.sqrt() / math.sqrt(1 - 0.95 ** t) + 1e-8)
+        pr = w.bfloat16()
+        cm, am = quant.quantize_blockwise(mr, 8, True, 256)
+        cv, av = quant.quantize_blockwise(vr, 8, False, 256)
+        mr = quant.dequantize_blockwise(cm, am, 8, True, 256)
+        vr = quant.dequantize_blockwise(cv, av, 8, False, 256)
+    md = quant.dequantize_blockwise(mq, mabs, 8, True, 256)
+    vd = quant.dequantize_blockwise(vq, vabs, 8, False, 256)
+    close(md, mr, 2e-2, 1e-3); close(vd, vr, 2e-2, 1e-3); close(p, pr, 2e-2, 2e-2)

@@ -1,0 +1,72 @@
+"""tcgen05 GEMM against an fp32 PyTorch matmul of the same bf16 inputs."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, b, a_mn, b_mn):
+    A = a.float().t() if a_mn else a.float()
+    B = b.float() if b_mn else b.float().t()
+    return A @ B
+
+
+def _mk(M, N, K, a_mn, b_mn):
+    a = torch.randn((K, M) if a_mn else (M, K), device="cuda").bfloat16()
+    b = torch.randn((K, N) if b_mn else (N, K), device="cuda").bfloat16()
+    return a, b
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 256), (1000, 264, 72), (4096, 2048, 1024)])
+def test_gemm_matches_fp32(native, shape, a_mn, b_mn):
+    M, N, K = shape
+    if (a_mn and M % 8) or (b_mn and N % 8):
+        pytest.skip("MN-major operands need a leading dimension that is a multiple of 8")
+    a, b = _mk(M, N, K, a_mn, b_mn)
+    c = native.gemm(a, b, a_mn, b_mn)
+    ref = _ref(a, b, a_mn, b_mn)
+    err = (c.float() - ref).abs().max().item()
+    scale = ref.abs().max().item()
+    assert err <= 1e-2 * scale + 1e-2, (err, scale)
+
+
+def test_gemm_fp32_accumulate(native):
+    M, N, K = 512, 384, 320
+    a, b = _mk(M, N, K, False, False)
+    out = torch.ones(M, N, device="cuda", dtype=torch.float32)
+    native.gemm(a, b, False, False, out=out, accumulate=True)
+    ref = _ref(a, b, False, False) + 1.0
+    assert torch.allclose(out, ref, rtol=1e-3, atol=1e-2)
+
+
+def test_gemm_many_tiles_persistent(native):
+    # more tiles than SMs: exercises the accumulator double-buffering and the stage ring wrap
+    M, N, K = 8192, 4096, 512
+    a, b = _mk(M, N, K, False, False)
+    c = native.gemm(a, b, False, False)
+    ref = _ref(a, b, False, False)
+    assert (c.float() - ref).abs().max().item() <= 1e-2 * ref.abs().max().item() + 1e-2
+
+
+def test_gemm_strided_views(native):
+    base = torch.randn(300, 1024, device="cuda").bfloat16()
+    a = base[:, 256:768]                      # row pitch 1024, width 512
+    w = torch.randn(136, 512, device="cuda").bfloat16()
+    c = native.gemm(a, w, False, False)
+    ref = a.float() @ w.float().t()
+    assert (c.float() - ref).abs().max().item() <= 1e-2 * ref.abs().max().item() + 1e-2
+
+
+def test_linear_autograd(native):
+    x = torch.randn(3, 200, 256, device="cuda").bfloat16().requires_grad_()
+    w = (torch.randn(384, 256, device="cuda") * 0.05).bfloat16().requires_grad_()
+    y = native.linear(x, w)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().float().requires_grad_()
+    yr = torch.nn.functional.linear(xr, wr)
+    yr.backward(g.float())
+    for got, ref in ((y, yr), (x.grad, xr.grad), (w.grad, wr.grad)):
+        assert (got.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2
