@@ -1,0 +1,141 @@
+"""Kernel micro-benchmarks, timed on the device.
+
+Reference counterpart (nngabe/nsa_optim): benchmarks/kernel_benchmark.py:41-559 and
+benchmarks/profile_kernels.py:33-393 time RMSNorm / SwiGLU / RoPE / fused CE with a host
+clock around ``cuda.synchronize``.  Here every number is CUDA-event time on the launching
+stream after warm-up, with an L2 flush (a write larger than the 126 MB L2) between timed
+iterations, and is reported next to the roofline it should be compared with
+(``MEASURED_PEAKS.json`` when present, else 6650 GB/s and 1590 TFLOP/s).
+
+    python -m nsa_optim_b200.benchmarks.kernel_benchmark --op gemm --m 8192 --n 8192 --k 8192
+    python -m nsa_optim_b200.benchmarks.kernel_benchmark --op all --backend native|torch
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+from typing import Callable, Dict, List
+
+import torch
+
+from .. import ops
+
+
+def peaks() -> Dict[str, float]:
+    here = os.path.dirname(os.path.abspath(__file__))
+    path = os.path.join(here, "..", "..", "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+_flush_buf = None
+
+
+def flush_l2() -> None:
+    global _flush_buf
+    if _flush_buf is None:
+        _flush_buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    _flush_buf.zero_()
+
+
+def time_ms(fn: Callable[[], None], iters: int = 10, warmup: int = 3, flush: bool = True) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if flush:
+            flush_l2()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / iters
+
+
+def bench_gemm(m: int, n: int, k: int, a_mn: bool, b_mn: bool, backend: str, iters: int) -> Dict:
+    a = torch.randn((k, m) if a_mn else (m, k), device="cuda").bfloat16()
+    b = torch.randn((k, n) if b_mn else (n, k), device="cuda").bfloat16()
+    if backend == "native":
+        nat = ops.native_module()
+        out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+        fn = lambda: nat.gemm(a, b, a_mn, b_mn, out=out)
+    else:
+        A = a.t() if a_mn else a
+        B = b if b_mn else b.t()
+        fn = lambda: torch.matmul(A, B)
+    ms = time_ms(fn, iters)
+    tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+    pk = peaks()
+    return {"op": f"gemm[{'mn' if a_mn else 'k'}{'mn' if b_mn else 'k'}] {m}x{n}x{k}", "backend": backend, "ms": ms,
+            "tflops": tf, "frac_of_peak": tf / pk["bf16_tflops"], "peak": f"{pk['bf16_tflops']} TFLOP/s of {pk['source']}"}
+
+
+def _bw_row(name: str, backend: str, ms: float, nbytes: float) -> Dict:
+    pk = peaks()
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    return {"op": name, "backend": backend, "ms": ms, "gbs": gbs, "frac_of_peak": gbs / pk["hbm_gbs"],
+            "peak": f"{pk['hbm_gbs']} GB/s of {pk['source']}"}
+
+
+def bench_elementwise(backend: str, rows: int, d: int, ffn: int, iters: int) -> List[Dict]:
+    out = []
+    x = torch.randn(rows, d, device="cuda").bfloat16().requires_grad_()
+    w = torch.ones(d, device="cuda").bfloat16().requires_grad_()
+    g = torch.randn(rows, d, device="cuda").bfloat16()
+    with ops.backend(backend):
+        out.append(_bw_row(f"rmsnorm fwd {rows}x{d}", backend, time_ms(lambda: ops.rms_norm(x, w), iters), 2 * rows * d * 2))
+        y = ops.rms_norm(x, w)
+        out.append(_bw_row(f"rmsnorm bwd {rows}x{d}", backend,
+                           time_ms(lambda: torch.autograd.grad(y, (x, w), g, retain_graph=True), iters), 3 * rows * d * 2))
+        a = torch.randn(rows, ffn, device="cuda").bfloat16().requires_grad_()
+        b = torch.randn(rows, ffn, device="cuda").bfloat16().requires_grad_()
+        gg = torch.randn(rows, ffn, device="cuda").bfloat16()
+        out.append(_bw_row(f"swiglu fwd {rows}x{ffn}", backend, time_ms(lambda: ops.swiglu(a, b), iters), 3 * rows * ffn * 2))
+        z = ops.swiglu(a, b)
+        out.append(_bw_row(f"swiglu bwd {rows}x{ffn}", backend,
+                           time_ms(lambda: torch.autograd.grad(z, (a, b), gg, retain_graph=True), iters), 5 * rows * ffn * 2))
+        q = torch.randn(1, rows, 32, 128, device="cuda").bfloat16()
+        cos, sin = ops.oracle.rope_tables(128, rows, 1e4, device="cuda")
+        out.append(_bw_row(f"rope fwd {rows}x32x128", backend, time_ms(lambda: ops.rope(q, cos, sin), iters), 2 * q.numel() * 2))
+    return out
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", default="all", choices=["all", "gemm", "elementwise"])
+    ap.add_argument("--backend", default="native", choices=["native", "torch"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--a_mn", action="store_true")
+    ap.add_argument("--b_mn", action="store_true")
+    ap.add_argument("--rows", type=int, default=65536)
+    ap.add_argument("--iters", type=int, default=10)
+    a = ap.parse_args()
+    rows: List[Dict] = []
+    if a.op in ("all", "gemm"):
+        if a.op == "gemm":
+            rows.append(bench_gemm(a.m, a.n, a.k, a.a_mn, a.b_mn, a.backend, a.iters))
+        else:
+            for (m, n, k, am, bm) in [(8192, 8192, 8192, False, False), (65536, 8512, 2048, False, False),
+                                      (65536, 2048, 5632, False, False), (65536, 2048, 8512, False, True),
+                                      (8512, 2048, 65536, True, True), (4096, 32000, 2048, False, False)]:
+                rows.append(bench_gemm(m, n, k, am, bm, a.backend, a.iters))
+    if a.op in ("all", "elementwise"):
+        rows += bench_elementwise(a.backend, a.rows, 2048, 5632, a.iters)
+    for r in rows:
+        print(json.dumps(r))
+    if a.backend == "native":
+        ops.native_module().check_status()
+
+
+if __name__ == "__main__":
+    main()

@@ -70,8 +70,21 @@ int sm_count() {
   return g_sms[dev];
 }
 
+// Driver-API calls need a context current on the calling thread.  Threads that have only been
+// handed a device index (autograd worker threads) get the primary context bound here.
+static void bind_primary_context() {
+  static thread_local bool bound = false;
+  if (bound) return;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  cudaSetDevice(dev);
+  cudaFree(nullptr);
+  bound = true;
+}
+
 int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
                    const uint64_t* strides_bytes, const uint32_t* box, int swizzle128) {
+  bind_primary_context();
   EncodeTiledFn enc = encoder();
   if (!enc) return fail(NSA_ERR_DRIVER_API, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t gd[5], gs[5];

@@ -54,7 +54,8 @@ def _codebook_cpu(bits: int, signed: bool) -> Tensor:
             pos = (torch.linspace(0, 1, 9)[1:]) ** 2
             neg = -(torch.linspace(0, 1, 8)[1:]) ** 2
             return torch.cat([neg.flip(0), torch.zeros(1), pos]).float()
-        return (torch.linspace(0, 1, 16) ** 2).float()
+        # no zero entry: a second moment that rounds to 0 would turn the update into m/eps
+        return (torch.linspace(0, 1, 17)[1:] ** 2).float()
     raise ValueError(bits)
 
 

@@ -51,6 +51,10 @@ def attention(q: Tensor, k: Tensor, v: Tensor, causal: bool = True, window: int 
     B, T, Hq, D = q.shape
     Hkv = k.shape[2]
     scale = D ** -0.5 if scale is None else scale
+    S = k.shape[1]
+    if S != T:
+        # queries are the last T positions of an S-long key sequence (KV-cache decoding)
+        return oracle.attention(q, k, v, causal, window, scale)
     if window <= 0 or window >= T:
         qh, kh, vh = (t.permute(0, 2, 1, 3) for t in (q, k, v))
         if Hq != Hkv:

@@ -633,7 +633,8 @@ def lr_multiplier(kind: str, step: int, total: int, warmup: int, min_ratio: floa
 
 def get_lr_scheduler(optimizer: Optimizer, scheduler_type: str, num_training_steps: int,
                      warmup_steps: int, min_lr_ratio: float = 0.1):
-    lr_multiplier(scheduler_type, 0, num_training_steps, warmup_steps, min_lr_ratio)  # validates kind
+    if scheduler_type not in ("cosine", "linear", "constant_with_warmup"):
+        raise ValueError(f"Unknown scheduler type: {scheduler_type}")
     return torch.optim.lr_scheduler.LambdaLR(
         optimizer, lambda s: lr_multiplier(scheduler_type, s, num_training_steps, warmup_steps, min_lr_ratio))
 

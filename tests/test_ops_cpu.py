@@ -1,0 +1,119 @@
+"""Chunked / streaming PyTorch implementations against the naive oracles (CPU, fp32)."""
+import pytest
+import torch
+
+from nsa_optim_b200.ops import oracle, quant, torch_impl
+
+
+def test_ssd_chunked_matches_recurrence():
+    B, T, H, P, N = 2, 70, 4, 8, 16
+    x, dt = torch.randn(B, T, H, P), torch.rand(B, T, H) * 0.5 + 0.01
+    A = -torch.rand(H) - 0.1
+    Bm, Cm, D = torch.randn(B, T, 1, N), torch.randn(B, T, 1, N), torch.randn(H)
+    ref, sref = oracle.ssd_scan(x, dt, A, Bm, Cm, D, return_state=True)
+    got, sgot = torch_impl.ssd_scan(x, dt, A, Bm, Cm, D, chunk=16, return_state=True)
+    assert torch.allclose(got, ref, atol=1e-4, rtol=1e-4)
+    assert torch.allclose(sgot, sref, atol=1e-4, rtol=1e-4)
+
+
+def test_gated_delta_rule_chunked_matches_recurrence():
+    B, T, H, K, V = 2, 50, 3, 16, 24
+    q, k = oracle.l2_norm(torch.randn(B, T, H, K)), oracle.l2_norm(torch.randn(B, T, H, K))
+    v = torch.randn(B, T, H, V)
+    g = -torch.rand(B, T, H) * 0.5
+    beta = torch.rand(B, T, H)
+    ref, sref = oracle.gated_delta_rule(q, k, v, g, beta, return_state=True)
+    got, sgot = torch_impl.gated_delta_rule(q, k, v, g, beta, chunk=16, return_state=True)
+    assert torch.allclose(got, ref, atol=1e-4, rtol=1e-3)
+    assert torch.allclose(sgot, sref, atol=1e-4, rtol=1e-3)
+
+
+@pytest.mark.parametrize("T", [1, 63, 64, 65, 257])
+def test_nsa_streaming_matches_oracle(T):
+    B, Hq, Hkv, D = 1, 4, 2, 16
+    q, k, v = torch.randn(B, T, Hq, D), torch.randn(B, T, Hkv, D), torch.randn(B, T, Hkv, D)
+    g = torch.rand(3, B, T, Hq)
+    kw = dict(cmp_block=8, cmp_stride=4, sel_block=16, top_n=3, window=24)
+    ref = oracle.nsa_attention(q, k, v, g[0], g[1], g[2], **kw)
+    got = torch_impl.nsa_attention(q, k, v, g[0], g[1], g[2], q_chunk=48, **kw)
+    assert torch.allclose(got, ref, atol=1e-4, rtol=1e-4)
+
+
+def test_nsa_selection_rules():
+    T, sel = 128, 16
+    p = torch.rand(1, 1, T, (T - 8) // 4 + 1)
+    idx = oracle.nsa_select(p, T, 8, 4, sel, 4)
+    for t in (0, 15, 16, 100, 127):
+        own = t // sel
+        chosen = set(idx[0, 0, t].tolist()) - {-1}
+        assert 0 in chosen and own in chosen and (own - 1 in chosen or own == 0)
+        assert all(j <= own for j in chosen)
+    assert (idx[0, 0, 5] == -1).sum() == 3       # only block 0 is visible
+
+
+def test_importance_band_is_1_2_2_2_1():
+    w = oracle.nsa_importance_weights(40, 8, 32, 16, 64)
+    assert w[3:8, 1].tolist() == [1, 2, 2, 2, 1] and w[:, 1].sum() == 8
+
+
+def test_windowed_attention_matches_oracle():
+    q, k, v = torch.randn(2, 90, 4, 16), torch.randn(2, 90, 2, 16), torch.randn(2, 90, 2, 16)
+    assert torch.allclose(torch_impl.attention(q, k, v, True, 20), oracle.attention(q, k, v, True, 20), atol=1e-5)
+    assert torch.allclose(torch_impl.attention(q, k, v, True, 0), oracle.attention(q, k, v, True, 0), atol=1e-5)
+
+
+def test_linear_cross_entropy_chunked():
+    h, w = torch.randn(50, 16, requires_grad=True), torch.randn(40, 16, requires_grad=True)
+    y = torch.randint(0, 40, (50,))
+    y[::5] = -100
+    loss = torch_impl.linear_cross_entropy(h, w, y, -100, 16)
+    loss.backward()
+    h2, w2 = h.detach().clone().requires_grad_(), w.detach().clone().requires_grad_()
+    ref = oracle.linear_cross_entropy(h2, w2, y)
+    ref.backward()
+    assert torch.allclose(loss, ref, atol=1e-5)
+    assert torch.allclose(h.grad, h2.grad, atol=1e-5) and torch.allclose(w.grad, w2.grad, atol=1e-5)
+
+
+def test_causal_conv1d_is_causal():
+    x = torch.randn(1, 20, 8)
+    w, b = torch.randn(8, 4), torch.randn(8)
+    y = oracle.causal_conv1d(x, w, b)
+    x2 = x.clone()
+    x2[:, 10:] += 1.0
+    y2 = oracle.causal_conv1d(x2, w, b)
+    assert torch.equal(y[:, :10], y2[:, :10]) and not torch.equal(y[:, 10:], y2[:, 10:])
+
+
+def test_rope_preserves_norm_and_relative_phase():
+    cos, sin = oracle.rope_tables(16, 32, 1e4)
+    x = torch.randn(1, 32, 2, 16)
+    y = oracle.rope(x, cos, sin)
+    assert torch.allclose(x.norm(dim=-1), y.norm(dim=-1), atol=1e-5)
+    q = torch.randn(16).expand(1, 32, 1, 16)
+    k = torch.randn(16).expand(1, 32, 1, 16)
+    s = (oracle.rope(q, cos, sin)[0, 5:, 0] * oracle.rope(k, cos, sin)[0, :-5, 0]).sum(-1)
+    assert torch.allclose(s, s[0].expand_as(s), atol=1e-4)
+
+
+def test_dynamic_codebooks():
+    for signed in (True, False):
+        cb = quant.codebook(8, signed, "cpu")
+        assert cb.numel() == 256 and torch.all(cb[1:] >= cb[:-1]) and cb.max() == 1.0
+        assert (cb.min() < 0) == signed
+    x = torch.randn(1024)
+    codes, absmax = quant.quantize_blockwise(x, 8, True, 256)
+    back = quant.dequantize_blockwise(codes, absmax, 8, True, 256)
+    assert (back - x).abs().max() < 0.05 * x.abs().max()
+    codes4, am4 = quant.quantize_blockwise(x, 4, True, 64)
+    assert codes4.numel() == 512
+    assert (quant.dequantize_blockwise(codes4, am4, 4, True, 64) - x).abs().mean() < 0.2
+
+
+@pytest.mark.parametrize("bits,tol", [(8, 0.01), (4, 0.1)])
+def test_affine_roundtrip(bits, tol):
+    q_in = torch.linalg.qr(torch.randn(70, 70))[0]
+    q, s, z, cols = quant.affine_quantize(q_in, bits, 32)
+    assert q.dtype == torch.uint8 and cols == 70 and q.shape == (70, 96)
+    back = quant.affine_dequantize(q, s, z, cols)
+    assert (back - q_in).abs().max() < tol
