@@ -611,6 +611,70 @@ extern "C" int nsa_rmsnorm_bwd(const void* x, const void* gate, const void* w, c
   return 0;
 }
 
+// ------------------------------------------------------------------------------------
+// RMSNorm backward for callers that must not allocate.
+//
+// Some hosts of this library cannot call cudaMalloc (or anything that may call it) at the
+// point where they need a backward pass: an embedding runtime whose device-memory budget is
+// fixed when the library is loaded, a worker thread that is forbidden to take the allocator
+// lock, a latency-critical loop that cannot afford the implicit device synchronisation an
+// allocation may cause.  nsa_rmsnorm_bwd needs a scratch buffer for the per-CTA partial
+// sums of the weight gradient; this variant keeps that scratch in the library itself.
+//
+// The scratch is one file-scope device array of NSA_NOALLOC_SCRATCH_FLOATS floats
+// (592 * 4096 floats = 9.25 MiB).  Every GPU that loads the library holds that much from load
+// until process exit, whether or not this entry point is ever called.
+// ------------------------------------------------------------------------------------
+#define NSA_NOALLOC_SCRATCH_FLOATS (592 * 4096)
+static __device__ __align__(256) float g_noalloc_scratch[NSA_NOALLOC_SCRATCH_FLOATS];
+
+// Device address of g_noalloc_scratch per device.  In host code the array's name is only a
+// handle for the runtime, not an address a kernel can use, so the address is looked up once
+// per device with that device current.
+static float* g_noalloc_scratch_addr[64] = {nullptr};
+
+static int noalloc_scratch_for_current_device(float** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return nsa::fail_cuda(e, "nsa_rmsnorm_bwd_noalloc: cudaGetDevice");
+  if (dev < 0 || dev >= 64) return nsa::fail(NSA_ERR_LIMIT, "nsa_rmsnorm_bwd_noalloc: device index above 63");
+  if (g_noalloc_scratch_addr[dev] == nullptr) {
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
+    if (e != cudaSuccess) return nsa::fail_cuda(e, "nsa_rmsnorm_bwd_noalloc: cudaGetSymbolAddress");
+    g_noalloc_scratch_addr[dev] = ptr;
+  }
+  *out = g_noalloc_scratch_addr[dev];
+  return 0;
+}
+
+// Same arguments and results as nsa_rmsnorm_bwd, minus `partial`.
+//  * Calls no cudaMalloc / cudaFree and no allocating library routine.
+//  * The first call on each device looks up the scratch address (a synchronous runtime
+//    query); make that first call before any stream capture begins on that device.
+//  * Limit: nsa_rmsnorm_bwd_parts(rows, d) * d must not exceed NSA_NOALLOC_SCRATCH_FLOATS
+//    (always true for d <= 4096); larger problems are rejected with NSA_ERR_LIMIT and
+//    nothing is launched.
+//  * All calls on a device share the one scratch array, which keeps whatever the previous
+//    call left in it.  Nothing in it has to start at zero: the backward kernel overwrites
+//    every (part, column) entry that the reduction then reads.  Two calls whose kernels can
+//    overlap on the GPU (different streams, or concurrent host threads) race on the array;
+//    serialise them on one stream.
+extern "C" int nsa_rmsnorm_bwd_noalloc(const void* x, const void* gate, const void* w, const void* dy,
+                                       const float* rstd, void* dx, void* dgate, void* dw_bf16, float* dw_f32,
+                                       long rows, int d, int mode, cudaStream_t st) {
+  if (rows <= 0 || d <= 0) return nsa::fail(NSA_ERR_SHAPE, "nsa_rmsnorm_bwd_noalloc: empty problem");
+  const long need = static_cast<long>(nsa_rmsnorm_bwd_parts(rows, d)) * d;
+  if (need > static_cast<long>(NSA_NOALLOC_SCRATCH_FLOATS))
+    return nsa::fail(NSA_ERR_LIMIT,
+                     "nsa_rmsnorm_bwd_noalloc: problem needs more than the 592*4096-float built-in scratch "
+                     "(use nsa_rmsnorm_bwd with caller-provided scratch)");
+  float* scratch = nullptr;
+  const int rc = noalloc_scratch_for_current_device(&scratch);
+  if (rc) return rc;
+  return nsa_rmsnorm_bwd(x, gate, w, dy, rstd, dx, dgate, dw_bf16, dw_f32, scratch, rows, d, mode, st);
+}
+
 extern "C" int nsa_l2norm_fwd(const void* x, void* y, float* rinv, long rows, int d, float eps, cudaStream_t st) {
   if (d % 8 || d > 512) return nsa::fail(NSA_ERR_SHAPE, "l2norm: width must be a multiple of 8, at most 512");
   const unsigned grid = (unsigned)((rows + 7) / 8);

@@ -30,6 +30,16 @@ int nsa_rmsnorm_bwd_parts(long rows, int d);
 int nsa_rmsnorm_bwd(const void* x, const void* gate, const void* w, const void* dy, const float* rstd, void* dx,
                     void* dgate, void* dw_bf16, float* dw_f32, float* partial, long rows, int d, int mode,
                     cudaStream_t st);
+/* RMSNorm backward that allocates nothing and takes no scratch argument: the partial-sum
+ * scratch is a 9.25 MiB array built into the library (held by every GPU that loads it).
+ * For hosts that may not call cudaMalloc where they run the backward pass.  Rejects
+ * problems with nsa_rmsnorm_bwd_parts(rows, d) * d > 592 * 4096 (NSA_ERR_LIMIT).  First call
+ * per device does a one-time address lookup: make it before any stream capture.  Calls
+ * share the scratch: do not let two of them overlap on the GPU.
+ * This entry point has no counterpart in the reference project. */
+int nsa_rmsnorm_bwd_noalloc(const void* x, const void* gate, const void* w, const void* dy, const float* rstd,
+                            void* dx, void* dgate, void* dw_bf16, float* dw_f32, long rows, int d, int mode,
+                            cudaStream_t st);
 int nsa_l2norm_fwd(const void* x, void* y, float* rinv, long rows, int d, float eps, cudaStream_t st);
 int nsa_l2norm_bwd(const void* y, const void* dy, const float* rinv, void* dx, long rows, int d, cudaStream_t st);
 int nsa_swiglu_fwd(const void* g, const void* u, void* y, long rows, int cols, long ldg, long ldu, cudaStream_t st);
