@@ -26,7 +26,7 @@ _lib: Optional[ctypes.CDLL] = None
 
 SUPPORTED = {
     "linear", "rms_norm", "gated_rms_norm", "swiglu", "l2_norm", "rope", "embedding",
-    "causal_conv1d", "linear_cross_entropy", "adamw", "adamw_lowbit",
+    "causal_conv1d", "linear_cross_entropy", "adamw", "adamw_lowbit", "gated_delta_rule",
 }
 
 STATUS_NAMES = {
@@ -468,3 +468,83 @@ def adamw8bit_step(p, g, mq, mabs, vq, vabs, step, lr, b1, b2, eps, wd, grad_sca
                                      c_long(p.numel()), c_int(int(p.dtype == torch.float32)),
                                      c_int(int(g.dtype == torch.float32)), c_int(step), c_float(lr), c_float(b1),
                                      c_float(b2), c_float(eps), c_float(wd), _stream()))
+
+
+# --------------------------------------------------------------------------------------
+# gated delta rule (chunk 64, key width 128)
+# --------------------------------------------------------------------------------------
+class _GDNSeq(torch.autograd.Function):
+    """Inter-chunk state recurrence of the gated delta rule on tcgen05 (``csrc/gdn.cu``).
+    Inputs are the per-chunk operands of the WY form, (BH, NC, 64, .) contiguous bf16."""
+
+    @staticmethod
+    def forward(ctx, w, qd, kt, u, gamma):
+        BH, NC, C, K = w.shape
+        V = u.shape[-1]
+        v_new = torch.empty_like(u)
+        o_inter = torch.empty(BH, NC, C, V, dtype=torch.float32, device=u.device)
+        S_all = torch.empty(BH, NC, K, V, dtype=torch.bfloat16, device=u.device)
+        _check(load().nsa_gdn_seq_fwd(_p(w), _p(qd), _p(kt), _p(u), _p(gamma), _p(v_new), _p(o_inter), _p(S_all),
+                                      c_int(BH), c_int(NC), c_int(K), c_int(V), _stream()))
+        ctx.save_for_backward(w, qd, kt, gamma, S_all, v_new)
+        return v_new, o_inter
+
+    @staticmethod
+    def backward(ctx, dv_new, do_inter):
+        w, qd, kt, gamma, S_all, v_new = ctx.saved_tensors
+        BH, NC, C, K = w.shape
+        V = v_new.shape[-1]
+        nvt = V // 64
+        dv = torch.zeros_like(v_new) if dv_new is None else dv_new.to(torch.bfloat16).contiguous()
+        do = torch.zeros_like(v_new) if do_inter is None else do_inter.to(torch.bfloat16).contiguous()
+        du = torch.empty_like(v_new)
+        parts = torch.empty(3, nvt, BH, NC, C, K, dtype=torch.bfloat16, device=w.device)
+        dgp = torch.empty(nvt, BH, NC, dtype=torch.float32, device=w.device)
+        _check(load().nsa_gdn_seq_bwd(_p(w), _p(qd), _p(kt), _p(S_all), _p(v_new), _p(dv), _p(do), _p(gamma), _p(du),
+                                      _p(parts[0]), _p(parts[1]), _p(parts[2]), _p(dgp), c_int(BH), c_int(NC),
+                                      c_int(K), c_int(V), _stream()))
+        red = parts.float().sum(1).to(torch.bfloat16)
+        return red[0], red[1], red[2], du, dgp.sum(0)
+
+
+def gated_delta_rule(q, k, v, g, beta, scale=None, chunk=64):
+    """Chunkwise gated delta rule.  The per-chunk WY pre-pass and the intra-chunk output term
+    are batched PyTorch ops over all chunks at once; the sequential state pass is native."""
+    B, T, H, K = q.shape
+    V = v.shape[-1]
+    if K != 128 or V % 64 or chunk != 64:
+        return torch_impl.gated_delta_rule(q, k, v, g, beta, scale, chunk)
+    scale = K ** -0.5 if scale is None else scale
+    C = 64
+    pad = (-T) % C
+    if pad:
+        q, k, v = (torch.nn.functional.pad(t, (0, 0, 0, 0, 0, pad)) for t in (q, k, v))
+        g, beta = torch.nn.functional.pad(g, (0, 0, 0, pad)), torch.nn.functional.pad(beta, (0, 0, 0, pad))
+    Tp = T + pad
+    nc = Tp // C
+    f32, bf = torch.float32, torch.bfloat16
+    qh = q.permute(0, 2, 1, 3).reshape(B * H, nc, C, K)
+    kh = k.permute(0, 2, 1, 3).reshape(B * H, nc, C, K)
+    vh = v.permute(0, 2, 1, 3).reshape(B * H, nc, C, V)
+    gh = g.to(f32).permute(0, 2, 1).reshape(B * H, nc, C)
+    bh = beta.to(f32).permute(0, 2, 1).reshape(B * H, nc, C)
+    gc = torch.cumsum(gh, -1)
+    diff = gc[..., :, None] - gc[..., None, :]
+    lower = torch.ones(C, C, dtype=torch.bool, device=q.device).tril(-1)
+    incl = torch.ones(C, C, dtype=torch.bool, device=q.device).tril(0)
+    kk = torch.matmul(kh, kh.transpose(-1, -2)).to(f32)
+    Amat = bh[..., None] * kk * torch.exp(diff.masked_fill(~lower, float("-inf")))
+    eye = torch.eye(C, device=q.device, dtype=f32)
+    rhs = torch.cat([vh.to(f32) * bh[..., None], kh.to(f32) * (bh * torch.exp(gc))[..., None]], -1)
+    sol = torch.linalg.solve_triangular(eye + Amat, rhs, upper=False, unitriangular=True)
+    u = sol[..., :V].to(bf).contiguous()
+    w = sol[..., V:].to(bf).contiguous()
+    qk = (torch.matmul(qh, kh.transpose(-1, -2)).to(f32) * scale
+          * torch.exp(diff.masked_fill(~incl, float("-inf")))).to(bf)
+    qd = (qh.to(f32) * (scale * torch.exp(gc))[..., None]).to(bf).contiguous()
+    kt = (kh.to(f32) * torch.exp(gc[..., -1:] - gc)[..., None]).to(bf).contiguous()
+    gamma = torch.exp(gc[..., -1]).contiguous()
+    v_new, o_inter = _GDNSeq.apply(w, qd, kt, u, gamma)
+    o = o_inter + torch.matmul(qk, v_new).to(f32)
+    o = o.reshape(B, H, Tp, V).permute(0, 2, 1, 3)[:, :T]
+    return o.to(v.dtype)
