@@ -1,0 +1,865 @@
+// Attention family on tcgen05: one forward kernel and one backward kernel cover dense causal
+// GQA attention, sliding-window attention, and the three branches of native sparse attention
+// (compressed-block attention, selected-block attention, plus the block-importance pass that
+// feeds top-n selection).
+//
+// Tiling.  A query tile is 128 rows = R consecutive tokens x G query heads of one KV head
+// (G = Hq / Hkv, R = 128 / G), so one K/V tile serves the whole GQA group.  A key tile is 128
+// keys, loaded as two 64-row TMA boxes: for dense / windowed / compressed attention they are
+// adjacent, for selected-block attention they are two (not necessarily adjacent) 64-key
+// selection blocks from the union of the blocks chosen by the tile's R tokens; a per-entry
+// bit mask says which tokens chose which block.
+//
+// Forward: S = Q K^T into one of two TMEM buffers (the MMA for tile j+1 is issued before the
+// softmax of tile j), each thread owns one row (tcgen05.ld 32x32b): running max with lazy
+// rescaling of the TMEM-resident O accumulator, P written to shared memory as bf16 in the
+// swizzled K-major layout, O += P V.  Output O (bf16) and L = log2-sum-exp (fp32).
+// Backward (query-tile outer): recomputes S and dP = dO V^T, forms P and dS in registers,
+// accumulates dQ in TMEM and adds each tile's dK / dV contribution to fp32 global buffers
+// with vector reductions.
+//
+// Key positions are affine in the key index (pos = idx * kp_stride + kp_off): identity for
+// ordinary attention, (stride, block-1) for compressed keys, which makes "causal on block
+// end" the same comparison as ordinary causality.
+#include "host.cuh"
+#include "tc5.cuh"
+
+namespace {
+typedef __nv_bfloat16 bf16;
+constexpr int BM = 128;
+constexpr int BN = 128;
+constexpr int HALF = 8192;          // bytes of a [64 rows][64 bf16] box
+
+struct AttnParams {
+  int B, T, S;                      // query tokens and keys per batch entry
+  int Hq, Hkv, G, R, D;
+  float scale_log2;                 // softmax scale * log2(e)
+  int causal, window;               // window 0 = unbounded
+  int kp_stride, kp_off;
+  // selected-block mode (null tile_blocks = contiguous key range)
+  const int* tile_blocks;           // [B, Hkv, nQt, max_u] 64-key block ids, -1 = none
+  const unsigned long long* tile_masks;   // [B, Hkv, nQt, max_u] bit i: token i of the tile chose the block
+  const int* tile_counts;           // [B, Hkv, nQt]
+  int max_u;
+  bf16* O;                          // [B, T, Hq, D]
+  float* L;                         // [B, T, Hq]  log2 domain
+  // importance mode
+  const float* L_in;
+  float* imp;                       // [B, Hkv, T, nS]
+  int nS, cells_per_block;          // cells_per_block = sel_block / kp_stride
+  // backward
+  const bf16* dO;
+  const float* delta;               // [B, T, Hq]  rowsum(dO * O)
+  float* dQ;                        // unused (dQ written as bf16 below)
+  bf16* dQb;                        // [B, T, Hq, D]
+  float* dK;                        // [B, S, Hkv, D] fp32, pre-zeroed
+  float* dV;
+  KernelStatus* status;
+};
+
+// Which key tiles a query tile visits, for contiguous-range modes.
+__device__ __forceinline__ void key_tile_range(const AttnParams& p, int t_lo, int t_hi, int& j0, int& j1) {
+  // keys with pos <= t_hi (causal) and pos > t_lo - window (window)
+  long last = p.S - 1;
+  if (p.causal) {
+    long lim = (static_cast<long>(t_hi) - p.kp_off);
+    lim = lim < 0 ? -1 : lim / p.kp_stride;
+    last = lim < last ? lim : last;
+  }
+  long first = 0;
+  if (p.window > 0) {
+    long lo = static_cast<long>(t_lo) - p.window + 1 - p.kp_off;   // pos >= t_lo - window + 1
+    first = lo <= 0 ? 0 : (lo + p.kp_stride - 1) / p.kp_stride;
+  }
+  j0 = static_cast<int>(first / BN);
+  j1 = last < first ? j0 : static_cast<int>(last / BN) + 1;        // exclusive
+}
+
+// --------------------------------------------------------------------------------------
+// Shared pieces of the forward and backward kernels.
+//
+// 256 threads: thread (r, ch) with r = threadIdx.x & 127, ch = threadIdx.x >> 7 owns query row
+// r and the 64 score columns of key half ch (warps w and w+4 read the same TMEM lane quarter).
+// A key half is 64 consecutive keys; per (CTA, half) a uniform flag says whether any mask test
+// is needed at all, so interior tiles run the mask-free path.
+// --------------------------------------------------------------------------------------
+struct HalfInfo {
+  int s_base;        // first key index of the half, -1 = absent
+  bool row_sel;      // this thread's row may see the half at all (selection bit, row validity)
+  bool need_check;   // uniform: causal / window / bounds tests needed for some element
+};
+
+__device__ __forceinline__ HalfInfo half_info(const AttnParams& p, bool selected, const int* blocks,
+                                              const unsigned long long* masks, int j0, int j, int ch, int q0,
+                                              int t_hi, int tok_local, bool row_ok) {
+  HalfInfo hi;
+  if (!selected) {
+    hi.s_base = (j0 + j) * BN + ch * 64;
+    hi.row_sel = row_ok;
+  } else {
+    const int e = 2 * j + ch;
+    const int blk = e < p.max_u ? blocks[e] : -1;
+    hi.s_base = blk < 0 ? -1 : blk * 64;
+    const unsigned long long mk = e < p.max_u ? masks[e] : 0ull;
+    hi.row_sel = row_ok && blk >= 0 && ((mk >> (tok_local & 63)) & 1ull);
+  }
+  const int s_lo = hi.s_base, s_hi = hi.s_base + 63;
+  bool need = s_hi >= p.S;
+  if (p.causal) need = need || (s_hi * p.kp_stride + p.kp_off > q0);
+  if (p.window > 0) need = need || (s_lo * p.kp_stride + p.kp_off <= t_hi - p.window);
+  hi.need_check = need;
+  return hi;
+}
+
+__device__ __forceinline__ bool key_visible(const AttnParams& p, int s, int t) {
+  const int pos = s * p.kp_stride + p.kp_off;
+  bool v = s < p.S;
+  if (p.causal) v = v && pos <= t;
+  if (p.window > 0) v = v && pos > t - p.window;
+  return v;
+}
+
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&v)[64]) {
+  uint32_t a[32], b[32];
+  tc5::tmem_ld_x32(taddr, a);
+  tc5::tmem_ld_x32(taddr + 32, b);
+  tc5::tmem_ld_wait();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) { v[i] = a[i]; v[32 + i] = b[i]; }
+}
+
+// write 64 bf16 (32 packed pairs) as row `row` of a [128][64] swizzled k-block
+__device__ __forceinline__ void store_row64(uint8_t* kblock, int row, const uint32_t (&pk)[32]) {
+  uint8_t* base = kblock + row * 128;
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    *reinterpret_cast<uint4*>(base + ((j ^ (row & 7)) << 4)) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+}
+
+// --------------------------------------------------------------------------------------
+// Forward.  MODE 0: attention output + L.  MODE 1: block importance from a second pass over
+// compressed keys (p = exp2(s*c - L_in), summed over the G heads of a token and binned into
+// selection blocks; requires sel_block = 4 * stride and cmp_block = 2 * stride).
+// --------------------------------------------------------------------------------------
+template <int D, int MODE>
+__global__ void __launch_bounds__(256, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+  constexpr int KB = D / 64;
+  constexpr int TILE = KB * 2 * HALF;
+  constexpr int DH = D / 2;                  // O columns per thread
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + TILE;
+  uint8_t* sV = sK + 2 * TILE;
+  uint8_t* sP = sV + 2 * TILE;               // [2 k-blocks][128][64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 4 * HALF);
+  uint64_t* qbar = bars;
+  uint64_t* kfull = bars + 1;
+  uint64_t* vfull = bars + 3;
+  uint64_t* sdone = bars + 5;
+  uint64_t* odone = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* red = reinterpret_cast<float*>(bars + 10);      // [2][128]
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int r = tid & 127, ch = tid >> 7;
+  const int qt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int q0 = qt * p.R;
+  const int tok_local = r / p.G, g = r % p.G;
+  const int t = q0 + tok_local;
+  const bool row_ok = t < p.T;
+  const int t_hi = min(q0 + p.R, p.T) - 1;
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    tc5::mbar_init(qbar, 1);
+    for (int i = 0; i < 2; ++i) { tc5::mbar_init(&kfull[i], 1); tc5::mbar_init(&vfull[i], 1); tc5::mbar_init(&sdone[i], 1); }
+    tc5::mbar_init(odone, 1);
+    tc5::fence_barrier_init();
+  }
+  if (warp == 0) { tc5::tmem_alloc(tmem_slot, 512); tc5::tmem_relinquish(); }
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+  const uint32_t cO = 256;
+
+  const bool selected = p.tile_blocks != nullptr;
+  const long tile_slot = (static_cast<long>(b) * p.Hkv + h) * gridDim.x + qt;
+  const int* blocks = selected ? p.tile_blocks + tile_slot * p.max_u : nullptr;
+  const unsigned long long* masks = selected ? p.tile_masks + tile_slot * p.max_u : nullptr;
+  int j0 = 0, j1 = 0;
+  if (selected) { j1 = (p.tile_counts[tile_slot] + 1) / 2; }
+  else key_tile_range(p, q0, t_hi, j0, j1);
+  const int n_tiles = j1 - j0;
+
+  auto load_kv = [&](const CUtensorMap* tm, uint8_t* dst, uint64_t* bar, int j) {
+    tc5::mbar_expect_tx(bar, TILE);
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      int s0;
+      if (!selected) s0 = (j0 + j) * BN + hh * 64;
+      else { const int e = 2 * j + hh; const int blk = e < p.max_u ? blocks[e] : -1; s0 = blk < 0 ? 0 : blk * 64; }
+#pragma unroll
+      for (int kb = 0; kb < KB; ++kb)
+        tc5::tma_load_4d(dst + kb * 2 * HALF + hh * HALF, tm, bar, kb * 64, h, s0, b);
+    }
+  };
+  constexpr uint32_t id_s = tc5::make_idesc_bf16(128, 128, 0, 0);
+  constexpr uint32_t id_o = tc5::make_idesc_bf16(128, D, 0, 1);
+  auto issue_s = [&](int j) {
+    const uint32_t q = tc5::smem_u32(sQ), k = tc5::smem_u32(sK + (j & 1) * TILE);
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk)
+      tc5::mma_ss(tmem + (j & 1) * 128, tc5::desc_kmajor(q + (kk >> 2) * 2 * HALF + (kk & 3) * 32),
+                  tc5::desc_kmajor(k + (kk >> 2) * 2 * HALF + (kk & 3) * 32), id_s, kk > 0 ? 1u : 0u);
+    tc5::mma_commit(&sdone[j & 1]);
+  };
+
+  if (tid == 0 && n_tiles > 0) {
+    tc5::mbar_expect_tx(qbar, TILE);
+#pragma unroll
+    for (int kb = 0; kb < KB; ++kb) tc5::tma_load_5d(sQ + kb * 2 * HALF, &tm_q, qbar, kb * 64, 0, h, q0, b);
+    load_kv(&tm_k, sK, &kfull[0], 0);
+    if (MODE == 0) load_kv(&tm_v, sV, &vfull[0], 0);
+    if (n_tiles > 1) load_kv(&tm_k, sK + TILE, &kfull[1], 1);
+  }
+
+  float m_ref = -INFINITY, l_sum = 0.f;
+  const float Lrow = (MODE == 1 && row_ok) ? p.L_in[(static_cast<long>(b) * p.T + t) * p.Hq + h * p.G + g] : 0.f;
+  const float sc = p.scale_log2;
+  bool ok = true;
+  for (int j = 0; j < n_tiles && ok; ++j) {
+    if (tid == 0) {
+      bool good = true;
+      if (j == 0) {
+        good = tc5::mbar_wait(qbar, 0, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL) &&
+               tc5::mbar_wait(&kfull[0], 0, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL);
+        if (good) { tc5::fence_after_sync(); issue_s(0); }
+      }
+      if (good && j + 1 < n_tiles) {
+        if (tc5::mbar_wait(&kfull[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL)) {
+          tc5::fence_after_sync();
+          issue_s(j + 1);
+        }
+      }
+    }
+    const HalfInfo hi = half_info(p, selected, blocks, masks, j0, j, ch, q0, t_hi, tok_local, row_ok);
+    if (!tc5::mbar_wait(&sdone[j & 1], (j >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) ok = false;
+    if (__syncthreads_or(!ok)) { ok = false; break; }
+    tc5::fence_after_sync();
+    if (tid == 0 && j + 2 < n_tiles) load_kv(&tm_k, sK + (j & 1) * TILE, &kfull[j & 1], j + 2);
+
+    uint32_t sv[64];
+    tmem_ld64(tmem + lane_off + (j & 1) * 128 + ch * 64, sv);
+
+    if (MODE == 0) {
+      float mx = -INFINITY;
+      if (hi.row_sel) {
+        if (!hi.need_check) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 64; ++i)
+            if (key_visible(p, hi.s_base + i, t)) mx = fmaxf(mx, __uint_as_float(sv[i]));
+        }
+      }
+      red[ch * 128 + r] = mx;
+      __syncthreads();
+      mx = fmaxf(red[r], red[128 + r]) * sc;
+      float alpha = 1.f;
+      if (mx != -INFINITY && (m_ref == -INFINITY || mx > m_ref + 8.f)) {
+        alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - mx);
+        m_ref = mx;
+      }
+      // probabilities (kept packed in registers until the previous P*V has released P)
+      uint32_t pk[32];
+      float psum = 0.f;
+      if (!hi.row_sel || m_ref == -INFINITY) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) pk[i] = 0u;
+      } else if (!hi.need_check) {
+#pragma unroll
+        for (int i = 0; i < 64; i += 2) {
+          const float a = exp2f(fmaf(__uint_as_float(sv[i]), sc, -m_ref));
+          const float c = exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -m_ref));
+          psum += a + c;
+          pk[i / 2] = tc5::pack_bf16(a, c);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; i += 2) {
+          const float a = key_visible(p, hi.s_base + i, t) ? exp2f(fmaf(__uint_as_float(sv[i]), sc, -m_ref)) : 0.f;
+          const float c = key_visible(p, hi.s_base + i + 1, t) ? exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -m_ref)) : 0.f;
+          psum += a + c;
+          pk[i / 2] = tc5::pack_bf16(a, c);
+        }
+      }
+      l_sum = l_sum * alpha + psum;
+      if (j > 0) {
+        if (!tc5::mbar_wait(odone, (j - 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) ok = false;
+        tc5::fence_after_sync();
+      }
+      if (tid == 0 && ok && j + 1 < n_tiles) load_kv(&tm_v, sV + ((j + 1) & 1) * TILE, &vfull[(j + 1) & 1], j + 1);
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+        for (int q4 = 0; q4 < DH / 32; ++q4) {
+          uint32_t v[32];
+          tc5::tmem_ld_x32(tmem + lane_off + cO + ch * DH + q4 * 32, v);
+          tc5::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+          tc5::tmem_st_x32(tmem + lane_off + cO + ch * DH + q4 * 32, v);
+        }
+        tc5::tmem_st_wait();
+      }
+      store_row64(sP + ch * 2 * HALF, r, pk);
+      tc5::fence_proxy_async();
+      tc5::fence_before_sync();
+      if (__syncthreads_or(!ok)) { ok = false; break; }
+      if (tid == 0) {
+        if (tc5::mbar_wait(&vfull[j & 1], (j >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL)) {
+          tc5::fence_after_sync();
+          const uint32_t pb = tc5::smem_u32(sP), vb = tc5::smem_u32(sV + (j & 1) * TILE);
+#pragma unroll
+          for (int kk = 0; kk < BN / 16; ++kk)
+            tc5::mma_ss(tmem + cO, tc5::desc_kmajor(pb + (kk >> 2) * 2 * HALF + (kk & 3) * 32),
+                        tc5::desc_mnmajor(vb + kk * 2048, 2 * HALF), id_o, (j > 0 || kk > 0) ? 1u : 0u);
+          tc5::mma_commit(odone);
+        }
+      }
+    } else {
+      // importance: compressed key i covers 16-token cells i and i+1; a selection block is 4 cells
+      float bins[17];
+#pragma unroll
+      for (int i = 0; i < 17; ++i) bins[i] = 0.f;
+      if (hi.row_sel) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          const bool vis = !hi.need_check || key_visible(p, hi.s_base + i, t);
+          const float pr = vis ? exp2f(fmaf(__uint_as_float(sv[i]), sc, -Lrow)) : 0.f;
+          bins[i / 4] += pr;
+          bins[(i + 1) / 4] += pr;
+        }
+      }
+      for (int o = p.G >> 1; o > 0; o >>= 1)
+#pragma unroll
+        for (int i = 0; i < 17; ++i) bins[i] += __shfl_xor_sync(0xffffffffu, bins[i], o);
+      if (g == 0 && row_ok) {
+        const int jb = (j0 + j) * (BN / 4) + ch * 16;
+        float* dst = p.imp + ((static_cast<long>(b) * p.Hkv + h) * p.T + t) * p.nS;
+#pragma unroll
+        for (int i = 0; i < 17; ++i)
+          if (jb + i < p.nS && bins[i] != 0.f) atomicAdd(dst + jb + i, bins[i]);
+      }
+      tc5::fence_before_sync();
+      __syncthreads();
+    }
+  }
+
+  if (MODE == 0) {
+    if (ok && n_tiles > 0) {
+      if (!tc5::mbar_wait(odone, (n_tiles - 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) ok = false;
+      tc5::fence_after_sync();
+    }
+    red[ch * 128 + r] = l_sum;
+    const bool have = !__syncthreads_or(!ok) && n_tiles > 0;
+    const float l_tot = red[r] + red[128 + r];
+    const long rowi = (static_cast<long>(b) * p.T + t) * p.Hq + h * p.G + g;
+    const float inv = (have && l_tot > 0.f) ? 1.f / l_tot : 0.f;
+    if (row_ok && ch == 0) p.L[rowi] = (have && l_tot > 0.f) ? m_ref + log2f(l_tot) : -INFINITY;
+    bf16* dst = p.O + rowi * D + ch * DH;
+#pragma unroll
+    for (int q4 = 0; q4 < DH / 32; ++q4) {
+      uint32_t v[32];
+      if (have) {
+        tc5::tmem_ld_x32(tmem + lane_off + cO + ch * DH + q4 * 32, v);
+        tc5::tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = 0u;
+      }
+      if (row_ok) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint4 o4;
+          o4.x = tc5::pack_bf16(__uint_as_float(v[8 * i]) * inv, __uint_as_float(v[8 * i + 1]) * inv);
+          o4.y = tc5::pack_bf16(__uint_as_float(v[8 * i + 2]) * inv, __uint_as_float(v[8 * i + 3]) * inv);
+          o4.z = tc5::pack_bf16(__uint_as_float(v[8 * i + 4]) * inv, __uint_as_float(v[8 * i + 5]) * inv);
+          o4.w = tc5::pack_bf16(__uint_as_float(v[8 * i + 6]) * inv, __uint_as_float(v[8 * i + 7]) * inv);
+          reinterpret_cast<uint4*>(dst + q4 * 32)[i] = o4;
+        }
+      }
+    }
+  }
+  if (!ok && tid == 0) {
+    const long long t0 = clock64();
+    uint64_t* pend[5] = {qbar, &kfull[0], &kfull[1], &vfull[0], &vfull[1]};
+    for (int i = 0; i < 5; ++i)
+      for (uint32_t n = 0; n < (1u << 16); ++n) {
+        if (tc5::mbar_try_wait(pend[i], 0) || tc5::mbar_try_wait(pend[i], 1)) break;
+        if (clock64() - t0 > tc5::kMaxWaitCycles) break;
+      }
+  }
+  tc5::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) { tc5::fence_after_sync(); tc5::tmem_dealloc(tmem, 512); }
+}
+
+// --------------------------------------------------------------------------------------
+// Backward, query-tile outer.  Per key tile: S = Q K^T and dP = dO V^T (TMEM), then in
+// registers P = exp2(S c - L), dS = P (dP - delta) scale; then dQ += dS K (TMEM resident),
+// and the tile's dV = P^T dO, dK = dS^T Q are added to fp32 global buffers.
+// --------------------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(256, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+                const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                const AttnParams p, const float scale) {
+  constexpr int KB = D / 64;
+  constexpr int TILE = KB * 2 * HALF;
+  constexpr int DH = D / 2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sDO = sQ + TILE;
+  uint8_t* sK = sDO + TILE;
+  uint8_t* sV = sK + TILE;
+  uint8_t* sP = sV + TILE;
+  uint8_t* sDS = sP + 4 * HALF;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + 4 * HALF);
+  uint64_t* qbar = bars;
+  uint64_t* kvbar = bars + 1;
+  uint64_t* m1 = bars + 2;
+  uint64_t* m2 = bars + 3;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int r = tid & 127, ch = tid >> 7;
+  const int qt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int q0 = qt * p.R;
+  const int tok_local = r / p.G, g = r % p.G;
+  const int t = q0 + tok_local;
+  const bool row_ok = t < p.T;
+  const int t_hi = min(q0 + p.R, p.T) - 1;
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    tc5::mbar_init(qbar, 1);
+    tc5::mbar_init(kvbar, 1);
+    tc5::mbar_init(m1, 1);
+    tc5::mbar_init(m2, 1);
+    tc5::fence_barrier_init();
+  }
+  if (warp == 0) { tc5::tmem_alloc(tmem_slot, 512); tc5::tmem_relinquish(); }
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+  const uint32_t cS = 0, cDP = 128, cDQ = 256, cDV = 384, cDK = 0;   // dK reuses the S columns
+
+  const bool selected = p.tile_blocks != nullptr;
+  const long tile_slot = (static_cast<long>(b) * p.Hkv + h) * gridDim.x + qt;
+  const int* blocks = selected ? p.tile_blocks + tile_slot * p.max_u : nullptr;
+  const unsigned long long* masks = selected ? p.tile_masks + tile_slot * p.max_u : nullptr;
+  int j0 = 0, j1 = 0;
+  if (selected) { j1 = (p.tile_counts[tile_slot] + 1) / 2; }
+  else key_tile_range(p, q0, t_hi, j0, j1);
+  const int n_tiles = j1 - j0;
+
+  const long rowi = (static_cast<long>(b) * p.T + t) * p.Hq + h * p.G + g;
+  const float Lrow = row_ok ? p.L[rowi] : 0.f;
+  const float drow = row_ok ? p.delta[rowi] : 0.f;
+  const float sc = p.scale_log2;
+
+  if (tid == 0 && n_tiles > 0) {
+    tc5::mbar_expect_tx(qbar, 2 * TILE);
+#pragma unroll
+    for (int kb = 0; kb < KB; ++kb) {
+      tc5::tma_load_5d(sQ + kb * 2 * HALF, &tm_q, qbar, kb * 64, 0, h, q0, b);
+      tc5::tma_load_5d(sDO + kb * 2 * HALF, &tm_do, qbar, kb * 64, 0, h, q0, b);
+    }
+  }
+  constexpr uint32_t id_s = tc5::make_idesc_bf16(128, 128, 0, 0);
+  constexpr uint32_t id_q = tc5::make_idesc_bf16(128, D, 0, 1);
+  constexpr uint32_t id_t = tc5::make_idesc_bf16(128, D, 1, 1);
+  bool ok = true;
+  for (int j = 0; j < n_tiles && ok; ++j) {
+    const HalfInfo hi = half_info(p, selected, blocks, masks, j0, j, ch, q0, t_hi, tok_local, row_ok);
+    if (tid == 0) {
+      tc5::mbar_expect_tx(kvbar, 2 * TILE);
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        int s0;
+        if (!selected) s0 = (j0 + j) * BN + hh * 64;
+        else { const int e = 2 * j + hh; const int blk = e < p.max_u ? blocks[e] : -1; s0 = blk < 0 ? 0 : blk * 64; }
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb) {
+          tc5::tma_load_4d(sK + kb * 2 * HALF + hh * HALF, &tm_k, kvbar, kb * 64, h, s0, b);
+          tc5::tma_load_4d(sV + kb * 2 * HALF + hh * HALF, &tm_v, kvbar, kb * 64, h, s0, b);
+        }
+      }
+      bool good = true;
+      if (j == 0) good = tc5::mbar_wait(qbar, 0, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL);
+      if (good && tc5::mbar_wait(kvbar, j & 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL)) {
+        tc5::fence_after_sync();
+        const uint32_t q = tc5::smem_u32(sQ), dob = tc5::smem_u32(sDO), k = tc5::smem_u32(sK), v = tc5::smem_u32(sV);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * 2 * HALF + (kk & 3) * 32;
+          tc5::mma_ss(tmem + cS, tc5::desc_kmajor(q + off), tc5::desc_kmajor(k + off), id_s, kk > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * 2 * HALF + (kk & 3) * 32;
+          tc5::mma_ss(tmem + cDP, tc5::desc_kmajor(dob + off), tc5::desc_kmajor(v + off), id_s, kk > 0 ? 1u : 0u);
+        }
+        tc5::mma_commit(m1);
+      }
+    }
+    if (!tc5::mbar_wait(m1, j & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) ok = false;
+    if (__syncthreads_or(!ok)) { ok = false; break; }
+    tc5::fence_after_sync();
+    {
+      uint32_t sv[64], dv[64], pp[32], ds[32];
+      tmem_ld64(tmem + lane_off + cS + ch * 64, sv);
+      tmem_ld64(tmem + lane_off + cDP + ch * 64, dv);
+      if (!hi.row_sel) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { pp[i] = 0u; ds[i] = 0u; }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; i += 2) {
+          const bool v0 = !hi.need_check || key_visible(p, hi.s_base + i, t);
+          const bool v1 = !hi.need_check || key_visible(p, hi.s_base + i + 1, t);
+          const float p0 = v0 ? exp2f(fmaf(__uint_as_float(sv[i]), sc, -Lrow)) : 0.f;
+          const float p1 = v1 ? exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -Lrow)) : 0.f;
+          pp[i / 2] = tc5::pack_bf16(p0, p1);
+          ds[i / 2] = tc5::pack_bf16(p0 * (__uint_as_float(dv[i]) - drow) * scale,
+                                     p1 * (__uint_as_float(dv[i + 1]) - drow) * scale);
+        }
+      }
+      store_row64(sP + ch * 2 * HALF, r, pp);
+      store_row64(sDS + ch * 2 * HALF, r, ds);
+    }
+    tc5::fence_proxy_async();
+    tc5::fence_before_sync();
+    __syncthreads();
+    if (tid == 0) {
+      tc5::fence_after_sync();
+      const uint32_t q = tc5::smem_u32(sQ), dob = tc5::smem_u32(sDO), k = tc5::smem_u32(sK);
+      const uint32_t pb = tc5::smem_u32(sP), dsb = tc5::smem_u32(sDS);
+#pragma unroll
+      for (int kk = 0; kk < BN / 16; ++kk)      // dQ += dS K
+        tc5::mma_ss(tmem + cDQ, tc5::desc_kmajor(dsb + (kk >> 2) * 2 * HALF + (kk & 3) * 32),
+                    tc5::desc_mnmajor(k + kk * 2048, 2 * HALF), id_q, (j > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+      for (int kk = 0; kk < BM / 16; ++kk)      // dV_tile = P^T dO
+        tc5::mma_ss(tmem + cDV, tc5::desc_mnmajor(pb + kk * 2048, 2 * HALF),
+                    tc5::desc_mnmajor(dob + kk * 2048, 2 * HALF), id_t, kk > 0 ? 1u : 0u);
+#pragma unroll
+      for (int kk = 0; kk < BM / 16; ++kk)      // dK_tile = dS^T Q
+        tc5::mma_ss(tmem + cDK, tc5::desc_mnmajor(dsb + kk * 2048, 2 * HALF),
+                    tc5::desc_mnmajor(q + kk * 2048, 2 * HALF), id_t, kk > 0 ? 1u : 0u);
+      tc5::mma_commit(m2);
+    }
+    // thread (r, ch) owns key row r of the tile, D-half ch
+    int sb_r;
+    if (!selected) sb_r = (j0 + j) * BN + (r >> 6) * 64;
+    else { const int e = 2 * j + (r >> 6); const int blk = e < p.max_u ? blocks[e] : -1; sb_r = blk < 0 ? -1 : blk * 64; }
+    const int s_r = sb_r + (r & 63);
+    const bool key_ok = sb_r >= 0 && s_r < p.S;
+    const long krow = ((static_cast<long>(b) * p.S + (key_ok ? s_r : 0)) * p.Hkv + h) * D + ch * DH;
+    if (!tc5::mbar_wait(m2, j & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) ok = false;
+    if (__syncthreads_or(!ok)) { ok = false; break; }
+    tc5::fence_after_sync();
+#pragma unroll
+    for (int q4 = 0; q4 < DH / 32; ++q4) {
+      uint32_t a[32], c[32];
+      tc5::tmem_ld_x32(tmem + lane_off + cDV + ch * DH + q4 * 32, a);
+      tc5::tmem_ld_x32(tmem + lane_off + cDK + ch * DH + q4 * 32, c);
+      tc5::tmem_ld_wait();
+      if (key_ok) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          atomicAdd(reinterpret_cast<float4*>(p.dV + krow + q4 * 32) + i,
+                    make_float4(__uint_as_float(a[4 * i]), __uint_as_float(a[4 * i + 1]),
+                                __uint_as_float(a[4 * i + 2]), __uint_as_float(a[4 * i + 3])));
+          atomicAdd(reinterpret_cast<float4*>(p.dK + krow + q4 * 32) + i,
+                    make_float4(__uint_as_float(c[4 * i]), __uint_as_float(c[4 * i + 1]),
+                                __uint_as_float(c[4 * i + 2]), __uint_as_float(c[4 * i + 3])));
+        }
+      }
+    }
+    tc5::fence_before_sync();
+    __syncthreads();
+  }
+  {
+    const bool have = !__syncthreads_or(!ok) && n_tiles > 0;
+    bf16* dst = p.dQb + rowi * D + ch * DH;
+#pragma unroll
+    for (int q4 = 0; q4 < DH / 32; ++q4) {
+      uint32_t v[32];
+      if (have) {
+        tc5::tmem_ld_x32(tmem + lane_off + cDQ + ch * DH + q4 * 32, v);
+        tc5::tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = 0u;
+      }
+      if (row_ok) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint4 o4;
+          o4.x = tc5::pack_bf16(__uint_as_float(v[8 * i]), __uint_as_float(v[8 * i + 1]));
+          o4.y = tc5::pack_bf16(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3]));
+          o4.z = tc5::pack_bf16(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5]));
+          o4.w = tc5::pack_bf16(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7]));
+          reinterpret_cast<uint4*>(dst + q4 * 32)[i] = o4;
+        }
+      }
+    }
+  }
+  if (!ok && tid == 0) {
+    const long long t0 = clock64();
+    uint64_t* pend[2] = {qbar, kvbar};
+    for (int i = 0; i < 2; ++i)
+      for (uint32_t n = 0; n < (1u << 16); ++n) {
+        if (tc5::mbar_try_wait(pend[i], 0) || tc5::mbar_try_wait(pend[i], 1)) break;
+        if (clock64() - t0 > tc5::kMaxWaitCycles) break;
+      }
+  }
+  tc5::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) { tc5::fence_after_sync(); tc5::tmem_dealloc(tmem, 512); }
+}
+
+// --------------------------------------------------------------------------------------
+// Helper kernels
+// --------------------------------------------------------------------------------------
+// delta[row] = sum_d dO[row, d] * O[row, d]; one warp per row.
+__global__ void __launch_bounds__(256) attn_delta_kernel(const bf16* __restrict__ O, const bf16* __restrict__ dO,
+                                                         float* __restrict__ delta, long rows, int D) {
+  const long row = static_cast<long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  float s = 0.f;
+  for (int c = lane * 2; c < D; c += 64) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(O + row * D + c));
+    const float2 d = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dO + row * D + c));
+    s += a.x * d.x + a.y * d.y;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0) delta[row] = s;
+}
+
+// Union of the selection blocks chosen by the R tokens of each query tile.
+// idx: [B, Hkv, T, top_n] int32 block ids (-1 = none).  Outputs per (b, h, tile): ascending
+// block list, per-entry token bit masks, and the entry count.  One CTA per tile.
+__global__ void __launch_bounds__(128) nsa_union_kernel(const int* __restrict__ idx, int* __restrict__ tile_blocks,
+                                                        unsigned long long* __restrict__ tile_masks,
+                                                        int* __restrict__ tile_counts, int T, int R, int top_n,
+                                                        int nS, int max_u) {
+  extern __shared__ unsigned int sh[];          // bitmap words, then per-word prefix counts
+  const int words = (nS + 31) / 32;
+  unsigned int* bitmap = sh;
+  unsigned int* prefix = sh + words;
+  const int qt = blockIdx.x;
+  const long bh = blockIdx.y;                   // b * Hkv + h
+  const long slot = bh * gridDim.x + qt;
+  int* ob = tile_blocks + slot * max_u;
+  unsigned long long* om = tile_masks + slot * max_u;
+  for (int i = threadIdx.x; i < words; i += blockDim.x) bitmap[i] = 0u;
+  for (int i = threadIdx.x; i < max_u; i += blockDim.x) { ob[i] = -1; om[i] = 0ull; }
+  __syncthreads();
+  const int q0 = qt * R;
+  const int n_cand = R * top_n;
+  for (int i = threadIdx.x; i < n_cand; i += blockDim.x) {
+    const int tl = i / top_n, t = q0 + tl;
+    if (t >= T) continue;
+    const int blk = idx[(bh * T + t) * top_n + (i - tl * top_n)];
+    if (blk >= 0 && blk < nS) atomicOr(&bitmap[blk >> 5], 1u << (blk & 31));
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned int run = 0;
+    for (int wd = 0; wd < words; ++wd) { prefix[wd] = run; run += __popc(bitmap[wd]); }
+    tile_counts[slot] = static_cast<int>(run < static_cast<unsigned>(max_u) ? run : max_u);
+  }
+  __syncthreads();
+  for (int wd = threadIdx.x; wd < words; wd += blockDim.x) {
+    unsigned int bits = bitmap[wd];
+    unsigned int pos = prefix[wd];
+    while (bits) {
+      const int bpos = __ffs(bits) - 1;
+      bits &= bits - 1;
+      if (pos < static_cast<unsigned>(max_u)) ob[pos] = wd * 32 + bpos;
+      ++pos;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_cand; i += blockDim.x) {
+    const int tl = i / top_n, t = q0 + tl;
+    if (t >= T) continue;
+    const int blk = idx[(bh * T + t) * top_n + (i - tl * top_n)];
+    if (blk < 0 || blk >= nS) continue;
+    const unsigned int below = bitmap[blk >> 5] & ((1u << (blk & 31)) - 1u);
+    const unsigned int pos = prefix[blk >> 5] + __popc(below);
+    if (pos < static_cast<unsigned>(max_u)) atomicOr(&om[pos], 1ull << tl);
+  }
+}
+
+int make_q_map(CUtensorMap* m, const void* base, int B, int T, int Hq, int Hkv, int D) {
+  const int G = Hq / Hkv, R = BM / G;
+  uint64_t dims[5] = {(uint64_t)D, (uint64_t)G, (uint64_t)Hkv, (uint64_t)T, (uint64_t)B};
+  uint64_t strides[4] = {(uint64_t)D * 2, (uint64_t)G * D * 2, (uint64_t)Hq * D * 2, (uint64_t)T * Hq * D * 2};
+  uint32_t box[5] = {64, (uint32_t)G, 1, (uint32_t)R, 1};
+  return nsa::make_tmap_bf16(m, base, 5, dims, strides, box, 1);
+}
+int make_kv_map(CUtensorMap* m, const void* base, int B, int S, int Hkv, int D) {
+  uint64_t dims[4] = {(uint64_t)D, (uint64_t)Hkv, (uint64_t)S, (uint64_t)B};
+  uint64_t strides[3] = {(uint64_t)D * 2, (uint64_t)Hkv * D * 2, (uint64_t)S * Hkv * D * 2};
+  uint32_t box[4] = {64, 1, 64, 1};
+  return nsa::make_tmap_bf16(m, base, 4, dims, strides, box, 1);
+}
+
+int check_shape(int Hq, int Hkv, int D, const int* tile_blocks) {
+  if (D != 64 && D != 128) return nsa::fail(NSA_ERR_SHAPE, "attention: head_dim must be 64 or 128");
+  if (Hkv <= 0 || Hq % Hkv) return nsa::fail(NSA_ERR_SHAPE, "attention: query heads must be a multiple of KV heads");
+  const int G = Hq / Hkv;
+  if (G > 128 || (G & (G - 1))) return nsa::fail(NSA_ERR_SHAPE, "attention: GQA group must be a power of two <= 128");
+  if (tile_blocks && BM / G > 64) return nsa::fail(NSA_ERR_SHAPE, "selected attention needs a GQA group of at least 2");
+  return 0;
+}
+
+template <typename K>
+int set_smem(K kern, int bytes) {
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  return e == cudaSuccess ? 0 : nsa::fail_cuda(e, "attention: shared memory attribute");
+}
+
+void fill_params(AttnParams& p, int B, int T, int S, int Hq, int Hkv, int D, float scale, int causal, int window,
+                 int kp_stride, int kp_off, const int* tb, const unsigned long long* tmk, const int* tc, int max_u) {
+  p = AttnParams{};
+  p.B = B; p.T = T; p.S = S; p.Hq = Hq; p.Hkv = Hkv; p.G = Hq / Hkv; p.R = BM / p.G; p.D = D;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.causal = causal; p.window = window; p.kp_stride = kp_stride; p.kp_off = kp_off;
+  p.tile_blocks = tb; p.tile_masks = tmk; p.tile_counts = tc; p.max_u = max_u;
+  p.status = nsa::status_ptr();
+}
+}  // namespace
+
+extern "C" int nsa_attn_fwd(const void* q, const void* k, const void* v, void* o, float* L, int B, int T, int S,
+                            int Hq, int Hkv, int D, float scale, int causal, int window, int kp_stride, int kp_off,
+                            const int* tile_blocks, const unsigned long long* tile_masks, const int* tile_counts,
+                            int max_u, cudaStream_t st) {
+  int rc = check_shape(Hq, Hkv, D, tile_blocks);
+  if (rc) return rc;
+  CUtensorMap tq, tk, tv;
+  if ((rc = make_q_map(&tq, q, B, T, Hq, Hkv, D))) return rc;
+  if ((rc = make_kv_map(&tk, k, B, S, Hkv, D))) return rc;
+  if ((rc = make_kv_map(&tv, v, B, S, Hkv, D))) return rc;
+  AttnParams p;
+  fill_params(p, B, T, S, Hq, Hkv, D, scale, causal, window, kp_stride, kp_off, tile_blocks, tile_masks, tile_counts, max_u);
+  p.O = (bf16*)o; p.L = L;
+  const dim3 grid((T + p.R - 1) / p.R, Hkv, B);
+  const int smem = (D / 64) * 2 * HALF * 5 + 4 * HALF + 1024 + 2048;
+  if (D == 128) {
+    static bool cfg = false;
+    if (!cfg) { if ((rc = set_smem(attn_fwd_kernel<128, 0>, smem))) return rc; cfg = true; }
+    attn_fwd_kernel<128, 0><<<grid, 256, smem, st>>>(tq, tk, tv, p);
+  } else {
+    static bool cfg = false;
+    if (!cfg) { if ((rc = set_smem(attn_fwd_kernel<64, 0>, smem))) return rc; cfg = true; }
+    attn_fwd_kernel<64, 0><<<grid, 256, smem, st>>>(tq, tk, tv, p);
+  }
+  nsa::count_launch();
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : nsa::fail_cuda(e, "nsa_attn_fwd launch");
+}
+
+// Block importance for top-n selection: imp[b,h,t,j] (pre-zeroed) += sum over the G heads of the
+// compressed-branch probabilities, binned into selection blocks of 4 strides; compressed blocks
+// span 2 strides.  L_in is the compressed branch's L from nsa_attn_fwd.
+extern "C" int nsa_attn_importance(const void* q, const void* k_cmp, const float* L_in, float* imp, int B, int T, int S,
+                                   int Hq, int Hkv, int D, float scale, int kp_stride, int kp_off, int nS,
+                                   cudaStream_t st) {
+  int rc = check_shape(Hq, Hkv, D, nullptr);
+  if (rc) return rc;
+  if (Hq / Hkv > 32) return nsa::fail(NSA_ERR_SHAPE, "importance: GQA group above 32 is not supported");
+  if (kp_off + 1 != 2 * kp_stride) return nsa::fail(NSA_ERR_SHAPE, "importance: compressed block must span two strides");
+  CUtensorMap tq, tk;
+  if ((rc = make_q_map(&tq, q, B, T, Hq, Hkv, D))) return rc;
+  if ((rc = make_kv_map(&tk, k_cmp, B, S, Hkv, D))) return rc;
+  AttnParams p;
+  fill_params(p, B, T, S, Hq, Hkv, D, scale, 1, 0, kp_stride, kp_off, nullptr, nullptr, nullptr, 0);
+  p.L_in = L_in; p.imp = imp; p.nS = nS; p.cells_per_block = 4;
+  const dim3 grid((T + p.R - 1) / p.R, Hkv, B);
+  const int smem = (D / 64) * 2 * HALF * 5 + 4 * HALF + 1024 + 2048;
+  if (D == 128) {
+    static bool cfg = false;
+    if (!cfg) { if ((rc = set_smem(attn_fwd_kernel<128, 1>, smem))) return rc; cfg = true; }
+    attn_fwd_kernel<128, 1><<<grid, 256, smem, st>>>(tq, tk, tk, p);
+  } else {
+    static bool cfg = false;
+    if (!cfg) { if ((rc = set_smem(attn_fwd_kernel<64, 1>, smem))) return rc; cfg = true; }
+    attn_fwd_kernel<64, 1><<<grid, 256, smem, st>>>(tq, tk, tk, p);
+  }
+  nsa::count_launch();
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : nsa::fail_cuda(e, "nsa_attn_importance launch");
+}
+
+// delta: scratch [B*T*Hq] fp32 (written here).  dK, dV: fp32 [B,S,Hkv,D], zeroed by the caller.
+extern "C" int nsa_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* L,
+                            float* delta, void* dq, float* dk, float* dv, int B, int T, int S, int Hq, int Hkv, int D,
+                            float scale, int causal, int window, int kp_stride, int kp_off, const int* tile_blocks,
+                            const unsigned long long* tile_masks, const int* tile_counts, int max_u, cudaStream_t st) {
+  int rc = check_shape(Hq, Hkv, D, tile_blocks);
+  if (rc) return rc;
+  CUtensorMap tq, tdo, tk, tv;
+  if ((rc = make_q_map(&tq, q, B, T, Hq, Hkv, D))) return rc;
+  if ((rc = make_q_map(&tdo, d_o, B, T, Hq, Hkv, D))) return rc;
+  if ((rc = make_kv_map(&tk, k, B, S, Hkv, D))) return rc;
+  if ((rc = make_kv_map(&tv, v, B, S, Hkv, D))) return rc;
+  const long rows = static_cast<long>(B) * T * Hq;
+  attn_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const bf16*)o, (const bf16*)d_o, delta, rows, D);
+  AttnParams p;
+  fill_params(p, B, T, S, Hq, Hkv, D, scale, causal, window, kp_stride, kp_off, tile_blocks, tile_masks, tile_counts, max_u);
+  p.L = const_cast<float*>(L); p.delta = delta; p.dQb = (bf16*)dq; p.dK = dk; p.dV = dv;
+  const dim3 grid((T + p.R - 1) / p.R, Hkv, B);
+  const int smem = (D / 64) * 2 * HALF * 4 + 8 * HALF + 1024 + 256;
+  if (D == 128) {
+    static bool cfg = false;
+    if (!cfg) { if ((rc = set_smem(attn_bwd_kernel<128>, smem))) return rc; cfg = true; }
+    attn_bwd_kernel<128><<<grid, 256, smem, st>>>(tq, tdo, tk, tv, p, scale);
+  } else {
+    static bool cfg = false;
+    if (!cfg) { if ((rc = set_smem(attn_bwd_kernel<64>, smem))) return rc; cfg = true; }
+    attn_bwd_kernel<64><<<grid, 256, smem, st>>>(tq, tdo, tk, tv, p, scale);
+  }
+  nsa::count_launch(2);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : nsa::fail_cuda(e, "nsa_attn_bwd launch");
+}
+
+// idx [B, Hkv, T, top_n] int32 -> per query tile (R = 128 / G tokens): block list, token masks, count.
+extern "C" int nsa_union_blocks(const int* idx, int* tile_blocks, unsigned long long* tile_masks, int* tile_counts,
+                                int B, int T, int Hkv, int G, int top_n, int nS, int max_u, cudaStream_t st) {
+  const int R = BM / G;
+  if (R > 64) return nsa::fail(NSA_ERR_SHAPE, "union: more than 64 tokens per tile");
+  const int words = (nS + 31) / 32;
+  const dim3 grid((T + R - 1) / R, B * Hkv);
+  nsa_union_kernel<<<grid, 128, words * 8, st>>>(idx, tile_blocks, tile_masks, tile_counts, T, R, top_n, nS, max_u);
+  nsa::count_launch();
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : nsa::fail_cuda(e, "nsa_union_blocks launch");
+}

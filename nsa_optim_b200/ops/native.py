@@ -27,6 +27,7 @@ _lib: Optional[ctypes.CDLL] = None
 SUPPORTED = {
     "linear", "rms_norm", "gated_rms_norm", "swiglu", "l2_norm", "rope", "embedding",
     "causal_conv1d", "linear_cross_entropy", "adamw", "adamw_lowbit", "gated_delta_rule",
+    "attention", "nsa_attention",
 }
 
 STATUS_NAMES = {
@@ -548,3 +549,137 @@ def gated_delta_rule(q, k, v, g, beta, scale=None, chunk=64):
     o = o_inter + torch.matmul(qk, v_new).to(f32)
     o = o.reshape(B, H, Tp, V).permute(0, 2, 1, 3)[:, :T]
     return o.to(v.dtype)
+
+
+# --------------------------------------------------------------------------------------
+# attention family (csrc/attention.cu)
+# --------------------------------------------------------------------------------------
+class _Attn(torch.autograd.Function):
+    """Softmax attention on (B, T, H, D) tensors through the tcgen05 kernels.  ``tiles`` is
+    ``None`` (contiguous key range bounded by causality / window) or the per-query-tile block
+    lists from :func:`union_blocks` (selected-block attention).  Key positions are
+    ``index * kp_stride + kp_off``.  Returns (output, L) with L the log2-sum-exp per row."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, causal, window, scale, kp_stride, kp_off, tiles):
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        B, T, Hq, D = q.shape
+        S, Hkv = k.shape[1], k.shape[2]
+        o = torch.empty_like(q)
+        L = torch.empty(B, T, Hq, dtype=torch.float32, device=q.device)
+        tb, tm, tc, mu = tiles if tiles is not None else (None, None, None, 0)
+        _check(load().nsa_attn_fwd(_p(q), _p(k), _p(v), _p(o), _p(L), c_int(B), c_int(T), c_int(S), c_int(Hq),
+                                   c_int(Hkv), c_int(D), c_float(scale), c_int(int(causal)), c_int(window),
+                                   c_int(kp_stride), c_int(kp_off), _p(tb), _p(tm), _p(tc), c_int(mu), _stream()))
+        ctx.save_for_backward(q, k, v, o, L)
+        ctx.cfg = (causal, window, scale, kp_stride, kp_off)
+        ctx.tiles = tiles
+        ctx.mark_non_differentiable(L)
+        return o, L
+
+    @staticmethod
+    def backward(ctx, do, _dL):
+        q, k, v, o, L = ctx.saved_tensors
+        causal, window, scale, kp_stride, kp_off = ctx.cfg
+        B, T, Hq, D = q.shape
+        S, Hkv = k.shape[1], k.shape[2]
+        do = do.contiguous()
+        dq = torch.empty_like(q)
+        dk = torch.zeros(k.shape, dtype=torch.float32, device=q.device)
+        dv = torch.zeros(v.shape, dtype=torch.float32, device=q.device)
+        delta = torch.empty(B, T, Hq, dtype=torch.float32, device=q.device)
+        tb, tm, tc, mu = ctx.tiles if ctx.tiles is not None else (None, None, None, 0)
+        _check(load().nsa_attn_bwd(_p(q), _p(k), _p(v), _p(o), _p(do), _p(L), _p(delta), _p(dq), _p(dk), _p(dv),
+                                   c_int(B), c_int(T), c_int(S), c_int(Hq), c_int(Hkv), c_int(D), c_float(scale),
+                                   c_int(int(causal)), c_int(window), c_int(kp_stride), c_int(kp_off),
+                                   _p(tb), _p(tm), _p(tc), c_int(mu), _stream()))
+        return dq, dk.to(k.dtype), dv.to(v.dtype), None, None, None, None, None, None
+
+
+def _attn_ok(q, k) -> bool:
+    Hq, Hkv, D = q.shape[2], k.shape[2], q.shape[3]
+    G = Hq // max(Hkv, 1)
+    return D in (64, 128) and Hkv > 0 and Hq % Hkv == 0 and G <= 128 and (G & (G - 1)) == 0
+
+
+def attention(q, k, v, causal=True, window=0, scale=None):
+    if not _attn_ok(q, k) or q.shape[1] != k.shape[1]:
+        return torch_impl.attention(q, k, v, causal, window, scale)
+    scale = q.shape[-1] ** -0.5 if scale is None else scale
+    return _Attn.apply(q, k, v, causal, int(window), float(scale), 1, 0, None)[0]
+
+
+def union_blocks(idx: Tensor, G: int, nS: int):
+    """idx (B, Hkv, T, top_n) int32 selection-block ids (-1 = none) -> per query tile
+    (128 // G tokens) ascending union list, token bit masks and counts."""
+    B, Hkv, T, top_n = idx.shape
+    R = 128 // G
+    nqt = -(-T // R)
+    max_u = min(R * top_n, nS)
+    max_u += max_u & 1
+    tb = torch.empty(B, Hkv, nqt, max_u, dtype=torch.int32, device=idx.device)
+    tm = torch.empty(B, Hkv, nqt, max_u, dtype=torch.int64, device=idx.device)
+    tc = torch.empty(B, Hkv, nqt, dtype=torch.int32, device=idx.device)
+    _check(load().nsa_union_blocks(_p(idx), _p(tb), _p(tm), _p(tc), c_int(B), c_int(T), c_int(Hkv), c_int(G),
+                                   c_int(top_n), c_int(nS), c_int(max_u), _stream()))
+    return tb, tm, tc, max_u
+
+
+def selected_attention(q, k, v, idx, scale=None):
+    """Causal attention of each query token over its own list of 64-key blocks ``idx``
+    (B, Hkv, T, top_n)."""
+    scale = q.shape[-1] ** -0.5 if scale is None else scale
+    G = q.shape[2] // k.shape[2]
+    nS = -(-k.shape[1] // 64)
+    tiles = union_blocks(idx.to(torch.int32).contiguous(), G, nS)
+    return _Attn.apply(q, k, v, True, 0, float(scale), 1, 0, tiles)[0]
+
+
+def nsa_importance(q, k_cmp, L_cmp, nS, stride, block, scale):
+    B, T, Hq, D = q.shape
+    Hkv = k_cmp.shape[2]
+    imp = torch.zeros(B, Hkv, T, nS, dtype=torch.float32, device=q.device)
+    _check(load().nsa_attn_importance(_p(q.contiguous()), _p(k_cmp.contiguous()), _p(L_cmp), _p(imp), c_int(B), c_int(T),
+                                      c_int(k_cmp.shape[1]), c_int(Hq), c_int(Hkv), c_int(D), c_float(scale),
+                                      c_int(stride), c_int(block - 1), c_int(nS), _stream()))
+    return imp
+
+
+def nsa_select(imp: Tensor, sel_block: int, top_n: int) -> Tensor:
+    """imp (B, Hkv, T, nS) -> int32 (B, Hkv, T, top_n): block 0, the query's own block and the one
+    before it always, then the most important causal blocks; -1 where fewer are visible."""
+    B, H, T, nS = imp.shape
+    own = (torch.arange(T, device=imp.device) // sel_block)[:, None]
+    j = torch.arange(nS, device=imp.device)[None, :]
+    forced = (j == 0) | (j == own) | (j == own - 1)
+    score = imp.masked_fill(forced, float("inf")).masked_fill_(j > own, float("-inf"))
+    n = min(top_n, nS)
+    val, idx = torch.topk(score, n, dim=-1)
+    idx = idx.masked_fill(val == float("-inf"), -1).to(torch.int32)
+    if n < top_n:
+        idx = torch.nn.functional.pad(idx, (0, top_n - n), value=-1)
+    return idx.contiguous()
+
+
+def nsa_attention(q, k, v, g_cmp, g_slc, g_swa, cmp_block=32, cmp_stride=16, sel_block=64, top_n=16,
+                  window=512, scale=None):
+    B, T, Hq, D = q.shape
+    Hkv = k.shape[2]
+    G = Hq // Hkv
+    if (not _attn_ok(q, k) or sel_block != 64 or sel_block != 4 * cmp_stride or cmp_block != 2 * cmp_stride
+            or G < 2 or G > 32 or T < cmp_block):
+        return torch_impl.nsa_attention(q, k, v, g_cmp, g_slc, g_swa, cmp_block, cmp_stride, sel_block, top_n,
+                                        window, scale)
+    scale = D ** -0.5 if scale is None else scale
+    kc = torch_impl.nsa_compress(k, cmp_block, cmp_stride)
+    vc = torch_impl.nsa_compress(v, cmp_block, cmp_stride)
+    o_cmp, L_cmp = _Attn.apply(q, kc, vc, True, 0, float(scale), cmp_stride, cmp_block - 1, None)
+    nS = -(-T // sel_block)
+    with torch.no_grad():
+        imp = nsa_importance(q, kc, L_cmp, nS, cmp_stride, cmp_block, float(scale))
+        idx = nsa_select(imp, sel_block, top_n)
+        del imp
+        tiles = union_blocks(idx, G, nS)
+    o_slc = _Attn.apply(q, k, v, True, 0, float(scale), 1, 0, tiles)[0]
+    o_swa = _Attn.apply(q, k, v, True, int(window), float(scale), 1, 0, None)[0]
+    return g_cmp.unsqueeze(-1) * o_cmp + g_slc.unsqueeze(-1) * o_slc + g_swa.unsqueeze(-1) * o_swa

@@ -1,0 +1,113 @@
+"""tcgen05 attention kernels against fp32 oracles: dense causal, sliding window, compressed
+keys (affine key positions), selected blocks, importance pass, full three-branch NSA."""
+import pytest
+import torch
+
+from nsa_optim_b200.ops import oracle, torch_impl
+
+pytestmark = pytest.mark.gpu
+
+
+def close(a, b, name, rtol=3e-2, atol=2e-2):
+    err, scale = (a.float() - b.float()).abs().max().item(), b.float().abs().max().item()
+    assert err <= rtol * scale + atol, (name, err, scale)
+
+
+def mk(B, T, Hq, Hkv, D, S=None):
+    S = S or T
+    q = torch.randn(B, T, Hq, D, device="cuda").bfloat16()
+    k = torch.randn(B, S, Hkv, D, device="cuda").bfloat16()
+    v = torch.randn(B, S, Hkv, D, device="cuda").bfloat16()
+    return q, k, v
+
+
+def run_pair(fn_native, fn_ref, tensors):
+    leaves = [t.clone().requires_grad_() for t in tensors]
+    o = fn_native(*leaves)
+    do = torch.randn_like(o)
+    o.backward(do)
+    refs = [t.float().clone().requires_grad_() for t in tensors]
+    o_ref = fn_ref(*refs)
+    o_ref.backward(do.float())
+    close(o, o_ref, "out")
+    for i, (a, b) in enumerate(zip(leaves, refs)):
+        close(a.grad, b.grad, f"grad{i}")
+
+
+@pytest.mark.parametrize("B,T,Hq,Hkv,D", [(2, 300, 4, 2, 64), (1, 1000, 8, 1, 128), (1, 257, 32, 2, 128), (2, 128, 2, 2, 64)])
+def test_dense_causal(native, B, T, Hq, Hkv, D):
+    run_pair(lambda q, k, v: native.attention(q, k, v, True, 0),
+             lambda q, k, v: oracle.attention(q, k, v, True, 0), mk(B, T, Hq, Hkv, D))
+
+
+@pytest.mark.parametrize("T,W", [(700, 100), (1500, 512), (65, 64)])
+def test_sliding_window(native, T, W):
+    run_pair(lambda q, k, v: native.attention(q, k, v, True, W),
+             lambda q, k, v: oracle.attention(q, k, v, True, W), mk(1, T, 8, 2, 128))
+
+
+def _cmp_ref(q, kc, vc, stride, block):
+    B, T, Hq, D = q.shape
+    G = Hq // kc.shape[2]
+    s = torch.einsum("bthd,bchd->bhtc", q, kc.repeat_interleave(G, 2)) * D ** -0.5
+    end = torch.arange(kc.shape[1], device=q.device) * stride + block - 1
+    vis = end[None, :] <= torch.arange(T, device=q.device)[:, None]
+    p = torch.nan_to_num(torch.softmax(s.masked_fill(~vis, float("-inf")), -1), nan=0.0)
+    return torch.einsum("bhtc,bchd->bthd", p, vc.repeat_interleave(G, 2)), p
+
+
+def test_compressed_branch_and_importance(native):
+    B, T, Hq, Hkv, D, stride, block = 1, 900, 8, 2, 128, 16, 32
+    q, k, v = mk(B, T, Hq, Hkv, D)
+    kc, vc = torch_impl.nsa_compress(k, block, stride), torch_impl.nsa_compress(v, block, stride)
+    run_pair(lambda q, kc, vc: native._Attn.apply(q, kc, vc, True, 0, D ** -0.5, stride, block - 1, None)[0],
+             lambda q, kc, vc: _cmp_ref(q, kc, vc, stride, block)[0], (q, kc, vc))
+    o, L = native._Attn.apply(q, kc, vc, True, 0, D ** -0.5, stride, block - 1, None)
+    nS = -(-T // 64)
+    imp = native.nsa_importance(q, kc, L, nS, stride, block, D ** -0.5)
+    _, p = _cmp_ref(q.float(), kc.float(), vc.float(), stride, block)
+    G = Hq // Hkv
+    pg = p.view(B, Hkv, G, T, -1).sum(2)
+    w = oracle.nsa_importance_weights(kc.shape[1], nS, block, stride, 64, device="cuda")
+    close(imp, pg @ w, "importance", rtol=3e-2, atol=3e-2)
+
+
+def _sel_ref(q, k, v, idx):
+    B, T, Hq, D = q.shape
+    Hkv = k.shape[2]
+    G = Hq // Hkv
+    nS = -(-T // 64)
+    m = torch.zeros(B, Hkv, T, nS + 1, dtype=torch.bool, device=q.device)
+    m.scatter_(-1, torch.where(idx < 0, torch.full_like(idx, nS), idx).long(), True)
+    tok = m[..., :nS].repeat_interleave(64, -1)[..., :T]
+    t = torch.arange(T, device=q.device)
+    tok = tok & (t[None, :] <= t[:, None])
+    s = torch.einsum("bthd,bshd->bhts", q, k.repeat_interleave(G, 2)) * D ** -0.5
+    s = s.masked_fill(~tok.repeat_interleave(G, 1), float("-inf"))
+    return torch.einsum("bhts,bshd->bthd", torch.softmax(s, -1), v.repeat_interleave(G, 2))
+
+
+@pytest.mark.parametrize("Hq,Hkv,D", [(32, 2, 128), (4, 2, 64)])
+def test_selected_blocks(native, Hq, Hkv, D):
+    B, T, top_n = 1, 600, 5
+    q, k, v = mk(B, T, Hq, Hkv, D)
+    nS = -(-T // 64)
+    t = torch.arange(T, device="cuda")
+    own = (t // 64)[None, None, :, None]
+    rnd = torch.randint(0, nS, (B, Hkv, T, top_n - 1), device="cuda")
+    rnd = torch.where(rnd <= own, rnd, -torch.ones_like(rnd))
+    idx = torch.cat([own.expand(B, Hkv, T, 1), rnd], -1).to(torch.int32)
+    run_pair(lambda q, k, v: native.selected_attention(q, k, v, idx),
+             lambda q, k, v: _sel_ref(q, k, v, idx), (q, k, v))
+
+
+def test_full_nsa_close_to_streaming_reference(native):
+    B, T, Hq, Hkv, D = 1, 1024, 16, 2, 128
+    q, k, v = mk(B, T, Hq, Hkv, D)
+    g = torch.rand(3, B, T, Hq, device="cuda").bfloat16()
+    kw = dict(cmp_block=32, cmp_stride=16, sel_block=64, top_n=4, window=128)
+    o = native.nsa_attention(q, k, v, g[0], g[1], g[2], **kw)
+    ref = torch_impl.nsa_attention(q.float(), k.float(), v.float(), g[0].float(), g[1].float(), g[2].float(), **kw)
+    # selection may differ on near-ties; require agreement on the bulk of the rows
+    err = (o.float() - ref).abs().amax(dim=(-1, -2))
+    assert (err < 0.05).float().mean() > 0.9, err.mean().item()
