@@ -27,7 +27,7 @@ _lib: Optional[ctypes.CDLL] = None
 SUPPORTED = {
     "linear", "rms_norm", "gated_rms_norm", "swiglu", "l2_norm", "rope", "embedding",
     "causal_conv1d", "linear_cross_entropy", "adamw", "adamw_lowbit", "gated_delta_rule",
-    "attention", "nsa_attention",
+    "attention", "nsa_attention", "ssd_scan",
 }
 
 STATUS_NAMES = {
@@ -683,3 +683,76 @@ def nsa_attention(q, k, v, g_cmp, g_slc, g_swa, cmp_block=32, cmp_stride=16, sel
     o_slc = _Attn.apply(q, k, v, True, 0, float(scale), 1, 0, tiles)[0]
     o_swa = _Attn.apply(q, k, v, True, int(window), float(scale), 1, 0, None)[0]
     return g_cmp.unsqueeze(-1) * o_cmp + g_slc.unsqueeze(-1) * o_slc + g_swa.unsqueeze(-1) * o_swa
+
+
+# --------------------------------------------------------------------------------------
+# Mamba-2 SSD
+# --------------------------------------------------------------------------------------
+class _SSDStatePass(torch.autograd.Function):
+    """Hprev[c+1] = gamma[c] * Hprev[c] + S[c] over chunks (``csrc/ssd.cu``).
+    S (B, nc, H, P, N) fp32, gamma (B, nc, H) fp32 -> Hprev, same shape as S."""
+
+    @staticmethod
+    def forward(ctx, S, gamma):
+        S, gamma = S.contiguous(), gamma.contiguous()
+        B, nc, H = gamma.shape
+        E = S[0, 0, 0].numel()
+        Hprev = torch.empty_like(S)
+        _check(load().nsa_ssd_state_fwd(_p(S), _p(gamma), _p(Hprev), c_void_p(0), c_int(B), c_int(nc), c_int(H),
+                                        c_long(E), _stream()))
+        ctx.save_for_backward(gamma, Hprev)
+        return Hprev
+
+    @staticmethod
+    def backward(ctx, dHprev):
+        gamma, Hprev = ctx.saved_tensors
+        B, nc, H = gamma.shape
+        E = Hprev[0, 0, 0].numel()
+        dHprev = dHprev.contiguous().float()
+        dS = torch.empty_like(Hprev)
+        _check(load().nsa_ssd_state_bwd(_p(dHprev), _p(gamma), _p(dS), c_int(B), c_int(nc), c_int(H), c_long(E), _stream()))
+        dgamma = (Hprev * dS).sum((-1, -2))
+        return dS, dgamma
+
+
+def ssd_scan(x, dt, A, Bm, Cm, D=None, chunk=256):
+    """Chunked SSD: the per-chunk terms are batched tensor-core matmuls over all chunks at once,
+    the inter-chunk recurrence is one native kernel (forward) and one (backward)."""
+    F = torch.nn.functional
+    Bsz, T, H, P = x.shape
+    G, N = Bm.shape[2], Bm.shape[3]
+    L = min(chunk, 128, T)
+    pad = (-T) % L
+    if pad:
+        x = F.pad(x, (0, 0, 0, 0, 0, pad))
+        dt = F.pad(dt, (0, 0, 0, pad))
+        Bm = F.pad(Bm, (0, 0, 0, 0, 0, pad))
+        Cm = F.pad(Cm, (0, 0, 0, 0, 0, pad))
+    Tp = T + pad
+    nc = Tp // L
+    rep = H // G
+    cdt = x.dtype
+    xr = x.reshape(Bsz, nc, L, H, P)
+    dtr = dt.float().reshape(Bsz, nc, L, H)
+    Br = Bm.reshape(Bsz, nc, L, G, N)
+    Cr = Cm.reshape(Bsz, nc, L, G, N)
+    a = dtr * A.float()[None, None, None, :]
+    cum = torch.cumsum(a, dim=2)
+    total = cum[:, :, -1]
+    xdt = (xr.float() * dtr[..., None]).to(cdt)
+    CB = torch.einsum("bclgn,bcsgn->bcgls", Cr, Br)                      # (B,nc,G,L,L) in the compute dtype
+    seg = cum.permute(0, 1, 3, 2)                                        # (B,nc,H,L)
+    tri = torch.ones(L, L, dtype=torch.bool, device=x.device).tril()
+    dec = torch.exp((seg[..., :, None] - seg[..., None, :]).masked_fill(~tri, float("-inf"))).to(cdt)
+    M = CB.repeat_interleave(rep, dim=2) * dec if rep > 1 else CB * dec  # (B,nc,H,L,L)
+    y = torch.einsum("bchls,bcshp->bclhp", M, xdt)
+    w_end = torch.exp(total[:, :, None, :] - cum)
+    Bh = Br.repeat_interleave(rep, dim=3) if rep > 1 else Br
+    S_loc = torch.einsum("bclhp,bclhn->bchpn", (xdt.float() * w_end[..., None]).to(cdt), Bh).float()
+    Hprev = _SSDStatePass.apply(S_loc, torch.exp(total))                 # (B,nc,H,P,N) fp32
+    Ch = Cr.repeat_interleave(rep, dim=3) if rep > 1 else Cr
+    y_inter = torch.einsum("bclhn,bchpn->bclhp", (Ch.float() * torch.exp(cum)[..., None]).to(cdt), Hprev.to(cdt))
+    y = (y + y_inter).reshape(Bsz, Tp, H, P)[:, :T]
+    if D is not None:
+        y = y + (x[:, :T].float() * D.float()[None, None, :, None]).to(cdt)
+    return y.to(cdt)
