@@ -32,15 +32,96 @@ constexpr int GROUP_M = 16;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr uint32_t TMEM_COLS = 512;
 
+// All-gather fused into the GEMM: the B operand (a weight inside a sharded unit's gathered
+// buffer `full`) is still being assembled while the GEMM runs.  The first `copy_ctas` CTAs of
+// the grid pull every rank's shard (peer memory, plain 16-byte loads) into `full` in chunks and
+// publish chunk_flags[id] = epoch; the TMA producer of each GEMM CTA waits for the chunks that
+// cover a B tile before loading it.  Ranks start pulling from different peers, and the
+// N-block order is rotated to follow the same order, so no peer is read by everyone at once.
+struct AgFuse {
+  int enabled;
+  int W, rank;
+  const uint4* const* shards;   // W pointers (device array), one shard per rank
+  uint4* full;                  // local gathered buffer: W * shard_vec 16-byte units
+  long shard_vec, chunk_vec;    // in 16-byte units
+  int chunks_per_shard;
+  unsigned* chunk_flags;        // local, W * chunks_per_shard words
+  const unsigned* peer_flags;   // local flag row: shard p is final when peer_flags[p] >= epoch
+  unsigned epoch;
+  long b_vec_offset;            // offset of B inside `full`, 16-byte units
+  long long max_cycles;
+  int copy_ctas;
+  int n_rot;                    // rotation of the N-block order
+};
+
 struct GemmParams {
+  AgFuse ag;
   int M, N, K;
-  int ldc;
+  int ldc, ldb;
   int a_mn, b_mn;
   int out_fp32;
   int accumulate;
   void* C;
   KernelStatus* status;
 };
+
+__device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ bool spin_until(const unsigned* flag, unsigned epoch, long long max_cycles, bool sys) {
+  const long long t0 = clock64();
+  for (;;) {
+    const unsigned v = sys ? ld_acquire_sys_u32(flag) : ld_acquire_gpu(flag);
+    if (v >= epoch) return true;
+    if (clock64() - t0 > max_cycles) return false;
+    __nanosleep(32);
+  }
+}
+__device__ __forceinline__ int ag_chunk_id(const AgFuse& ag, long g) {
+  const long pidx = g / ag.shard_vec;
+  const long i = g - pidx * ag.shard_vec;
+  return static_cast<int>(pidx * ag.chunks_per_shard + i / ag.chunk_vec);
+}
+
+// Copy role of the fused all-gather (all threads of the CTA).
+__device__ void ag_copy_role(const AgFuse& ag, int cta, KernelStatus* status) {
+  __shared__ int sh_ok;
+  const int jobs = ag.W * ag.chunks_per_shard;
+  int ready_peer = -1;
+  for (int q = cta; q < jobs; q += ag.copy_ctas) {
+    const int k = q / ag.chunks_per_shard, c = q - k * ag.chunks_per_shard;
+    const int pr = (ag.rank + k) % ag.W;
+    if (pr != ag.rank && pr != ready_peer) {
+      if (threadIdx.x == 0) {
+        sh_ok = 1;
+        if (ag.peer_flags != nullptr && !spin_until(ag.peer_flags + pr, ag.epoch, ag.max_cycles, true)) {
+          status_report(status, STATUS_TIMEOUT_PEER_FLAG, pr, (int)ag.epoch);
+          sh_ok = 0;
+        }
+      }
+      __syncthreads();
+      if (!sh_ok) return;
+      ready_peer = pr;
+    }
+    const long lo = static_cast<long>(c) * ag.chunk_vec;
+    const long hi = lo + ag.chunk_vec < ag.shard_vec ? lo + ag.chunk_vec : ag.shard_vec;
+    const uint4* src = ag.shards[pr];
+    uint4* dst = ag.full + static_cast<long>(pr) * ag.shard_vec;
+    for (long i = lo + threadIdx.x; i < hi; i += blockDim.x) dst[i] = src[i];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(ag.chunk_flags + pr * ag.chunks_per_shard + c), "r"(ag.epoch) : "memory");
+    }
+  }
+}
 
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& mb, int& nb) {
   const int per_group = GROUP_M * tiles_n;
@@ -66,6 +147,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  if (p.ag.enabled && static_cast<int>(blockIdx.x) < p.ag.copy_ctas) {
+    ag_copy_role(p.ag, blockIdx.x, p.status);
+    return;
+  }
+  const int cta = p.ag.enabled ? blockIdx.x - p.ag.copy_ctas : blockIdx.x;
+  const int n_ctas = p.ag.enabled ? gridDim.x - p.ag.copy_ctas : gridDim.x;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int tiles_m = (p.M + BM - 1) / BM;
@@ -101,10 +188,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     if (lane == 0) {
       uint32_t it = 0;   // global k-block counter across tiles
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = cta; t < num_tiles && ok; t += n_ctas) {
         int mb, nb;
         tile_coords(t, tiles_m, tiles_n, mb, nb);
+        if (p.ag.enabled) nb = (nb + p.ag.n_rot) % tiles_n;
         const int m0 = mb * BM, n0 = nb * BN;
+        if (p.ag.enabled) {
+          // B rows [n0, n1) live at 16-byte units [g_lo, g_hi] of the gathered buffer
+          const int n1 = n0 + BN < p.N ? n0 + BN : p.N;
+          const long g_lo = p.ag.b_vec_offset + static_cast<long>(n0) * p.ldb / 8;
+          const long g_hi = p.ag.b_vec_offset + static_cast<long>(n1) * p.ldb / 8 - 1;
+          const int id_lo = ag_chunk_id(p.ag, g_lo), id_hi = ag_chunk_id(p.ag, g_hi);
+          for (int id = id_lo; id <= id_hi && ok; ++id)
+            if (!spin_until(p.ag.chunk_flags + id, p.ag.epoch, p.ag.max_cycles, false)) {
+              *abort_flag = 1;
+              status_report(p.status, STATUS_TIMEOUT_LOCAL_FLAG, blockIdx.x, id);
+              ok = false;
+            }
+          if (!ok) break;
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -147,7 +250,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t it = 0;
       uint32_t tile_i = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_i) {
+      for (int t = cta; t < num_tiles && ok; t += n_ctas, ++tile_i) {
         const uint32_t acc = tile_i & 1;
         const uint32_t acc_ph = (tile_i >> 1) & 1;
         if (!tc5::mbar_wait(&tempty_bar[acc], acc_ph ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
@@ -176,9 +279,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int quarter = warp & 3;                 // TMEM lanes [32*quarter, 32*quarter+32)
     uint32_t tile_i = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_i) {
+    for (int t = cta; t < num_tiles && ok; t += n_ctas, ++tile_i) {
       int mb, nb;
       tile_coords(t, tiles_m, tiles_n, mb, nb);
+      if (p.ag.enabled) nb = (nb + p.ag.n_rot) % tiles_n;
       const uint32_t acc = tile_i & 1;
       const uint32_t acc_ph = (tile_i >> 1) & 1;
       if (!tc5::mbar_wait(&tfull_bar[acc], acc_ph, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
@@ -280,7 +384,8 @@ extern "C" int nsa_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   else       rc = nsa::make_tmap_2d_bf16(&tb, B, N, K, ldb, 64, BK);
   if (rc) return rc;
   GemmParams p;
-  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.a_mn = a_mn; p.b_mn = b_mn;
+  p.ag = AgFuse{};
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldb = ldb; p.a_mn = a_mn; p.b_mn = b_mn;
   p.out_fp32 = out_fp32; p.accumulate = accumulate; p.C = C; p.status = nsa::status_ptr();
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int sms = nsa::sm_count();
@@ -292,4 +397,63 @@ extern "C" int nsa_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   else if (a_mn && !b_mn) e = launch<1, 0>(ta, tb, p, grid, stream);
   else e = launch<1, 1>(ta, tb, p, grid, stream);
   return e == cudaSuccess ? 0 : nsa::fail_cuda(e, "nsa_gemm_bf16 launch");
+}
+
+// y[M,N] = x[M,K] * W[N,K]^T where W lives at element offset `b_elem_offset` of the sharded
+// unit's gathered buffer `full`, which this same kernel assembles from the W ranks' shards
+// (see AgFuse).  After the kernel the whole unit (not only W) is gathered.
+//   shards      device array of W pointers to the ranks' shards (shard_elems bf16 each)
+//   chunk_flags local scratch, W * chunks_per_shard words, values < epoch on entry
+//   peer_flags  local flag row, peer p's shard is final once peer_flags[p] >= epoch (may be null)
+extern "C" int nsa_gemm_bf16_ag(const void* A, void* C, int M, int N, int K, int lda, int ldc,
+                                const void* const* shards, void* full, long shard_elems, long b_elem_offset,
+                                int W, int rank, unsigned* chunk_flags, int chunks_per_shard, const unsigned* peer_flags,
+                                unsigned epoch, long long max_cycles, int copy_ctas, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const char* Bp = reinterpret_cast<const char*>(full) + b_elem_offset * 2;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(Bp) & 15) || (lda & 7) || (K & 7) ||
+      (shard_elems & 7) || (b_elem_offset & 7))
+    return nsa::fail(NSA_ERR_ALIGNMENT, "nsa_gemm_bf16_ag: operands need 16-byte alignment");
+  CUtensorMap ta, tb;
+  int rc;
+  if ((rc = nsa::make_tmap_2d_bf16(&ta, A, K, M, lda, BK, BM))) return rc;
+  if ((rc = nsa::make_tmap_2d_bf16(&tb, Bp, K, N, K, BK, BN))) return rc;
+  GemmParams p;
+  p.ag = AgFuse{};
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldb = K; p.a_mn = 0; p.b_mn = 0;
+  p.out_fp32 = 0; p.accumulate = 0; p.C = C; p.status = nsa::status_ptr();
+  const int sms = nsa::sm_count();
+  if (copy_ctas <= 0) copy_ctas = 16;
+  if (copy_ctas > sms / 2) copy_ctas = sms / 2;
+  const long shard_vec = shard_elems / 8;
+  AgFuse& ag = p.ag;
+  ag.enabled = 1; ag.W = W; ag.rank = rank;
+  ag.shards = reinterpret_cast<const uint4* const*>(shards);
+  ag.full = reinterpret_cast<uint4*>(full);
+  ag.shard_vec = shard_vec;
+  ag.chunks_per_shard = chunks_per_shard;
+  ag.chunk_vec = (shard_vec + chunks_per_shard - 1) / chunks_per_shard;
+  ag.chunk_flags = chunk_flags; ag.peer_flags = peer_flags; ag.epoch = epoch;
+  ag.b_vec_offset = b_elem_offset / 8;
+  ag.max_cycles = max_cycles; ag.copy_ctas = copy_ctas;
+  // start the N sweep at the first shard, in pull order (rank, rank+1, ...), that overlaps W
+  const long b_lo = ag.b_vec_offset, b_hi = b_lo + static_cast<long>(N) * K / 8;
+  const int tiles_n = (N + BN - 1) / BN;
+  ag.n_rot = 0;
+  for (int k = 0; k < W; ++k) {
+    const int pr = (rank + k) % W;
+    const long s_lo = pr * shard_vec, s_hi = s_lo + shard_vec;
+    const long lo = s_lo > b_lo ? s_lo : b_lo, hi = s_hi < b_hi ? s_hi : b_hi;
+    if (lo < hi) {
+      // first N block that starts at or after the shard's first row (a straddling block comes last)
+      const long row = ((lo - b_lo) * 8 + K - 1) / K;
+      ag.n_rot = static_cast<int>((row + BN - 1) / BN) % tiles_n;
+      break;
+    }
+  }
+  const int tiles = ((M + BM - 1) / BM) * tiles_n;
+  int gemm_ctas = sms - copy_ctas;
+  if (tiles < gemm_ctas) gemm_ctas = tiles;
+  cudaError_t e = launch<0, 0>(ta, tb, p, copy_ctas + gemm_ctas, stream);
+  return e == cudaSuccess ? 0 : nsa::fail_cuda(e, "nsa_gemm_bf16_ag launch");
 }
