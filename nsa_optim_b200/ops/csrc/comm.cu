@@ -20,6 +20,7 @@
 // Peer memory is only ever accessed with plain loads and stores issued by these kernels.
 #include "host.cuh"
 #include <cuda_bf16.h>
+#include <cstring>
 
 namespace {
 typedef __nv_bfloat16 bf16;
@@ -256,4 +257,37 @@ extern "C" int nsa_comm_rs_adamw8bit(const float* const* grads, void* p_shard, i
                                                     wd_mask, nb, S, W, rank, scale, a, flags, epoch, max_cycles, nsa::status_ptr());
   nsa::count_launch();
   return 0;
+}
+
+// ---- arena allocation and CUDA IPC.  The arena is a plain cudaMalloc allocation so that its
+// handle describes exactly this buffer.  A peer must open the handle with ITS OWN device
+// current: the mapping (and the lazily enabled peer access) then belongs to the context whose
+// kernels will dereference the pointer.
+extern "C" int nsa_ipc_alloc(long nbytes, void** out_ptr, unsigned char* handle64) {
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, static_cast<size_t>(nbytes));
+  if (e != cudaSuccess) return nsa::fail_cuda(e, "nsa_ipc_alloc: cudaMalloc");
+  e = cudaMemset(p, 0, static_cast<size_t>(nbytes));
+  if (e != cudaSuccess) return nsa::fail_cuda(e, "nsa_ipc_alloc: cudaMemset");
+  cudaIpcMemHandle_t h;
+  e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) { cudaFree(p); return nsa::fail_cuda(e, "nsa_ipc_alloc: cudaIpcGetMemHandle"); }
+  static_assert(sizeof(h) == 64, "IPC handle size");
+  memcpy(handle64, &h, 64);
+  *out_ptr = p;
+  return 0;
+}
+extern "C" int nsa_ipc_open(const unsigned char* handle64, void** out_ptr) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  cudaError_t e = cudaIpcOpenMemHandle(out_ptr, h, cudaIpcMemLazyEnablePeerAccess);
+  return e == cudaSuccess ? 0 : nsa::fail_cuda(e, "nsa_ipc_open: cudaIpcOpenMemHandle");
+}
+extern "C" int nsa_ipc_close(void* p) {
+  cudaError_t e = cudaIpcCloseMemHandle(p);
+  return e == cudaSuccess ? 0 : nsa::fail_cuda(e, "nsa_ipc_close");
+}
+extern "C" int nsa_ipc_free(void* p) {
+  cudaError_t e = cudaFree(p);
+  return e == cudaSuccess ? 0 : nsa::fail_cuda(e, "nsa_ipc_free");
 }

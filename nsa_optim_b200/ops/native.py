@@ -153,9 +153,61 @@ class _Linear(torch.autograd.Function):
         return dx, dw
 
 
+# A sharded unit may defer its all-gather to the first matmul that touches one of its weights:
+# (lo, hi) is the address range of the unit's gathered buffer, ``run(x, w)`` launches the GEMM
+# whose kernel also assembles that buffer, ``fallback()`` gathers it without a matmul.
+_pending_gather = None
+
+
+def set_pending_gather(lo: int, hi: int, run, fallback) -> None:
+    global _pending_gather
+    flush_pending_gather()
+    _pending_gather = (lo, hi, run, fallback)
+
+
+def clear_pending_gather() -> None:
+    global _pending_gather
+    _pending_gather = None
+
+
+def flush_pending_gather() -> None:
+    global _pending_gather
+    if _pending_gather is not None:
+        fb = _pending_gather[3]
+        _pending_gather = None
+        fb()
+
+
+class _LinearGather(torch.autograd.Function):
+    """y = x W^T where the kernel that computes y also gathers W's sharded unit (see
+    ``parallel/symm.py``); the backward is the ordinary one."""
+
+    @staticmethod
+    def forward(ctx, x, w, run):
+        x2 = _as_2d(x)
+        y = run(x2, w)
+        ctx.save_for_backward(x2, w)
+        ctx.xshape = x.shape
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = _as_2d(dy)
+        dx = gemm(dy2, w, False, True).view(ctx.xshape) if ctx.needs_input_grad[0] else None
+        dw = gemm(dy2, x2, True, True) if ctx.needs_input_grad[1] else None
+        return dx, dw, None
+
+
 def linear(x: Tensor, w: Tensor) -> Tensor:
     if (x.shape[-1] % 8) or (w.shape[0] % 8):
+        flush_pending_gather()
         return torch_impl.linear(x, w)
+    pg = _pending_gather
+    if pg is not None:
+        if pg[0] <= w.data_ptr() < pg[1] and w.is_contiguous():
+            return _LinearGather.apply(x, w, pg[2])
+        flush_pending_gather()
     return _Linear.apply(x, w)
 
 

@@ -76,9 +76,15 @@ class FlatUnit:
         self.world, self.rank, self.device, self.dtype, self.reduce_dtype = world, rank, device, dtype, reduce_dtype
         self.slots: List[ParamSlot] = []
         off = 0
+        # 1-D tensors (norm weights, per-head scalars, biases) first: they are needed before the
+        # first matmul of the block, so a fused gather can fetch this small head region eagerly
+        named_params = sorted(named_params, key=lambda np_: 0 if np_[1].ndim <= 1 else 1)
+        self.head_elems = 0
         for n, p in named_params:
             self.slots.append(ParamSlot(n, tuple(p.shape), off, p.numel(), p))
             off = _round_up(off + p.numel(), ALIGN)
+            if p.ndim <= 1:
+                self.head_elems = off
         self.total = _round_up(max(off, ALIGN), world * ALIGN)
         self.shard_size = self.total // world
         # gathered buffer; parameters become views of an alias with its own version counter
@@ -228,9 +234,108 @@ class ShardedModel(nn.Module):
         self._order: List[FlatUnit] = []
         self._micro_steps = 0
         self.launch_counter = 0
+        self.arena = None
+        if self.comm_mode == "fused":
+            try:
+                self._setup_arena()
+            except Exception as exc:  # noqa: BLE001 - fall back to the collective library, loudly
+                if self.rank == 0:
+                    print(f"[nsa_optim_b200] peer-memory setup failed ({type(exc).__name__}: {exc}); using NCCL collectives")
+                self.comm_mode, self.arena = "torch", None
         if self.world > 1 and self.strategy == ShardingStrategy.FULL_SHARD:
             for u in self.units:
                 u.free_full()
+
+    # ------------------------------------------------------------------ peer-memory mode
+    def _setup_arena(self) -> None:
+        """Move every unit's shard and an fp32 gradient staging buffer into one IPC-shared arena
+        and open three epoch channels per unit: shard-ready, grads-ready, grads-consumed."""
+        from . import symm
+        W = self.world
+        units = self.all_units()
+        es = units[0].shard.element_size()
+        need = sum(_round_up(u.shard_size * es, 1024) + _round_up(W * u.shard_size * 4, 1024) for u in units) + 4096
+        arena = symm.SymmetricArena(need, 3 * len(units), self.rank, W, self.info.device, self.group)
+        for i, u in enumerate(units):
+            u.off_shard = arena.alloc(u.shard_size * es)
+            u.off_grad = arena.alloc(W * u.shard_size * 4)
+            new_shard = arena.view(u.off_shard, u.shard_size, u.dtype)
+            new_shard.copy_(u.shard)
+            u.shard = new_shard
+            u.grad_stage = arena.view(u.off_grad, W * u.shard_size, torch.float32)
+            u.ch_shard, u.ch_grad, u.ch_done = 3 * i, 3 * i + 1, 3 * i + 2
+            u.chunks_per_shard = max(1, min(16, (u.shard_size * es) // (1 << 20)))
+            u.chunk_flags = torch.zeros(W * u.chunks_per_shard, dtype=torch.int32, device=u.device)
+            u.rs_partial = torch.zeros(symm.reduce_scatter_parts(), dtype=torch.float32, device=u.device)
+            u._build_pieces()
+        self.arena = arena
+        self.shard_epoch = 1
+        self.grad_epoch = 0
+        self.fuse_first_gemm = True
+        for u in units:
+            symm.signal(arena, u.ch_shard, self.shard_epoch)
+        torch.cuda.synchronize()
+        pdist.barrier()
+
+    def _fused_gather(self, unit: FlatUnit, lazy: bool) -> None:
+        """P2P all-gather of a unit.  ``lazy`` (forward of a block): fetch only the small head
+        region now and leave the rest to the first matmul of the block, whose kernel pulls the
+        shards itself while it computes."""
+        from . import symm
+        from ..ops import native
+        es = unit.shard.element_size()
+        if lazy and self.fuse_first_gemm and unit.module is not None and unit.head_elems < unit.total:
+            cur = torch.cuda.current_stream()
+            symm.wait(self.arena, unit.ch_shard, self.shard_epoch)
+            hi = unit.head_elems
+            for p in range(self.world):
+                a, b = p * unit.shard_size, min((p + 1) * unit.shard_size, hi)
+                if a >= b:
+                    break
+                src = self.arena.view(unit.off_shard, unit.shard_size, unit.dtype, peer=p)[: b - a]
+                unit.full[a:b].copy_(src, non_blocking=True)
+            lo_ptr = unit.full.data_ptr()
+            hi_ptr = lo_ptr + unit.total * es
+            epoch = self.shard_epoch
+
+            def run(x, weight, _u=unit):
+                native.clear_pending_gather()
+                y = symm.gemm_all_gather(self.arena, x, _u.full, _u.off_shard, _u.shard_size,
+                                         (weight.data_ptr() - lo_ptr) // es, weight.shape[0], _u.chunk_flags,
+                                         _u.chunks_per_shard, _u.ch_shard, epoch)
+                _u.chunk_flags_epoch = epoch
+                return y
+
+            # chunk flags count epochs too: they are below `epoch` until this step's kernel sets them
+            native.set_pending_gather(lo_ptr, hi_ptr, run, lambda _u=unit: self._fused_gather_now(_u))
+            return
+        self._fused_gather_now(unit)
+
+    def _fused_gather_now(self, unit: FlatUnit) -> None:
+        from . import symm
+        es = unit.shard.element_size()
+        symm.all_gather(self.arena, unit.off_shard, unit.shard_size * es, unit.full, unit.ch_shard, self.shard_epoch)
+
+    def _fused_reduce(self, unit: FlatUnit) -> None:
+        from . import symm
+        epoch = self.grad_epoch
+        if epoch > 1:
+            symm.wait(self.arena, unit.ch_done, epoch - 1)         # peers have consumed the previous buffer
+        stage = unit.grad_stage
+        for s in unit.slots:
+            g = s.param.grad
+            dst = stage[s.offset:s.offset + s.numel]
+            if g is not None:
+                dst.copy_(g.reshape(-1))
+                s.param.grad = None
+            else:
+                dst.zero_()
+        symm.signal(self.arena, unit.ch_grad, epoch)
+        self.comm_stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self.comm_stream):
+            symm.reduce_scatter(self.arena, unit.off_grad, unit.grad_shard, 1.0 / self.world, True, unit.ch_grad, epoch,
+                                unit.rs_partial)
+            symm.signal(self.arena, unit.ch_done, epoch)
 
     # ------------------------------------------------------------------ comm selection
     def _resolve_comm(self, comm: str) -> str:
@@ -246,10 +351,22 @@ class ShardedModel(nn.Module):
     def all_units(self) -> List[FlatUnit]:
         return [self.root] + self.units
 
-    def _gather(self, unit: FlatUnit, async_: bool = True) -> None:
+    def _gather(self, unit: FlatUnit, async_: bool = True, lazy: bool = False) -> None:
         if self.world == 1 or unit.gathered:
             return
         unit.alloc_full()
+        if self.arena is not None:
+            if lazy:
+                self._fused_gather(unit, True)          # on the compute stream, inside the first matmul
+            else:
+                self.comm_stream.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(self.comm_stream):
+                    self._fused_gather_now(unit)
+                    unit.ready_event = torch.cuda.Event()
+                    unit.ready_event.record(self.comm_stream)
+                unit.full.record_stream(self.comm_stream)
+            unit.gathered = True
+            return
         if self.comm_stream is not None:
             self.comm_stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(self.comm_stream):
@@ -269,6 +386,9 @@ class ShardedModel(nn.Module):
     def _reduce_grads(self, unit: FlatUnit) -> None:
         """Pack parameter gradients, reduce-scatter, accumulate 1/world of the sum."""
         if self.world == 1:
+            return
+        if self.arena is not None:
+            self._fused_reduce(unit)
             return
         flat = torch.zeros(unit.total, dtype=unit.reduce_dtype, device=unit.device)
         for s in unit.slots:
@@ -295,14 +415,23 @@ class ShardedModel(nn.Module):
         i = self.units.index(unit) + step
         return self.units[i] if 0 <= i < len(self.units) else None
 
+    def _lazy(self) -> bool:
+        return self.arena is not None and self.fuse_first_gemm
+
     def _pre_forward(self, unit: FlatUnit) -> None:
-        self._gather(unit)
-        nxt = self._neighbour(unit, +1)
-        if nxt is not None:
-            self._gather(nxt)
+        if self._lazy():
+            self._gather(unit, lazy=True)        # the block's first matmul pulls the shards itself
+        else:
+            self._gather(unit)
+            nxt = self._neighbour(unit, +1)
+            if nxt is not None:
+                self._gather(nxt)
         self._wait_ready(unit)
 
     def _post_forward(self, unit: FlatUnit) -> None:
+        if self.arena is not None:
+            from ..ops import native
+            native.flush_pending_gather()        # nothing consumed the deferred gather: do it now
         if self.strategy == ShardingStrategy.FULL_SHARD:
             unit.free_full()
 
@@ -334,12 +463,14 @@ class ShardedModel(nn.Module):
     def forward(self, *args, **kwargs):
         self._gather(self.root)
         self._wait_ready(self.root)
-        if self.units:
+        if self.units and not self._lazy():
             self._gather(self.units[0])
         return self.module(*args, **kwargs)
 
     def backward(self, loss: Tensor) -> None:
         """``loss.backward()`` followed by the root unit's gradient reduction."""
+        if self.arena is not None:
+            self.grad_epoch += 1
         loss.backward()
         self._reduce_grads(self.root)
         self._micro_steps += 1
@@ -349,11 +480,16 @@ class ShardedModel(nn.Module):
         strategies) re-issue every all-gather on the communication stream."""
         if self.world == 1:
             return
+        if self.arena is not None:
+            from . import symm
+            self.shard_epoch += 1
+            for u in self.all_units():
+                symm.signal(self.arena, u.ch_shard, self.shard_epoch)
         for u in self.all_units():
             u.gathered = False
-            if self.strategy != ShardingStrategy.FULL_SHARD or u is self.root:
+            if u is self.root or (self.strategy != ShardingStrategy.FULL_SHARD and not self._lazy()):
                 self._gather(u)
-            else:
+            elif self.strategy == ShardingStrategy.FULL_SHARD:
                 u.full.untyped_storage().resize_(0)
 
     def wait_reductions(self) -> None:

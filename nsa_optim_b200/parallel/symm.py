@@ -41,31 +41,58 @@ class SymmetricArena:
         self.nbytes = self.flag_bytes + _round_up(nbytes, 4096)
         self.cursor = self.flag_bytes
         self.channels = channels
+        self._raw_local = None
+        self._raw_peers: List[int] = []
         if local_peers is not None:
             # single-process emulation: the "peers" are other tensors on this GPU
             self.peers = local_peers
             self.local = local_peers[rank]
         else:
-            self.local = torch.zeros(self.nbytes, dtype=torch.uint8, device=device)
-            self.peers = self._exchange(group)
+            self._exchange(group)
         self._ptr_cache = {}
 
-    def _exchange(self, group) -> List[torch.Tensor]:
-        from torch.multiprocessing.reductions import reduce_tensor
-        fn, args = reduce_tensor(self.local)
-        gathered: List = [None] * self.world
-        dist.all_gather_object(gathered, args, group=group)
+    @staticmethod
+    def _wrap(ptr: int, nbytes: int, device: torch.device) -> torch.Tensor:
+        """A uint8 tensor aliasing raw device memory (no ownership)."""
+        class _Raw:
+            pass
+        raw = _Raw()
+        raw.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+        return torch.as_tensor(raw, device=device)
+
+    def _exchange(self, group) -> None:
+        """cudaMalloc the arena, export its IPC handle, and open every peer's handle with this
+        rank's device current, so the mappings belong to the context whose kernels use them."""
+        import ctypes
         lib = native.load()
-        peers = []
+        ptr = c_void_p()
+        handle = (ctypes.c_ubyte * 64)()
+        native._check(lib.nsa_ipc_alloc(c_long(self.nbytes), ctypes.byref(ptr), handle))
+        self._raw_local = ptr.value
+        self.local = self._wrap(ptr.value, self.nbytes, self.device)
+        gathered: List = [None] * self.world
+        dist.all_gather_object(gathered, bytes(handle), group=group)
+        self.peers = []
         for r in range(self.world):
             if r == self.rank:
-                peers.append(self.local)
+                self.peers.append(self.local)
                 continue
-            t = fn(*gathered[r])
-            native._check(lib.nsa_enable_peer_access(c_int(t.device.index)))
-            peers.append(t)
+            h = (ctypes.c_ubyte * 64).from_buffer_copy(gathered[r])
+            pp = c_void_p()
+            native._check(lib.nsa_ipc_open(h, ctypes.byref(pp)))
+            self._raw_peers.append(pp.value)
+            self.peers.append(self._wrap(pp.value, self.nbytes, self.device))
         dist.barrier(group=group)
-        return peers
+
+    def close(self) -> None:
+        """Unmap the peers and free the arena (call after a barrier, with no kernel in flight)."""
+        lib = native.load()
+        for p in self._raw_peers:
+            lib.nsa_ipc_close(c_void_p(p))
+        self._raw_peers = []
+        if self._raw_local is not None:
+            lib.nsa_ipc_free(c_void_p(self._raw_local))
+            self._raw_local = None
 
     def alloc(self, nbytes: int, align: int = 1024) -> int:
         """Reserve ``nbytes`` at the same offset on every rank; returns the offset."""
