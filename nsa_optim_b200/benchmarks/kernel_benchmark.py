@@ -108,9 +108,58 @@ def bench_elementwise(backend: str, rows: int, d: int, ffn: int, iters: int) -> 
     return out
 
 
+def bench_attention(backend: str, T: int, iters: int, window: int = 0) -> List[Dict]:
+    """Causal GQA attention 32 q / 2 kv heads of 128, forward and forward+backward."""
+    q = torch.randn(1, T, 32, 128, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(1, T, 2, 128, device="cuda").bfloat16().requires_grad_()
+    v = torch.randn(1, T, 2, 128, device="cuda").bfloat16().requires_grad_()
+    keys = min(window, T) if window else T / 2
+    flops_fwd = 4.0 * T * keys * 128 * 32
+    pk = peaks()
+    rows = []
+    with ops.backend(backend):
+        def fwd():
+            with torch.no_grad():
+                ops.attention(q, k, v, True, window)
+        def fb():
+            o = ops.attention(q, k, v, True, window)
+            o.backward(torch.ones_like(o))
+        for name, fn, mult in (("fwd", fwd, 1.0), ("fwd+bwd", fb, 3.5)):
+            ms = time_ms(fn, iters)
+            tf = flops_fwd * mult / (ms * 1e-3) / 1e12
+            rows.append({"op": f"attention {name} T={T} window={window} 32q/2kv hd128", "backend": backend, "ms": ms,
+                         "tflops": tf, "frac_of_peak": tf / pk["bf16_tflops"], "peak": f"{pk['bf16_tflops']} TFLOP/s of {pk['source']}"})
+    return rows
+
+
+def bench_mixers(backend: str, T: int, iters: int) -> List[Dict]:
+    """Gated delta rule (16 heads, K128/V256) and Mamba-2 SSD (64 heads of 64, N128), fwd+bwd."""
+    rows = []
+    with ops.backend(backend):
+        q = torch.nn.functional.normalize(torch.randn(1, T, 16, 128, device="cuda"), dim=-1).bfloat16().requires_grad_()
+        k = torch.nn.functional.normalize(torch.randn(1, T, 16, 128, device="cuda"), dim=-1).bfloat16().requires_grad_()
+        v = torch.randn(1, T, 16, 256, device="cuda").bfloat16().requires_grad_()
+        g = (-torch.rand(1, T, 16, device="cuda") * 0.1).requires_grad_()
+        beta = torch.rand(1, T, 16, device="cuda").requires_grad_()
+        def gdn():
+            o = ops.gated_delta_rule(q, k, v, g, beta)
+            o.backward(torch.ones_like(o))
+        rows.append({"op": f"gated_delta_rule fwd+bwd T={T}", "backend": backend, "ms": time_ms(gdn, iters)})
+        x = torch.randn(1, T, 64, 64, device="cuda").bfloat16().requires_grad_()
+        dt = (torch.rand(1, T, 64, device="cuda") * 0.1 + 0.001).requires_grad_()
+        A = (-torch.rand(64, device="cuda") * 4 - 0.5).requires_grad_()
+        Bm = torch.randn(1, T, 1, 128, device="cuda").bfloat16().requires_grad_()
+        Cm = torch.randn(1, T, 1, 128, device="cuda").bfloat16().requires_grad_()
+        def ssd():
+            y = ops.ssd_scan(x, dt, A, Bm, Cm, None, 256)
+            y.backward(torch.ones_like(y))
+        rows.append({"op": f"ssd_scan fwd+bwd T={T}", "backend": backend, "ms": time_ms(ssd, iters)})
+    return rows
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["all", "gemm", "elementwise"])
+    ap.add_argument("--op", default="all", choices=["all", "gemm", "elementwise", "attention", "mixers"])
     ap.add_argument("--backend", default="native", choices=["native", "torch"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
@@ -119,6 +168,8 @@ def main() -> None:
     ap.add_argument("--b_mn", action="store_true")
     ap.add_argument("--rows", type=int, default=65536)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--seq", type=int, default=16384)
+    ap.add_argument("--window", type=int, default=0)
     a = ap.parse_args()
     rows: List[Dict] = []
     if a.op in ("all", "gemm"):
@@ -131,6 +182,10 @@ def main() -> None:
                 rows.append(bench_gemm(m, n, k, am, bm, a.backend, a.iters))
     if a.op in ("all", "elementwise"):
         rows += bench_elementwise(a.backend, a.rows, 2048, 5632, a.iters)
+    if a.op in ("all", "attention"):
+        rows += bench_attention(a.backend, a.seq, a.iters, a.window)
+    if a.op in ("all", "mixers"):
+        rows += bench_mixers(a.backend, a.seq, a.iters)
     for r in rows:
         print(json.dumps(r))
     if a.backend == "native":
