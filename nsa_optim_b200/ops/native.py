@@ -750,8 +750,8 @@ class _SSDStatePass(torch.autograd.Function):
         B, nc, H = gamma.shape
         E = S[0, 0, 0].numel()
         Hprev = torch.empty_like(S)
-        _check(load().nsa_ssd_state_fwd(_p(S), _p(gamma), _p(Hprev), c_void_p(0), c_int(B), c_int(nc), c_int(H),
-                                        c_long(E), _stream()))
+        _check(load().nsa_ssd_state_fwd(_p(S), _p(gamma), _p(Hprev), c_void_p(0), c_void_p(0), c_int(B), c_int(nc),
+                                        c_int(H), c_long(E), _stream()))
         ctx.save_for_backward(gamma, Hprev)
         return Hprev
 
@@ -762,12 +762,103 @@ class _SSDStatePass(torch.autograd.Function):
         E = Hprev[0, 0, 0].numel()
         dHprev = dHprev.contiguous().float()
         dS = torch.empty_like(Hprev)
-        _check(load().nsa_ssd_state_bwd(_p(dHprev), _p(gamma), _p(dS), c_int(B), c_int(nc), c_int(H), c_long(E), _stream()))
+        _check(load().nsa_ssd_state_bwd(_p(dHprev), _p(gamma), _p(dS), c_void_p(0), c_int(B), c_int(nc), c_int(H), c_long(E),
+                                        _stream()))
         dgamma = (Hprev * dS).sum((-1, -2))
         return dS, dgamma
 
 
+def _token_view(t: Tensor, inner: int):
+    """(B, T, ..., inner-contiguous) view -> (tensor, token stride in elements) usable by a TMA
+    map with rows = tokens; copies when the view is not row-strided."""
+    B, T = t.shape[0], t.shape[1]
+    width = t[0, 0].numel()
+    ok = (t.stride(-1) == 1 and t.stride(0) == T * t.stride(1) and t.stride(1) % 8 == 0 and t.data_ptr() % 16 == 0
+          and t[0, 0].is_contiguous())
+    if not ok:
+        t = t.contiguous()
+    return t, t.stride(1) if ok else width
+
+
+class _SSD(torch.autograd.Function):
+    """Mamba-2 SSD through the tcgen05 chunk kernels of ``csrc/ssd.cu`` (chunk 128, d_state 128,
+    headdim 64, one B/C group)."""
+
+    @staticmethod
+    def forward(ctx, x, dt, A, Bm, Cm, D):
+        Bsz, T, H, P = x.shape
+        N = Bm.shape[-1]
+        nc = -(-T // 128)
+        x, ldx = _token_view(x, P)
+        Bm, ldb = _token_view(Bm, N)
+        Cm, ldc = _token_view(Cm, N)
+        dt = dt.float().contiguous()
+        A = A.float().contiguous()
+        Df = None if D is None else D.float().contiguous()
+        dev = x.device
+        S_loc = torch.empty(Bsz, nc, H, N, P, dtype=torch.float32, device=dev)
+        gamma = torch.empty(Bsz, nc, H, dtype=torch.float32, device=dev)
+        lib = load()
+        _check(lib.nsa_ssd_chunk_state(c_int(0), _p(Bm), c_long(ldb), _p(x), c_long(ldx), _p(dt), _p(A), _p(S_loc), _p(gamma),
+                                       c_int(Bsz), c_int(T), c_int(H), c_int(N), c_int(P), _stream()))
+        Hb = torch.empty(Bsz, nc, H, N, P, dtype=torch.bfloat16, device=dev)
+        _check(lib.nsa_ssd_state_fwd(_p(S_loc), _p(gamma), c_void_p(0), _p(Hb), c_void_p(0), c_int(Bsz), c_int(nc), c_int(H),
+                                     c_long(N * P), _stream()))
+        del S_loc
+        y = torch.empty(Bsz, T, H, P, dtype=torch.bfloat16, device=dev)
+        _check(lib.nsa_ssd_chunk_out(_p(Cm), c_long(ldc), _p(Bm), c_long(ldb), _p(x), c_long(ldx), _p(Hb), _p(dt), _p(A),
+                                     _p(Df), _p(y), c_int(Bsz), c_int(T), c_int(H), c_int(N), c_int(P), _stream()))
+        ctx.save_for_backward(x, dt, A, Bm, Cm, Df if Df is not None else torch.empty(0, device=dev), y, gamma, Hb)
+        ctx.lds = (ldx, ldb, ldc)
+        ctx.has_D = D is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, dt, A, Bm, Cm, Df, y, gamma, Hb = ctx.saved_tensors
+        ldx, ldb, ldc = ctx.lds
+        Df = Df if ctx.has_D else None
+        Bsz, T, H, P = y.shape
+        N = Bm.shape[-1]
+        nc = gamma.shape[1]
+        dev = y.device
+        dy = dy.contiguous()
+        lib = load()
+        G = torch.empty(Bsz, nc, H, N, P, dtype=torch.float32, device=dev)
+        _check(lib.nsa_ssd_chunk_state(c_int(1), _p(Cm), c_long(ldc), _p(dy), c_long(H * P), _p(dt), _p(A), _p(G), c_void_p(0),
+                                       c_int(Bsz), c_int(T), c_int(H), c_int(N), c_int(P), _stream()))
+        dHn = torch.empty(Bsz, nc, H, N, P, dtype=torch.bfloat16, device=dev)
+        _check(lib.nsa_ssd_state_bwd(_p(G), _p(gamma), c_void_p(0), _p(dHn), c_int(Bsz), c_int(nc), c_int(H), c_long(N * P),
+                                     _stream()))
+        del G
+        dx = torch.empty(Bsz, T, H, P, dtype=torch.bfloat16, device=dev)
+        dB = torch.zeros(Bsz, T, N, dtype=torch.float32, device=dev)
+        dC = torch.zeros(Bsz, T, N, dtype=torch.float32, device=dev)
+        q = torch.empty(Bsz, T, H, dtype=torch.float32, device=dev)
+        k = torch.empty(Bsz, T, H, dtype=torch.float32, device=dev)
+        _check(lib.nsa_ssd_chunk_grad(_p(Cm), c_long(ldc), _p(Bm), c_long(ldb), _p(x), c_long(ldx), _p(dy), _p(y), _p(Hb),
+                                      _p(dHn), _p(dt), _p(A), _p(Df), _p(dx), _p(dB), _p(dC), _p(q), _p(k), c_int(Bsz),
+                                      c_int(T), c_int(H), c_int(N), c_int(P), _stream()))
+        # d(cum_t) = dy_t.(y_t - D x_t) - x_t.dx_t ;  a_k = dt_k A enters every cum_t with t >= k
+        dcum = q - k
+        da = torch.flip(torch.cumsum(torch.flip(dcum, (1,)), 1), (1,))
+        ddt = da * A[None, None, :] + k / dt.clamp_min(1e-20)
+        dA = (da * dt).sum((0, 1))
+        dD = (dy.float() * x.float()).sum((0, 1, 3)) if ctx.has_D else None
+        return (dx, ddt, dA, dB.view(Bsz, T, 1, N).to(torch.bfloat16), dC.view(Bsz, T, 1, N).to(torch.bfloat16), dD)
+
+
 def ssd_scan(x, dt, A, Bm, Cm, D=None, chunk=256):
+    """Mamba-2 SSD.  The shapes of the hybrid models (d_state 128, headdim 64, one group) run on
+    the fused tcgen05 chunk kernels; other shapes use batched matmuls plus the native
+    inter-chunk state pass."""
+    if (x.shape[-1] == 64 and Bm.shape[-1] == 128 and Bm.shape[2] == 1 and x.dtype == torch.bfloat16
+            and Bm.dtype == torch.bfloat16 and Cm.dtype == torch.bfloat16):
+        return _SSD.apply(x, dt, A, Bm, Cm, D)
+    return _ssd_scan_batched(x, dt, A, Bm, Cm, D, chunk)
+
+
+def _ssd_scan_batched(x, dt, A, Bm, Cm, D=None, chunk=256):
     """Chunked SSD: the per-chunk terms are batched tensor-core matmuls over all chunks at once,
     the inter-chunk recurrence is one native kernel (forward) and one (backward)."""
     F = torch.nn.functional

@@ -7,15 +7,21 @@ from nsa_optim_b200.ops import oracle, torch_impl
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("T,chunk", [(300, 256), (512, 64), (129, 128)])
-def test_ssd_forward_backward(native, T, chunk):
-    B, H, P, N = 2, 4, 64, 128
+@pytest.mark.parametrize("T,chunk,P,N", [(300, 256, 64, 128), (512, 64, 64, 128), (129, 128, 64, 128),
+                                          (300, 256, 32, 64)])
+def test_ssd_forward_backward(native, T, chunk, P, N):
+    B, H = 2, 4
     x = torch.randn(B, T, H, P, device="cuda").bfloat16()
     dt = torch.rand(B, T, H, device="cuda") * 0.1 + 0.001
     A = -torch.rand(H, device="cuda") * 4 - 0.5
     Bm = torch.randn(B, T, 1, N, device="cuda").bfloat16() * 0.3
     Cm = torch.randn(B, T, 1, N, device="cuda").bfloat16() * 0.3
     Dp = torch.randn(H, device="cuda")
+    if P == 64:      # the mixer hands the kernels strided slices of one projection: exercise that
+        packed = torch.cat([x.reshape(B, T, H * P), Bm.reshape(B, T, N), Cm.reshape(B, T, N)], -1).contiguous()
+        x = packed[..., :H * P].view(B, T, H, P)
+        Bm = packed[..., H * P:H * P + N].view(B, T, 1, N)
+        Cm = packed[..., H * P + N:].view(B, T, 1, N)
     leaves = [t.clone().requires_grad_() for t in (x, dt, A, Bm, Cm, Dp)]
     y = native.ssd_scan(*leaves, chunk=chunk)
     dy = torch.randn_like(y)
