@@ -31,7 +31,7 @@ import torch
 import torch.nn as nn
 
 from . import checkpoint as ckpt
-from .config import (AttentionType, MambaType, OptimizerConfig, OptimizerType, TrainingConfig,
+from .config import (AttentionType, MambaType, ModelConfig, OptimizerConfig, OptimizerType, TrainingConfig,
                      resolve_attention_type)
 from .data import DataConfig, create_dataloader, create_synthetic_loader, get_tokenizer
 from .models import (create_gated_deltanet, create_hybrid_model, create_mamba2, create_model,
@@ -369,6 +369,22 @@ def format_log_line(step: int, total_steps: int, tokens: int, loss: float, lr: f
             f"LR: {lr:.2e} | Tok/s: {tok_s:.0f} | Grad: {grad:.4f}")
 
 
+def _model_flops_per_token(trainer: "Trainer") -> float:
+    """Model FLOPs (forward + backward, no recompute) per trained token, 0 when the model family
+    has no FLOP model."""
+    from .models import HybridConfig
+    from .profiling import calculate_flops_per_token, hybrid_flops_per_token
+    mc = getattr(trainer.model.module if hasattr(trainer.model, "module") else trainer.model, "config", None)
+    try:
+        if isinstance(mc, HybridConfig):
+            return float(hybrid_flops_per_token(mc, trainer.cfg.max_seq_length, training=True, recompute=False)["model_flops"])
+        if isinstance(mc, ModelConfig):
+            return float(calculate_flops_per_token(mc, trainer.cfg.max_seq_length)["total"])
+    except Exception:  # noqa: BLE001 - the figure is informational
+        pass
+    return 0.0
+
+
 def train(args: argparse.Namespace) -> Dict[str, Any]:
     trainer = Trainer(args)
     cfg, info = trainer.cfg, trainer.info
@@ -394,6 +410,7 @@ def train(args: argparse.Namespace) -> Dict[str, Any]:
         print(f"Effective batch: {eff} sequences x {cfg.max_seq_length} tokens "
               f"({cfg.batch_size} per GPU x {cfg.gradient_accumulation_steps} accumulation x {info.world_size} ranks)")
     use_events = trainer.device.type == "cuda"
+    flops_per_token = _model_flops_per_token(trainer)
     window_losses: List[torch.Tensor] = []
     window_tokens = 0
     last = {"loss": float("nan"), "tok_s": 0.0}
@@ -431,6 +448,9 @@ def train(args: argparse.Namespace) -> Dict[str, Any]:
                       flush=True)
                 rec = {"step": s, "tokens": trainer.total_tokens, "loss": loss, "lr": out["lr"],
                        "tokens_per_sec": tok_s, "grad_norm": grad}
+                if flops_per_token:
+                    from .profiling import model_flops_utilisation
+                    rec["mfu"] = model_flops_utilisation(flops_per_token, tok_s, info.world_size)
                 history.append(rec)
                 log_f.write(json.dumps(rec) + "\n")
                 log_f.flush()
