@@ -129,6 +129,8 @@ def main() -> None:
     ap.add_argument("--seq_len", type=int, default=65536)
     ap.add_argument("--comm", type=str, default="auto")
     ap.add_argument("--skip_e2e", action="store_true")
+    ap.add_argument("--checkpoint_blocks", type=str, default="M",
+                    help="block kinds whose activations are recomputed in backward ('MDA' = all, '' = none)")
     a = ap.parse_args()
     if a.impl == "reference":
         reference_arm(a)
@@ -145,7 +147,12 @@ def main() -> None:
     world = int(os.environ.get("WORLD_SIZE", 1))
     if world != a.gpus:
         raise SystemExit(f"--gpus {a.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
-    args = parse_args(flagship_args(a.seq_len, ["--comm", a.comm]))
+    extra = ["--comm", a.comm]
+    if a.checkpoint_blocks:
+        extra += ["--checkpoint_blocks", a.checkpoint_blocks]
+    args = parse_args(flagship_args(a.seq_len, extra))
+    if not a.checkpoint_blocks:
+        args.gradient_checkpointing = False
     tr = Trainer(args, verbose=False)
     info, dev = tr.info, tr.device
     native = ops.native_module() if a.impl == "native" else None
@@ -218,10 +225,12 @@ def main() -> None:
             "vs_baseline": value / PUBLISHED_TOK_S, "dtype": "bf16", "data": "synthetic uniform random tokens, random-init weights",
             "impl": a.impl,
             "config": {"model": "1B hybrid MDMAx4 (16 layers, d2048, FFN 5632, V32000; NSA 32q/2kv hd128 cmp32/16 sel64 top16 win512; "
-                                "Mamba-2 N128 hd64 chunk256; GatedDeltaNet 16x128)",
+                                "Mamba-2 N128 hd64 expand 2 (SSD kernels tile the scan in chunks of 128); GatedDeltaNet 16x128)",
                        "params": tr.n_params, "global_batch": args.batch_size * world, "seq_len": args.context_length,
                        "optimizer": "adamw8bit (block 256, dynamic-tree code book)", "grad_clip": 1.0,
-                       "activation_checkpointing": True, "parallelism": f"dp{world} sharded ({tr.model.strategy.value})",
+                       "activation_checkpointing": (f"block kinds {a.checkpoint_blocks} recomputed, others keep activations"
+                                                    if a.checkpoint_blocks else "off"),
+                       "peak_memory_gb": round(torch.cuda.max_memory_allocated(dev) / 2**30, 2), "parallelism": f"dp{world} sharded ({tr.model.strategy.value})",
                        "comm": tr.model.comm_mode,
                        "l2": "no explicit flush: per-step working set (2.4 GB weights + >4 GB activations) exceeds the 126 MB L2",
                        "baseline_note": "vs_baseline divides by the reference's only published number (11589 tok/s, 0.5B MDMA, "

@@ -102,6 +102,7 @@ class GatedDeltaNetConfig:
 
 
 class GatedDeltaNetBlock(nn.Module):
+    block_kind = "D"
     def __init__(self, config: GatedDeltaNetConfig, layer_idx: int):
         super().__init__()
         self.layer_idx = layer_idx

@@ -93,6 +93,7 @@ def apply_rotary_pos_emb_hybrid(q: Tensor, k: Tensor, cos: Tensor, sin: Tensor):
 
 
 class MambaBlock(nn.Module):
+    block_kind = "M"
     def __init__(self, config: HybridConfig, layer_idx: int):
         super().__init__()
         self.layer_idx = layer_idx
@@ -109,6 +110,7 @@ class MambaBlock(nn.Module):
 
 
 class DeltaNetBlock(nn.Module):
+    block_kind = "D"
     def __init__(self, config: HybridConfig, layer_idx: int):
         super().__init__()
         self.layer_idx = layer_idx
@@ -127,6 +129,7 @@ class DeltaNetBlock(nn.Module):
 
 
 class AttentionBlock(nn.Module):
+    block_kind = "A"
     def __init__(self, config: HybridConfig, layer_idx: int):
         super().__init__()
         self.layer_idx = layer_idx

@@ -98,6 +98,7 @@ def _mlp_width(d_model: int) -> int:
 
 class Mamba2Block(nn.Module):
     """norm -> mixer -> +residual -> norm -> SwiGLU MLP -> +residual."""
+    block_kind = "M"
 
     def __init__(self, config: Mamba2Config, layer_idx: int):
         super().__init__()
@@ -197,6 +198,7 @@ class Mamba3Config:
 
 
 class Mamba3Block(nn.Module):
+    block_kind = "M"
     def __init__(self, d_model: int, d_state: int = 128, expand: int = 2, headdim: int = 64,
                  use_conv: bool = False, use_complex: bool = True, dt_min: float = 0.001,
                  dt_max: float = 0.1):

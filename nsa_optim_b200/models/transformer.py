@@ -135,6 +135,7 @@ _ATTENTION = {
 
 
 class TransformerBlock(nn.Module):
+    block_kind = "A"
     def __init__(self, config: ModelConfig, layer_idx: int, kernel_type: KernelType = "liger"):
         super().__init__()
         self.layer_idx = layer_idx

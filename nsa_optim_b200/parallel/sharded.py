@@ -158,7 +158,7 @@ class _UnitFunction(torch.autograd.Function):
     def forward(ctx, runtime: "ShardedModel", unit: FlatUnit, hidden: Tensor, *args):
         ctx.runtime, ctx.unit, ctx.args = runtime, unit, args
         runtime._pre_forward(unit)
-        if runtime.activation_checkpointing:
+        if runtime._checkpointed(unit):
             with torch.no_grad():
                 out = unit.module(hidden, *args)
             ctx.save_for_backward(hidden)
@@ -196,7 +196,7 @@ class ShardedModel(nn.Module):
                  strategy: "ShardingStrategy | str | None" = None,
                  param_dtype: Optional[torch.dtype] = None, reduce_dtype: torch.dtype = torch.float32,
                  activation_checkpointing: Optional[bool] = None, comm: str = "auto",
-                 process_group=None):
+                 process_group=None, checkpoint_blocks: Optional[str] = None):
         super().__init__()
         self.module = model
         self.info = info or pdist.DistInfo(device=next(model.parameters()).device)
@@ -213,6 +213,10 @@ class ShardedModel(nn.Module):
         if activation_checkpointing is None:
             activation_checkpointing = bool(getattr(model, "gradient_checkpointing", False))
         self.activation_checkpointing = activation_checkpointing
+        # With checkpointing on, ``checkpoint_blocks`` narrows it to the block kinds named (letters of
+        # the hybrid pattern: M, D, A); the other blocks keep their activations.  Recomputing only the
+        # cheap-to-recompute, activation-heavy kinds trades spare HBM for step time.
+        self.checkpoint_kinds = set(checkpoint_blocks.upper()) if checkpoint_blocks else None
         self.comm_mode = self._resolve_comm(comm)
         # ---- units: root first (gathered for the whole step), then one per block
         blocks = model.block_modules()
@@ -447,6 +451,13 @@ class ShardedModel(nn.Module):
         if self.strategy == ShardingStrategy.FULL_SHARD:
             unit.free_full()
 
+    def _checkpointed(self, unit: FlatUnit) -> bool:
+        if not self.activation_checkpointing:
+            return False
+        if self.checkpoint_kinds is None:
+            return True
+        return getattr(unit.module, "block_kind", "A") in self.checkpoint_kinds
+
     def _run_layer(self, layer: nn.Module, hidden: Tensor, *args) -> Tensor:
         unit = self._unit_of[id(layer)]
         if not (torch.is_grad_enabled() and self.module.training):
@@ -455,7 +466,7 @@ class ShardedModel(nn.Module):
             if self.strategy == ShardingStrategy.FULL_SHARD:
                 unit.free_full()
             return out
-        if self.world == 1 and not self.activation_checkpointing:
+        if self.world == 1 and not self._checkpointed(unit):
             return layer(hidden, *args)
         return _UnitFunction.apply(self, unit, hidden, *args)
 

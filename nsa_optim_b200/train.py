@@ -82,6 +82,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--max_precond_dim", type=int, default=8192)
     p.add_argument("--dtype", type=str, default="bfloat16", choices=list(DTYPES))
     p.add_argument("--gradient_checkpointing", action="store_true")
+    p.add_argument("--checkpoint_blocks", type=str, default=None,
+                   help="with --gradient_checkpointing: recompute only these block kinds (letters M, D, A)")
     p.add_argument("--dataset_name", type=str, default="HuggingFaceFW/fineweb-edu")
     p.add_argument("--dataset_subset", type=str, default="sample-10BT")
     p.add_argument("--output_dir", type=str, default="./outputs")
@@ -245,7 +247,8 @@ class Trainer:
         model.to(self.dtype)
         comm = args.comm
         self.model = ShardedModel(model, self.info, strategy=args.sharding, param_dtype=self.dtype,
-                                  activation_checkpointing=self.cfg.gradient_checkpointing, comm=comm)
+                                  activation_checkpointing=self.cfg.gradient_checkpointing, comm=comm,
+                                  checkpoint_blocks=getattr(args, "checkpoint_blocks", None))
         self.n_params = sum(p.numel() for p in model.parameters())
         if self.verbose:
             print(f"Model dtype: {self.cfg.dtype}")

@@ -131,7 +131,9 @@ def run_ranks(tmp_path, world, mode, extra=(), port=29731):
 
 
 @pytest.mark.parametrize("opt,extra", [("adamw", ()), ("adamw8bit", ("--gradient_checkpointing",)),
-                                       ("adamw", ("--sharding", "full_shard"))])
+                                       ("adamw", ("--sharding", "full_shard")),
+                                       ("adamw", ("--sharding", "full_shard", "--gradient_checkpointing",
+                                                  "--checkpoint_blocks", "M"))])
 def test_two_ranks_match_one_rank(tmp_path, opt, extra):
     args = ("--optimizer_type", opt) + tuple(extra)
     run_ranks(tmp_path, 1, "train", args)
