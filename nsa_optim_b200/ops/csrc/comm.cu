@@ -105,17 +105,34 @@ __global__ void __launch_bounds__(256) reduce_scatter_kernel(const float* const*
   if (!cta_wait_peers(flags, W, rank, epoch, max_cycles, status, &sh_ok)) return;
   float ss = 0.f;
   const long base = static_cast<long>(rank) * S4;
-  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < S4; i += static_cast<long>(gridDim.x) * blockDim.x) {
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+  constexpr int U = 4;                                  // independent 16-byte loads in flight per thread and peer
+  for (long i0 = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < S4; i0 += stride * U) {
+    float4 acc[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int p = 0; p < W; ++p) {                      // fixed order: bitwise reproducible
-      const float4 v = reinterpret_cast<const float4*>(grads[p])[base + i];
-      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      const float4* g = reinterpret_cast<const float4*>(grads[p]) + base;
+      float4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long i = i0 + u * stride;
+        v[u] = i < S4 ? g[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) { acc[u].x += v[u].x; acc[u].y += v[u].y; acc[u].z += v[u].z; acc[u].w += v[u].w; }
     }
-    acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
-    float4* o = reinterpret_cast<float4*>(grad_shard) + i;
-    if (accumulate) { const float4 q = *o; acc.x += q.x; acc.y += q.y; acc.z += q.z; acc.w += q.w; }
-    *o = acc;
-    ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long i = i0 + u * stride;
+      if (i >= S4) break;
+      float4 a = acc[u];
+      a.x *= scale; a.y *= scale; a.z *= scale; a.w *= scale;
+      float4* o = reinterpret_cast<float4*>(grad_shard) + i;
+      if (accumulate) { const float4 q = *o; a.x += q.x; a.y += q.y; a.z += q.z; a.w += q.w; }
+      *o = a;
+      ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+    }
   }
   if (sumsq_partial) {
 #pragma unroll
@@ -225,7 +242,10 @@ extern "C" int nsa_comm_allgather(const void* const* shards, void* out, long sha
   nsa::count_launch();
   return 0;
 }
-extern "C" int nsa_comm_reduce_scatter_parts(void) { return nsa::sm_count() * 2; }
+// A reduce-scatter runs beside the backward pass of the next block: a small grid (well under one
+// CTA per SM) with several loads in flight per thread keeps the link busy without taking the
+// compute kernels' SMs.
+extern "C" int nsa_comm_reduce_scatter_parts(void) { return 64; }
 // grads: device array of W pointers to full fp32 gradient buffers (W*S floats); S multiple of 4.
 extern "C" int nsa_comm_reduce_scatter(const float* const* grads, float* grad_shard, long S, int W, int rank, float scale,
                                        int accumulate, float* sumsq_partial, const unsigned* flags, unsigned epoch,

@@ -100,6 +100,12 @@ def all_reduce_sum(t: torch.Tensor, group=None) -> torch.Tensor:
     return t
 
 
+def all_reduce_min(t: torch.Tensor, group=None) -> torch.Tensor:
+    if is_dist():
+        dist.all_reduce(t, op=dist.ReduceOp.MIN, group=group)
+    return t
+
+
 def all_reduce_max(t: torch.Tensor, group=None) -> torch.Tensor:
     if is_dist():
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)

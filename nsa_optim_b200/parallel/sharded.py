@@ -33,6 +33,7 @@ Design here
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass, field
 from enum import Enum
 from typing import Any, Callable, Dict, Iterable, List, Optional, Tuple
@@ -246,6 +247,10 @@ class ShardedModel(nn.Module):
                 if self.rank == 0:
                     print(f"[nsa_optim_b200] peer-memory setup failed ({type(exc).__name__}: {exc}); using NCCL collectives")
                 self.comm_mode, self.arena = "torch", None
+            ok = torch.tensor([1.0 if self.arena is not None else 0.0], device=device)
+            pdist.all_reduce_min(ok, self.group)
+            if float(ok) == 0.0:                      # every rank takes the same path
+                self.comm_mode, self.arena = "torch", None
         if self.world > 1 and self.strategy == ShardingStrategy.FULL_SHARD:
             for u in self.units:
                 u.free_full()
@@ -318,7 +323,8 @@ class ShardedModel(nn.Module):
     def _fused_gather_now(self, unit: FlatUnit) -> None:
         from . import symm
         es = unit.shard.element_size()
-        symm.all_gather(self.arena, unit.off_shard, unit.shard_size * es, unit.full, unit.ch_shard, self.shard_epoch)
+        symm.all_gather(self.arena, unit.off_shard, unit.shard_size * es, unit.full, unit.ch_shard, self.shard_epoch,
+                        ctas_per_peer=max(4, 64 // self.world))
 
     def _fused_reduce(self, unit: FlatUnit) -> None:
         from . import symm
@@ -348,6 +354,10 @@ class ShardedModel(nn.Module):
         if comm in ("nccl", "gloo", "torch"):
             return "torch"
         if comm == "fused":
+            return "fused"
+        # auto: the peer-memory kernels wherever they can run (CUDA ranks of one node), else the library
+        dev = self.info.device
+        if dev.type == "cuda" and torch.cuda.device_count() >= self.world and os.environ.get("NSA_B200_COMM", "") != "nccl":
             return "fused"
         return "torch"
 

@@ -246,7 +246,14 @@ class Trainer:
         model, self.model_type, self.model_config = build_model(self.cfg, args, self.verbose)
         model.to(self.dtype)
         comm = args.comm
-        self.model = ShardedModel(model, self.info, strategy=args.sharding, param_dtype=self.dtype,
+        sharding = args.sharding
+        if sharding is None and self.info.world_size > 1:
+            # the reference's rule (train.py:188-196): whole-matrix preconditioners keep parameters
+            # gathered (SHARD_GRAD_OP), every other optimizer runs fully sharded
+            keep = self.cfg.optimizer_type in (OptimizerType.SOAP, OptimizerType.SOAP_4BIT, OptimizerType.SOAP_8BIT,
+                                               OptimizerType.SHAMPOO)
+            sharding = (ShardingStrategy.SHARD_GRAD_OP if keep else ShardingStrategy.FULL_SHARD).value
+        self.model = ShardedModel(model, self.info, strategy=sharding, param_dtype=self.dtype,
                                   activation_checkpointing=self.cfg.gradient_checkpointing, comm=comm,
                                   checkpoint_blocks=getattr(args, "checkpoint_blocks", None))
         self.n_params = sum(p.numel() for p in model.parameters())
