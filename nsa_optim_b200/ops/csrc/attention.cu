@@ -21,6 +21,8 @@
 // Key positions are affine in the key index (pos = idx * kp_stride + kp_off): identity for
 // ordinary attention, (stride, block-1) for compressed keys, which makes "causal on block
 // end" the same comparison as ordinary causality.
+#include <algorithm>
+
 #include "host.cuh"
 #include "tc5.cuh"
 
@@ -466,6 +468,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t cS = 0, cDP = 128, cDQ = 256, cDV = 384, cDK = 0;   // dK reuses the S columns
 
   const bool selected = p.tile_blocks != nullptr;
+  const bool with_dkv = p.dK != nullptr;          // null: dK / dV come from the key-stationary kernel
   const long tile_slot = (static_cast<long>(b) * p.Hkv + h) * gridDim.x + qt;
   const int* blocks = selected ? p.tile_blocks + tile_slot * p.max_u : nullptr;
   const unsigned long long* masks = selected ? p.tile_masks + tile_slot * p.max_u : nullptr;
@@ -560,14 +563,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       for (int kk = 0; kk < BN / 16; ++kk)      // dQ += dS K
         tc5::mma_ss(tmem + cDQ, tc5::desc_kmajor(dsb + (kk >> 2) * 2 * HALF + (kk & 3) * 32),
                     tc5::desc_mnmajor(k + kk * 2048, 2 * HALF), id_q, (j > 0 || kk > 0) ? 1u : 0u);
+      if (with_dkv) {
 #pragma unroll
-      for (int kk = 0; kk < BM / 16; ++kk)      // dV_tile = P^T dO
-        tc5::mma_ss(tmem + cDV, tc5::desc_mnmajor(pb + kk * 2048, 2 * HALF),
-                    tc5::desc_mnmajor(dob + kk * 2048, 2 * HALF), id_t, kk > 0 ? 1u : 0u);
+        for (int kk = 0; kk < BM / 16; ++kk)      // dV_tile = P^T dO
+          tc5::mma_ss(tmem + cDV, tc5::desc_mnmajor(pb + kk * 2048, 2 * HALF),
+                      tc5::desc_mnmajor(dob + kk * 2048, 2 * HALF), id_t, kk > 0 ? 1u : 0u);
 #pragma unroll
-      for (int kk = 0; kk < BM / 16; ++kk)      // dK_tile = dS^T Q
-        tc5::mma_ss(tmem + cDK, tc5::desc_mnmajor(dsb + kk * 2048, 2 * HALF),
-                    tc5::desc_mnmajor(q + kk * 2048, 2 * HALF), id_t, kk > 0 ? 1u : 0u);
+        for (int kk = 0; kk < BM / 16; ++kk)      // dK_tile = dS^T Q
+          tc5::mma_ss(tmem + cDK, tc5::desc_mnmajor(dsb + kk * 2048, 2 * HALF),
+                      tc5::desc_mnmajor(q + kk * 2048, 2 * HALF), id_t, kk > 0 ? 1u : 0u);
+      }
       tc5::mma_commit(m2);
     }
     // thread (r, ch) owns key row r of the tile, D-half ch
@@ -580,6 +585,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (!tc5::mbar_wait(m2, j & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) ok = false;
     if (__syncthreads_or(!ok)) { ok = false; break; }
     tc5::fence_after_sync();
+    if (with_dkv)
 #pragma unroll
     for (int q4 = 0; q4 < DH / 32; ++q4) {
       uint32_t a[32], c[32];
@@ -639,6 +645,313 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   tc5::fence_before_sync();
   __syncthreads();
   if (warp == 0) { tc5::fence_after_sync(); tc5::tmem_dealloc(tmem, 512); }
+}
+
+// --------------------------------------------------------------------------------------
+// Backward for dK / dV, key-block stationary.  A CTA owns one 64-key block of one KV head and
+// walks over "visits": query tiles of 128 rows (R tokens x G heads) that can see the block.
+//   contiguous modes: the visits are the query tiles of an analytic range (causality, window),
+//     split into chunks of `visits_per_cta` along grid.x;
+//   selected mode: the visits come from the inverse selection map: for every (batch, KV head,
+//     block) the ascending list of tokens that selected it, R tokens per visit, each token's
+//     G query rows fetched by its own TMA box.
+// dV^T (D x 64) += dO^T P and dK^T (D x 64) += Q^T dS stay in TMEM for the whole walk, so global
+// memory sees one fp32 reduction per CTA instead of one per (query tile, key tile) pair.
+// Roles: warps 0-7 softmax (thread (r, ch) = row r, 32 key columns), warp 8 TMA producer,
+// warp 9 MMA issuer.  Q/dO are double-buffered in shared memory and S/dP in TMEM: while the
+// softmax warps work on visit v the tensor pipe runs S/dP of visit v+1 and dV/dK of visit v-1.
+// Needs D = 128 (the accumulators put D on the 128 TMEM lanes).
+// --------------------------------------------------------------------------------------
+struct KvWalk {
+  int visits_per_cta;
+  const int* tok_list;      // selected mode: tokens grouped by (b, h, block), ascending inside a group
+  const int* list_start;    // [n_lists + 1]
+  const int* item_start;    // [n_lists + 1] exclusive prefix of CTAs per list
+  int n_lists, nS;
+};
+
+constexpr int KV_THREADS = 320;
+
+__global__ void __launch_bounds__(KV_THREADS, 1)
+attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+                   const __grid_constant__ CUtensorMap tm_q1, const __grid_constant__ CUtensorMap tm_do1,
+                   const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                   const AttnParams p, const KvWalk w, const float scale) {
+  constexpr int D = 128;
+  constexpr int QT = 4 * HALF;                   // one [128 rows][128] bf16 operand: two 64-column k-blocks
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;                            // [2 k-blocks][64 keys][64]
+  uint8_t* sV = sK + 2 * HALF;
+  uint8_t* sQ = sV + 2 * HALF;                   // [2 buffers][QT]
+  uint8_t* sDO = sQ + 2 * QT;
+  uint8_t* sP = sDO + 2 * QT;                    // [128 rows][64 keys]
+  uint8_t* sDS = sP + 2 * HALF;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + 2 * HALF);
+  uint64_t* kv_full = bars;
+  uint64_t* q_full = bars + 1;                   // [2] TMA -> MMA
+  uint64_t* q_empty = bars + 3;                  // [2] MMA -> TMA
+  uint64_t* s_full = bars + 5;                   // [2] MMA -> softmax
+  uint64_t* s_empty = bars + 7;                  // [2] softmax -> MMA
+  uint64_t* p_full = bars + 9;                   // softmax -> MMA
+  uint64_t* p_empty = bars + 10;                 // MMA -> softmax
+  uint64_t* acc_done = bars + 11;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool selected = w.tok_list != nullptr;
+  // ---- which block, which visits (uniform over the CTA; CTAs without work leave before any setup)
+  int b, h, s0, v0, n_vis, lst0 = 0, cnt = 0;
+  if (selected) {
+    const int item = blockIdx.x;
+    if (item >= w.item_start[w.n_lists]) return;
+    int lo = 0, hi = w.n_lists;                  // largest l with item_start[l] <= item
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (w.item_start[mid] <= item) lo = mid; else hi = mid;
+    }
+    const int l = lo;
+    const int bh = l / w.nS;
+    b = bh / p.Hkv; h = bh - b * p.Hkv;
+    s0 = (l - bh * w.nS) * 64;
+    lst0 = w.list_start[l];
+    cnt = w.list_start[l + 1] - lst0;
+    v0 = (item - w.item_start[l]) * w.visits_per_cta;
+    n_vis = min(w.visits_per_cta, (cnt + p.R - 1) / p.R - v0);
+  } else {
+    const int bh = blockIdx.z;
+    b = bh / p.Hkv; h = bh - b * p.Hkv;
+    s0 = blockIdx.y * 64;
+    const int s_hi = min(s0 + 63, p.S - 1);
+    const int n_qt = (p.T + p.R - 1) / p.R;
+    int qt_lo = 0, qt_hi = n_qt;
+    if (p.causal) qt_lo = max(0, (s0 * p.kp_stride + p.kp_off) / p.R);
+    if (p.window > 0) qt_hi = min(n_qt, (s_hi * p.kp_stride + p.kp_off + p.window - 1) / p.R + 1);
+    v0 = qt_lo + blockIdx.x * w.visits_per_cta;
+    n_vis = min(w.visits_per_cta, qt_hi - v0);
+  }
+  if (n_vis <= 0) return;
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    tc5::mbar_init(kv_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      tc5::mbar_init(q_full + i, 1);
+      tc5::mbar_init(q_empty + i, 1);
+      tc5::mbar_init(s_full + i, 1);
+      tc5::mbar_init(s_empty + i, 256);
+    }
+    tc5::mbar_init(p_full, 256);
+    tc5::mbar_init(p_empty, 1);
+    tc5::mbar_init(acc_done, 1);
+    tc5::fence_barrier_init();
+  }
+  if (warp == 9) { tc5::tmem_alloc(tmem_slot, 512); tc5::tmem_relinquish(); }
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  constexpr uint32_t cDV = 256, cDK = 320;       // S/dP of buffer i at columns i*128 + {0, 64}
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ TMA producer
+    bool ok = true;
+    if (lane == 0) {
+      tc5::mbar_expect_tx(kv_full, 4 * HALF);
+#pragma unroll
+      for (int kb = 0; kb < 2; ++kb) {
+        tc5::tma_load_4d(sK + kb * HALF, &tm_k, kv_full, kb * 64, h, s0, b);
+        tc5::tma_load_4d(sV + kb * HALF, &tm_v, kv_full, kb * 64, h, s0, b);
+      }
+    }
+    int issued = 0;
+    for (int v = 0; v < n_vis; ++v) {
+      const int buf = v & 1;
+      if (lane == 0) {
+        ok = tc5::mbar_wait(q_empty + buf, ((v >> 1) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_EMPTY);
+        if (ok) tc5::mbar_expect_tx(q_full + buf, 2 * QT);
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      uint8_t* dq_ = sQ + buf * QT;
+      uint8_t* dd_ = sDO + buf * QT;
+      if (!selected) {
+        if (lane == 0) {
+          const int q0 = (v0 + v) * p.R;
+#pragma unroll
+          for (int kb = 0; kb < 2; ++kb) {
+            tc5::tma_load_5d(dq_ + kb * 2 * HALF, &tm_q, q_full + buf, kb * 64, 0, h, q0, b);
+            tc5::tma_load_5d(dd_ + kb * 2 * HALF, &tm_do, q_full + buf, kb * 64, 0, h, q0, b);
+          }
+        }
+      } else {
+        for (int j = lane; j < p.R; j += 32) {
+          const int li = (v0 + v) * p.R + j;
+          const int tok = li < cnt ? w.tok_list[lst0 + li] : 0;     // rows past the list read token 0 and are masked
+          const int off = j * p.G * 128;
+#pragma unroll
+          for (int kb = 0; kb < 2; ++kb) {
+            tc5::tma_load_5d(dq_ + kb * 2 * HALF + off, &tm_q1, q_full + buf, kb * 64, 0, h, tok, b);
+            tc5::tma_load_5d(dd_ + kb * 2 * HALF + off, &tm_do1, q_full + buf, kb * 64, 0, h, tok, b);
+          }
+        }
+      }
+      __syncwarp();
+      issued = v + 1;
+    }
+    if (!ok && lane == 0) {
+      // let the copies already issued land before the CTA's shared memory is released
+      for (int j = max(0, issued - 2); j < issued; ++j) {
+        const long long t0 = clock64();
+        for (uint32_t i = 0; i < tc5::kMaxPolls; ++i) {
+          if (tc5::mbar_try_wait(q_full + (j & 1), (j >> 1) & 1)) break;
+          if ((i & 255u) == 255u && clock64() - t0 > tc5::kMaxWaitCycles) break;
+        }
+      }
+      const long long t0 = clock64();
+      for (uint32_t i = 0; i < tc5::kMaxPolls; ++i) {
+        if (tc5::mbar_try_wait(kv_full, 0)) break;
+        if ((i & 255u) == 255u && clock64() - t0 > tc5::kMaxWaitCycles) break;
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t id_s = tc5::make_idesc_bf16(128, 64, 0, 0);
+      constexpr uint32_t id_t = tc5::make_idesc_bf16(128, 64, 1, 1);
+      const uint32_t k = tc5::smem_u32(sK), vv = tc5::smem_u32(sV);
+      const uint32_t pb = tc5::smem_u32(sP), dsb = tc5::smem_u32(sDS);
+      bool ok = tc5::mbar_wait(kv_full, 0, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL);
+      for (int v = 0; v <= n_vis && ok; ++v) {
+        if (v < n_vis) {
+          const int buf = v & 1;
+          const uint32_t ph = (v >> 1) & 1;
+          if (!tc5::mbar_wait(q_full + buf, ph, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL)) { ok = false; break; }
+          if (!tc5::mbar_wait(s_empty + buf, ph ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+          tc5::fence_after_sync();
+          const uint32_t q = tc5::smem_u32(sQ + buf * QT), dob = tc5::smem_u32(sDO + buf * QT);
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t a_off = (kk >> 2) * 2 * HALF + (kk & 3) * 32, b_off = (kk >> 2) * HALF + (kk & 3) * 32;
+            tc5::mma_ss(tmem + buf * 128, tc5::desc_kmajor(q + a_off), tc5::desc_kmajor(k + b_off), id_s, kk > 0 ? 1u : 0u);
+          }
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t a_off = (kk >> 2) * 2 * HALF + (kk & 3) * 32, b_off = (kk >> 2) * HALF + (kk & 3) * 32;
+            tc5::mma_ss(tmem + buf * 128 + 64, tc5::desc_kmajor(dob + a_off), tc5::desc_kmajor(vv + b_off), id_s, kk > 0 ? 1u : 0u);
+          }
+          tc5::mma_commit(s_full + buf);
+        }
+        if (v >= 1) {
+          const int u = v - 1, buf = u & 1;
+          if (!tc5::mbar_wait(p_full, u & 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL)) { ok = false; break; }
+          tc5::fence_after_sync();
+          const uint32_t q = tc5::smem_u32(sQ + buf * QT), dob = tc5::smem_u32(sDO + buf * QT);
+#pragma unroll
+          for (int kk = 0; kk < BM / 16; ++kk)     // dV^T += dO^T P
+            tc5::mma_ss(tmem + cDV, tc5::desc_mnmajor(dob + kk * 2048, 2 * HALF), tc5::desc_mnmajor(pb + kk * 2048, 2 * HALF),
+                        id_t, (u > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+          for (int kk = 0; kk < BM / 16; ++kk)     // dK^T += Q^T dS
+            tc5::mma_ss(tmem + cDK, tc5::desc_mnmajor(q + kk * 2048, 2 * HALF), tc5::desc_mnmajor(dsb + kk * 2048, 2 * HALF),
+                        id_t, (u > 0 || kk > 0) ? 1u : 0u);
+          tc5::mma_commit(q_empty + buf);
+          tc5::mma_commit(p_empty);
+        }
+      }
+      if (ok) tc5::mma_commit(acc_done);
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax warps
+    const int r = tid & 127, ch = tid >> 7;
+    const int tok_local = r / p.G, g = r % p.G;
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const float sc = p.scale_log2;
+    const int sb = s0 + ch * 32;                   // this thread's first key
+    bool ok = true;
+    for (int v = 0; v < n_vis; ++v) {
+      const int buf = v & 1;
+      int t;
+      if (selected) {
+        const int li = (v0 + v) * p.R + tok_local;
+        t = li < cnt ? w.tok_list[lst0 + li] : -1;
+      } else {
+        t = (v0 + v) * p.R + tok_local;
+        if (t >= p.T) t = -1;
+      }
+      float Lrow = 0.f, drow = 0.f;
+      if (t >= 0) {
+        const long rowi = (static_cast<long>(b) * p.T + t) * p.Hq + h * p.G + g;
+        Lrow = p.L[rowi];
+        drow = p.delta[rowi];
+      }
+      if (!__all_sync(0xffffffffu, tc5::mbar_wait(s_full + buf, (v >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL))) {
+        ok = false;
+        break;
+      }
+      tc5::fence_after_sync();
+      uint32_t sv[32], dv[32], pp[16], ds[16];
+      tc5::tmem_ld_x32(tmem + lane_off + buf * 128 + ch * 32, sv);
+      tc5::tmem_ld_x32(tmem + lane_off + buf * 128 + 64 + ch * 32, dv);
+      tc5::tmem_ld_wait();
+      tc5::fence_before_sync();
+      tc5::mbar_arrive(s_empty + buf);
+      if (t < 0) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { pp[i] = 0u; ds[i] = 0u; }
+      } else {
+        bool check = sb + 31 >= p.S;
+        if (p.causal) check = check || ((sb + 31) * p.kp_stride + p.kp_off > t);
+        if (p.window > 0) check = check || (sb * p.kp_stride + p.kp_off <= t - p.window);
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const bool v0_ = !check || key_visible(p, sb + i, t);
+          const bool v1_ = !check || key_visible(p, sb + i + 1, t);
+          const float p0 = v0_ ? exp2f(fmaf(__uint_as_float(sv[i]), sc, -Lrow)) : 0.f;
+          const float p1 = v1_ ? exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -Lrow)) : 0.f;
+          pp[i / 2] = tc5::pack_bf16(p0, p1);
+          ds[i / 2] = tc5::pack_bf16(p0 * (__uint_as_float(dv[i]) - drow) * scale,
+                                     p1 * (__uint_as_float(dv[i + 1]) - drow) * scale);
+        }
+      }
+      if (!__all_sync(0xffffffffu, tc5::mbar_wait(p_empty, (v & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_EMPTY))) {
+        ok = false;
+        break;
+      }
+      {
+        uint8_t* rp = sP + r * 128;
+        uint8_t* rd = sDS + r * 128;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int c = ((ch * 4 + j) ^ (r & 7)) << 4;
+          *reinterpret_cast<uint4*>(rp + c) = make_uint4(pp[4 * j], pp[4 * j + 1], pp[4 * j + 2], pp[4 * j + 3]);
+          *reinterpret_cast<uint4*>(rd + c) = make_uint4(ds[4 * j], ds[4 * j + 1], ds[4 * j + 2], ds[4 * j + 3]);
+        }
+      }
+      tc5::fence_proxy_async();
+      tc5::mbar_arrive(p_full);
+    }
+    // ---- accumulators -> global: lane = d, columns = keys; one fp32 reduction per element
+    if (__all_sync(0xffffffffu, ok && tc5::mbar_wait(acc_done, 0, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL))) {
+      tc5::fence_after_sync();
+      const int d = (warp & 3) * 32 + lane;
+      float* dst = (warp < 4 ? p.dV : p.dK) + ((static_cast<long>(b) * p.S + s0) * p.Hkv + h) * D + d;
+      const uint32_t col = warp < 4 ? cDV : cDK;
+#pragma unroll
+      for (int c0 = 0; c0 < 64; c0 += 32) {
+        uint32_t a[32];
+        tc5::tmem_ld_x32(tmem + lane_off + col + c0, a);
+        tc5::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (s0 + c0 + i < p.S) atomicAdd(dst + static_cast<long>(c0 + i) * p.Hkv * D, __uint_as_float(a[i]));
+      }
+    }
+  }
+  tc5::fence_before_sync();
+  __syncthreads();
+  if (warp == 9) { tc5::fence_after_sync(); tc5::tmem_dealloc(tmem, 512); }
 }
 
 // --------------------------------------------------------------------------------------
@@ -717,8 +1030,9 @@ __global__ void __launch_bounds__(128) nsa_union_kernel(const int* __restrict__ 
   }
 }
 
-int make_q_map(CUtensorMap* m, const void* base, int B, int T, int Hq, int Hkv, int D) {
-  const int G = Hq / Hkv, R = BM / G;
+// box_tokens 0: a whole query tile (128 / G tokens); otherwise that many tokens per box
+int make_q_map(CUtensorMap* m, const void* base, int B, int T, int Hq, int Hkv, int D, int box_tokens = 0) {
+  const int G = Hq / Hkv, R = box_tokens > 0 ? box_tokens : BM / G;
   uint64_t dims[5] = {(uint64_t)D, (uint64_t)G, (uint64_t)Hkv, (uint64_t)T, (uint64_t)B};
   uint64_t strides[4] = {(uint64_t)D * 2, (uint64_t)G * D * 2, (uint64_t)Hq * D * 2, (uint64_t)T * Hq * D * 2};
   uint32_t box[5] = {64, (uint32_t)G, 1, (uint32_t)R, 1};
@@ -849,6 +1163,69 @@ extern "C" int nsa_attn_bwd(const void* q, const void* k, const void* v, const v
   nsa::count_launch(2);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : nsa::fail_cuda(e, "nsa_attn_bwd launch");
+}
+
+// Backward in two kernels without per-tile global reductions: dQ from the query-tile-outer
+// kernel (its dK / dV part switched off) and dK / dV from the key-block-stationary kernel.
+// Selected mode additionally takes the inverse selection map: tok_list (tokens grouped by
+// (b, h, block), ascending), list_start / item_start ([B*Hkv*nS + 1] exclusive prefixes of list
+// lengths and of CTAs per list, a CTA covering visits_per_cta * (128 / G) tokens) and
+// item_bound >= item_start[last].  head_dim 128 only; selected mode needs G >= 8.
+extern "C" int nsa_attn_bwd_split(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                                  const float* L, float* delta, void* dq, float* dk, float* dv, int B, int T, int S,
+                                  int Hq, int Hkv, int D, float scale, int causal, int window, int kp_stride, int kp_off,
+                                  const int* tile_blocks, const unsigned long long* tile_masks, const int* tile_counts,
+                                  int max_u, const int* tok_list, const int* list_start, const int* item_start, int nS,
+                                  int item_bound, int visits_per_cta, cudaStream_t st) {
+  int rc = check_shape(Hq, Hkv, D, tile_blocks);
+  if (rc) return rc;
+  const int G = Hq / Hkv;
+  if (D != 128) return nsa::fail(NSA_ERR_SHAPE, "attn_bwd_split: head_dim must be 128");
+  if (tile_blocks && (G < 8 || tok_list == nullptr))
+    return nsa::fail(NSA_ERR_SHAPE, "attn_bwd_split: selected mode needs a GQA group of at least 8 and the inverse map");
+  if (visits_per_cta <= 0) return nsa::fail(NSA_ERR_SHAPE, "attn_bwd_split: visits_per_cta must be positive");
+  CUtensorMap tq, tdo, tq1, tdo1, tk, tv;
+  if ((rc = make_q_map(&tq, q, B, T, Hq, Hkv, D))) return rc;
+  if ((rc = make_q_map(&tdo, d_o, B, T, Hq, Hkv, D))) return rc;
+  if ((rc = make_q_map(&tq1, q, B, T, Hq, Hkv, D, 1))) return rc;
+  if ((rc = make_q_map(&tdo1, d_o, B, T, Hq, Hkv, D, 1))) return rc;
+  if ((rc = make_kv_map(&tk, k, B, S, Hkv, D))) return rc;
+  if ((rc = make_kv_map(&tv, v, B, S, Hkv, D))) return rc;
+  const long rows = static_cast<long>(B) * T * Hq;
+  attn_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const bf16*)o, (const bf16*)d_o, delta, rows, D);
+  AttnParams p;
+  fill_params(p, B, T, S, Hq, Hkv, D, scale, causal, window, kp_stride, kp_off, tile_blocks, tile_masks, tile_counts, max_u);
+  p.L = const_cast<float*>(L); p.delta = delta; p.dQb = (bf16*)dq; p.dK = nullptr; p.dV = nullptr;
+  {
+    const dim3 grid((T + p.R - 1) / p.R, Hkv, B);
+    const int smem = (D / 64) * 2 * HALF * 4 + 8 * HALF + 1024 + 256;
+    static bool cfg = false;
+    if (!cfg) { if ((rc = set_smem(attn_bwd_kernel<128>, smem))) return rc; cfg = true; }
+    attn_bwd_kernel<128><<<grid, 256, smem, st>>>(tq, tdo, tk, tv, p, scale);
+  }
+  p.dK = dk; p.dV = dv;
+  KvWalk w{};
+  w.visits_per_cta = visits_per_cta;
+  dim3 grid;
+  if (tile_blocks) {
+    w.tok_list = tok_list; w.list_start = list_start; w.item_start = item_start; w.n_lists = B * Hkv * nS; w.nS = nS;
+    if (item_bound <= 0) return nsa::fail(NSA_ERR_SHAPE, "attn_bwd_split: item_bound must be positive");
+    grid = dim3(item_bound, 1, 1);
+  } else {
+    const int n_qt = (T + p.R - 1) / p.R;
+    int max_vis = n_qt;
+    if (window > 0) max_vis = std::min(n_qt, (63 * kp_stride + window - 1) / p.R + 2);
+    grid = dim3((max_vis + visits_per_cta - 1) / visits_per_cta, (S + 63) / 64, B * Hkv);
+  }
+  {
+    const int smem = 24 * HALF + 1024 + 256;
+    static bool cfg = false;
+    if (!cfg) { if ((rc = set_smem(attn_bwd_kv_kernel, smem))) return rc; cfg = true; }
+    attn_bwd_kv_kernel<<<grid, KV_THREADS, smem, st>>>(tq, tdo, tq1, tdo1, tk, tv, p, w, scale);
+  }
+  nsa::count_launch(3);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : nsa::fail_cuda(e, "nsa_attn_bwd_split launch");
 }
 
 // idx [B, Hkv, T, top_n] int32 -> per query tile (R = 128 / G tokens): block list, token masks, count.

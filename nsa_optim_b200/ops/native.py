@@ -619,7 +619,7 @@ class _Attn(torch.autograd.Function):
         S, Hkv = k.shape[1], k.shape[2]
         o = torch.empty_like(q)
         L = torch.empty(B, T, Hq, dtype=torch.float32, device=q.device)
-        tb, tm, tc, mu = tiles if tiles is not None else (None, None, None, 0)
+        tb, tm, tc, mu = tiles[:4] if tiles is not None else (None, None, None, 0)
         _check(load().nsa_attn_fwd(_p(q), _p(k), _p(v), _p(o), _p(L), c_int(B), c_int(T), c_int(S), c_int(Hq),
                                    c_int(Hkv), c_int(D), c_float(scale), c_int(int(causal)), c_int(window),
                                    c_int(kp_stride), c_int(kp_off), _p(tb), _p(tm), _p(tc), c_int(mu), _stream()))
@@ -640,11 +640,28 @@ class _Attn(torch.autograd.Function):
         dk = torch.zeros(k.shape, dtype=torch.float32, device=q.device)
         dv = torch.zeros(v.shape, dtype=torch.float32, device=q.device)
         delta = torch.empty(B, T, Hq, dtype=torch.float32, device=q.device)
-        tb, tm, tc, mu = ctx.tiles if ctx.tiles is not None else (None, None, None, 0)
-        _check(load().nsa_attn_bwd(_p(q), _p(k), _p(v), _p(o), _p(do), _p(L), _p(delta), _p(dq), _p(dk), _p(dv),
-                                   c_int(B), c_int(T), c_int(S), c_int(Hq), c_int(Hkv), c_int(D), c_float(scale),
-                                   c_int(int(causal)), c_int(window), c_int(kp_stride), c_int(kp_off),
-                                   _p(tb), _p(tm), _p(tc), c_int(mu), _stream()))
+        tb, tm, tc, mu = ctx.tiles[:4] if ctx.tiles is not None else (None, None, None, 0)
+        G = Hq // Hkv
+        split = D == 128 and os.environ.get("NSA_B200_ATTN_BWD", "split") == "split" and (ctx.tiles is None or G >= 8)
+        if split:
+            # dQ from the query-tile-outer kernel, dK / dV from the key-block-stationary kernel
+            R = 128 // G
+            inv = (None, None, None, 0, 0)
+            visits = 128
+            if ctx.tiles is not None:
+                idx, nS = ctx.tiles[4], ctx.tiles[5]
+                visits = 64
+                inv = inverse_blocks(idx, nS, R, visits)
+            _check(load().nsa_attn_bwd_split(_p(q), _p(k), _p(v), _p(o), _p(do), _p(L), _p(delta), _p(dq), _p(dk), _p(dv),
+                                             c_int(B), c_int(T), c_int(S), c_int(Hq), c_int(Hkv), c_int(D), c_float(scale),
+                                             c_int(int(causal)), c_int(window), c_int(kp_stride), c_int(kp_off),
+                                             _p(tb), _p(tm), _p(tc), c_int(mu), _p(inv[0]), _p(inv[1]), _p(inv[2]),
+                                             c_int(inv[3]), c_int(inv[4]), c_int(visits), _stream()))
+        else:
+            _check(load().nsa_attn_bwd(_p(q), _p(k), _p(v), _p(o), _p(do), _p(L), _p(delta), _p(dq), _p(dk), _p(dv),
+                                       c_int(B), c_int(T), c_int(S), c_int(Hq), c_int(Hkv), c_int(D), c_float(scale),
+                                       c_int(int(causal)), c_int(window), c_int(kp_stride), c_int(kp_off),
+                                       _p(tb), _p(tm), _p(tc), c_int(mu), _stream()))
         return dq, dk.to(k.dtype), dv.to(v.dtype), None, None, None, None, None, None
 
 
@@ -677,13 +694,40 @@ def union_blocks(idx: Tensor, G: int, nS: int):
     return tb, tm, tc, max_u
 
 
+def inverse_blocks(idx: Tensor, nS: int, R: int, visits_per_cta: int):
+    """Inverse of the selection map.  idx (B, Hkv, T, top_n) -> (tok_list, list_start, item_start,
+    nS, item_bound): for every (b, h, block) the ascending tokens that selected the block, laid out
+    back to back; ``list_start`` / ``item_start`` are the exclusive prefixes of the list lengths and
+    of the CTAs per list (a CTA covers ``visits_per_cta`` groups of R tokens); ``item_bound`` is a
+    host-side upper bound of the CTA count, so nothing here waits for the device.  Entries that are
+    negative, out of range or repeated inside a token's list are dropped."""
+    B, Hkv, T, n = idx.shape
+    dev = idx.device
+    lists = B * Hkv * nS
+    s, _ = idx.sort(dim=-1)
+    ok = (s >= 0) & (s < nS)
+    ok[..., 1:] &= s[..., 1:] != s[..., :-1]
+    bh = torch.arange(B * Hkv, device=dev, dtype=torch.int64).view(B, Hkv, 1, 1)
+    key = torch.where(ok, bh * nS + s.to(torch.int64), torch.full((), lists, device=dev, dtype=torch.int64)).reshape(-1)
+    skey, order = key.sort(stable=True)                       # (b, h, t) order survives inside a list
+    tok = ((order // n) % T).to(torch.int32)
+    list_start = torch.searchsorted(skey, torch.arange(lists + 1, device=dev, dtype=torch.int64)).to(torch.int32)
+    cnt = list_start[1:] - list_start[:-1]
+    items = (-(-cnt // R) + visits_per_cta - 1) // visits_per_cta
+    item_start = torch.zeros(lists + 1, dtype=torch.int32, device=dev)
+    item_start[1:] = items.cumsum(0)
+    bound = (B * Hkv * T * n) // (R * visits_per_cta) + lists
+    return tok, list_start, item_start, nS, bound
+
+
 def selected_attention(q, k, v, idx, scale=None):
     """Causal attention of each query token over its own list of 64-key blocks ``idx``
     (B, Hkv, T, top_n)."""
     scale = q.shape[-1] ** -0.5 if scale is None else scale
     G = q.shape[2] // k.shape[2]
     nS = -(-k.shape[1] // 64)
-    tiles = union_blocks(idx.to(torch.int32).contiguous(), G, nS)
+    idx = idx.to(torch.int32).contiguous()
+    tiles = union_blocks(idx, G, nS) + (idx, nS)
     return _Attn.apply(q, k, v, True, 0, float(scale), 1, 0, tiles)[0]
 
 
@@ -731,7 +775,7 @@ def nsa_attention(q, k, v, g_cmp, g_slc, g_swa, cmp_block=32, cmp_stride=16, sel
         imp = nsa_importance(q, kc, L_cmp, nS, cmp_stride, cmp_block, float(scale))
         idx = nsa_select(imp, sel_block, top_n)
         del imp
-        tiles = union_blocks(idx, G, nS)
+        tiles = union_blocks(idx, G, nS) + (idx, nS)
     o_slc = _Attn.apply(q, k, v, True, 0, float(scale), 1, 0, tiles)[0]
     o_swa = _Attn.apply(q, k, v, True, int(window), float(scale), 1, 0, None)[0]
     return g_cmp.unsqueeze(-1) * o_cmp + g_slc.unsqueeze(-1) * o_slc + g_swa.unsqueeze(-1) * o_swa

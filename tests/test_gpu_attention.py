@@ -111,3 +111,11 @@ def test_full_nsa_close_to_streaming_reference(native):
     # selection may differ on near-ties; require agreement on the bulk of the rows
     err = (o.float() - ref).abs().amax(dim=(-1, -2))
     assert (err < 0.05).float().mean() > 0.9, err.mean().item()
+
+
+def test_backward_atomic_path_still_matches(native, monkeypatch):
+    """head_dim 128 normally takes the split backward (dQ kernel + key-stationary dK/dV kernel);
+    the single-kernel backward with per-tile reductions stays as the fallback for other shapes."""
+    monkeypatch.setenv("NSA_B200_ATTN_BWD", "atomic")
+    run_pair(lambda q, k, v: native.attention(q, k, v, True, 0),
+             lambda q, k, v: oracle.attention(q, k, v, True, 0), mk(1, 500, 8, 1, 128))
