@@ -164,6 +164,12 @@ def mamba3_scan(x: Tensor, dt: Tensor, A: Tensor, Bc: Tensor, Cc: Tensor, D: Ten
     Bsz, L, DI = x.shape
     H = dt.shape[2]
     P = DI // H
+    needs_grad = torch.is_grad_enabled() and any(t.requires_grad for t in (x, dt, A, Bc, Cc, D))
+    if x.is_cuda and not needs_grad and ops.get_backend() != "torch" and A.shape[1] <= 256:
+        # forward-only CUDA scan, like the reference's kernel; training goes through the loop below
+        xs = x.view(Bsz, L, H, P)
+        gate = ops.native_module().mamba3_gate(xs.float().sum(-1), dt, A, Bc, Cc, D)
+        return (xs.float() * gate[..., None]).reshape(Bsz, L, DI).to(x.dtype)
     Ac = torch.view_as_complex(A.float().contiguous())
     Bz = torch.view_as_complex(Bc.float().contiguous())
     Cz = torch.view_as_complex(Cc.float().contiguous())

@@ -892,6 +892,20 @@ class _SSD(torch.autograd.Function):
         return (dx, ddt, dA, dB.view(Bsz, T, 1, N).to(torch.bfloat16), dC.view(Bsz, T, 1, N).to(torch.bfloat16), dD)
 
 
+def mamba3_gate(u: Tensor, dt: Tensor, A: Tensor, Bc: Tensor, Cc: Tensor, D: Tensor) -> Tensor:
+    """Forward-only sequential scan of the complex-state SSM (``csrc/mamba3.cu``).
+    u, dt (B, L, H) ; A (H, N, 2) ; Bc, Cc (B, L, H, N, 2) ; D (H)  ->  gate (B, L, H) fp32 with
+    gate_t = Re<C_t, h_t> + D; the block output is x_t * gate_t."""
+    B, L, H = u.shape
+    N = A.shape[1]
+    f = lambda t: t.detach().float().contiguous()
+    u, dt, A, Bc, Cc, D = f(u), f(dt), f(A), f(Bc), f(Cc), f(D)
+    gate = torch.empty(B, L, H, dtype=torch.float32, device=u.device)
+    _check(load().nsa_mamba3_scan(_p(u), _p(dt), _p(A), _p(Bc), _p(Cc), _p(D), _p(gate), c_int(B), c_int(L), c_int(H),
+                                  c_int(N), _stream()))
+    return gate
+
+
 def ssd_scan(x, dt, A, Bm, Cm, D=None, chunk=256):
     """Mamba-2 SSD.  The shapes of the hybrid models (d_state 128, headdim 64, one group) run on
     the fused tcgen05 chunk kernels; other shapes use batched matmuls plus the native

@@ -37,3 +37,21 @@ def test_ssd_forward_backward(native, T, chunk, P, N):
     close(y, y_ref, "y")
     for name, a, b in zip(("dx", "ddt", "dA", "dB", "dC", "dD"), leaves, refs):
         close(a.grad, b.grad, name)
+
+
+def test_mamba3_forward_scan_matches_loop(native):
+    """The forward-only CUDA scan of the complex-state block against the sequential torch loop."""
+    from nsa_optim_b200 import ops
+    from nsa_optim_b200.models.mamba import mamba3_scan
+    torch.manual_seed(0)
+    B, L, H, P, N = 2, 300, 3, 16, 40
+    x = torch.randn(B, L, H * P, device="cuda")
+    dt = torch.rand(B, L, H, device="cuda") * 0.1 + 0.001
+    A = torch.stack([-torch.rand(H, N, device="cuda"), torch.randn(H, N, device="cuda") * 0.1], -1)
+    Bc, Cc = torch.randn(B, L, H, N, 2, device="cuda"), torch.randn(B, L, H, N, 2, device="cuda")
+    D = torch.randn(H, device="cuda")
+    with torch.no_grad():
+        got = mamba3_scan(x, dt, A, Bc, Cc, D)
+        with ops.backend("torch"):
+            want = mamba3_scan(x, dt, A, Bc, Cc, D)
+    assert torch.allclose(got, want, rtol=1e-3, atol=1e-3 * want.abs().max().item())
