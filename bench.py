@@ -129,8 +129,9 @@ def main() -> None:
     ap.add_argument("--seq_len", type=int, default=65536)
     ap.add_argument("--comm", type=str, default="auto")
     ap.add_argument("--skip_e2e", action="store_true")
-    ap.add_argument("--checkpoint_blocks", type=str, default="M",
-                    help="block kinds whose activations are recomputed in backward ('MDA' = all, '' = none)")
+    ap.add_argument("--checkpoint_blocks", type=str, default="auto",
+                    help="block kinds whose activations are recomputed in backward ('MDA' = all, '' = none, "
+                         "'auto' = none on a GPU with at least 170 GB, else the Mamba blocks)")
     a = ap.parse_args()
     if a.impl == "reference":
         reference_arm(a)
@@ -147,6 +148,10 @@ def main() -> None:
     world = int(os.environ.get("WORLD_SIZE", 1))
     if world != a.gpus:
         raise SystemExit(f"--gpus {a.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    if a.checkpoint_blocks == "auto":
+        # the 64K step keeps about 136 GB of activations alive when nothing is recomputed
+        big = torch.cuda.is_available() and torch.cuda.get_device_properties(0).total_memory >= 170e9
+        a.checkpoint_blocks = "" if (big and a.seq_len <= 65536) else "M"
     extra = ["--comm", a.comm]
     if a.checkpoint_blocks:
         extra += ["--checkpoint_blocks", a.checkpoint_blocks]
@@ -230,7 +235,8 @@ def main() -> None:
                        "optimizer": "adamw8bit (block 256, dynamic-tree code book)", "grad_clip": 1.0,
                        "activation_checkpointing": (f"block kinds {a.checkpoint_blocks} recomputed, others keep activations"
                                                     if a.checkpoint_blocks else "off"),
-                       "peak_memory_gb": round(torch.cuda.max_memory_allocated(dev) / 2**30, 2), "parallelism": f"dp{world} sharded ({tr.model.strategy.value})",
+                       "peak_memory_gb": round(torch.cuda.max_memory_allocated(dev) / 2**30, 2),
+                       "peak_reserved_gb": round(torch.cuda.max_memory_reserved(dev) / 2**30, 2), "parallelism": f"dp{world} sharded ({tr.model.strategy.value})",
                        "comm": tr.model.comm_mode,
                        "l2": "no explicit flush: per-step working set (2.4 GB weights + >4 GB activations) exceeds the 126 MB L2",
                        "baseline_note": "vs_baseline divides by the reference's only published number (11589 tok/s, 0.5B MDMA, "
