@@ -648,6 +648,263 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 }
 
 // --------------------------------------------------------------------------------------
+// Backward for dQ, query-tile stationary, pipelined.  Same roles as the dK/dV kernel below:
+// warps 0-7 turn S and dP into dS, warp 8 streams 64-key K/V blocks through a 4-stage ring,
+// warp 9 issues S = Q K^T, dP = dO V^T (double-buffered in TMEM) and dQ += dS K (resident in
+// TMEM).  Visits are 64-key blocks: the contiguous range allowed by causality / window, or the
+// entries of the tile's union list (selected mode, with the per-token bit masks).
+// Needs D = 128.
+// --------------------------------------------------------------------------------------
+constexpr int DQ_STAGES = 4;
+
+__global__ void __launch_bounds__(320, 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+                   const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                   const AttnParams p, const float scale) {
+  constexpr int D = 128;
+  constexpr int QT = 4 * HALF;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sDO = sQ + QT;
+  uint8_t* sKV = sDO + QT;                       // [stages][K: 2 k-blocks of [64][64] | V: same]
+  uint8_t* sDS = sKV + DQ_STAGES * 4 * HALF;     // [128 rows][64 keys]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + 2 * HALF);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;                  // [stages] TMA -> MMA
+  uint64_t* kv_empty = kv_full + DQ_STAGES;      // [stages] MMA -> TMA
+  uint64_t* s_full = kv_empty + DQ_STAGES;       // [2] MMA -> softmax
+  uint64_t* s_empty = s_full + 2;                // [2] softmax -> MMA
+  uint64_t* ds_full = s_empty + 2;               // softmax -> MMA
+  uint64_t* ds_empty = ds_full + 1;              // MMA -> softmax
+  uint64_t* acc_done = ds_empty + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int qt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int q0 = qt * p.R;
+  const int t_hi = min(q0 + p.R, p.T) - 1;
+  const bool selected = p.tile_blocks != nullptr;
+  const long tile_slot = (static_cast<long>(b) * p.Hkv + h) * gridDim.x + qt;
+  const int* blocks = selected ? p.tile_blocks + tile_slot * p.max_u : nullptr;
+  const unsigned long long* masks = selected ? p.tile_masks + tile_slot * p.max_u : nullptr;
+  int kb0 = 0, n_vis;
+  if (selected) {
+    n_vis = min(p.tile_counts[tile_slot], p.max_u);
+  } else {
+    long last = p.S - 1;
+    if (p.causal) {
+      long lim = static_cast<long>(t_hi) - p.kp_off;
+      lim = lim < 0 ? -1 : lim / p.kp_stride;
+      last = lim < last ? lim : last;
+    }
+    long first = 0;
+    if (p.window > 0) {
+      const long lo = static_cast<long>(q0) - p.window + 1 - p.kp_off;
+      first = lo <= 0 ? 0 : (lo + p.kp_stride - 1) / p.kp_stride;
+    }
+    kb0 = static_cast<int>(first / 64);
+    n_vis = last < first ? 0 : static_cast<int>(last / 64) + 1 - kb0;
+  }
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    tc5::mbar_init(q_full, 1);
+    for (int i = 0; i < DQ_STAGES; ++i) { tc5::mbar_init(kv_full + i, 1); tc5::mbar_init(kv_empty + i, 1); }
+    for (int i = 0; i < 2; ++i) { tc5::mbar_init(s_full + i, 1); tc5::mbar_init(s_empty + i, 256); }
+    tc5::mbar_init(ds_full, 256);
+    tc5::mbar_init(ds_empty, 1);
+    tc5::mbar_init(acc_done, 1);
+    tc5::fence_barrier_init();
+  }
+  if (warp == 9) { tc5::tmem_alloc(tmem_slot, 512); tc5::tmem_relinquish(); }
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  constexpr uint32_t cDQ = 256;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0 && n_vis > 0) {
+      tc5::mbar_expect_tx(q_full, 2 * QT);
+#pragma unroll
+      for (int kb = 0; kb < 2; ++kb) {
+        tc5::tma_load_5d(sQ + kb * 2 * HALF, &tm_q, q_full, kb * 64, 0, h, q0, b);
+        tc5::tma_load_5d(sDO + kb * 2 * HALF, &tm_do, q_full, kb * 64, 0, h, q0, b);
+      }
+      bool ok = true;
+      int issued = 0;
+      for (int v = 0; v < n_vis; ++v) {
+        const int st = v % DQ_STAGES;
+        if (!tc5::mbar_wait(kv_empty + st, ((v / DQ_STAGES) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_EMPTY)) { ok = false; break; }
+        int s0;
+        if (!selected) s0 = (kb0 + v) * 64;
+        else { const int blk = blocks[v]; s0 = blk < 0 ? 0 : blk * 64; }
+        uint8_t* kd = sKV + st * 4 * HALF;
+        tc5::mbar_expect_tx(kv_full + st, 4 * HALF);
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb) {
+          tc5::tma_load_4d(kd + kb * HALF, &tm_k, kv_full + st, kb * 64, h, s0, b);
+          tc5::tma_load_4d(kd + 2 * HALF + kb * HALF, &tm_v, kv_full + st, kb * 64, h, s0, b);
+        }
+        issued = v + 1;
+      }
+      if (!ok) {
+        // let the copies already issued land before the CTA's shared memory is released
+        for (int j = max(0, issued - DQ_STAGES); j < issued; ++j) {
+          const long long t0 = clock64();
+          for (uint32_t i = 0; i < tc5::kMaxPolls; ++i) {
+            if (tc5::mbar_try_wait(kv_full + (j % DQ_STAGES), (j / DQ_STAGES) & 1)) break;
+            if ((i & 255u) == 255u && clock64() - t0 > tc5::kMaxWaitCycles) break;
+          }
+        }
+        const long long t0 = clock64();
+        for (uint32_t i = 0; i < tc5::kMaxPolls; ++i) {
+          if (tc5::mbar_try_wait(q_full, 0)) break;
+          if ((i & 255u) == 255u && clock64() - t0 > tc5::kMaxWaitCycles) break;
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && n_vis > 0) {
+      constexpr uint32_t id_s = tc5::make_idesc_bf16(128, 64, 0, 0);
+      constexpr uint32_t id_q = tc5::make_idesc_bf16(128, D, 0, 1);
+      const uint32_t q = tc5::smem_u32(sQ), dob = tc5::smem_u32(sDO), dsb = tc5::smem_u32(sDS);
+      bool ok = tc5::mbar_wait(q_full, 0, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL);
+      for (int v = 0; v <= n_vis && ok; ++v) {
+        if (v < n_vis) {
+          const int st = v % DQ_STAGES, buf = v & 1;
+          if (!tc5::mbar_wait(kv_full + st, (v / DQ_STAGES) & 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL)) { ok = false; break; }
+          if (!tc5::mbar_wait(s_empty + buf, ((v >> 1) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+          tc5::fence_after_sync();
+          const uint32_t k = tc5::smem_u32(sKV + st * 4 * HALF), vv = k + 2 * HALF;
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t a_off = (kk >> 2) * 2 * HALF + (kk & 3) * 32, b_off = (kk >> 2) * HALF + (kk & 3) * 32;
+            tc5::mma_ss(tmem + buf * 128, tc5::desc_kmajor(q + a_off), tc5::desc_kmajor(k + b_off), id_s, kk > 0 ? 1u : 0u);
+          }
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t a_off = (kk >> 2) * 2 * HALF + (kk & 3) * 32, b_off = (kk >> 2) * HALF + (kk & 3) * 32;
+            tc5::mma_ss(tmem + buf * 128 + 64, tc5::desc_kmajor(dob + a_off), tc5::desc_kmajor(vv + b_off), id_s, kk > 0 ? 1u : 0u);
+          }
+          tc5::mma_commit(s_full + buf);
+        }
+        if (v >= 1) {
+          const int u = v - 1, st = u % DQ_STAGES;
+          if (!tc5::mbar_wait(ds_full, u & 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL)) { ok = false; break; }
+          tc5::fence_after_sync();
+          const uint32_t k = tc5::smem_u32(sKV + st * 4 * HALF);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)          // dQ += dS K  (64 keys per visit)
+            tc5::mma_ss(tmem + cDQ, tc5::desc_kmajor(dsb + kk * 32), tc5::desc_mnmajor(k + kk * 2048, HALF), id_q,
+                        (u > 0 || kk > 0) ? 1u : 0u);
+          tc5::mma_commit(kv_empty + st);
+          tc5::mma_commit(ds_empty);
+        }
+      }
+      if (ok) tc5::mma_commit(acc_done);
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax warps
+    const int r = tid & 127, ch = tid >> 7;
+    const int tok_local = r / p.G, g = r % p.G;
+    const int t = q0 + tok_local;
+    const bool row_ok = t < p.T;
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const long rowi = (static_cast<long>(b) * p.T + (row_ok ? t : 0)) * p.Hq + h * p.G + g;
+    const float Lrow = row_ok ? p.L[rowi] : 0.f;
+    const float drow = row_ok ? p.delta[rowi] : 0.f;
+    const float sc = p.scale_log2;
+    bool ok = true;
+    for (int v = 0; v < n_vis; ++v) {
+      const int buf = v & 1;
+      int sb;
+      bool row_sel = row_ok;
+      if (!selected) sb = (kb0 + v) * 64 + ch * 32;
+      else {
+        const int blk = blocks[v];
+        sb = blk < 0 ? -1 : blk * 64 + ch * 32;
+        row_sel = row_ok && blk >= 0 && ((masks[v] >> (tok_local & 63)) & 1ull);
+      }
+      if (!__all_sync(0xffffffffu, tc5::mbar_wait(s_full + buf, (v >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL))) {
+        ok = false;
+        break;
+      }
+      tc5::fence_after_sync();
+      uint32_t sv[32], dv[32], ds[16];
+      tc5::tmem_ld_x32(tmem + lane_off + buf * 128 + ch * 32, sv);
+      tc5::tmem_ld_x32(tmem + lane_off + buf * 128 + 64 + ch * 32, dv);
+      tc5::tmem_ld_wait();
+      tc5::fence_before_sync();
+      tc5::mbar_arrive(s_empty + buf);
+      if (!row_sel) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) ds[i] = 0u;
+      } else {
+        bool check = sb + 31 >= p.S;
+        if (p.causal) check = check || ((sb + 31) * p.kp_stride + p.kp_off > t);
+        if (p.window > 0) check = check || (sb * p.kp_stride + p.kp_off <= t - p.window);
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const bool v0_ = !check || key_visible(p, sb + i, t);
+          const bool v1_ = !check || key_visible(p, sb + i + 1, t);
+          const float p0 = v0_ ? exp2f(fmaf(__uint_as_float(sv[i]), sc, -Lrow)) : 0.f;
+          const float p1 = v1_ ? exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -Lrow)) : 0.f;
+          ds[i / 2] = tc5::pack_bf16(p0 * (__uint_as_float(dv[i]) - drow) * scale,
+                                     p1 * (__uint_as_float(dv[i + 1]) - drow) * scale);
+        }
+      }
+      if (!__all_sync(0xffffffffu, tc5::mbar_wait(ds_empty, (v & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_EMPTY))) {
+        ok = false;
+        break;
+      }
+      {
+        uint8_t* rd = sDS + r * 128;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          *reinterpret_cast<uint4*>(rd + (((ch * 4 + j) ^ (r & 7)) << 4)) = make_uint4(ds[4 * j], ds[4 * j + 1], ds[4 * j + 2], ds[4 * j + 3]);
+      }
+      tc5::fence_proxy_async();
+      tc5::mbar_arrive(ds_full);
+    }
+    // ---- dQ: thread (r, ch) stores D-half ch of row r
+    const bool have = __all_sync(0xffffffffu, ok && n_vis > 0 &&
+                                 tc5::mbar_wait(acc_done, 0, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL));
+    if (have) tc5::fence_after_sync();
+    bf16* dst = p.dQb + rowi * D + ch * 64;
+#pragma unroll
+    for (int q4 = 0; q4 < 2; ++q4) {
+      uint32_t a[32];
+      if (have) {
+        tc5::tmem_ld_x32(tmem + lane_off + cDQ + ch * 64 + q4 * 32, a);
+        tc5::tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) a[i] = 0u;
+      }
+      if (row_ok) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint4 o4;
+          o4.x = tc5::pack_bf16(__uint_as_float(a[8 * i]), __uint_as_float(a[8 * i + 1]));
+          o4.y = tc5::pack_bf16(__uint_as_float(a[8 * i + 2]), __uint_as_float(a[8 * i + 3]));
+          o4.z = tc5::pack_bf16(__uint_as_float(a[8 * i + 4]), __uint_as_float(a[8 * i + 5]));
+          o4.w = tc5::pack_bf16(__uint_as_float(a[8 * i + 6]), __uint_as_float(a[8 * i + 7]));
+          reinterpret_cast<uint4*>(dst + q4 * 32)[i] = o4;
+        }
+      }
+    }
+  }
+  tc5::fence_before_sync();
+  __syncthreads();
+  if (warp == 9) { tc5::fence_after_sync(); tc5::tmem_dealloc(tmem, 512); }
+}
+
+// --------------------------------------------------------------------------------------
 // Backward for dK / dV, key-block stationary.  A CTA owns one 64-key block of one KV head and
 // walks over "visits": query tiles of 128 rows (R tokens x G heads) that can see the block.
 //   contiguous modes: the visits are the query tiles of an analytic range (causality, window),
@@ -722,14 +979,19 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   } else {
     const int bh = blockIdx.z;
     b = bh / p.Hkv; h = bh - b * p.Hkv;
-    s0 = blockIdx.y * 64;
+    s0 = blockIdx.x * 64;                         // key block fastest: concurrent CTAs share a Q/dO range in L2
     const int s_hi = min(s0 + 63, p.S - 1);
     const int n_qt = (p.T + p.R - 1) / p.R;
     int qt_lo = 0, qt_hi = n_qt;
     if (p.causal) qt_lo = max(0, (s0 * p.kp_stride + p.kp_off) / p.R);
     if (p.window > 0) qt_hi = min(n_qt, (s_hi * p.kp_stride + p.kp_off + p.window - 1) / p.R + 1);
-    v0 = qt_lo + blockIdx.x * w.visits_per_cta;
-    n_vis = min(w.visits_per_cta, qt_hi - v0);
+    if (p.window > 0) {                          // short ranges: chunks counted from the block's first tile
+      v0 = qt_lo + blockIdx.y * w.visits_per_cta;
+      n_vis = min(w.visits_per_cta, qt_hi - v0);
+    } else {                                     // long ranges: absolute chunks, the same Q/dO range for every key block
+      v0 = max(qt_lo, static_cast<int>(blockIdx.y) * w.visits_per_cta);
+      n_vis = min(qt_hi, (static_cast<int>(blockIdx.y) + 1) * w.visits_per_cta) - v0;
+    }
   }
   if (n_vis <= 0) return;
 
@@ -1198,10 +1460,10 @@ extern "C" int nsa_attn_bwd_split(const void* q, const void* k, const void* v, c
   p.L = const_cast<float*>(L); p.delta = delta; p.dQb = (bf16*)dq; p.dK = nullptr; p.dV = nullptr;
   {
     const dim3 grid((T + p.R - 1) / p.R, Hkv, B);
-    const int smem = (D / 64) * 2 * HALF * 4 + 8 * HALF + 1024 + 256;
+    const int smem = (8 + 4 * DQ_STAGES + 2) * HALF + 1024 + 256;
     static bool cfg = false;
-    if (!cfg) { if ((rc = set_smem(attn_bwd_kernel<128>, smem))) return rc; cfg = true; }
-    attn_bwd_kernel<128><<<grid, 256, smem, st>>>(tq, tdo, tk, tv, p, scale);
+    if (!cfg) { if ((rc = set_smem(attn_bwd_dq_kernel, smem))) return rc; cfg = true; }
+    attn_bwd_dq_kernel<<<grid, 320, smem, st>>>(tq, tdo, tk, tv, p, scale);
   }
   p.dK = dk; p.dV = dv;
   KvWalk w{};
@@ -1215,7 +1477,7 @@ extern "C" int nsa_attn_bwd_split(const void* q, const void* k, const void* v, c
     const int n_qt = (T + p.R - 1) / p.R;
     int max_vis = n_qt;
     if (window > 0) max_vis = std::min(n_qt, (63 * kp_stride + window - 1) / p.R + 2);
-    grid = dim3((max_vis + visits_per_cta - 1) / visits_per_cta, (S + 63) / 64, B * Hkv);
+    grid = dim3((S + 63) / 64, (max_vis + visits_per_cta - 1) / visits_per_cta, B * Hkv);
   }
   {
     const int smem = 24 * HALF + 1024 + 256;
