@@ -157,9 +157,75 @@ def bench_mixers(backend: str, T: int, iters: int) -> List[Dict]:
     return rows
 
 
+def bench_nsa(backend: str, T: int, iters: int) -> List[Dict]:
+    """Three-branch sparse attention (32 query / 2 KV heads, head_dim 128, compression 32/16,
+    top-16 blocks of 64, window 512): forward and forward+backward."""
+    torch.manual_seed(0)
+    q = torch.randn(1, T, 32, 128, device="cuda").bfloat16().requires_grad_(True)
+    k = torch.randn(1, T, 2, 128, device="cuda").bfloat16().requires_grad_(True)
+    v = torch.randn(1, T, 2, 128, device="cuda").bfloat16().requires_grad_(True)
+    g = torch.rand(1, T, 32, device="cuda").bfloat16()
+    rows = []
+    with ops.backend(backend):
+        with torch.no_grad():
+            ms = time_ms(lambda: ops.nsa_attention(q, k, v, g, g, g), iters)
+        rows.append({"op": f"nsa_attention fwd T={T}", "backend": backend, "ms": ms})
+
+        def fb():
+            ops.nsa_attention(q, k, v, g, g, g).sum().backward()
+        rows.append({"op": f"nsa_attention fwd+bwd T={T}", "backend": backend, "ms": time_ms(fb, iters)})
+    return rows
+
+
+def bench_comm(iters: int, world: int = 4, shard_mb: int = 32) -> List[Dict]:
+    """Peer-memory kernels with the ranks emulated on ONE GPU (every "peer" buffer is local and
+    every flag is set beforehand, so no kernel waits for another launch): the figures are the
+    kernels' local memory throughput, an upper bound of what NVLink can feed them."""
+    from ..parallel import symm
+    from ..parallel.symm import SymmetricArena, _round_up
+    W = world
+    S = shard_mb * (1 << 20) // 2                      # bf16 elements per shard
+    payload = S * 2 + W * S * 4 + 8192
+    total = _round_up(8 * 32 * 4, 4096) + _round_up(payload, 4096)
+    bufs = [torch.zeros(total, dtype=torch.uint8, device="cuda") for _ in range(W)]
+    arenas = [SymmetricArena(payload, 8, r, W, torch.device("cuda"), local_peers=bufs) for r in range(W)]
+    off_sh = [a.alloc(S * 2) for a in arenas][0]
+    off_g = [a.alloc(W * S * 4) for a in arenas][0]
+    for a in arenas:
+        a.view(off_sh, S, torch.bfloat16).normal_()
+        a.view(off_g, W * S, torch.float32).normal_()
+        symm.signal(a, 0, 1)
+    torch.cuda.synchronize()
+    a0 = arenas[0]
+    pk = peaks()
+    rows = []
+    full = torch.empty(W * S, dtype=torch.bfloat16, device="cuda")
+    ms = time_ms(lambda: symm.all_gather(a0, off_sh, S * 2, full, 0, 1), iters)
+    rows.append(_bw_row(f"p2p all_gather W={W} shard={shard_mb}MB (emulated)", "native", ms, 2.0 * W * S * 2))
+    gs = torch.zeros(S, device="cuda")
+    parts = torch.zeros(symm.reduce_scatter_parts(), device="cuda")
+    ms = time_ms(lambda: symm.reduce_scatter(a0, off_g, gs, 1.0 / W, True, 0, 1, parts), iters)
+    rows.append(_bw_row(f"p2p reduce_scatter+scale+sumsq W={W} (emulated)", "native", ms, (W + 2.0) * S * 4))
+    M, K = 16384, 2048
+    N = (W * S - 4096) // K // 8 * 8
+    N = min(N, 8512)
+    cps = 16
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    epoch = [1]
+
+    def fused():
+        flags = torch.zeros(W * cps, dtype=torch.int32, device="cuda")
+        symm.gemm_all_gather(a0, x, full, off_sh, S, 4096, N, flags, cps, 0, 1)
+    ms = time_ms(fused, iters)
+    rows.append({"op": f"gemm + fused all_gather {M}x{N}x{K} W={W} (emulated)", "backend": "native", "ms": ms,
+                 "tflops": 2.0 * M * N * K / ms / 1e9, "frac_of_peak": 2.0 * M * N * K / ms / 1e9 / pk["bf16_tflops"],
+                 "gathered_mb": W * S * 2 / 2**20})
+    return rows
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["all", "gemm", "elementwise", "attention", "mixers"])
+    ap.add_argument("--op", default="all", choices=["all", "gemm", "elementwise", "attention", "mixers", "nsa", "comm"])
     ap.add_argument("--backend", default="native", choices=["native", "torch"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
@@ -186,6 +252,10 @@ def main() -> None:
         rows += bench_attention(a.backend, a.seq, a.iters, a.window)
     if a.op in ("all", "mixers"):
         rows += bench_mixers(a.backend, a.seq, a.iters)
+    if a.op == "nsa":
+        rows += bench_nsa(a.backend, a.seq, a.iters)
+    if a.op == "comm":
+        rows += bench_comm(a.iters)
     for r in rows:
         print(json.dumps(r))
     if a.backend == "native":

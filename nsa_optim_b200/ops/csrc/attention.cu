@@ -736,12 +736,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       }
       bool ok = true;
       int issued = 0;
+      int blk_n = selected ? blocks[0] : 0;
       for (int v = 0; v < n_vis; ++v) {
         const int st = v % DQ_STAGES;
+        const int blk = blk_n;
+        if (selected && v + 1 < n_vis) blk_n = blocks[v + 1];
         if (!tc5::mbar_wait(kv_empty + st, ((v / DQ_STAGES) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_EMPTY)) { ok = false; break; }
         int s0;
         if (!selected) s0 = (kb0 + v) * 64;
-        else { const int blk = blocks[v]; s0 = blk < 0 ? 0 : blk * 64; }
+        else s0 = blk < 0 ? 0 : blk * 64;
         uint8_t* kd = sKV + st * 4 * HALF;
         tc5::mbar_expect_tx(kv_full + st, 4 * HALF);
 #pragma unroll
@@ -818,17 +821,24 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const long rowi = (static_cast<long>(b) * p.T + (row_ok ? t : 0)) * p.Hq + h * p.G + g;
     const float Lrow = row_ok ? p.L[rowi] : 0.f;
     const float drow = row_ok ? p.delta[rowi] : 0.f;
+    const float nds = -drow * scale;
     const float sc = p.scale_log2;
     bool ok = true;
+    // selected mode: the block id and token mask of visit v+1 are fetched during visit v, so the
+    // global-memory latency is off the per-visit critical path
+    int blk_n = (selected && n_vis > 0) ? blocks[0] : 0;
+    unsigned long long msk_n = (selected && n_vis > 0) ? masks[0] : 0ull;
     for (int v = 0; v < n_vis; ++v) {
       const int buf = v & 1;
       int sb;
       bool row_sel = row_ok;
       if (!selected) sb = (kb0 + v) * 64 + ch * 32;
       else {
-        const int blk = blocks[v];
+        const int blk = blk_n;
+        const unsigned long long msk = msk_n;
+        if (v + 1 < n_vis) { blk_n = blocks[v + 1]; msk_n = masks[v + 1]; }
         sb = blk < 0 ? -1 : blk * 64 + ch * 32;
-        row_sel = row_ok && blk >= 0 && ((masks[v] >> (tok_local & 63)) & 1ull);
+        row_sel = row_ok && blk >= 0 && ((msk >> (tok_local & 63)) & 1ull);
       }
       if (!__all_sync(0xffffffffu, tc5::mbar_wait(s_full + buf, (v >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL))) {
         ok = false;
@@ -854,8 +864,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           const bool v1_ = !check || key_visible(p, sb + i + 1, t);
           const float p0 = v0_ ? exp2f(fmaf(__uint_as_float(sv[i]), sc, -Lrow)) : 0.f;
           const float p1 = v1_ ? exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -Lrow)) : 0.f;
-          ds[i / 2] = tc5::pack_bf16(p0 * (__uint_as_float(dv[i]) - drow) * scale,
-                                     p1 * (__uint_as_float(dv[i + 1]) - drow) * scale);
+          ds[i / 2] = tc5::pack_bf16(p0 * fmaf(__uint_as_float(dv[i]), scale, nds),
+                                     p1 * fmaf(__uint_as_float(dv[i + 1]), scale, nds));
         }
       }
       if (!__all_sync(0xffffffffu, tc5::mbar_wait(ds_empty, (v & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_EMPTY))) {
@@ -1050,7 +1060,7 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       } else {
         for (int j = lane; j < p.R; j += 32) {
           const int li = (v0 + v) * p.R + j;
-          const int tok = li < cnt ? w.tok_list[lst0 + li] : 0;     // rows past the list read token 0 and are masked
+          const int tok = li < cnt ? __ldg(w.tok_list + lst0 + li) : 0;   // rows past the list read token 0 and are masked
           const int off = j * p.G * 128;
 #pragma unroll
           for (int kb = 0; kb < 2; ++kb) {
@@ -1132,21 +1142,37 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const float sc = p.scale_log2;
     const int sb = s0 + ch * 32;                   // this thread's first key
     bool ok = true;
-    for (int v = 0; v < n_vis; ++v) {
-      const int buf = v & 1;
-      int t;
+    // The row's token (selected mode: from the inverse list) and its L / delta are fetched one and
+    // two visits ahead, so the two dependent global loads are off the per-visit critical path.
+    auto token_of = [&](int v) -> int {
+      if (v >= n_vis) return -1;
       if (selected) {
         const int li = (v0 + v) * p.R + tok_local;
-        t = li < cnt ? w.tok_list[lst0 + li] : -1;
-      } else {
-        t = (v0 + v) * p.R + tok_local;
-        if (t >= p.T) t = -1;
+        return li < cnt ? w.tok_list[lst0 + li] : -1;
       }
-      float Lrow = 0.f, drow = 0.f;
-      if (t >= 0) {
-        const long rowi = (static_cast<long>(b) * p.T + t) * p.Hq + h * p.G + g;
-        Lrow = p.L[rowi];
-        drow = p.delta[rowi];
+      const int tt = (v0 + v) * p.R + tok_local;
+      return tt < p.T ? tt : -1;
+    };
+    int t_cur = token_of(0), t_nxt = token_of(1);
+    float L_cur = 0.f, d_cur = 0.f;
+    if (t_cur >= 0) {
+      const long rowi = (static_cast<long>(b) * p.T + t_cur) * p.Hq + h * p.G + g;
+      L_cur = p.L[rowi];
+      d_cur = p.delta[rowi];
+    }
+    for (int v = 0; v < n_vis; ++v) {
+      const int buf = v & 1;
+      const int t = t_cur;
+      const float Lrow = L_cur, nds = -d_cur * scale;
+      {
+        float Ln = 0.f, dn = 0.f;
+        if (t_nxt >= 0) {
+          const long rowi = (static_cast<long>(b) * p.T + t_nxt) * p.Hq + h * p.G + g;
+          Ln = p.L[rowi];
+          dn = p.delta[rowi];
+        }
+        t_cur = t_nxt; L_cur = Ln; d_cur = dn;
+        t_nxt = token_of(v + 2);
       }
       if (!__all_sync(0xffffffffu, tc5::mbar_wait(s_full + buf, (v >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL))) {
         ok = false;
@@ -1173,8 +1199,8 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           const float p0 = v0_ ? exp2f(fmaf(__uint_as_float(sv[i]), sc, -Lrow)) : 0.f;
           const float p1 = v1_ ? exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -Lrow)) : 0.f;
           pp[i / 2] = tc5::pack_bf16(p0, p1);
-          ds[i / 2] = tc5::pack_bf16(p0 * (__uint_as_float(dv[i]) - drow) * scale,
-                                     p1 * (__uint_as_float(dv[i + 1]) - drow) * scale);
+          ds[i / 2] = tc5::pack_bf16(p0 * fmaf(__uint_as_float(dv[i]), scale, nds),
+                                     p1 * fmaf(__uint_as_float(dv[i + 1]), scale, nds));
         }
       }
       if (!__all_sync(0xffffffffu, tc5::mbar_wait(p_empty, (v & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_EMPTY))) {

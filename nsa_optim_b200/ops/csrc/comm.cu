@@ -91,8 +91,21 @@ __global__ void __launch_bounds__(256) allgather_kernel(const uint4* const* shar
   if (!sh_ok) return;
   const uint4* src = shards[p];
   uint4* dst = out + static_cast<long>(p) * shard_vec;
-  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < shard_vec; i += static_cast<long>(gridDim.x) * blockDim.x)
-    dst[i] = src[i];
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+  constexpr int U = 8;                                  // independent 16-byte peer loads in flight per thread
+  for (long i0 = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < shard_vec; i0 += stride * U) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long i = i0 + u * stride;
+      if (i < shard_vec) v[u] = src[i];
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long i = i0 + u * stride;
+      if (i < shard_vec) dst[i] = v[u];
+    }
+  }
 }
 
 // grads[p]: rank p's full fp32 gradient buffer (W * S floats).  This rank reduces slice `rank`.
@@ -106,7 +119,7 @@ __global__ void __launch_bounds__(256) reduce_scatter_kernel(const float* const*
   float ss = 0.f;
   const long base = static_cast<long>(rank) * S4;
   const long stride = static_cast<long>(gridDim.x) * blockDim.x;
-  constexpr int U = 4;                                  // independent 16-byte loads in flight per thread and peer
+  constexpr int U = 8;                                  // independent 16-byte loads in flight per thread and peer
   for (long i0 = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < S4; i0 += stride * U) {
     float4 acc[U];
 #pragma unroll
@@ -245,7 +258,7 @@ extern "C" int nsa_comm_allgather(const void* const* shards, void* out, long sha
 // A reduce-scatter runs beside the backward pass of the next block: a small grid (well under one
 // CTA per SM) with several loads in flight per thread keeps the link busy without taking the
 // compute kernels' SMs.
-extern "C" int nsa_comm_reduce_scatter_parts(void) { return 64; }
+extern "C" int nsa_comm_reduce_scatter_parts(void) { return 96; }
 // grads: device array of W pointers to full fp32 gradient buffers (W*S floats); S multiple of 4.
 extern "C" int nsa_comm_reduce_scatter(const float* const* grads, float* grad_shard, long S, int W, int rank, float scale,
                                        int accumulate, float* sumsq_partial, const unsigned* flags, unsigned epoch,

@@ -114,7 +114,22 @@ __device__ void ag_copy_role(const AgFuse& ag, int cta, KernelStatus* status) {
     const long hi = lo + ag.chunk_vec < ag.shard_vec ? lo + ag.chunk_vec : ag.shard_vec;
     const uint4* src = ag.shards[pr];
     uint4* dst = ag.full + static_cast<long>(pr) * ag.shard_vec;
-    for (long i = lo + threadIdx.x; i < hi; i += blockDim.x) dst[i] = src[i];
+    // eight independent 16-byte loads in flight per thread: a peer load takes microseconds, and one
+    // load at a time per thread would leave the link almost idle
+    constexpr int U = 8;
+    for (long i0 = lo + threadIdx.x; i0 < hi; i0 += static_cast<long>(blockDim.x) * U) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long i = i0 + static_cast<long>(u) * blockDim.x;
+        if (i < hi) v[u] = src[i];
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long i = i0 + static_cast<long>(u) * blockDim.x;
+        if (i < hi) dst[i] = v[u];
+      }
+    }
     __syncthreads();
     if (threadIdx.x == 0) {
       __threadfence();
