@@ -22,6 +22,8 @@
 // ordinary attention, (stride, block-1) for compressed keys, which makes "causal on block
 // end" the same comparison as ordinary causality.
 #include <algorithm>
+#include <cstdlib>
+#include <cstring>
 
 #include "host.cuh"
 #include "tc5.cuh"
@@ -414,6 +416,326 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 }
 
 // --------------------------------------------------------------------------------------
+// Forward, warp-specialised (head_dim 128, output mode).  Visits are 64-key blocks as in the
+// dQ kernel.  Warp 8 streams K/V through a 4-stage ring, warp 9 issues S = Q K^T and O += P V.
+// The 8 softmax warps form two groups of 128 threads (one thread per query row): group g takes
+// the visits with v mod 2 = g and runs its own online softmax over them, with its own running
+// maximum / sum, its own S buffer, P buffer and O accumulator in TMEM, so the groups never
+// exchange anything per visit; the two partial results are merged once at the end:
+//   m = max(m0, m1), O = (2^(m0-m) O0 + 2^(m1-m) O1) / (2^(m0-m) l0 + 2^(m1-m) l1).
+// tcgen05 MMAs complete in issue order, and S of visit v is issued after P V of visit v-2, so a
+// group that has received S_v may rescale its O accumulator in place.
+// --------------------------------------------------------------------------------------
+constexpr int FW_STAGES = 4;
+
+__global__ void __launch_bounds__(320, 1)
+attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                   const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+  constexpr int D = 128;
+  constexpr int QT = 4 * HALF;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sKV = sQ + QT;                        // [stages][K: 2 k-blocks of [64][64] | V: same]
+  uint8_t* sP = sKV + FW_STAGES * 4 * HALF;      // [2 groups][128 rows][64 keys]
+  float* merge = reinterpret_cast<float*>(sP + 4 * HALF);   // [2][128]: group 1's m and l
+  uint64_t* bars = reinterpret_cast<uint64_t*>(merge + 256);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;                  // [stages]
+  uint64_t* kv_empty = kv_full + FW_STAGES;      // [stages]
+  uint64_t* s_full = kv_empty + FW_STAGES;       // [2]
+  uint64_t* s_empty = s_full + 2;                // [2]
+  uint64_t* p_full = s_empty + 2;                // [2]
+  uint64_t* p_empty = p_full + 2;                // [2]
+  uint64_t* acc_done = p_empty + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int qt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int q0 = qt * p.R;
+  const int t_hi = min(q0 + p.R, p.T) - 1;
+  const bool selected = p.tile_blocks != nullptr;
+  const long tile_slot = (static_cast<long>(b) * p.Hkv + h) * gridDim.x + qt;
+  const int* blocks = selected ? p.tile_blocks + tile_slot * p.max_u : nullptr;
+  const unsigned long long* masks = selected ? p.tile_masks + tile_slot * p.max_u : nullptr;
+  int kb0 = 0, n_vis;
+  if (selected) {
+    n_vis = min(p.tile_counts[tile_slot], p.max_u);
+  } else {
+    long last = p.S - 1;
+    if (p.causal) {
+      long lim = static_cast<long>(t_hi) - p.kp_off;
+      lim = lim < 0 ? -1 : lim / p.kp_stride;
+      last = lim < last ? lim : last;
+    }
+    long first = 0;
+    if (p.window > 0) {
+      const long lo = static_cast<long>(q0) - p.window + 1 - p.kp_off;
+      first = lo <= 0 ? 0 : (lo + p.kp_stride - 1) / p.kp_stride;
+    }
+    kb0 = static_cast<int>(first / 64);
+    n_vis = last < first ? 0 : static_cast<int>(last / 64) + 1 - kb0;
+  }
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    tc5::mbar_init(q_full, 1);
+    for (int i = 0; i < FW_STAGES; ++i) { tc5::mbar_init(kv_full + i, 1); tc5::mbar_init(kv_empty + i, 1); }
+    for (int i = 0; i < 2; ++i) {
+      tc5::mbar_init(s_full + i, 1);
+      tc5::mbar_init(s_empty + i, 128);
+      tc5::mbar_init(p_full + i, 128);
+      tc5::mbar_init(p_empty + i, 1);
+    }
+    tc5::mbar_init(acc_done, 1);
+    tc5::fence_barrier_init();
+  }
+  if (warp == 9) { tc5::tmem_alloc(tmem_slot, 512); tc5::tmem_relinquish(); }
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  // columns: S of group g at g*64; O of group g at 128 + g*128
+  constexpr uint32_t cO = 128;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0 && n_vis > 0) {
+      tc5::mbar_expect_tx(q_full, QT);
+#pragma unroll
+      for (int kb = 0; kb < 2; ++kb) tc5::tma_load_5d(sQ + kb * 2 * HALF, &tm_q, q_full, kb * 64, 0, h, q0, b);
+      bool ok = true;
+      int issued = 0;
+      int blk_n = selected ? blocks[0] : 0;
+      for (int v = 0; v < n_vis; ++v) {
+        const int st = v % FW_STAGES;
+        const int blk = blk_n;
+        if (selected && v + 1 < n_vis) blk_n = blocks[v + 1];
+        if (!tc5::mbar_wait(kv_empty + st, ((v / FW_STAGES) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_EMPTY)) { ok = false; break; }
+        const int s0 = selected ? (blk < 0 ? 0 : blk * 64) : (kb0 + v) * 64;
+        uint8_t* kd = sKV + st * 4 * HALF;
+        tc5::mbar_expect_tx(kv_full + st, 4 * HALF);
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb) {
+          tc5::tma_load_4d(kd + kb * HALF, &tm_k, kv_full + st, kb * 64, h, s0, b);
+          tc5::tma_load_4d(kd + 2 * HALF + kb * HALF, &tm_v, kv_full + st, kb * 64, h, s0, b);
+        }
+        issued = v + 1;
+      }
+      if (!ok) {
+        // let the copies already issued land before the CTA's shared memory is released
+        for (int j = max(0, issued - FW_STAGES); j < issued; ++j) {
+          const long long t0 = clock64();
+          for (uint32_t i = 0; i < tc5::kMaxPolls; ++i) {
+            if (tc5::mbar_try_wait(kv_full + (j % FW_STAGES), (j / FW_STAGES) & 1)) break;
+            if ((i & 255u) == 255u && clock64() - t0 > tc5::kMaxWaitCycles) break;
+          }
+        }
+        const long long t0 = clock64();
+        for (uint32_t i = 0; i < tc5::kMaxPolls; ++i) {
+          if (tc5::mbar_try_wait(q_full, 0)) break;
+          if ((i & 255u) == 255u && clock64() - t0 > tc5::kMaxWaitCycles) break;
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && n_vis > 0) {
+      constexpr uint32_t id_s = tc5::make_idesc_bf16(128, 64, 0, 0);
+      constexpr uint32_t id_o = tc5::make_idesc_bf16(128, D, 0, 1);
+      uint64_t aQ[D / 16];
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) aQ[kk] = tc5::desc_kmajor(tc5::smem_u32(sQ) + (kk >> 2) * 2 * HALF + (kk & 3) * 32);
+      const uint64_t bK0 = tc5::desc_kmajor(tc5::smem_u32(sKV));
+      const uint64_t bVmn0 = tc5::desc_mnmajor(tc5::smem_u32(sKV) + 2 * HALF, HALF);
+      const uint64_t aP0 = tc5::desc_kmajor(tc5::smem_u32(sP));
+      bool ok = tc5::mbar_wait(q_full, 0, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL);
+      for (int v = 0; v <= n_vis && ok; ++v) {
+        if (v < n_vis) {
+          const int st = v % FW_STAGES, g = v & 1;
+          if (!tc5::mbar_wait(kv_full + st, (v / FW_STAGES) & 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL)) { ok = false; break; }
+          if (!tc5::mbar_wait(s_empty + g, ((v >> 1) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+          tc5::fence_after_sync();
+          const uint64_t bK = bK0 + static_cast<uint64_t>((st * 4 * HALF) >> 4);
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk)
+            tc5::mma_ss(tmem + g * 64, aQ[kk], bK + static_cast<uint64_t>(((kk >> 2) * HALF + (kk & 3) * 32) >> 4), id_s,
+                        kk > 0 ? 1u : 0u);
+          tc5::mma_commit(s_full + g);
+        }
+        if (v >= 1) {
+          const int u = v - 1, st = u % FW_STAGES, g = u & 1;
+          if (!tc5::mbar_wait(p_full + g, (u >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL)) { ok = false; break; }
+          tc5::fence_after_sync();
+          const uint64_t aP = aP0 + static_cast<uint64_t>((g * 2 * HALF) >> 4);
+          const uint64_t bV = bVmn0 + static_cast<uint64_t>((st * 4 * HALF) >> 4);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)          // O_g += P V  (64 keys per visit)
+            tc5::mma_ss(tmem + cO + g * 128, aP + static_cast<uint64_t>((kk * 32) >> 4), bV + static_cast<uint64_t>((kk * 2048) >> 4),
+                        id_o, (u > 1 || kk > 0) ? 1u : 0u);
+          tc5::mma_commit(kv_empty + st);
+          tc5::mma_commit(p_empty + g);
+        }
+      }
+      if (ok) tc5::mma_commit(acc_done);
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax groups
+    const int r = tid & 127, grp = tid >> 7;
+    const int tok_local = r / p.G, gh = r % p.G;
+    const int t = q0 + tok_local;
+    const bool row_ok = t < p.T;
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const long rowi = (static_cast<long>(b) * p.T + (row_ok ? t : 0)) * p.Hq + h * p.G + gh;
+    const float sc = p.scale_log2;
+    float m_ref = -INFINITY, l_sum = 0.f;
+    bool ok = true;
+    int blk_n = 0;
+    unsigned long long msk_n = 0ull;
+    if (selected && grp < n_vis) { blk_n = blocks[grp]; msk_n = masks[grp]; }
+    int n_mine = 0;
+    for (int v = grp; v < n_vis; v += 2, ++n_mine) {
+      int sb;
+      bool row_sel = row_ok;
+      if (!selected) sb = (kb0 + v) * 64;
+      else {
+        const int blk = blk_n;
+        const unsigned long long msk = msk_n;
+        if (v + 2 < n_vis) { blk_n = blocks[v + 2]; msk_n = masks[v + 2]; }
+        sb = blk < 0 ? -1 : blk * 64;
+        row_sel = row_ok && blk >= 0 && ((msk >> (tok_local & 63)) & 1ull);
+      }
+      if (!__all_sync(0xffffffffu, tc5::mbar_wait(s_full + grp, n_mine & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL))) {
+        ok = false;
+        break;
+      }
+      tc5::fence_after_sync();
+      uint32_t sv[64];
+      tmem_ld64(tmem + lane_off + grp * 64, sv);
+      tc5::fence_before_sync();
+      tc5::mbar_arrive(s_empty + grp);
+      bool check = false;
+      float mx = -INFINITY;
+      if (row_sel) {
+        check = sb + 63 >= p.S;
+        if (p.causal) check = check || ((sb + 63) * p.kp_stride + p.kp_off > t);
+        if (p.window > 0) check = check || (sb * p.kp_stride + p.kp_off <= t - p.window);
+        if (!check) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 64; ++i)
+            if (key_visible(p, sb + i, t)) mx = fmaxf(mx, __uint_as_float(sv[i]));
+        }
+      }
+      mx *= sc;
+      float alpha = 1.f;
+      if (mx != -INFINITY && (m_ref == -INFINITY || mx > m_ref + 8.f)) {
+        alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - mx);
+        m_ref = mx;
+      }
+      uint32_t pk[32];
+      float psum = 0.f;
+      if (!row_sel || m_ref == -INFINITY) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) pk[i] = 0u;
+      } else if (!check) {
+#pragma unroll
+        for (int i = 0; i < 64; i += 2) {
+          const float a = exp2f(fmaf(__uint_as_float(sv[i]), sc, -m_ref));
+          const float c = exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -m_ref));
+          psum += a + c;
+          pk[i / 2] = tc5::pack_bf16(a, c);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; i += 2) {
+          const float a = key_visible(p, sb + i, t) ? exp2f(fmaf(__uint_as_float(sv[i]), sc, -m_ref)) : 0.f;
+          const float c = key_visible(p, sb + i + 1, t) ? exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -m_ref)) : 0.f;
+          psum += a + c;
+          pk[i / 2] = tc5::pack_bf16(a, c);
+        }
+      }
+      l_sum = l_sum * alpha + psum;
+      // O_g is quiescent here: P V of this group's previous visit completed before S of this visit
+      if (n_mine > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+        for (int q4 = 0; q4 < D / 32; ++q4) {
+          uint32_t o[32];
+          tc5::tmem_ld_x32(tmem + lane_off + cO + grp * 128 + q4 * 32, o);
+          tc5::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tc5::tmem_st_x32(tmem + lane_off + cO + grp * 128 + q4 * 32, o);
+        }
+        tc5::tmem_st_wait();
+      }
+      if (!__all_sync(0xffffffffu, tc5::mbar_wait(p_empty + grp, (n_mine & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_EMPTY))) {
+        ok = false;
+        break;
+      }
+      store_row64(sP + grp * 2 * HALF, r, pk);
+      tc5::fence_proxy_async();
+      tc5::fence_before_sync();
+      tc5::mbar_arrive(p_full + grp);
+    }
+    // ---- merge the two groups' partial results and write O (thread (r, grp): columns grp*64..)
+    const bool done = __all_sync(0xffffffffu, ok && n_vis > 0 &&
+                                 tc5::mbar_wait(acc_done, 0, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL));
+    if (done) tc5::fence_after_sync();
+    if (grp == 1) { merge[r] = m_ref; merge[128 + r] = l_sum; }
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    float m0, l0, m1, l1;
+    if (grp == 0) { m0 = m_ref; l0 = l_sum; m1 = merge[r]; l1 = merge[128 + r]; }
+    else { m1 = m_ref; l1 = l_sum; }
+    if (grp == 0) { merge[r] = m0; merge[128 + r] = l0; }
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (grp == 1) { m0 = merge[r]; l0 = merge[128 + r]; }
+    const float m = fmaxf(m0, m1);
+    const float w0 = (l0 > 0.f) ? exp2f(m0 - m) : 0.f;
+    const float w1 = (l1 > 0.f) ? exp2f(m1 - m) : 0.f;
+    const float l_tot = w0 * l0 + w1 * l1;
+    const bool have = done && l_tot > 0.f;
+    const float f0 = have ? w0 / l_tot : 0.f, f1 = have ? w1 / l_tot : 0.f;
+    if (row_ok && grp == 0) p.L[rowi] = have ? m + log2f(l_tot) : -INFINITY;
+    bf16* dst = p.O + rowi * D + grp * 64;
+    // every thread of a warp takes the same branches below (done, and the visit counts, are uniform)
+    const bool use0 = done && n_vis > 0, use1 = done && n_vis > 1;
+#pragma unroll
+    for (int q4 = 0; q4 < 2; ++q4) {
+      uint32_t a[32], c[32];
+      if (use0) tc5::tmem_ld_x32(tmem + lane_off + cO + grp * 64 + q4 * 32, a);
+      if (use1) tc5::tmem_ld_x32(tmem + lane_off + cO + 128 + grp * 64 + q4 * 32, c);
+      if (use0 || use1) tc5::tmem_ld_wait();
+      if (row_ok) {
+        float o[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float x = 0.f;
+          if (use0 && f0 != 0.f) x = __uint_as_float(a[i]) * f0;
+          if (use1 && f1 != 0.f) x += __uint_as_float(c[i]) * f1;
+          o[i] = x;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint4 o4;
+          o4.x = tc5::pack_bf16(o[8 * i], o[8 * i + 1]);
+          o4.y = tc5::pack_bf16(o[8 * i + 2], o[8 * i + 3]);
+          o4.z = tc5::pack_bf16(o[8 * i + 4], o[8 * i + 5]);
+          o4.w = tc5::pack_bf16(o[8 * i + 6], o[8 * i + 7]);
+          reinterpret_cast<uint4*>(dst + q4 * 32)[i] = o4;
+        }
+      }
+    }
+  }
+  tc5::fence_before_sync();
+  __syncthreads();
+  if (warp == 9) { tc5::fence_after_sync(); tc5::tmem_dealloc(tmem, 512); }
+}
+
+// --------------------------------------------------------------------------------------
 // Backward, query-tile outer.  Per key tile: S = Q K^T and dP = dO V^T (TMEM), then in
 // registers P = exp2(S c - L), dS = P (dP - delta) scale; then dQ += dS K (TMEM resident),
 // and the tile's dV = P^T dO, dK = dS^T Q are added to fp32 global buffers.
@@ -775,7 +1097,21 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     if (lane == 0 && n_vis > 0) {
       constexpr uint32_t id_s = tc5::make_idesc_bf16(128, 64, 0, 0);
       constexpr uint32_t id_q = tc5::make_idesc_bf16(128, D, 0, 1);
-      const uint32_t q = tc5::smem_u32(sQ), dob = tc5::smem_u32(sDO), dsb = tc5::smem_u32(sDS);
+      // Every shared-memory descriptor is built once.  The address field (bits 0-13, address >> 4) of
+      // a descriptor can be advanced by adding the byte offset >> 4, so the per-visit work of this
+      // thread is one add per operand and the MMA itself: with 64-key MMAs of about 32 cycles the
+      // issuing thread's instruction count, not the tensor pipe, sets the pace otherwise.
+      uint64_t aQ[D / 16], aDO[D / 16], aDS[4];
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint32_t a_off = (kk >> 2) * 2 * HALF + (kk & 3) * 32;
+        aQ[kk] = tc5::desc_kmajor(tc5::smem_u32(sQ) + a_off);
+        aDO[kk] = tc5::desc_kmajor(tc5::smem_u32(sDO) + a_off);
+      }
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) aDS[kk] = tc5::desc_kmajor(tc5::smem_u32(sDS) + kk * 32);
+      const uint64_t bK0 = tc5::desc_kmajor(tc5::smem_u32(sKV));             // stage 0, K, k-step 0
+      const uint64_t bKmn0 = tc5::desc_mnmajor(tc5::smem_u32(sKV), HALF);    // same tile as an MN-major operand
       bool ok = tc5::mbar_wait(q_full, 0, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL);
       for (int v = 0; v <= n_vis && ok; ++v) {
         if (v < n_vis) {
@@ -783,28 +1119,26 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           if (!tc5::mbar_wait(kv_full + st, (v / DQ_STAGES) & 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL)) { ok = false; break; }
           if (!tc5::mbar_wait(s_empty + buf, ((v >> 1) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
           tc5::fence_after_sync();
-          const uint32_t k = tc5::smem_u32(sKV + st * 4 * HALF), vv = k + 2 * HALF;
+          const uint64_t bK = bK0 + static_cast<uint64_t>((st * 4 * HALF) >> 4);
+          const uint64_t bV = bK + static_cast<uint64_t>((2 * HALF) >> 4);
 #pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) {
-            const uint32_t a_off = (kk >> 2) * 2 * HALF + (kk & 3) * 32, b_off = (kk >> 2) * HALF + (kk & 3) * 32;
-            tc5::mma_ss(tmem + buf * 128, tc5::desc_kmajor(q + a_off), tc5::desc_kmajor(k + b_off), id_s, kk > 0 ? 1u : 0u);
-          }
+          for (int kk = 0; kk < D / 16; ++kk)
+            tc5::mma_ss(tmem + buf * 128, aQ[kk], bK + static_cast<uint64_t>(((kk >> 2) * HALF + (kk & 3) * 32) >> 4), id_s,
+                        kk > 0 ? 1u : 0u);
 #pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) {
-            const uint32_t a_off = (kk >> 2) * 2 * HALF + (kk & 3) * 32, b_off = (kk >> 2) * HALF + (kk & 3) * 32;
-            tc5::mma_ss(tmem + buf * 128 + 64, tc5::desc_kmajor(dob + a_off), tc5::desc_kmajor(vv + b_off), id_s, kk > 0 ? 1u : 0u);
-          }
+          for (int kk = 0; kk < D / 16; ++kk)
+            tc5::mma_ss(tmem + buf * 128 + 64, aDO[kk], bV + static_cast<uint64_t>(((kk >> 2) * HALF + (kk & 3) * 32) >> 4), id_s,
+                        kk > 0 ? 1u : 0u);
           tc5::mma_commit(s_full + buf);
         }
         if (v >= 1) {
           const int u = v - 1, st = u % DQ_STAGES;
           if (!tc5::mbar_wait(ds_full, u & 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL)) { ok = false; break; }
           tc5::fence_after_sync();
-          const uint32_t k = tc5::smem_u32(sKV + st * 4 * HALF);
+          const uint64_t bKmn = bKmn0 + static_cast<uint64_t>((st * 4 * HALF) >> 4);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)          // dQ += dS K  (64 keys per visit)
-            tc5::mma_ss(tmem + cDQ, tc5::desc_kmajor(dsb + kk * 32), tc5::desc_mnmajor(k + kk * 2048, HALF), id_q,
-                        (u > 0 || kk > 0) ? 1u : 0u);
+            tc5::mma_ss(tmem + cDQ, aDS[kk], bKmn + static_cast<uint64_t>((kk * 2048) >> 4), id_q, (u > 0 || kk > 0) ? 1u : 0u);
           tc5::mma_commit(kv_empty + st);
           tc5::mma_commit(ds_empty);
         }
@@ -1092,8 +1426,21 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     if (lane == 0) {
       constexpr uint32_t id_s = tc5::make_idesc_bf16(128, 64, 0, 0);
       constexpr uint32_t id_t = tc5::make_idesc_bf16(128, 64, 1, 1);
-      const uint32_t k = tc5::smem_u32(sK), vv = tc5::smem_u32(sV);
-      const uint32_t pb = tc5::smem_u32(sP), dsb = tc5::smem_u32(sDS);
+      // descriptors are built once; a buffer switch is an add on the address field (see the dQ kernel)
+      uint64_t bK[D / 16], bV[D / 16], bP[BM / 16], bDS[BM / 16];
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint32_t b_off = (kk >> 2) * HALF + (kk & 3) * 32;
+        bK[kk] = tc5::desc_kmajor(tc5::smem_u32(sK) + b_off);
+        bV[kk] = tc5::desc_kmajor(tc5::smem_u32(sV) + b_off);
+      }
+#pragma unroll
+      for (int kk = 0; kk < BM / 16; ++kk) {
+        bP[kk] = tc5::desc_mnmajor(tc5::smem_u32(sP) + kk * 2048, 2 * HALF);
+        bDS[kk] = tc5::desc_mnmajor(tc5::smem_u32(sDS) + kk * 2048, 2 * HALF);
+      }
+      const uint64_t aQ0 = tc5::desc_kmajor(tc5::smem_u32(sQ)), aDO0 = tc5::desc_kmajor(tc5::smem_u32(sDO));
+      const uint64_t aQmn0 = tc5::desc_mnmajor(tc5::smem_u32(sQ), 2 * HALF), aDOmn0 = tc5::desc_mnmajor(tc5::smem_u32(sDO), 2 * HALF);
       bool ok = tc5::mbar_wait(kv_full, 0, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL);
       for (int v = 0; v <= n_vis && ok; ++v) {
         if (v < n_vis) {
@@ -1102,32 +1449,28 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           if (!tc5::mbar_wait(q_full + buf, ph, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL)) { ok = false; break; }
           if (!tc5::mbar_wait(s_empty + buf, ph ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
           tc5::fence_after_sync();
-          const uint32_t q = tc5::smem_u32(sQ + buf * QT), dob = tc5::smem_u32(sDO + buf * QT);
+          const uint64_t aQ = aQ0 + static_cast<uint64_t>((buf * QT) >> 4), aDO = aDO0 + static_cast<uint64_t>((buf * QT) >> 4);
 #pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) {
-            const uint32_t a_off = (kk >> 2) * 2 * HALF + (kk & 3) * 32, b_off = (kk >> 2) * HALF + (kk & 3) * 32;
-            tc5::mma_ss(tmem + buf * 128, tc5::desc_kmajor(q + a_off), tc5::desc_kmajor(k + b_off), id_s, kk > 0 ? 1u : 0u);
-          }
+          for (int kk = 0; kk < D / 16; ++kk)
+            tc5::mma_ss(tmem + buf * 128, aQ + static_cast<uint64_t>(((kk >> 2) * 2 * HALF + (kk & 3) * 32) >> 4), bK[kk], id_s,
+                        kk > 0 ? 1u : 0u);
 #pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) {
-            const uint32_t a_off = (kk >> 2) * 2 * HALF + (kk & 3) * 32, b_off = (kk >> 2) * HALF + (kk & 3) * 32;
-            tc5::mma_ss(tmem + buf * 128 + 64, tc5::desc_kmajor(dob + a_off), tc5::desc_kmajor(vv + b_off), id_s, kk > 0 ? 1u : 0u);
-          }
+          for (int kk = 0; kk < D / 16; ++kk)
+            tc5::mma_ss(tmem + buf * 128 + 64, aDO + static_cast<uint64_t>(((kk >> 2) * 2 * HALF + (kk & 3) * 32) >> 4), bV[kk], id_s,
+                        kk > 0 ? 1u : 0u);
           tc5::mma_commit(s_full + buf);
         }
         if (v >= 1) {
           const int u = v - 1, buf = u & 1;
           if (!tc5::mbar_wait(p_full, u & 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL)) { ok = false; break; }
           tc5::fence_after_sync();
-          const uint32_t q = tc5::smem_u32(sQ + buf * QT), dob = tc5::smem_u32(sDO + buf * QT);
+          const uint64_t aQmn = aQmn0 + static_cast<uint64_t>((buf * QT) >> 4), aDOmn = aDOmn0 + static_cast<uint64_t>((buf * QT) >> 4);
 #pragma unroll
           for (int kk = 0; kk < BM / 16; ++kk)     // dV^T += dO^T P
-            tc5::mma_ss(tmem + cDV, tc5::desc_mnmajor(dob + kk * 2048, 2 * HALF), tc5::desc_mnmajor(pb + kk * 2048, 2 * HALF),
-                        id_t, (u > 0 || kk > 0) ? 1u : 0u);
+            tc5::mma_ss(tmem + cDV, aDOmn + static_cast<uint64_t>((kk * 2048) >> 4), bP[kk], id_t, (u > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
           for (int kk = 0; kk < BM / 16; ++kk)     // dK^T += Q^T dS
-            tc5::mma_ss(tmem + cDK, tc5::desc_mnmajor(q + kk * 2048, 2 * HALF), tc5::desc_mnmajor(dsb + kk * 2048, 2 * HALF),
-                        id_t, (u > 0 || kk > 0) ? 1u : 0u);
+            tc5::mma_ss(tmem + cDK, aQmn + static_cast<uint64_t>((kk * 2048) >> 4), bDS[kk], id_t, (u > 0 || kk > 0) ? 1u : 0u);
           tc5::mma_commit(q_empty + buf);
           tc5::mma_commit(p_empty);
         }
@@ -1374,7 +1717,13 @@ extern "C" int nsa_attn_fwd(const void* q, const void* k, const void* v, void* o
   p.O = (bf16*)o; p.L = L;
   const dim3 grid((T + p.R - 1) / p.R, Hkv, B);
   const int smem = (D / 64) * 2 * HALF * 5 + 4 * HALF + 1024 + 2048;
-  if (D == 128) {
+  static const bool legacy = [] { const char* e = getenv("NSA_B200_ATTN_FWD"); return e && !strcmp(e, "legacy"); }();
+  if (D == 128 && !legacy) {
+    const int smem_ws = (4 + 4 * FW_STAGES + 4) * HALF + 1024 + 1024 + 256;
+    static bool cfg = false;
+    if (!cfg) { if ((rc = set_smem(attn_fwd_ws_kernel, smem_ws))) return rc; cfg = true; }
+    attn_fwd_ws_kernel<<<grid, 320, smem_ws, st>>>(tq, tk, tv, p);
+  } else if (D == 128) {
     static bool cfg = false;
     if (!cfg) { if ((rc = set_smem(attn_fwd_kernel<128, 0>, smem))) return rc; cfg = true; }
     attn_fwd_kernel<128, 0><<<grid, 256, smem, st>>>(tq, tk, tv, p);

@@ -331,6 +331,73 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const bf16* __restrict_
 }
 
 // ------------------------------------------------------------------------------------
+// Gated combine of the three sparse-attention branches: o = g1 o1 + g2 o2 + g3 o3 with one gate
+// per (token, head) row.  Backward: do_i = g_i do and dg_i = sum_d do * o_i.  LANES = D / 8 threads
+// share a row (8 elements each); LANES is a power of two <= 32 so a row never straddles a warp.
+// ------------------------------------------------------------------------------------
+template <int LANES>
+__global__ void __launch_bounds__(256) gate_combine_fwd_kernel(const bf16* __restrict__ o1, const bf16* __restrict__ o2,
+                                                               const bf16* __restrict__ o3, const bf16* __restrict__ g1,
+                                                               const bf16* __restrict__ g2, const bf16* __restrict__ g3,
+                                                               bf16* __restrict__ o, long n8) {
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long row = i / LANES;
+    const float a = __bfloat162float(g1[row]), b = __bfloat162float(g2[row]), c = __bfloat162float(g3[row]);
+    float x[8], y[8], z[8], r[8];
+    load8(o1 + i * 8, x);
+    load8(o2 + i * 8, y);
+    load8(o3 + i * 8, z);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r[j] = a * x[j] + b * y[j] + c * z[j];
+    store8(o + i * 8, r);
+  }
+}
+template <int LANES>
+__global__ void __launch_bounds__(256) gate_combine_bwd_kernel(const bf16* __restrict__ o1, const bf16* __restrict__ o2,
+                                                               const bf16* __restrict__ o3, const bf16* __restrict__ g1,
+                                                               const bf16* __restrict__ g2, const bf16* __restrict__ g3,
+                                                               const bf16* __restrict__ d_o, bf16* __restrict__ do1,
+                                                               bf16* __restrict__ do2, bf16* __restrict__ do3,
+                                                               bf16* __restrict__ dg1, bf16* __restrict__ dg2,
+                                                               bf16* __restrict__ dg3, long n8) {
+  // the grid is sized so that every thread handles exactly one vector (rows stay inside a warp)
+  const long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const bool live = i < n8;
+  const long row = (live ? i : 0) / LANES;
+  float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  if (live) {
+    const float a = __bfloat162float(g1[row]), b = __bfloat162float(g2[row]), c = __bfloat162float(g3[row]);
+    float x[8], y[8], z[8], d[8], r[8];
+    load8(o1 + i * 8, x);
+    load8(o2 + i * 8, y);
+    load8(o3 + i * 8, z);
+    load8(d_o + i * 8, d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { s1 += d[j] * x[j]; s2 += d[j] * y[j]; s3 += d[j] * z[j]; }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r[j] = a * d[j];
+    store8(do1 + i * 8, r);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r[j] = b * d[j];
+    store8(do2 + i * 8, r);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r[j] = c * d[j];
+    store8(do3 + i * 8, r);
+  }
+#pragma unroll
+  for (int o = LANES / 2; o > 0; o >>= 1) {
+    s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+    s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+    s3 += __shfl_xor_sync(0xffffffffu, s3, o);
+  }
+  if (live && (threadIdx.x % LANES) == 0) {
+    dg1[row] = __float2bfloat16(s1);
+    dg2[row] = __float2bfloat16(s2);
+    dg3[row] = __float2bfloat16(s3);
+  }
+}
+
+// ------------------------------------------------------------------------------------
 // Rotary embedding, halves layout.  x (tokens T per batch, H heads, D); cos/sin (T, D/2).
 // sign = +1 forward, -1 backward (rotation by the opposite angle).  In-place safe.
 // ------------------------------------------------------------------------------------
@@ -706,6 +773,35 @@ extern "C" int nsa_swiglu_bwd(const void* g, const void* u, const void* dy, void
   const long n8 = rows * (cols / 8);
   swiglu_bwd_kernel<<<grid_for(n8, 256), 256, 0, st>>>((const bf16*)g, (const bf16*)u, (const bf16*)dy, (bf16*)dg, (bf16*)du,
                                                         n8, cols / 8, ldg / 8, ldu / 8, ldo / 8);
+  nsa::count_launch();
+  return 0;
+}
+
+// o, o1..o3: [rows, D] bf16 contiguous; g1..g3: [rows] bf16.  D in {64, 128, 256}.
+extern "C" int nsa_gate_combine_fwd(const void* o1, const void* o2, const void* o3, const void* g1, const void* g2,
+                                    const void* g3, void* o, long rows, int D, cudaStream_t st) {
+  if (D != 64 && D != 128 && D != 256) return nsa::fail(NSA_ERR_SHAPE, "gate_combine: head_dim must be 64, 128 or 256");
+  const long n8 = rows * (D / 8);
+  const int grid = grid_for(n8, 256);
+#define NSA_GC_FWD(L) gate_combine_fwd_kernel<L><<<grid, 256, 0, st>>>((const bf16*)o1, (const bf16*)o2, (const bf16*)o3, \
+    (const bf16*)g1, (const bf16*)g2, (const bf16*)g3, (bf16*)o, n8)
+  if (D == 64) NSA_GC_FWD(8); else if (D == 128) NSA_GC_FWD(16); else NSA_GC_FWD(32);
+#undef NSA_GC_FWD
+  nsa::count_launch();
+  return 0;
+}
+extern "C" int nsa_gate_combine_bwd(const void* o1, const void* o2, const void* o3, const void* g1, const void* g2,
+                                    const void* g3, const void* d_o, void* do1, void* do2, void* do3, void* dg1,
+                                    void* dg2, void* dg3, long rows, int D, cudaStream_t st) {
+  if (D != 64 && D != 128 && D != 256) return nsa::fail(NSA_ERR_SHAPE, "gate_combine: head_dim must be 64, 128 or 256");
+  const long n8 = rows * (D / 8);
+  const long blocks = (n8 + 255) / 256;
+  if (blocks > 2147483647L) return nsa::fail(NSA_ERR_SHAPE, "gate_combine: problem too large for one launch");
+#define NSA_GC_BWD(L) gate_combine_bwd_kernel<L><<<(unsigned)blocks, 256, 0, st>>>((const bf16*)o1, (const bf16*)o2, \
+    (const bf16*)o3, (const bf16*)g1, (const bf16*)g2, (const bf16*)g3, (const bf16*)d_o, (bf16*)do1, (bf16*)do2, (bf16*)do3, \
+    (bf16*)dg1, (bf16*)dg2, (bf16*)dg3, n8)
+  if (D == 64) NSA_GC_BWD(8); else if (D == 128) NSA_GC_BWD(16); else NSA_GC_BWD(32);
+#undef NSA_GC_BWD
   nsa::count_launch();
   return 0;
 }

@@ -65,6 +65,80 @@ int nsa_sumsq(const void* g, long n, int g_fp32, float* partial, float* out, int
 int nsa_cross_entropy(void* logits, const long* labels, float* loss_rows, const float* inv_count, long rows, int V,
                       long ld, long ignore_index, int write_grad, cudaStream_t st);
 
+/* ---- attention family: (B, T, H, D) bf16 tensors, L = log2-sum-exp per row (csrc/attention.cu) ---- */
+int nsa_attn_fwd(const void* q, const void* k, const void* v, void* o, float* L, int B, int T, int S, int Hq, int
+    Hkv, int D, float scale, int causal, int window, int kp_stride, int kp_off, const int* tile_blocks, const unsigned
+    long long* tile_masks, const int* tile_counts, int max_u, cudaStream_t st);
+int nsa_attn_importance(const void* q, const void* k_cmp, const float* L_in, float* imp, int B, int T, int S, int Hq,
+    int Hkv, int D, float scale, int kp_stride, int kp_off, int nS, cudaStream_t st);
+int nsa_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* L, float*
+    delta, void* dq, float* dk, float* dv, int B, int T, int S, int Hq, int Hkv, int D, float scale, int causal, int
+    window, int kp_stride, int kp_off, const int* tile_blocks, const unsigned long long* tile_masks, const int*
+    tile_counts, int max_u, cudaStream_t st);
+int nsa_attn_bwd_split(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* L,
+    float* delta, void* dq, float* dk, float* dv, int B, int T, int S, int Hq, int Hkv, int D, float scale, int causal,
+    int window, int kp_stride, int kp_off, const int* tile_blocks, const unsigned long long* tile_masks, const int*
+    tile_counts, int max_u, const int* tok_list, const int* list_start, const int* item_start, int nS, int item_bound,
+    int visits_per_cta, cudaStream_t st);
+int nsa_union_blocks(const int* idx, int* tile_blocks, unsigned long long* tile_masks, int* tile_counts, int B, int
+    T, int Hkv, int G, int top_n, int nS, int max_u, cudaStream_t st);
+
+/* ---- peer-memory collectives and the IPC arena (csrc/comm.cu) ---- */
+int nsa_enable_peer_access(int peer_device);
+int nsa_comm_signal(unsigned* const* flag_rows, int W, int slot, unsigned epoch, cudaStream_t st);
+int nsa_comm_wait(const unsigned* flags, int n, unsigned epoch, long long max_cycles, cudaStream_t st);
+int nsa_comm_allgather(const void* const* shards, void* out, long shard_bytes, int W, int rank, const unsigned*
+    flags, unsigned epoch, long long max_cycles, int ctas_per_peer, cudaStream_t st);
+int nsa_comm_reduce_scatter_parts(void);
+int nsa_comm_reduce_scatter(const float* const* grads, float* grad_shard, long S, int W, int rank, float scale, int
+    accumulate, float* sumsq_partial, const unsigned* flags, unsigned epoch, long long max_cycles, cudaStream_t st);
+int nsa_comm_rs_adamw8bit(const float* const* grads, void* p_shard, int p_fp32, uint8_t* mq, float* mabs, uint8_t*
+    vq, float* vabs, const float* cb_signed, const float* cb_unsigned, const uint8_t* wd_mask, long S, int W, int rank,
+    float scale, int step, float lr, float b1, float b2, float eps, float wd, const unsigned* flags, unsigned epoch, long
+    long max_cycles, cudaStream_t st);
+int nsa_ipc_alloc(long nbytes, void** out_ptr, unsigned char* handle64);
+int nsa_ipc_open(const unsigned char* handle64, void** out_ptr);
+int nsa_ipc_close(void* p);
+int nsa_ipc_free(void* p);
+
+/* ---- more element-wise kernels (csrc/elementwise.cu) ---- */
+int nsa_gate_combine_fwd(const void* o1, const void* o2, const void* o3, const void* g1, const void* g2, const void*
+    g3, void* o, long rows, int D, cudaStream_t st);
+int nsa_gate_combine_bwd(const void* o1, const void* o2, const void* o3, const void* g1, const void* g2, const void*
+    g3, const void* d_o, void* do1, void* do2, void* do3, void* dg1, void* dg2, void* dg3, long rows, int D, cudaStream_t
+    st);
+
+/* ---- Gated DeltaNet state recurrence (csrc/gdn.cu) ---- */
+int nsa_gdn_seq_fwd(const void* w, const void* qd, const void* kt, const void* u, const float* gamma, void* v_new,
+    float* o_inter, void* S_all, int BH, int NC, int K, int V, cudaStream_t st);
+int nsa_gdn_seq_bwd(const void* w, const void* qd, const void* kt, const void* S_all, const void* v_new, const void*
+    dv_new, const void* d_o, const float* gamma, void* du, void* dw_part, void* dqd_part, void* dkt_part, float*
+    dgamma_part, int BH, int NC, int K, int V, cudaStream_t st);
+
+/* ---- GEMM (csrc/gemm.cu) ---- */
+int nsa_gemm_bf16_ag(const void* A, void* C, int M, int N, int K, int lda, int ldc, const void* const* shards, void*
+    full, long shard_elems, long b_elem_offset, int W, int rank, unsigned* chunk_flags, int chunks_per_shard, const
+    unsigned* peer_flags, unsigned epoch, long long max_cycles, int copy_ctas, cudaStream_t stream);
+
+/* ---- forward-only scan of the complex-state block (csrc/mamba3.cu) ---- */
+int nsa_mamba3_scan(const float* u, const float* dt, const float* A, const float* Bc, const float* Cc, const float*
+    D, float* gate, int B, int L, int H, int N, cudaStream_t st);
+
+/* ---- Mamba-2 SSD chunk kernels (csrc/ssd.cu) ---- */
+int nsa_ssd_state_fwd(const float* S, const float* gamma, float* Hprev, void* Hprev_bf16, float* Hlast, int B, int
+    nc, int H, long E, cudaStream_t st);
+int nsa_ssd_state_bwd(const float* dHprev, const float* gamma, float* dS, void* dS_bf16, int B, int nc, int H, long
+    E, cudaStream_t st);
+int nsa_ssd_chunk_state(int mode, const void* bc, long ld_bc, const void* v, long ld_v, const float* dt, const float*
+    A, float* S_out, float* gamma_out, int B, int T, int H, int N, int P, cudaStream_t st);
+int nsa_ssd_chunk_out(const void* Cm, long ld_c, const void* Bm, long ld_b, const void* x, long ld_x, const void*
+    Hprev_bf16, const float* dt, const float* A, const float* Dskip, void* y, int B, int T, int H, int N, int P,
+    cudaStream_t st);
+int nsa_ssd_chunk_grad(const void* Cm, long ld_c, const void* Bm, long ld_b, const void* x, long ld_x, const void*
+    dy, const void* y, const void* Hprev_bf16, const void* dHn_bf16, const float* dt, const float* A, const float* Dskip,
+    void* dx, float* dB_acc, float* dC_acc, float* q_out, float* k_out, int B, int T, int H, int N, int P, cudaStream_t
+    st);
+
 #ifdef __cplusplus
 }
 #endif

@@ -757,6 +757,35 @@ def nsa_select(imp: Tensor, sel_block: int, top_n: int) -> Tensor:
     return idx.contiguous()
 
 
+class _GateCombine(torch.autograd.Function):
+    """o = g1 o1 + g2 o2 + g3 o3 with one gate per (token, head): the sigmoid-gated combine of the
+    three sparse-attention branches in one pass each way (``csrc/elementwise.cu``)."""
+
+    @staticmethod
+    def forward(ctx, o1, o2, o3, g1, g2, g3):
+        o1, o2, o3 = o1.contiguous(), o2.contiguous(), o3.contiguous()
+        g1, g2, g3 = (g.to(torch.bfloat16).contiguous() for g in (g1, g2, g3))
+        D = o1.shape[-1]
+        rows = o1.numel() // D
+        o = torch.empty_like(o1)
+        _check(load().nsa_gate_combine_fwd(_p(o1), _p(o2), _p(o3), _p(g1), _p(g2), _p(g3), _p(o), c_long(rows), c_int(D),
+                                           _stream()))
+        ctx.save_for_backward(o1, o2, o3, g1, g2, g3)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        o1, o2, o3, g1, g2, g3 = ctx.saved_tensors
+        do = do.contiguous()
+        D = o1.shape[-1]
+        rows = o1.numel() // D
+        d1, d2, d3 = torch.empty_like(o1), torch.empty_like(o1), torch.empty_like(o1)
+        e1, e2, e3 = torch.empty_like(g1), torch.empty_like(g1), torch.empty_like(g1)
+        _check(load().nsa_gate_combine_bwd(_p(o1), _p(o2), _p(o3), _p(g1), _p(g2), _p(g3), _p(do), _p(d1), _p(d2), _p(d3),
+                                           _p(e1), _p(e2), _p(e3), c_long(rows), c_int(D), _stream()))
+        return d1, d2, d3, e1, e2, e3
+
+
 def nsa_attention(q, k, v, g_cmp, g_slc, g_swa, cmp_block=32, cmp_stride=16, sel_block=64, top_n=16,
                   window=512, scale=None):
     B, T, Hq, D = q.shape
@@ -778,6 +807,8 @@ def nsa_attention(q, k, v, g_cmp, g_slc, g_swa, cmp_block=32, cmp_stride=16, sel
         tiles = union_blocks(idx, G, nS) + (idx, nS)
     o_slc = _Attn.apply(q, k, v, True, 0, float(scale), 1, 0, tiles)[0]
     o_swa = _Attn.apply(q, k, v, True, int(window), float(scale), 1, 0, None)[0]
+    if q.dtype == torch.bfloat16 and D in (64, 128, 256):
+        return _GateCombine.apply(o_cmp, o_slc, o_swa, g_cmp, g_slc, g_swa)
     return g_cmp.unsqueeze(-1) * o_cmp + g_slc.unsqueeze(-1) * o_slc + g_swa.unsqueeze(-1) * o_swa
 
 

@@ -119,3 +119,19 @@ def test_backward_atomic_path_still_matches(native, monkeypatch):
     monkeypatch.setenv("NSA_B200_ATTN_BWD", "atomic")
     run_pair(lambda q, k, v: native.attention(q, k, v, True, 0),
              lambda q, k, v: oracle.attention(q, k, v, True, 0), mk(1, 500, 8, 1, 128))
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_gate_combine_matches_torch(native, D):
+    torch.manual_seed(1)
+    rows_shape = (2, 37, 5)
+    o = [torch.randn(*rows_shape, D, device="cuda").bfloat16().requires_grad_(True) for _ in range(3)]
+    g = [torch.rand(*rows_shape, device="cuda").bfloat16().requires_grad_(True) for _ in range(3)]
+    out = native._GateCombine.apply(*o, *g)
+    ref = sum(gi.float().unsqueeze(-1) * oi.float() for gi, oi in zip(g, o))
+    assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2)
+    w = torch.randn_like(out)
+    grads = torch.autograd.grad(out, o + g, w)
+    refs = torch.autograd.grad(ref, o + g, w.float())
+    for a, b in zip(grads, refs):
+        assert torch.allclose(a.float(), b.float(), atol=3e-2 * max(1.0, b.abs().max().item()), rtol=3e-2)
