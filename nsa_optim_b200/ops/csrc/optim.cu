@@ -8,6 +8,8 @@
 //     logits overwritten in place by d(loss)/d(logits).
 // Gradients may be bf16 or fp32; an optional device scalar `grad_scale` multiplies them
 // (clip coefficient), so no host synchronisation is needed between norm and update.
+#include <algorithm>
+
 #include "host.cuh"
 #include <cuda_bf16.h>
 
@@ -205,6 +207,55 @@ AdamArgs make_args(int step, float lr, float b1, float b2, float eps, float wd) 
   a.bc2_sqrt = sqrtf(1.f - powf(b2, (float)step));
   return a;
 }
+// ------------------------------------------------------------------------------------
+// Asymmetric affine block quantisation of SOAP's eigenbases: every row is cut into blocks of
+// q_block columns; a block stores uint8 codes q = round(x / scale + zero) with
+// scale = (max - min) / (2^bits - 1) and zero = round(-min / scale).  One warp per block.
+// Divisions are IEEE (not the fast-math approximations) so the codes match the PyTorch form.
+// ------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) affine_quant_kernel(const float* __restrict__ t, uint8_t* __restrict__ q,
+                                                           float* __restrict__ scale, float* __restrict__ zero, long rows,
+                                                           int cols, int q_block, int nblk, float qmax) {
+  const int lane = threadIdx.x & 31;
+  const long wid = static_cast<long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (wid >= rows * nblk) return;
+  const long row = wid / nblk;
+  const int blk = static_cast<int>(wid - row * nblk);
+  const float* src = t + row * cols;
+  const int c0 = blk * q_block;
+  float lo = INFINITY, hi = -INFINITY;
+  for (int j = lane; j < q_block; j += 32) {
+    const int c = min(c0 + j, cols - 1);            // the padded tail repeats the last column
+    const float x = src[c];
+    lo = fminf(lo, x);
+    hi = fmaxf(hi, x);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+    hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+  }
+  const float sc = fmaxf(__fdiv_rn(hi - lo, qmax), 1e-12f);
+  const float zp = fminf(fmaxf(rintf(__fdiv_rn(-lo, sc)), 0.f), qmax);
+  if (lane == 0) { scale[wid] = sc; zero[wid] = zp; }
+  uint8_t* dst = q + (row * nblk + blk) * static_cast<long>(q_block);
+  for (int j = lane; j < q_block; j += 32) {
+    const int c = min(c0 + j, cols - 1);
+    const float v = fminf(fmaxf(rintf(__fadd_rn(__fdiv_rn(src[c], sc), zp)), 0.f), qmax);
+    dst[j] = static_cast<uint8_t>(v);
+  }
+}
+__global__ void __launch_bounds__(256) affine_dequant_kernel(const uint8_t* __restrict__ q, const float* __restrict__ scale,
+                                                             const float* __restrict__ zero, float* __restrict__ out,
+                                                             long rows, int cols, int q_block, int nblk) {
+  const long n = rows * cols;
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long row = i / cols;
+    const int c = static_cast<int>(i - row * cols);
+    const long b = row * nblk + c / q_block;
+    out[i] = (static_cast<float>(q[row * static_cast<long>(nblk) * q_block + c]) - zero[b]) * scale[b];
+  }
+}
 }  // namespace
 
 // p: bf16 (p_fp32 = 0) or fp32; g: bf16 (g_fp32 = 0) or fp32; m, v fp32; master fp32 or null.
@@ -256,6 +307,28 @@ extern "C" int nsa_cross_entropy(void* logits, const long* labels, float* loss_r
   if (rows <= 0) return 0;
   if (ld % 8) return nsa::fail(NSA_ERR_SHAPE, "cross_entropy: row pitch must be a multiple of 8");
   cross_entropy_kernel<<<(unsigned)rows, 256, 0, st>>>((bf16*)logits, labels, loss_rows, inv_count, V, ld, ignore_index, write_grad);
+  nsa::count_launch();
+  return 0;
+}
+
+// t: [rows, cols] fp32 -> q: [rows, nblk * q_block] uint8, scale / zero: [rows, nblk] with nblk = ceil(cols / q_block).
+extern "C" int nsa_affine_quant(const float* t, uint8_t* q, float* scale, float* zero, long rows, int cols, int q_block,
+                                int bits, cudaStream_t st) {
+  if (rows <= 0 || cols <= 0 || q_block <= 0 || bits < 1 || bits > 8) return nsa::fail(NSA_ERR_SHAPE, "affine_quant: bad shape");
+  const int nblk = (cols + q_block - 1) / q_block;
+  const long warps = rows * nblk;
+  affine_quant_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(t, q, scale, zero, rows, cols, q_block, nblk,
+                                                                   static_cast<float>((1 << bits) - 1));
+  nsa::count_launch();
+  return 0;
+}
+extern "C" int nsa_affine_dequant(const uint8_t* q, const float* scale, const float* zero, float* out, long rows, int cols,
+                                  int q_block, cudaStream_t st) {
+  if (rows <= 0 || cols <= 0 || q_block <= 0) return nsa::fail(NSA_ERR_SHAPE, "affine_dequant: bad shape");
+  const int nblk = (cols + q_block - 1) / q_block;
+  const long n = rows * cols;
+  const long blocks = std::min<long>((n + 255) / 256, 148L * 16);
+  affine_dequant_kernel<<<(unsigned)blocks, 256, 0, st>>>(q, scale, zero, out, rows, cols, q_block, nblk);
   nsa::count_launch();
   return 0;
 }

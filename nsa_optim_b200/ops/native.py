@@ -925,6 +925,28 @@ class _SSD(torch.autograd.Function):
         return (dx, ddt, dA, dB.view(Bsz, T, 1, N).to(torch.bfloat16), dC.view(Bsz, T, 1, N).to(torch.bfloat16), dD)
 
 
+def affine_quantize(t: Tensor, bits: int, q_block: int):
+    """CUDA form of :func:`nsa_optim_b200.ops.quant.affine_quantize` for fp32 matrices."""
+    rows, cols = t.shape
+    nblk = -(-cols // q_block)
+    t = t.float().contiguous()
+    q = torch.empty(rows, nblk * q_block, dtype=torch.uint8, device=t.device)
+    scale = torch.empty(rows, nblk, dtype=torch.float32, device=t.device)
+    zero = torch.empty(rows, nblk, dtype=torch.float32, device=t.device)
+    _check(load().nsa_affine_quant(_p(t), _p(q), _p(scale), _p(zero), c_long(rows), c_int(cols), c_int(q_block), c_int(bits),
+                                   _stream()))
+    return q, scale, zero, cols
+
+
+def affine_dequantize(q: Tensor, scale: Tensor, zero: Tensor, orig_cols: int) -> Tensor:
+    rows = q.shape[0]
+    q_block = q.shape[1] // scale.shape[1]
+    out = torch.empty(rows, orig_cols, dtype=torch.float32, device=q.device)
+    _check(load().nsa_affine_dequant(_p(q.contiguous()), _p(scale.contiguous()), _p(zero.contiguous()), _p(out), c_long(rows),
+                                     c_int(orig_cols), c_int(q_block), _stream()))
+    return out
+
+
 def mamba3_gate(u: Tensor, dt: Tensor, A: Tensor, Bc: Tensor, Cc: Tensor, D: Tensor) -> Tensor:
     """Forward-only sequential scan of the complex-state SSM (``csrc/mamba3.cu``).
     u, dt (B, L, H) ; A (H, N, 2) ; Bc, Cc (B, L, H, N, 2) ; D (H)  ->  gate (B, L, H) fp32 with

@@ -95,11 +95,19 @@ def dequantize_blockwise(codes: Tensor, absmax: Tensor, bits: int, signed: bool,
     return (vals * absmax[:, None]).reshape(-1)
 
 
+def _native_ok() -> bool:
+    from . import get_backend
+    return get_backend() != "torch"
+
+
 # ------------------------------------------------------------------ affine sub-row codec
 def affine_quantize(t: Tensor, bits: int, q_block: int) -> Tuple[Tensor, Tensor, Tensor, int]:
     """2-D ``t`` -> (uint8 codes [rows, cols_padded], scale [rows, nblk], zero_point [rows, nblk],
     original column count)."""
     rows, cols = t.shape
+    if t.is_cuda and _native_ok():
+        from . import native
+        return native.affine_quantize(t, bits, q_block)
     pad = (-cols) % q_block
     tp = F.pad(t.float(), (0, pad)) if pad else t.float()
     if pad:
@@ -115,6 +123,9 @@ def affine_quantize(t: Tensor, bits: int, q_block: int) -> Tuple[Tensor, Tensor,
 
 
 def affine_dequantize(q: Tensor, scale: Tensor, zero_point: Tensor, orig_cols: int) -> Tensor:
+    if q.is_cuda and q.dim() == 2 and scale.dim() == 2 and _native_ok():
+        from . import native
+        return native.affine_dequantize(q, scale, zero_point, orig_cols)
     rows = q.shape[0]
     nblk = scale.shape[1]
     blk = q.reshape(rows, nblk, -1).float()

@@ -168,3 +168,22 @@ def test_adamw8bit_kernel_matches_torch_codec(native):
     md = quant.dequantize_blockwise(mq, mabs, 8, True, 256)
     vd = quant.dequantize_blockwise(vq, vabs, 8, False, 256)
     close(md, mr, 2e-2, 1e-3); close(vd, vr, 2e-2, 1e-3); close(p, pr, 2e-2, 2e-2)
+
+
+@pytest.mark.parametrize("cols,q_block,bits", [(256, 64, 4), (100, 32, 8), (70, 64, 4)])
+def test_affine_block_quant_matches_torch_form(native, cols, q_block, bits):
+    """The CUDA affine codec of SOAP's eigenbases against the PyTorch form (same codes, scales, zeros)."""
+    from nsa_optim_b200 import ops
+    from nsa_optim_b200.ops import quant
+    torch.manual_seed(0)
+    t = torch.randn(37, cols, device="cuda")
+    q, sc, zp, oc = quant.affine_quantize(t, bits, q_block)
+    with ops.backend("torch"):
+        q2, sc2, zp2, oc2 = quant.affine_quantize(t, bits, q_block)
+        back2 = quant.affine_dequantize(q2, sc2, zp2, oc2)
+    assert oc == oc2 and torch.allclose(sc, sc2, rtol=1e-6) and torch.equal(zp, zp2)
+    assert (q[:, :cols].int() - q2[:, :cols].int()).abs().max() <= 1          # a tie may round either way
+    assert (q[:, :cols] != q2[:, :cols]).float().mean() < 1e-3
+    back = quant.affine_dequantize(q, sc, zp, oc)
+    assert back.shape == (37, cols) and torch.allclose(back, back2, atol=float(sc.max()) * 1.01)
+    assert (back - t).abs().max() <= float(sc.max()) * 0.51 + 1e-6

@@ -117,3 +117,21 @@ def test_affine_roundtrip(bits, tol):
     assert q.dtype == torch.uint8 and cols == 70 and q.shape == (70, 96)
     back = quant.affine_dequantize(q, s, z, cols)
     assert (back - q_in).abs().max() < tol
+
+
+def test_inverse_selection_map_lists_tokens_per_block():
+    """inverse_blocks: for every (batch, head, block) the ascending tokens that selected it,
+    duplicates and invalid entries dropped, plus a CTA bound that covers the work items."""
+    from nsa_optim_b200.ops import native
+    torch.manual_seed(0)
+    B, Hkv, T, n, nS, R, C = 2, 2, 300, 4, 5, 8, 3
+    idx = torch.randint(-1, nS, (B, Hkv, T, n), dtype=torch.int32)
+    tok, ls, its, ns_out, bound = native.inverse_blocks(idx, nS, R, C)
+    assert ns_out == nS and int(its[-1]) <= bound
+    for b in range(B):
+        for h in range(Hkv):
+            for blk in range(nS):
+                l = (b * Hkv + h) * nS + blk
+                want = [t for t in range(T) if blk in idx[b, h, t].tolist()]
+                assert tok[ls[l]:ls[l + 1]].tolist() == want
+                assert int(its[l + 1] - its[l]) == -(-(-(-len(want) // R)) // C)
