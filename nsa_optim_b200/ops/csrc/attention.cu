@@ -1586,6 +1586,67 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 }
 
 // --------------------------------------------------------------------------------------
+// Top-n block selection.  One warp per (batch, KV head, token) row of the importance tensor:
+// block 0, the token's own block and the one before it are always taken; the remaining slots go
+// to the causal blocks of highest importance (ties: lower block index first); slots that cannot
+// be filled hold -1.  Lane l keeps blocks l, l + 32, ... in registers; every round is a
+// lane-local scan plus a five-step warp arg-max.
+// --------------------------------------------------------------------------------------
+template <int PER_LANE>
+__global__ void __launch_bounds__(256) nsa_select_kernel(const float* __restrict__ imp, int* __restrict__ idx, long rows,
+                                                         int T, int nS, int sel_block, int top_n) {
+  const int lane = threadIdx.x & 31;
+  const long row = static_cast<long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int t = static_cast<int>(row % T);
+  const int own = min(t / sel_block, nS - 1);
+  const float* src = imp + row * nS;
+  float v[PER_LANE];
+#pragma unroll
+  for (int k = 0; k < PER_LANE; ++k) {
+    const int j = lane + 32 * k;
+    v[k] = (j <= own) ? src[j] : -INFINITY;
+    if (j == 0 || j == own || j == own - 1) v[k] = -INFINITY;       // forced blocks are emitted below
+  }
+  int* dst = idx + row * top_n;
+  int n_out = 0;
+  if (lane == 0) {
+    dst[n_out] = 0;
+    if (own > 0 && n_out + 1 < top_n) dst[n_out + 1] = own;
+    if (own > 1 && n_out + 2 < top_n) dst[n_out + 2] = own - 1;
+  }
+  n_out = min(top_n, 1 + (own > 0 ? 1 : 0) + (own > 1 ? 1 : 0));
+  const int candidates = max(0, own + 1 - n_out);                     // causal blocks that are not forced
+  const int rounds = min(top_n - n_out, candidates);
+  for (int rd = 0; rd < rounds; ++rd) {
+    float best = -INFINITY;
+    int bk = -1;
+#pragma unroll
+    for (int k = 0; k < PER_LANE; ++k)
+      if (v[k] > best) {                                              // strict: the lowest index wins a tie
+        best = v[k];
+        bk = k;
+      }
+    int bj = bk < 0 ? 0x7fffffff : lane + 32 * bk;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oj = __shfl_xor_sync(0xffffffffu, bj, o);
+      if (ob > best || (ob == best && oj < bj)) { best = ob; bj = oj; }
+    }
+    if (bj == 0x7fffffff) break;                                      // only -inf importances left (cannot happen for finite input)
+    if ((bj & 31) == lane) {
+#pragma unroll
+      for (int k = 0; k < PER_LANE; ++k)
+        if (k == (bj >> 5)) v[k] = -INFINITY;
+    }
+    if (lane == 0) dst[n_out] = bj;
+    ++n_out;
+  }
+  for (int i = n_out + lane; i < top_n; i += 32) dst[i] = -1;
+}
+
+// --------------------------------------------------------------------------------------
 // Helper kernels
 // --------------------------------------------------------------------------------------
 // delta[row] = sum_d dO[row, d] * O[row, d]; one warp per row.
@@ -1863,6 +1924,18 @@ extern "C" int nsa_attn_bwd_split(const void* q, const void* k, const void* v, c
   nsa::count_launch(3);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : nsa::fail_cuda(e, "nsa_attn_bwd_split launch");
+}
+
+// imp [B, Hkv, T, nS] fp32 -> idx [B, Hkv, T, top_n] int32 (see nsa_select_kernel).  nS <= 2048.
+extern "C" int nsa_select_blocks(const float* imp, int* idx, long rows, int T, int nS, int sel_block, int top_n,
+                                 cudaStream_t st) {
+  if (nS <= 0 || nS > 2048 || top_n <= 0 || sel_block <= 0) return nsa::fail(NSA_ERR_SHAPE, "select_blocks: nS must be in 1..2048");
+  const unsigned grid = static_cast<unsigned>((rows + 7) / 8);
+  if (nS <= 1024) nsa_select_kernel<32><<<grid, 256, 0, st>>>(imp, idx, rows, T, nS, sel_block, top_n);
+  else nsa_select_kernel<64><<<grid, 256, 0, st>>>(imp, idx, rows, T, nS, sel_block, top_n);
+  nsa::count_launch();
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : nsa::fail_cuda(e, "nsa_select_blocks launch");
 }
 
 // idx [B, Hkv, T, top_n] int32 -> per query tile (R = 128 / G tokens): block list, token masks, count.

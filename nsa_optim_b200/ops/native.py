@@ -743,7 +743,19 @@ def nsa_importance(q, k_cmp, L_cmp, nS, stride, block, scale):
 
 def nsa_select(imp: Tensor, sel_block: int, top_n: int) -> Tensor:
     """imp (B, Hkv, T, nS) -> int32 (B, Hkv, T, top_n): block 0, the query's own block and the one
-    before it always, then the most important causal blocks; -1 where fewer are visible."""
+    before it always, then the most important causal blocks (ties: lower index); -1 where fewer
+    are visible.  One warp per row (``nsa_select_kernel``); more than 2048 blocks use torch.topk."""
+    B, H, T, nS = imp.shape
+    if imp.is_cuda and nS <= 2048 and imp.dtype == torch.float32:
+        imp = imp.contiguous()
+        idx = torch.empty(B, H, T, top_n, dtype=torch.int32, device=imp.device)
+        _check(load().nsa_select_blocks(_p(imp), _p(idx), c_long(B * H * T), c_int(T), c_int(nS), c_int(sel_block),
+                                        c_int(top_n), _stream()))
+        return idx
+    return _nsa_select_torch(imp, sel_block, top_n)
+
+
+def _nsa_select_torch(imp: Tensor, sel_block: int, top_n: int) -> Tensor:
     B, H, T, nS = imp.shape
     own = (torch.arange(T, device=imp.device) // sel_block)[:, None]
     j = torch.arange(nS, device=imp.device)[None, :]

@@ -135,3 +135,19 @@ def test_gate_combine_matches_torch(native, D):
     refs = torch.autograd.grad(ref, o + g, w.float())
     for a, b in zip(grads, refs):
         assert torch.allclose(a.float(), b.float(), atol=3e-2 * max(1.0, b.abs().max().item()), rtol=3e-2)
+
+
+@pytest.mark.parametrize("T,top_n", [(700, 5), (64 * 40, 16), (100, 16)])
+def test_block_selection_kernel_matches_topk(native, T, top_n):
+    """The warp-per-row selection against the torch.topk form: same set of blocks per row
+    (random importances have no ties)."""
+    torch.manual_seed(2)
+    nS = -(-T // 64)
+    imp = torch.rand(2, 2, T, nS, device="cuda")
+    got = native.nsa_select(imp, 64, top_n)
+    want = native._nsa_select_torch(imp, 64, top_n)
+    assert got.shape == want.shape and got.dtype == torch.int32
+    assert torch.equal(got.sort(-1).values, want.sort(-1).values)
+    # forced blocks first, never a future block
+    t = torch.arange(T, device="cuda")
+    assert (got[..., 0] == 0).all() and (got.max(-1).values <= (t // 64)).all()
