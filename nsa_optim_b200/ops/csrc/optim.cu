@@ -210,7 +210,7 @@ AdamArgs make_args(int step, float lr, float b1, float b2, float eps, float wd) 
 // ------------------------------------------------------------------------------------
 // Asymmetric affine block quantisation of SOAP's eigenbases: every row is cut into blocks of
 // q_block columns; a block stores uint8 codes q = round(x / scale + zero) with
-// scale = (max - min) / (2^bits - 1) and zero = round(-min / scale).  One warp per block.
+// scale = (max - min) / (2^bits - 1) and zero = round(-min / scale) kept as a float.  One warp per block.
 // Divisions are IEEE (not the fast-math approximations) so the codes match the PyTorch form.
 // ------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) affine_quant_kernel(const float* __restrict__ t, uint8_t* __restrict__ q,
@@ -236,7 +236,7 @@ __global__ void __launch_bounds__(256) affine_quant_kernel(const float* __restri
     hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o));
   }
   const float sc = fmaxf(__fdiv_rn(hi - lo, qmax), 1e-12f);
-  const float zp = fminf(fmaxf(rintf(__fdiv_rn(-lo, sc)), 0.f), qmax);
+  const float zp = rintf(__fdiv_rn(-lo, sc));        // not clamped: a one-signed block has its zero outside the code range
   if (lane == 0) { scale[wid] = sc; zero[wid] = zp; }
   uint8_t* dst = q + (row * nblk + blk) * static_cast<long>(q_block);
   for (int j = lane; j < q_block; j += 32) {

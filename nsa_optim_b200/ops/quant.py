@@ -117,7 +117,10 @@ def affine_quantize(t: Tensor, bits: int, q_block: int) -> Tuple[Tensor, Tensor,
     lo, hi = blk.amin(-1), blk.amax(-1)
     qmax = float(2 ** bits - 1)
     scale = ((hi - lo) / qmax).clamp_min(1e-12)
-    zp = torch.round(-lo / scale).clamp_(0, qmax)
+    # The zero point is kept as a float and NOT clamped to the code range: a block whose values are
+    # all of one sign has its zero outside [0, qmax], and clamping it (as integer-zero-point codecs
+    # do) would saturate the whole block.
+    zp = torch.round(-lo / scale)
     q = torch.round(blk / scale[..., None] + zp[..., None]).clamp_(0, qmax).to(torch.uint8)
     return q.reshape(rows, -1), scale, zp, cols
 
@@ -138,7 +141,7 @@ def affine_quantize_tensor(t: Tensor, bits: int) -> Tuple[Tensor, Tensor, Tensor
     lo, hi = t.float().min(), t.float().max()
     qmax = float(2 ** bits - 1)
     scale = ((hi - lo) / qmax).clamp_min(1e-12)
-    zp = torch.round(-lo / scale).clamp_(0, qmax)
+    zp = torch.round(-lo / scale)
     q = torch.round(t.float() / scale + zp).clamp_(0, qmax).to(torch.uint8)
     return q, scale, zp, None
 
