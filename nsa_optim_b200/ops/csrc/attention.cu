@@ -1332,8 +1332,11 @@ attn_bwd_dq_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   uint64_t* kv_empty = kv_full + DQT_STAGES;      // [stages] MMA -> TMA
   uint64_t* s_full = kv_empty + DQT_STAGES;       // [2] MMA -> softmax
   uint64_t* s_empty = s_full + 2;                // [2] softmax -> MMA
-  uint64_t* ds_full = s_empty + 2;               // softmax -> MMA
-  uint64_t* qt_full = ds_full + 1;               // softmax -> MMA: Q and dO are in tensor memory
+  // One dS barrier per S buffer: warps whose rows are all masked finish a visit early and may
+  // already be in the next visit (other buffer); with a single barrier their second arrival
+  // would complete the phase of the visit the slower warps are still writing.
+  uint64_t* ds_full = s_empty + 2;               // [2] softmax -> MMA
+  uint64_t* qt_full = ds_full + 2;               // softmax -> MMA: Q and dO are in tensor memory
   uint64_t* acc_done = qt_full + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -1371,6 +1374,7 @@ attn_bwd_dq_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     for (int i = 0; i < DQT_STAGES; ++i) { tc5::mbar_init(kv_full + i, 1); tc5::mbar_init(kv_empty + i, 1); }
     for (int i = 0; i < 2; ++i) { tc5::mbar_init(s_full + i, 1); tc5::mbar_init(s_empty + i, 1); }
     tc5::mbar_init(ds_full, 256);
+    tc5::mbar_init(ds_full + 1, 256);
     tc5::mbar_init(qt_full, 256);
     tc5::mbar_init(acc_done, 1);
     tc5::fence_barrier_init();
@@ -1460,7 +1464,7 @@ attn_bwd_dq_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         }
         if (v >= 1) {
           const int u = v - 1, st = u % DQT_STAGES, buf = u & 1;
-          if (!tc5::mbar_wait(ds_full, u & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+          if (!tc5::mbar_wait(ds_full + buf, (u >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
           tc5::fence_after_sync();
           const uint64_t bKmn = bKmn0 + static_cast<uint64_t>((st * 4 * HALF) >> 4);
 #pragma unroll
@@ -1553,7 +1557,7 @@ attn_bwd_dq_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       tc5::tmem_st_x16(tmem + lane_off + buf * 128 + ch * 32, ds);
       tc5::tmem_st_wait();
       tc5::fence_before_sync();
-      tc5::mbar_arrive(ds_full);
+      tc5::mbar_arrive(ds_full + buf);
     }
     // ---- dQ: thread (r, ch) stores D-half ch of row r
     const bool have = __all_sync(0xffffffffu, ok && n_vis > 0 &&
@@ -2521,8 +2525,7 @@ extern "C" int nsa_attn_bwd_split(const void* q, const void* k, const void* v, c
   p.L = const_cast<float*>(L); p.delta = delta; p.dQb = (bf16*)dq; p.dK = nullptr; p.dV = nullptr;
   {
     const dim3 grid((T + p.R - 1) / p.R, Hkv, B);
-    // the TMEM-operand variant is opt-in (NSA_B200_ATTN_DQ=tmem) until it passes every shape of the test-suite
-    static const bool smem_operands = [] { const char* e = getenv("NSA_B200_ATTN_DQ"); return !(e && !strcmp(e, "tmem")); }();
+    static const bool smem_operands = [] { const char* e = getenv("NSA_B200_ATTN_DQ"); return e && !strcmp(e, "smem"); }();
     if (!smem_operands) {
       const int smem = (8 + 4 * DQT_STAGES) * HALF + 1024 + 256;
       static bool cfg = false;
