@@ -398,6 +398,104 @@ __global__ void __launch_bounds__(256) gate_combine_bwd_kernel(const bf16* __res
 }
 
 // ------------------------------------------------------------------------------------
+// Gated DeltaNet layout pass.  q, k (B, T, H, 128) and v (B, T, H, V) arrive token-major; the
+// chunk kernels want head-major rows (B*H, Tp, .) with Tp the padded length.  One warp per row
+// writes the copies qh, kh, vh and the decay-scaled operands qd = q * sq, kt = k * sk in one pass
+// (rows >= T are zero).  The backward folds the five incoming gradients back to token-major and
+// reduces d sq = sum(dqd * q), d sk = sum(dkt * k).
+// ------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) gdn_pack_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
+                                                           const bf16* __restrict__ v, const float* __restrict__ sq,
+                                                           const float* __restrict__ sk, bf16* __restrict__ qh,
+                                                           bf16* __restrict__ kh, bf16* __restrict__ vh,
+                                                           bf16* __restrict__ qd, bf16* __restrict__ kt, int B, int T,
+                                                           int Tp, int H, int V) {
+  constexpr int K = 128;
+  const int lane = threadIdx.x & 31;
+  const long row = static_cast<long>(blockIdx.x) * 8 + (threadIdx.x >> 5);     // (b*H + h) * Tp + t
+  if (row >= static_cast<long>(B) * H * Tp) return;
+  const int t = static_cast<int>(row % Tp);
+  const long bh = row / Tp;
+  const int h = static_cast<int>(bh % H);
+  const long b = bh / H;
+  const bool live = t < T;
+  const long tok = (b * T + (live ? t : 0)) * H + h;
+  float x[8], y[8];
+  const int part = lane >> 4, c = (lane & 15) * 8;                             // lanes 0-15: q, 16-31: k
+  const bf16* src = (part ? k : q) + tok * K + c;
+  const float s = live ? (part ? sk : sq)[row] : 0.f;
+  if (live) load8(src, x);
+  else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] = 0.f;
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) y[j] = x[j] * s;
+  store8((part ? kh : qh) + row * K + c, x);
+  store8((part ? kt : qd) + row * K + c, y);
+  for (int cv = lane * 8; cv < V; cv += 256) {
+    if (live) load8(v + tok * V + cv, x);
+    store8(vh + row * V + cv, x);            // x is zero on padded rows
+  }
+}
+__global__ void __launch_bounds__(256) gdn_pack_bwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
+                                                           const float* __restrict__ sq, const float* __restrict__ sk,
+                                                           const bf16* __restrict__ dqh, const bf16* __restrict__ dkh,
+                                                           const bf16* __restrict__ dvh, const bf16* __restrict__ dqd,
+                                                           const bf16* __restrict__ dkt, bf16* __restrict__ dq,
+                                                           bf16* __restrict__ dk, bf16* __restrict__ dv,
+                                                           float* __restrict__ dsq, float* __restrict__ dsk, int B, int T,
+                                                           int Tp, int H, int V) {
+  constexpr int K = 128;
+  const int lane = threadIdx.x & 31;
+  const long row = static_cast<long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (row >= static_cast<long>(B) * H * Tp) return;
+  const int t = static_cast<int>(row % Tp);
+  const long bh = row / Tp;
+  const int h = static_cast<int>(bh % H);
+  const long b = bh / H;
+  const int part = lane >> 4, c = (lane & 15) * 8;
+  if (t >= T) {                                                                // padded row: no token, zero scale gradients
+    if ((lane & 15) == 0) (part ? dsk : dsq)[row] = 0.f;
+    return;
+  }
+  const long tok = (b * T + t) * H + h;
+  float x[8], g1[8], g2[8], o[8];
+  load8((part ? k : q) + tok * K + c, x);
+  const bf16* a = part ? dkh : dqh;
+  const bf16* d = part ? dkt : dqd;
+  if (a) load8(a + row * K + c, g1);
+  else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) g1[j] = 0.f;
+  }
+  if (d) load8(d + row * K + c, g2);
+  else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) g2[j] = 0.f;
+  }
+  const float s = (part ? sk : sq)[row];
+  float dot = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    o[j] = g1[j] + g2[j] * s;
+    dot += g2[j] * x[j];
+  }
+  store8((part ? dk : dq) + tok * K + c, o);
+#pragma unroll
+  for (int m = 8; m > 0; m >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, m);   // within each half-warp
+  if ((lane & 15) == 0) (part ? dsk : dsq)[row] = dot;
+  for (int cv = lane * 8; cv < V; cv += 256) {
+    if (dvh) load8(dvh + row * V + cv, o);
+    else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = 0.f;
+    }
+    store8(dv + tok * V + cv, o);
+  }
+}
+
+// ------------------------------------------------------------------------------------
 // Rotary embedding, halves layout.  x (tokens T per batch, H heads, D); cos/sin (T, D/2).
 // sign = +1 forward, -1 backward (rotation by the opposite angle).  In-place safe.
 // ------------------------------------------------------------------------------------
@@ -802,6 +900,31 @@ extern "C" int nsa_gate_combine_bwd(const void* o1, const void* o2, const void* 
     (bf16*)dg1, (bf16*)dg2, (bf16*)dg3, n8)
   if (D == 64) NSA_GC_BWD(8); else if (D == 128) NSA_GC_BWD(16); else NSA_GC_BWD(32);
 #undef NSA_GC_BWD
+  nsa::count_launch();
+  return 0;
+}
+
+// q, k: [B, T, H, 128]; v: [B, T, H, V] (V multiple of 8); sq, sk: [B*H, Tp] fp32;
+// outputs [B*H, Tp, 128 or V] bf16.
+extern "C" int nsa_gdn_pack_fwd(const void* q, const void* k, const void* v, const float* sq, const float* sk, void* qh,
+                                void* kh, void* vh, void* qd, void* kt, int B, int T, int Tp, int H, int K, int V,
+                                cudaStream_t st) {
+  if (K != 128 || V % 8 || Tp < T) return nsa::fail(NSA_ERR_SHAPE, "gdn_pack: key width 128 and value width multiple of 8 required");
+  const long rows = static_cast<long>(B) * H * Tp;
+  gdn_pack_fwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, sq, sk, (bf16*)qh,
+                                                                  (bf16*)kh, (bf16*)vh, (bf16*)qd, (bf16*)kt, B, T, Tp, H, V);
+  nsa::count_launch();
+  return 0;
+}
+// dqh, dkh, dvh, dqd, dkt may be null (treated as zero).  dq, dk, dv: token-major outputs; dsq, dsk: [B*H, Tp] fp32.
+extern "C" int nsa_gdn_pack_bwd(const void* q, const void* k, const float* sq, const float* sk, const void* dqh,
+                                const void* dkh, const void* dvh, const void* dqd, const void* dkt, void* dq, void* dk,
+                                void* dv, float* dsq, float* dsk, int B, int T, int Tp, int H, int K, int V, cudaStream_t st) {
+  if (K != 128 || V % 8 || Tp < T) return nsa::fail(NSA_ERR_SHAPE, "gdn_pack: key width 128 and value width multiple of 8 required");
+  const long rows = static_cast<long>(B) * H * Tp;
+  gdn_pack_bwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const bf16*)q, (const bf16*)k, sq, sk, (const bf16*)dqh,
+                                                                  (const bf16*)dkh, (const bf16*)dvh, (const bf16*)dqd, (const bf16*)dkt,
+                                                                  (bf16*)dq, (bf16*)dk, (bf16*)dv, dsq, dsk, B, T, Tp, H, V);
   nsa::count_launch();
   return 0;
 }

@@ -560,29 +560,65 @@ class _GDNSeq(torch.autograd.Function):
         return red[0], red[1], red[2], du, dgp.sum(0)
 
 
+class _GDNPack(torch.autograd.Function):
+    """Token-major q, k, v -> head-major chunk rows (B*H, Tp, .): copies qh, kh, vh and the
+    decay-scaled operands qd = q * sq, kt = k * sk in one pass each way (``csrc/elementwise.cu``)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, sq, sk):
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        sq, sk = sq.float().contiguous(), sk.float().contiguous()
+        B, T, H, K = q.shape
+        V = v.shape[-1]
+        Tp = sq.shape[-1]
+        mk = lambda w: torch.empty(B * H, Tp, w, dtype=torch.bfloat16, device=q.device)
+        qh, kh, vh, qd, kt = mk(K), mk(K), mk(V), mk(K), mk(K)
+        _check(load().nsa_gdn_pack_fwd(_p(q), _p(k), _p(v), _p(sq), _p(sk), _p(qh), _p(kh), _p(vh), _p(qd), _p(kt),
+                                       c_int(B), c_int(T), c_int(Tp), c_int(H), c_int(K), c_int(V), _stream()))
+        ctx.save_for_backward(q, k, sq, sk)
+        ctx.V = V
+        return qh, kh, vh, qd, kt
+
+    @staticmethod
+    def backward(ctx, dqh, dkh, dvh, dqd, dkt):
+        q, k, sq, sk = ctx.saved_tensors
+        B, T, H, K = q.shape
+        V, Tp = ctx.V, sq.shape[-1]
+        c = lambda t: None if t is None else t.to(torch.bfloat16).contiguous()
+        dqh, dkh, dvh, dqd, dkt = c(dqh), c(dkh), c(dvh), c(dqd), c(dkt)
+        dq, dk = torch.empty_like(q), torch.empty_like(k)
+        dv = torch.empty(B, T, H, V, dtype=torch.bfloat16, device=q.device)
+        dsq, dsk = torch.empty_like(sq), torch.empty_like(sk)
+        _check(load().nsa_gdn_pack_bwd(_p(q), _p(k), _p(sq), _p(sk), _p(dqh), _p(dkh), _p(dvh), _p(dqd), _p(dkt), _p(dq), _p(dk),
+                                       _p(dv), _p(dsq), _p(dsk), c_int(B), c_int(T), c_int(Tp), c_int(H), c_int(K), c_int(V),
+                                       _stream()))
+        return dq, dk, dv, dsq, dsk
+
+
 def gated_delta_rule(q, k, v, g, beta, scale=None, chunk=64):
-    """Chunkwise gated delta rule.  The per-chunk WY pre-pass and the intra-chunk output term
-    are batched PyTorch ops over all chunks at once; the sequential state pass is native."""
+    """Chunkwise gated delta rule.  One layout pass brings q, k, v to head-major chunk rows together
+    with the decay-scaled operands; the 64 x 64 per-chunk matrices (K K^T, the unit-triangular
+    inverse, Q K^T) are batched PyTorch ops; the sequential state pass is native."""
     B, T, H, K = q.shape
     V = v.shape[-1]
-    if K != 128 or V % 64 or chunk != 64:
+    if K != 128 or V % 64 or chunk != 64 or q.dtype != torch.bfloat16:
         return torch_impl.gated_delta_rule(q, k, v, g, beta, scale, chunk)
     scale = K ** -0.5 if scale is None else scale
     C = 64
     pad = (-T) % C
-    if pad:
-        q, k, v = (torch.nn.functional.pad(t, (0, 0, 0, 0, 0, pad)) for t in (q, k, v))
-        g, beta = torch.nn.functional.pad(g, (0, 0, 0, pad)), torch.nn.functional.pad(beta, (0, 0, 0, pad))
     Tp = T + pad
     nc = Tp // C
     f32, bf = torch.float32, torch.bfloat16
-    qh = q.permute(0, 2, 1, 3).reshape(B * H, nc, C, K)
-    kh = k.permute(0, 2, 1, 3).reshape(B * H, nc, C, K)
-    vh = v.permute(0, 2, 1, 3).reshape(B * H, nc, C, V)
-    gh = g.to(f32).permute(0, 2, 1).reshape(B * H, nc, C)
-    bh = beta.to(f32).permute(0, 2, 1).reshape(B * H, nc, C)
+    gh = g.to(f32).permute(0, 2, 1)
+    bh = beta.to(f32).permute(0, 2, 1)
+    if pad:
+        gh, bh = torch.nn.functional.pad(gh, (0, pad)), torch.nn.functional.pad(bh, (0, pad))
+    gh, bh = gh.reshape(B * H, nc, C), bh.reshape(B * H, nc, C)
     gc = torch.cumsum(gh, -1)
     eg = torch.exp(gc)
+    sq = (scale * eg).reshape(B * H, Tp)
+    sk = torch.exp(gc[..., -1:] - gc).reshape(B * H, Tp)
+    qh, kh, vh, qd, kt = (t.view(B * H, nc, C, -1) for t in _GDNPack.apply(q, k, v.to(bf), sq, sk))
     incl = torch.ones(C, C, dtype=torch.bool, device=q.device).tril(0)
     decay = torch.exp((gc[..., :, None] - gc[..., None, :]).masked_fill(~incl, float("-inf")))   # 1 on the diagonal
     eye = torch.eye(C, device=q.device, dtype=f32)
@@ -594,12 +630,11 @@ def gated_delta_rule(q, k, v, g, beta, scale=None, chunk=64):
     u = torch.matmul((Tm * bh[..., None, :]).to(bf), vh)
     w = torch.matmul((Tm * (bh * eg)[..., None, :]).to(bf), kh)
     qk = (torch.matmul(qh, kh.transpose(-1, -2)).to(f32) * scale * decay).to(bf)
-    qd = (qh * (scale * eg)[..., None]).to(bf).contiguous()
-    kt = (kh * torch.exp(gc[..., -1:] - gc)[..., None]).to(bf).contiguous()
     gamma = eg[..., -1].contiguous()
     v_new, o_inter = _GDNSeq.apply(w, qd, kt, u, gamma)
-    o = o_inter + torch.matmul(qk, v_new).to(f32)
-    o = o.reshape(B, H, Tp, V).permute(0, 2, 1, 3)[:, :T]
+    # o = o_inter + qk v_new in one batched GEMM with fp32 accumulation
+    o = torch.baddbmm(o_inter.to(bf).view(-1, C, V), qk.view(-1, C, C), v_new.view(-1, C, V))
+    o = o.view(B, H, Tp, V).permute(0, 2, 1, 3)[:, :T]
     return o.to(v.dtype)
 
 
