@@ -496,6 +496,195 @@ __global__ void __launch_bounds__(256) gdn_pack_bwd_kernel(const bf16* __restric
 }
 
 // ------------------------------------------------------------------------------------
+// Gated DeltaNet per-chunk matrices (chunk 64), one CTA of 64 threads per chunk.
+//   A[i][j] = beta_i * kk[i][j] * exp(gc_i - gc_j)   (i > j)       kk = K K^T of the chunk
+//   X = (I + A)^-1    by forward substitution, thread c owning column c in registers
+//   Tu = X diag(beta),  Tw = X diag(beta * exp(gc)),  qk[i][j] = scale * qkr[i][j] * exp(gc_i - gc_j)  (i >= j)
+// The backward takes dA = -(X^T dX X^T) (two batched matmuls done by the caller) and folds it,
+// together with dTu, dTw, dqk, into dkk, dqkr, d gc and d beta.
+// ------------------------------------------------------------------------------------
+constexpr int GC = 64;
+
+__device__ __forceinline__ void load_row64(const bf16* p, float (&v)[GC]) {
+#pragma unroll
+  for (int j = 0; j < GC / 8; ++j) {
+    float t[8];
+    load8(p + 8 * j, t);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[8 * j + e] = t[e];
+  }
+}
+__device__ __forceinline__ void store_row64(bf16* p, const float (&v)[GC]) {
+#pragma unroll
+  for (int j = 0; j < GC / 8; ++j) {
+    float t[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) t[e] = v[8 * j + e];
+    store8(p + 8 * j, t);
+  }
+}
+
+__global__ void __launch_bounds__(64) gdn_tmat_fwd_kernel(const bf16* __restrict__ kk, const bf16* __restrict__ qkr,
+                                                          const float* __restrict__ gc, const float* __restrict__ beta,
+                                                          bf16* __restrict__ Tu, bf16* __restrict__ Tw, bf16* __restrict__ qk,
+                                                          float* __restrict__ X, float scale) {
+  __shared__ float As[GC][GC + 1];
+  __shared__ float g_s[GC], b_s[GC];
+  const long ch = blockIdx.x;
+  const int i = threadIdx.x;
+  const long mat = ch * GC * GC;
+  g_s[i] = gc[ch * GC + i];
+  b_s[i] = beta[ch * GC + i];
+  __syncthreads();
+  const float gi = g_s[i], bi = b_s[i];
+  float row[GC];
+  load_row64(kk + mat + i * GC, row);
+#pragma unroll
+  for (int j = 0; j < GC; ++j) As[i][j] = (j < i) ? bi * row[j] * __expf(gi - g_s[j]) : 0.f;
+  // qk row while the A tile settles
+  load_row64(qkr + mat + i * GC, row);
+#pragma unroll
+  for (int j = 0; j < GC; ++j) row[j] = (j <= i) ? scale * row[j] * __expf(gi - g_s[j]) : 0.f;
+  store_row64(qk + mat + i * GC, row);
+  __syncthreads();
+  // column c = threadIdx.x of X: x[r] = [r == c] - sum_{j < r} A[r][j] x[j]
+  const int c = i;
+  float x[GC];
+#pragma unroll
+  for (int r = 0; r < GC; ++r) {
+    float acc = (r == c) ? 1.f : 0.f;
+#pragma unroll
+    for (int j = 0; j < r; ++j) acc = fmaf(-As[r][j], x[j], acc);
+    x[r] = acc;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < GC; ++r) As[r][c] = x[r];          // reuse the tile for X
+  __syncthreads();
+  float tu[GC], tw[GC];
+#pragma unroll
+  for (int j = 0; j < GC; ++j) {
+    const float xv = As[i][j];
+    row[j] = xv;
+    tu[j] = xv * b_s[j];
+    tw[j] = tu[j] * __expf(g_s[j]);
+  }
+  float4* xo = reinterpret_cast<float4*>(X + mat + i * GC);
+#pragma unroll
+  for (int j = 0; j < GC / 4; ++j) xo[j] = make_float4(row[4 * j], row[4 * j + 1], row[4 * j + 2], row[4 * j + 3]);
+  store_row64(Tu + mat + i * GC, tu);
+  store_row64(Tw + mat + i * GC, tw);
+}
+
+// dX[i][c] = (dTu[i][c] + dTw[i][c] * exp(gc_c)) * beta_c   for c <= i, else 0
+__global__ void __launch_bounds__(64) gdn_tmat_dx_kernel(const bf16* __restrict__ dTu, const bf16* __restrict__ dTw,
+                                                         const float* __restrict__ gc, const float* __restrict__ beta,
+                                                         float* __restrict__ dX) {
+  __shared__ float g_s[GC], b_s[GC];
+  const long ch = blockIdx.x;
+  const int i = threadIdx.x;
+  const long mat = ch * GC * GC;
+  g_s[i] = __expf(gc[ch * GC + i]);
+  b_s[i] = beta[ch * GC + i];
+  __syncthreads();
+  float a[GC], b[GC];
+  load_row64(dTu + mat + i * GC, a);
+  load_row64(dTw + mat + i * GC, b);
+  float4* o = reinterpret_cast<float4*>(dX + mat + i * GC);
+#pragma unroll
+  for (int j = 0; j < GC; ++j) a[j] = (j <= i) ? (a[j] + b[j] * g_s[j]) * b_s[j] : 0.f;
+#pragma unroll
+  for (int j = 0; j < GC / 4; ++j) o[j] = make_float4(a[4 * j], a[4 * j + 1], a[4 * j + 2], a[4 * j + 3]);
+}
+
+__global__ void __launch_bounds__(64) gdn_tmat_bwd_kernel(const float* __restrict__ dA, const bf16* __restrict__ kk,
+                                                          const bf16* __restrict__ qkr, const bf16* __restrict__ dqk,
+                                                          const bf16* __restrict__ dTu, const bf16* __restrict__ dTw,
+                                                          const float* __restrict__ X, const float* __restrict__ gc,
+                                                          const float* __restrict__ beta, bf16* __restrict__ dkk,
+                                                          bf16* __restrict__ dqkr, float* __restrict__ dgc,
+                                                          float* __restrict__ dbeta, float scale) {
+  __shared__ float Cg[GC][GC + 1];      // per element: contribution to d gc of its column index
+  __shared__ float Cb[GC][GC + 1];      // per element: contribution to d beta of its column index
+  __shared__ float g_s[GC], b_s[GC];
+  const long ch = blockIdx.x;
+  const int i = threadIdx.x;
+  const long mat = ch * GC * GC;
+  g_s[i] = gc[ch * GC + i];
+  b_s[i] = beta[ch * GC + i];
+  __syncthreads();
+  const float gi = g_s[i], bi = b_s[i];
+  float r1[GC], r2[GC], out[GC];
+  float dg_row = 0.f, db_row = 0.f;
+  // ---- A part: dA (fp32 row) with kk
+  load_row64(kk + mat + i * GC, r1);
+  const float4* da4 = reinterpret_cast<const float4*>(dA + mat + i * GC);
+#pragma unroll
+  for (int j = 0; j < GC / 4; ++j) {
+    const float4 v = da4[j];
+    r2[4 * j] = v.x; r2[4 * j + 1] = v.y; r2[4 * j + 2] = v.z; r2[4 * j + 3] = v.w;
+  }
+#pragma unroll
+  for (int j = 0; j < GC; ++j) {
+    float cg = 0.f;
+    out[j] = 0.f;
+    if (j < i) {
+      const float e = __expf(gi - g_s[j]);
+      const float araw = r1[j] * e;
+      const float d = r2[j];
+      out[j] = d * bi * e;
+      db_row += d * araw;
+      const float t = d * bi * araw;
+      dg_row += t;
+      cg = -t;
+    }
+    Cg[i][j] = cg;
+  }
+  store_row64(dkk + mat + i * GC, out);
+  // ---- qk part
+  load_row64(qkr + mat + i * GC, r1);
+  load_row64(dqk + mat + i * GC, r2);
+#pragma unroll
+  for (int j = 0; j < GC; ++j) {
+    out[j] = 0.f;
+    if (j <= i) {
+      const float e = __expf(gi - g_s[j]);
+      out[j] = r2[j] * scale * e;
+      const float t = out[j] * r1[j];
+      dg_row += t;
+      Cg[i][j] -= t;
+    }
+  }
+  store_row64(dqkr + mat + i * GC, out);
+  // ---- Tu / Tw part (column-indexed scalings)
+  load_row64(dTu + mat + i * GC, r1);
+  load_row64(dTw + mat + i * GC, r2);
+  const float4* x4 = reinterpret_cast<const float4*>(X + mat + i * GC);
+#pragma unroll
+  for (int j = 0; j < GC / 4; ++j) {
+    const float4 v = x4[j];
+    out[4 * j] = v.x; out[4 * j + 1] = v.y; out[4 * j + 2] = v.z; out[4 * j + 3] = v.w;
+  }
+#pragma unroll
+  for (int j = 0; j < GC; ++j) {
+    float cb = 0.f;
+    if (j <= i) {
+      const float eg = __expf(g_s[j]);
+      const float xv = out[j];
+      cb = (r1[j] + r2[j] * eg) * xv;
+      Cg[i][j] += r2[j] * xv * b_s[j] * eg;
+    }
+    Cb[i][j] = cb;
+  }
+  __syncthreads();
+  float dg_col = 0.f, db_col = 0.f;
+#pragma unroll 8
+  for (int r = 0; r < GC; ++r) { dg_col += Cg[r][i]; db_col += Cb[r][i]; }
+  dgc[ch * GC + i] = dg_row + dg_col;
+  dbeta[ch * GC + i] = db_row + db_col;
+}
+
+// ------------------------------------------------------------------------------------
 // Rotary embedding, halves layout.  x (tokens T per batch, H heads, D); cos/sin (T, D/2).
 // sign = +1 forward, -1 backward (rotation by the opposite angle).  In-place safe.
 // ------------------------------------------------------------------------------------
@@ -925,6 +1114,32 @@ extern "C" int nsa_gdn_pack_bwd(const void* q, const void* k, const float* sq, c
   gdn_pack_bwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const bf16*)q, (const bf16*)k, sq, sk, (const bf16*)dqh,
                                                                   (const bf16*)dkh, (const bf16*)dvh, (const bf16*)dqd, (const bf16*)dkt,
                                                                   (bf16*)dq, (bf16*)dk, (bf16*)dv, dsq, dsk, B, T, Tp, H, V);
+  nsa::count_launch();
+  return 0;
+}
+
+// Per-chunk matrices of the gated delta rule; n_chunks = B*H*NC, every matrix 64 x 64 row-major.
+extern "C" int nsa_gdn_tmat_fwd(const void* kk, const void* qkr, const float* gc, const float* beta, void* Tu, void* Tw,
+                                void* qk, float* X, long n_chunks, float scale, cudaStream_t st) {
+  if (n_chunks <= 0 || n_chunks > 2147483647L) return nsa::fail(NSA_ERR_SHAPE, "gdn_tmat: bad chunk count");
+  gdn_tmat_fwd_kernel<<<(unsigned)n_chunks, 64, 0, st>>>((const bf16*)kk, (const bf16*)qkr, gc, beta, (bf16*)Tu, (bf16*)Tw,
+                                                        (bf16*)qk, X, scale);
+  nsa::count_launch();
+  return 0;
+}
+extern "C" int nsa_gdn_tmat_dx(const void* dTu, const void* dTw, const float* gc, const float* beta, float* dX,
+                               long n_chunks, cudaStream_t st) {
+  if (n_chunks <= 0 || n_chunks > 2147483647L) return nsa::fail(NSA_ERR_SHAPE, "gdn_tmat: bad chunk count");
+  gdn_tmat_dx_kernel<<<(unsigned)n_chunks, 64, 0, st>>>((const bf16*)dTu, (const bf16*)dTw, gc, beta, dX);
+  nsa::count_launch();
+  return 0;
+}
+extern "C" int nsa_gdn_tmat_bwd(const float* dA, const void* kk, const void* qkr, const void* dqk, const void* dTu,
+                                const void* dTw, const float* X, const float* gc, const float* beta, void* dkk, void* dqkr,
+                                float* dgc, float* dbeta, long n_chunks, float scale, cudaStream_t st) {
+  if (n_chunks <= 0 || n_chunks > 2147483647L) return nsa::fail(NSA_ERR_SHAPE, "gdn_tmat: bad chunk count");
+  gdn_tmat_bwd_kernel<<<(unsigned)n_chunks, 64, 0, st>>>(dA, (const bf16*)kk, (const bf16*)qkr, (const bf16*)dqk, (const bf16*)dTu,
+                                                        (const bf16*)dTw, X, gc, beta, (bf16*)dkk, (bf16*)dqkr, dgc, dbeta, scale);
   nsa::count_launch();
   return 0;
 }

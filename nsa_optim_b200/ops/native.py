@@ -595,10 +595,50 @@ class _GDNPack(torch.autograd.Function):
         return dq, dk, dv, dsq, dsk
 
 
+class _GDNTmat(torch.autograd.Function):
+    """Per-chunk 64 x 64 matrices of the gated delta rule (``gdn_tmat_*`` in ``csrc/elementwise.cu``):
+    from kk = K K^T, qkr = Q K^T (bf16), the cumulative gate gc and beta build
+    Tu = X diag(beta), Tw = X diag(beta e^gc) with X = (I + A)^-1 and the decayed, scaled, causal qk.
+    The backward needs dA = -(X^T dX X^T): two batched fp32 matmuls between two small kernels."""
+
+    @staticmethod
+    def forward(ctx, kk, qkr, gc, bh, scale):
+        kk, qkr = kk.contiguous(), qkr.contiguous()
+        gc, bh = gc.float().contiguous(), bh.float().contiguous()
+        n = gc.numel() // 64
+        Tu, Tw, qk = torch.empty_like(kk), torch.empty_like(kk), torch.empty_like(kk)
+        X = torch.empty(kk.shape, dtype=torch.float32, device=kk.device)
+        _check(load().nsa_gdn_tmat_fwd(_p(kk), _p(qkr), _p(gc), _p(bh), _p(Tu), _p(Tw), _p(qk), _p(X), c_long(n), c_float(scale),
+                                       _stream()))
+        ctx.save_for_backward(kk, qkr, gc, bh, X)
+        ctx.scale = scale
+        return Tu, Tw, qk
+
+    @staticmethod
+    def backward(ctx, dTu, dTw, dqk):
+        kk, qkr, gc, bh, X = ctx.saved_tensors
+        n = gc.numel() // 64
+        z = lambda t: torch.zeros_like(kk) if t is None else t.to(torch.bfloat16).contiguous()
+        dTu, dTw, dqk = z(dTu), z(dTw), z(dqk)
+        dX = torch.empty_like(X)
+        lib = load()
+        _check(lib.nsa_gdn_tmat_dx(_p(dTu), _p(dTw), _p(gc), _p(bh), _p(dX), c_long(n), _stream()))
+        Xt = X.transpose(-1, -2)
+        dA = -torch.matmul(torch.matmul(Xt, dX), Xt)
+        del dX
+        dkk, dqkr = torch.empty_like(kk), torch.empty_like(kk)
+        dgc, dbh = torch.empty_like(gc), torch.empty_like(bh)
+        _check(lib.nsa_gdn_tmat_bwd(_p(dA.contiguous()), _p(kk), _p(qkr), _p(dqk), _p(dTu), _p(dTw), _p(X), _p(gc), _p(bh), _p(dkk),
+                                    _p(dqkr), _p(dgc), _p(dbh), c_long(n), c_float(ctx.scale), _stream()))
+        return dkk, dqkr, dgc, dbh, None
+
+
 def gated_delta_rule(q, k, v, g, beta, scale=None, chunk=64):
     """Chunkwise gated delta rule.  One layout pass brings q, k, v to head-major chunk rows together
-    with the decay-scaled operands; the 64 x 64 per-chunk matrices (K K^T, the unit-triangular
-    inverse, Q K^T) are batched PyTorch ops; the sequential state pass is native."""
+    with the decay-scaled operands; K K^T, Q K^T and the applications of the per-chunk matrices are
+    batched bf16 matmuls; the 64 x 64 matrices themselves (decay masks, the unit-triangular inverse
+    by substitution, their gradients) come from one small kernel each way; the sequential state
+    pass is the tcgen05 kernel of ``csrc/gdn.cu``."""
     B, T, H, K = q.shape
     V = v.shape[-1]
     if K != 128 or V % 64 or chunk != 64 or q.dtype != torch.bfloat16:
@@ -619,17 +659,10 @@ def gated_delta_rule(q, k, v, g, beta, scale=None, chunk=64):
     sq = (scale * eg).reshape(B * H, Tp)
     sk = torch.exp(gc[..., -1:] - gc).reshape(B * H, Tp)
     qh, kh, vh, qd, kt = (t.view(B * H, nc, C, -1) for t in _GDNPack.apply(q, k, v.to(bf), sq, sk))
-    incl = torch.ones(C, C, dtype=torch.bool, device=q.device).tril(0)
-    decay = torch.exp((gc[..., :, None] - gc[..., None, :]).masked_fill(~incl, float("-inf")))   # 1 on the diagonal
-    eye = torch.eye(C, device=q.device, dtype=f32)
-    kk = torch.matmul(kh, kh.transpose(-1, -2)).to(f32)
-    Amat = bh[..., None] * kk * (decay - eye)
-    # (I + A)^-1 per chunk is only 64 x 64: invert it alone in fp32, then apply it to beta*v and
-    # beta*e^gc*k with bf16 tensor-core matmuls (the column scalings are folded into the inverse)
-    Tm = torch.linalg.solve_triangular(eye + Amat, eye.expand_as(Amat), upper=False, unitriangular=True)
-    u = torch.matmul((Tm * bh[..., None, :]).to(bf), vh)
-    w = torch.matmul((Tm * (bh * eg)[..., None, :]).to(bf), kh)
-    qk = (torch.matmul(qh, kh.transpose(-1, -2)).to(f32) * scale * decay).to(bf)
+    kT = kh.transpose(-1, -2)
+    Tu, Tw, qk = _GDNTmat.apply(torch.matmul(kh, kT), torch.matmul(qh, kT), gc, bh, float(scale))
+    u = torch.matmul(Tu, vh)
+    w = torch.matmul(Tw, kh)
     gamma = eg[..., -1].contiguous()
     v_new, o_inter = _GDNSeq.apply(w, qd, kt, u, gamma)
     # o = o_inter + qk v_new in one batched GEMM with fp32 accumulation
