@@ -94,6 +94,8 @@ struct SsdParams {
   bf16* dx;            // [B, T, H, PD]
   float* dB_acc;       // [B, T, NS] fp32 (pre-zeroed, summed over heads)
   float* dC_acc;       // [B, T, NS]
+  bf16* dB_heads;      // [B, T, H, NS] per-head results written with plain stores (null: use the fp32 reductions above);
+  bf16* dC_heads;      //   the caller sums over heads: 64 heads adding into one row contend for the same L2 lines otherwise
   float* q_out;        // [B, T, H]  dy . (y - D x)
   float* k_out;        // [B, T, H]  x . dx (without the D term)
   KernelStatus* status;
@@ -522,7 +524,24 @@ ssd_chunk_grad_kernel(const __grid_constant__ CUtensorMap tm_c, const __grid_con
 #pragma unroll
         for (int j = 0; j < 64; ++j) q_inter += cv[j] * dci[j];
       }
-      if (row_ok) {
+      if (row_ok && p.dB_heads != nullptr) {
+        uint4* pc = reinterpret_cast<uint4*>(p.dC_heads + (tok * p.H + h) * NS + half * 64);
+        uint4* pb = reinterpret_cast<uint4*>(p.dB_heads + (tok * p.H + h) * NS + half * 64);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          uint4 vc, vb;
+          vc.x = tc5::pack_bf16(dc[8 * j] + e * dci[8 * j], dc[8 * j + 1] + e * dci[8 * j + 1]);
+          vc.y = tc5::pack_bf16(dc[8 * j + 2] + e * dci[8 * j + 2], dc[8 * j + 3] + e * dci[8 * j + 3]);
+          vc.z = tc5::pack_bf16(dc[8 * j + 4] + e * dci[8 * j + 4], dc[8 * j + 5] + e * dci[8 * j + 5]);
+          vc.w = tc5::pack_bf16(dc[8 * j + 6] + e * dci[8 * j + 6], dc[8 * j + 7] + e * dci[8 * j + 7]);
+          vb.x = tc5::pack_bf16(db[8 * j], db[8 * j + 1]);
+          vb.y = tc5::pack_bf16(db[8 * j + 2], db[8 * j + 3]);
+          vb.z = tc5::pack_bf16(db[8 * j + 4], db[8 * j + 5]);
+          vb.w = tc5::pack_bf16(db[8 * j + 6], db[8 * j + 7]);
+          pc[j] = vc;
+          pb[j] = vb;
+        }
+      } else if (row_ok) {
         float4* pc = reinterpret_cast<float4*>(p.dC_acc + tok * NS + half * 64);
         float4* pb = reinterpret_cast<float4*>(p.dB_acc + tok * NS + half * 64);
 #pragma unroll
@@ -668,11 +687,11 @@ extern "C" int nsa_ssd_chunk_out(const void* Cm, long ld_c, const void* Bm, long
 }
 
 // dB_acc / dC_acc: fp32 [B, T, N], zeroed by the caller.  q_out / k_out: fp32 [B, T, H].
-extern "C" int nsa_ssd_chunk_grad(const void* Cm, long ld_c, const void* Bm, long ld_b, const void* x, long ld_x,
-                                  const void* dy, const void* y, const void* Hprev_bf16, const void* dHn_bf16,
-                                  const float* dt, const float* A, const float* Dskip, void* dx, float* dB_acc,
-                                  float* dC_acc, float* q_out, float* k_out, int B, int T, int H, int N, int P,
-                                  cudaStream_t st) {
+static int ssd_chunk_grad_impl(const void* Cm, long ld_c, const void* Bm, long ld_b, const void* x, long ld_x,
+                               const void* dy, const void* y, const void* Hprev_bf16, const void* dHn_bf16,
+                               const float* dt, const float* A, const float* Dskip, void* dx, float* dB_acc,
+                               float* dC_acc, void* dB_heads, void* dC_heads, float* q_out, float* k_out, int B, int T,
+                               int H, int N, int P, cudaStream_t st) {
   int rc = check_dims(N, P, ld_c | ld_b, ld_x);
   if (rc) return rc;
   const int nc = (T + L - 1) / L;
@@ -688,6 +707,7 @@ extern "C" int nsa_ssd_chunk_grad(const void* Cm, long ld_c, const void* Bm, lon
   p.dt = dt; p.A = A; p.Dskip = Dskip; p.B = B; p.T = T; p.H = H; p.nc = nc;
   p.x_raw = (const bf16*)x; p.ldx = ld_x; p.y_in = (const bf16*)y; p.dy_raw = (const bf16*)dy; p.dx = (bf16*)dx;
   p.dB_acc = dB_acc; p.dC_acc = dC_acc; p.q_out = q_out; p.k_out = k_out; p.status = nsa::status_ptr();
+  p.dB_heads = (bf16*)dB_heads; p.dC_heads = (bf16*)dC_heads;
   const int smem = 13 * BOXB + 1024 + 2048;
   static bool cfg = false;
   if (!cfg) { if ((rc = smem_attr(ssd_chunk_grad_kernel, smem))) return rc; cfg = true; }
@@ -695,4 +715,23 @@ extern "C" int nsa_ssd_chunk_grad(const void* Cm, long ld_c, const void* Bm, lon
   nsa::count_launch();
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : nsa::fail_cuda(e, "nsa_ssd_chunk_grad launch");
+}
+
+extern "C" int nsa_ssd_chunk_grad(const void* Cm, long ld_c, const void* Bm, long ld_b, const void* x, long ld_x,
+                                  const void* dy, const void* y, const void* Hprev_bf16, const void* dHn_bf16,
+                                  const float* dt, const float* A, const float* Dskip, void* dx, float* dB_acc,
+                                  float* dC_acc, float* q_out, float* k_out, int B, int T, int H, int N, int P,
+                                  cudaStream_t st) {
+  return ssd_chunk_grad_impl(Cm, ld_c, Bm, ld_b, x, ld_x, dy, y, Hprev_bf16, dHn_bf16, dt, A, Dskip, dx, dB_acc, dC_acc,
+                             nullptr, nullptr, q_out, k_out, B, T, H, N, P, st);
+}
+// Same, with dB / dC written per head as bf16 [B, T, H, N] (plain stores); the caller sums over heads.
+extern "C" int nsa_ssd_chunk_grad_heads(const void* Cm, long ld_c, const void* Bm, long ld_b, const void* x, long ld_x,
+                                        const void* dy, const void* y, const void* Hprev_bf16, const void* dHn_bf16,
+                                        const float* dt, const float* A, const float* Dskip, void* dx, void* dB_heads,
+                                        void* dC_heads, float* q_out, float* k_out, int B, int T, int H, int N, int P,
+                                        cudaStream_t st) {
+  if (dB_heads == nullptr || dC_heads == nullptr) return nsa::fail(NSA_ERR_SHAPE, "ssd_chunk_grad_heads: null output");
+  return ssd_chunk_grad_impl(Cm, ld_c, Bm, ld_b, x, ld_x, dy, y, Hprev_bf16, dHn_bf16, dt, A, Dskip, dx, nullptr, nullptr,
+                             dB_heads, dC_heads, q_out, k_out, B, T, H, N, P, st);
 }

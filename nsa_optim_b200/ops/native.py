@@ -987,13 +987,18 @@ class _SSD(torch.autograd.Function):
                                      _stream()))
         del G
         dx = torch.empty(Bsz, T, H, P, dtype=torch.bfloat16, device=dev)
-        dB = torch.zeros(Bsz, T, N, dtype=torch.float32, device=dev)
-        dC = torch.zeros(Bsz, T, N, dtype=torch.float32, device=dev)
+        # dB / dC: every head writes its own bf16 rows, summed afterwards (64 heads reducing into the
+        # same fp32 rows with vector atomics was the slowest part of the kernel)
+        dBh = torch.empty(Bsz, T, H, N, dtype=torch.bfloat16, device=dev)
+        dCh = torch.empty(Bsz, T, H, N, dtype=torch.bfloat16, device=dev)
         q = torch.empty(Bsz, T, H, dtype=torch.float32, device=dev)
         k = torch.empty(Bsz, T, H, dtype=torch.float32, device=dev)
-        _check(lib.nsa_ssd_chunk_grad(_p(Cm), c_long(ldc), _p(Bm), c_long(ldb), _p(x), c_long(ldx), _p(dy), _p(y), _p(Hb),
-                                      _p(dHn), _p(dt), _p(A), _p(Df), _p(dx), _p(dB), _p(dC), _p(q), _p(k), c_int(Bsz),
-                                      c_int(T), c_int(H), c_int(N), c_int(P), _stream()))
+        _check(lib.nsa_ssd_chunk_grad_heads(_p(Cm), c_long(ldc), _p(Bm), c_long(ldb), _p(x), c_long(ldx), _p(dy), _p(y), _p(Hb),
+                                            _p(dHn), _p(dt), _p(A), _p(Df), _p(dx), _p(dBh), _p(dCh), _p(q), _p(k), c_int(Bsz),
+                                            c_int(T), c_int(H), c_int(N), c_int(P), _stream()))
+        dB = dBh.sum(2, dtype=torch.float32)
+        dC = dCh.sum(2, dtype=torch.float32)
+        del dBh, dCh
         # d(cum_t) = dy_t.(y_t - D x_t) - x_t.dx_t ;  a_k = dt_k A enters every cum_t with t >= k
         # (suffix sum over time, taken with time innermost: a scan along an outer dimension is slow)
         dcum = (q - k).transpose(1, 2).contiguous()
