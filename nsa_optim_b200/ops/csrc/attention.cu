@@ -746,6 +746,219 @@ attn_fwd_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 }
 
 // --------------------------------------------------------------------------------------
+// Block importance for top-n selection, warp-specialised (head_dim 128).  A second pass over the
+// compressed keys with the row statistics L of the compressed branch: p = 2^(S c - L), summed over
+// the G heads of the group and binned into selection blocks (a compressed key covers two
+// 16-token cells, a selection block four cells).  Same pipeline as the forward kernel above
+// without the P V product: Q in tensor memory, K stream through the shared-memory ring, the two
+// softmax groups on alternate 64-key visits.
+// --------------------------------------------------------------------------------------
+constexpr int IMP_STAGES = 6;
+
+__global__ void __launch_bounds__(320, 1)
+attn_importance_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                   const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+  constexpr int D = 128;
+  constexpr int QT = 4 * HALF;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sKV = sQ + QT;                        // [stages][K: 2 k-blocks of [64][64] | V: same]
+  float* merge = reinterpret_cast<float*>(sKV + IMP_STAGES * 2 * HALF);   // [2][128]: group 1's m and l
+  uint64_t* bars = reinterpret_cast<uint64_t*>(merge + 256);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;                  // [stages]
+  uint64_t* kv_empty = kv_full + IMP_STAGES;      // [stages]
+  uint64_t* s_full = kv_empty + IMP_STAGES;       // [2]
+  uint64_t* s_empty = s_full + 2;                // [2]
+  uint64_t* p_full = s_empty + 2;                // [2]
+  uint64_t* qt_full = p_full + 2;                // softmax -> MMA: Q is in tensor memory
+  uint64_t* acc_done = qt_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int qt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int q0 = qt * p.R;
+  const int t_hi = min(q0 + p.R, p.T) - 1;
+  const bool selected = p.tile_blocks != nullptr;
+  const long tile_slot = (static_cast<long>(b) * p.Hkv + h) * gridDim.x + qt;
+  const int* blocks = selected ? p.tile_blocks + tile_slot * p.max_u : nullptr;
+  const unsigned long long* masks = selected ? p.tile_masks + tile_slot * p.max_u : nullptr;
+  int kb0 = 0, n_vis;
+  if (selected) {
+    n_vis = min(p.tile_counts[tile_slot], p.max_u);
+  } else {
+    long last = p.S - 1;
+    if (p.causal) {
+      long lim = static_cast<long>(t_hi) - p.kp_off;
+      lim = lim < 0 ? -1 : lim / p.kp_stride;
+      last = lim < last ? lim : last;
+    }
+    long first = 0;
+    if (p.window > 0) {
+      const long lo = static_cast<long>(q0) - p.window + 1 - p.kp_off;
+      first = lo <= 0 ? 0 : (lo + p.kp_stride - 1) / p.kp_stride;
+    }
+    kb0 = static_cast<int>(first / 64);
+    n_vis = last < first ? 0 : static_cast<int>(last / 64) + 1 - kb0;
+  }
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    tc5::mbar_init(q_full, 1);
+    for (int i = 0; i < IMP_STAGES; ++i) { tc5::mbar_init(kv_full + i, 1); tc5::mbar_init(kv_empty + i, 1); }
+    for (int i = 0; i < 2; ++i) {
+      tc5::mbar_init(s_full + i, 1);
+      tc5::mbar_init(s_empty + i, 128);
+      tc5::mbar_init(p_full + i, 128);
+    }
+    tc5::mbar_init(qt_full, 256);
+    tc5::mbar_init(acc_done, 1);
+    tc5::fence_barrier_init();
+  }
+  if (warp == 9) { tc5::tmem_alloc(tmem_slot, 512); tc5::tmem_relinquish(); }
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  // columns: S of group g at g*64; O of group g at 128 + g*128
+  constexpr uint32_t cO = 128, cQ = 384;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0 && n_vis > 0) {
+      tc5::mbar_expect_tx(q_full, QT);
+#pragma unroll
+      for (int kb = 0; kb < 2; ++kb) tc5::tma_load_5d(sQ + kb * 2 * HALF, &tm_q, q_full, kb * 64, 0, h, q0, b);
+      bool ok = true;
+      int issued = 0;
+      int blk_n = selected ? blocks[0] : 0;
+      for (int v = 0; v < n_vis; ++v) {
+        const int st = v % IMP_STAGES;
+        const int blk = blk_n;
+        if (selected && v + 1 < n_vis) blk_n = blocks[v + 1];
+        if (!tc5::mbar_wait(kv_empty + st, ((v / IMP_STAGES) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_EMPTY)) { ok = false; break; }
+        const int s0 = selected ? (blk < 0 ? 0 : blk * 64) : (kb0 + v) * 64;
+        uint8_t* kd = sKV + st * 2 * HALF;
+        tc5::mbar_expect_tx(kv_full + st, 2 * HALF);
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb) tc5::tma_load_4d(kd + kb * HALF, &tm_k, kv_full + st, kb * 64, h, s0, b);
+        issued = v + 1;
+      }
+      if (!ok) {
+        // let the copies already issued land before the CTA's shared memory is released
+        for (int j = max(0, issued - IMP_STAGES); j < issued; ++j) {
+          const long long t0 = clock64();
+          for (uint32_t i = 0; i < tc5::kMaxPolls; ++i) {
+            if (tc5::mbar_try_wait(kv_full + (j % IMP_STAGES), (j / IMP_STAGES) & 1)) break;
+            if ((i & 255u) == 255u && clock64() - t0 > tc5::kMaxWaitCycles) break;
+          }
+        }
+        const long long t0 = clock64();
+        for (uint32_t i = 0; i < tc5::kMaxPolls; ++i) {
+          if (tc5::mbar_try_wait(q_full, 0)) break;
+          if ((i & 255u) == 255u && clock64() - t0 > tc5::kMaxWaitCycles) break;
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && n_vis > 0) {
+      constexpr uint32_t id_s = tc5::make_idesc_bf16(128, 64, 0, 0);
+      const uint64_t bK0 = tc5::desc_kmajor(tc5::smem_u32(sKV));
+      bool ok = tc5::mbar_wait(qt_full, 0, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL);
+      if (ok) tc5::fence_after_sync();
+      for (int v = 0; v < n_vis && ok; ++v) {
+        const int st = v % IMP_STAGES, g = v & 1;
+        if (!tc5::mbar_wait(kv_full + st, (v / IMP_STAGES) & 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL)) { ok = false; break; }
+        if (!tc5::mbar_wait(s_empty + g, ((v >> 1) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+        tc5::fence_after_sync();
+        const uint64_t bK = bK0 + static_cast<uint64_t>((st * 2 * HALF) >> 4);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          tc5::mma_ts(tmem + g * 64, tmem + cQ + kk * 8, bK + static_cast<uint64_t>(((kk >> 2) * HALF + (kk & 3) * 32) >> 4), id_s,
+                      kk > 0 ? 1u : 0u);
+        tc5::mma_commit(s_full + g);
+        tc5::mma_commit(kv_empty + st);            // the K stage is free once S is complete
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax groups
+    const int r = tid & 127, grp = tid >> 7;
+    const int tok_local = r / p.G, gh = r % p.G;
+    const int t = q0 + tok_local;
+    const bool row_ok = t < p.T;
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const long rowi = (static_cast<long>(b) * p.T + (row_ok ? t : 0)) * p.Hq + h * p.G + gh;
+    const float sc = p.scale_log2;
+    const float Lrow = row_ok ? p.L_in[rowi] : 0.f;
+    bool ok = true;
+    if (n_vis > 0) {
+      // Q: shared memory (swizzled [128 rows][64] k-blocks) -> TMEM; thread (r, grp) copies k-block grp of its row
+      ok = __all_sync(0xffffffffu, tc5::mbar_wait(q_full, 0, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL));
+      if (ok) {
+        uint32_t w[32];
+        const uint8_t* rowp = sQ + grp * 2 * HALF + r * 128;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint4 x = *reinterpret_cast<const uint4*>(rowp + ((j ^ (r & 7)) << 4));
+          w[4 * j] = x.x; w[4 * j + 1] = x.y; w[4 * j + 2] = x.z; w[4 * j + 3] = x.w;
+        }
+        tc5::tmem_st_x32(tmem + lane_off + cQ + grp * 32, w);
+        tc5::tmem_st_wait();
+        tc5::fence_before_sync();
+        tc5::mbar_arrive(qt_full);
+      }
+    }
+    int n_mine = 0;
+    for (int v = grp; v < n_vis && ok; v += 2, ++n_mine) {
+      const int sb = (kb0 + v) * 64;
+      if (!__all_sync(0xffffffffu, tc5::mbar_wait(s_full + grp, n_mine & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL))) {
+        ok = false;
+        break;
+      }
+      tc5::fence_after_sync();
+      uint32_t sv[64];
+      tmem_ld64(tmem + lane_off + grp * 64, sv);
+      tc5::fence_before_sync();
+      tc5::mbar_arrive(s_empty + grp);
+      // compressed key i covers 16-token cells i and i+1; a selection block is 4 cells
+      float bins[17];
+#pragma unroll
+      for (int i = 0; i < 17; ++i) bins[i] = 0.f;
+      if (row_ok) {
+        const bool check = (sb + 63 >= p.S) || ((sb + 63) * p.kp_stride + p.kp_off > t);
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          const bool vis = !check || key_visible(p, sb + i, t);
+          const float pr = vis ? exp2f(fmaf(__uint_as_float(sv[i]), sc, -Lrow)) : 0.f;
+          bins[i / 4] += pr;
+          bins[(i + 1) / 4] += pr;
+        }
+      }
+      for (int o = p.G >> 1; o > 0; o >>= 1)
+#pragma unroll
+        for (int i = 0; i < 17; ++i) bins[i] += __shfl_xor_sync(0xffffffffu, bins[i], o);
+      if (gh == 0 && row_ok) {
+        // bins 1..15 receive keys of this visit only: plain stores.  Bin 0 also receives the last key
+        // of the previous visit (its bin 16), so only those two go through a reduction.
+        const int jb = sb / 4;
+        float* dst = p.imp + ((static_cast<long>(b) * p.Hkv + h) * p.T + t) * p.nS;
+#pragma unroll
+        for (int i = 1; i < 16; ++i)
+          if (jb + i < p.nS) dst[jb + i] = bins[i];
+        if (jb < p.nS && bins[0] != 0.f) atomicAdd(dst + jb, bins[0]);
+        if (jb + 16 < p.nS && bins[16] != 0.f) atomicAdd(dst + jb + 16, bins[16]);
+      }
+    }
+  }
+  tc5::fence_before_sync();
+  __syncthreads();
+  if (warp == 9) { tc5::fence_after_sync(); tc5::tmem_dealloc(tmem, 512); }
+}
+
+// --------------------------------------------------------------------------------------
 // Forward, warp-specialised (head_dim 128, output mode).  Visits are 64-key blocks as in the
 // dQ kernel.  Warp 8 streams K/V through a 4-stage ring, warp 9 issues S = Q K^T and O += P V.
 // The 8 softmax warps form two groups of 128 threads (one thread per query row): group g takes
@@ -2445,7 +2658,13 @@ extern "C" int nsa_attn_importance(const void* q, const void* k_cmp, const float
   p.L_in = L_in; p.imp = imp; p.nS = nS; p.cells_per_block = 4;
   const dim3 grid((T + p.R - 1) / p.R, Hkv, B);
   const int smem = (D / 64) * 2 * HALF * 5 + 4 * HALF + 1024 + 2048;
-  if (D == 128) {
+  static const bool legacy = [] { const char* e = getenv("NSA_B200_ATTN_IMP"); return e && !strcmp(e, "legacy"); }();
+  if (D == 128 && !legacy && 128 % (Hq / Hkv) == 0) {
+    const int smem_ts = (4 + 2 * IMP_STAGES) * HALF + 1024 + 1024 + 256;
+    static bool cfg = false;
+    if (!cfg) { if ((rc = set_smem(attn_importance_ts_kernel, smem_ts))) return rc; cfg = true; }
+    attn_importance_ts_kernel<<<grid, 320, smem_ts, st>>>(tq, tk, tk, p);
+  } else if (D == 128) {
     static bool cfg = false;
     if (!cfg) { if ((rc = set_smem(attn_fwd_kernel<128, 1>, smem))) return rc; cfg = true; }
     attn_fwd_kernel<128, 1><<<grid, 256, smem, st>>>(tq, tk, tk, p);
