@@ -25,7 +25,7 @@ from torch import Tensor
 
 from .. import ops
 from .base import CausalLMBase, default_loss_fn, init_linear_embedding_
-from .kernels import Embedding, Linear, create_mlp, create_rms_norm
+from .kernels import Embedding, Linear, create_mlp, create_rms_norm, split_last
 
 
 def _inv_softplus_dt(n: int, dt_min: float = 1e-3, dt_max: float = 1e-1, floor: float = 1e-4) -> Tensor:
@@ -61,9 +61,9 @@ class Mamba2Mixer(nn.Module):
         B, T, _ = u.shape
         zxbcdt = self.in_proj(u)
         d_in, gn, H = self.d_inner, self.ngroups * self.d_state, self.nheads
-        z, xBC, dt = torch.split(zxbcdt, [d_in, d_in + 2 * gn, H], dim=-1)
+        z, xBC, dt = split_last(zxbcdt, [d_in, d_in + 2 * gn, H])
         xBC = ops.causal_conv1d(xBC, self.conv1d.weight.squeeze(1), self.conv1d.bias, activation=True)
-        x, Bm, Cm = torch.split(xBC, [d_in, gn, gn], dim=-1)
+        x, Bm, Cm = split_last(xBC, [d_in, gn, gn])
         dt = F.softplus(dt.float() + self.dt_bias.float())
         A = -torch.exp(self.A_log.float())
         y = ops.ssd_scan(x.reshape(B, T, H, self.headdim), dt, A,

@@ -14,6 +14,15 @@ namespace {
 
 typedef __nv_bfloat16 bf16;
 
+__device__ __forceinline__ void unpack8(const uint4& u, float (&v)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f = __bfloat1622float2(h[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
 __device__ __forceinline__ void load8(const bf16* p, float (&v)[8]) {
   uint4 u = *reinterpret_cast<const uint4*>(p);
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
@@ -802,6 +811,18 @@ __global__ void __launch_bounds__(128) conv1d_bwd_kernel(const bf16* __restrict_
       for (int k = 0; k < 8; ++k) xw[j + 1][k] = 0.f;
     }
   }
+  // raw rows of x and dy are fetched PF steps ahead: with about 150 registers per thread few warps
+  // fit on an SM, so the loads in flight per thread decide the achieved bandwidth
+  constexpr int PF = 3;
+  uint4 xq[PF], yq[PF];
+#pragma unroll
+  for (int i = 0; i < PF; ++i) {
+    const int t = t0 + i;
+    if (t < T) {
+      xq[i] = *reinterpret_cast<const uint4*>(x + (b * T + t) * ldx + c);
+      yq[i] = *reinterpret_cast<const uint4*>(dy + (b * T + t) * C + c);
+    } else { xq[i] = make_uint4(0, 0, 0, 0); yq[i] = make_uint4(0, 0, 0, 0); }
+  }
   for (int tt = 0; tt < CONV_TCHUNK + W - 1; ++tt) {
     const int t = t0 + tt;
 #pragma unroll
@@ -812,10 +833,20 @@ __global__ void __launch_bounds__(128) conv1d_bwd_kernel(const bf16* __restrict_
     for (int j = W - 1; j > 0; --j)
 #pragma unroll
       for (int k = 0; k < 8; ++k) dq[j][k] = dq[j - 1][k];
+    const uint4 xr = xq[0], yr = yq[0];
+#pragma unroll
+    for (int i = 0; i < PF - 1; ++i) { xq[i] = xq[i + 1]; yq[i] = yq[i + 1]; }
+    {
+      const int tn = t + PF;
+      if (tt + PF < CONV_TCHUNK + W - 1 && tn < T) {
+        xq[PF - 1] = *reinterpret_cast<const uint4*>(x + (b * T + tn) * ldx + c);
+        yq[PF - 1] = *reinterpret_cast<const uint4*>(dy + (b * T + tn) * C + c);
+      }
+    }
     if (t < T) {
-      load8(x + (b * T + t) * ldx + c, xw[W - 1]);
+      unpack8(xr, xw[W - 1]);
       float dv[8];
-      load8(dy + (b * T + t) * C + c, dv);
+      unpack8(yr, dv);
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
         float pre = bv[k];

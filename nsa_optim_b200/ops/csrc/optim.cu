@@ -60,7 +60,29 @@ __device__ __forceinline__ int nearest_code(const float* cb, float x) {
   return (x - cb[lo] <= cb[hi] - x) ? lo : hi;
 }
 
-// One CTA (256 threads) per 256-element block.
+__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
+  const float4 x = *reinterpret_cast<const float4*>(p);
+  v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+}
+__device__ __forceinline__ void load4(const bf16* p, float (&v)[4]) {
+  const uint2 x = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x.x));
+  const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x.y));
+  v[0] = a.x; v[1] = a.y; v[2] = c.x; v[3] = c.y;
+}
+__device__ __forceinline__ void store4(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(bf16* p, const float (&v)[4]) {
+  uint2 x;
+  *reinterpret_cast<__nv_bfloat162*>(&x.x) = __floats2bfloat162_rn(v[0], v[1]);
+  *reinterpret_cast<__nv_bfloat162*>(&x.y) = __floats2bfloat162_rn(v[2], v[3]);
+  *reinterpret_cast<uint2*>(p) = x;
+}
+
+// A CTA of 256 threads takes four 256-element quantisation blocks per iteration: 64 threads per
+// block, four consecutive elements per thread (8- or 16-byte loads of p and g, 4-byte loads of
+// the state codes).
 template <typename PT, typename GT>
 __global__ void __launch_bounds__(256) adamw8bit_kernel(PT* __restrict__ p, const GT* __restrict__ g,
                                                         uint8_t* __restrict__ mq, float* __restrict__ mabs,
@@ -75,25 +97,57 @@ __global__ void __launch_bounds__(256) adamw8bit_kernel(PT* __restrict__ p, cons
   __syncthreads();
   const float gs = grad_scale ? *grad_scale : 1.f;
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
-  for (long b = blockIdx.x; b < nblocks; b += gridDim.x) {
-    const long i = b * 256 + threadIdx.x;
-    const float gr = static_cast<float>(g[i]) * gs;
-    const float mm = a.beta1 * (cs[mq[i]] * mabs[b]) + (1.f - a.beta1) * gr;
-    const float vv = a.beta2 * (cu[vq[i]] * vabs[b]) + (1.f - a.beta2) * gr * gr;
-    float wt = static_cast<float>(p[i]);
-    wt *= (1.f - a.lr * a.wd);
-    wt -= (a.lr / a.bc1) * mm / (sqrtf(vv) / a.bc2_sqrt + a.eps);
-    p[i] = static_cast<PT>(wt);
-    float am = warp_max(fabsf(mm)), av = warp_max(vv);
+  const int grp = threadIdx.x >> 6, t64 = threadIdx.x & 63;
+  const long quads = (nblocks + 3) / 4;
+  const float decay = 1.f - a.lr * a.wd, step_size = a.lr / a.bc1;
+  for (long q = blockIdx.x; q < quads; q += gridDim.x) {
+    const long b = q * 4 + grp;
+    const bool live = b < nblocks;
+    const long i = b * 256 + t64 * 4;
+    float mm[4], vv[4];
+    float am = 0.f, av = 0.f;
+    if (live) {
+      float gr[4], wt[4];
+      load4(g + i, gr);
+      load4(p + i, wt);
+      const uchar4 mc = *reinterpret_cast<const uchar4*>(mq + i);
+      const uchar4 vc = *reinterpret_cast<const uchar4*>(vq + i);
+      const float ms = mabs[b], vs = vabs[b];
+      const float m0[4] = {cs[mc.x], cs[mc.y], cs[mc.z], cs[mc.w]};
+      const float v0[4] = {cu[vc.x], cu[vc.y], cu[vc.z], cu[vc.w]};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float x = gr[k] * gs;
+        mm[k] = a.beta1 * (m0[k] * ms) + (1.f - a.beta1) * x;
+        vv[k] = a.beta2 * (v0[k] * vs) + (1.f - a.beta2) * x * x;
+        wt[k] = wt[k] * decay - step_size * mm[k] / (sqrtf(vv[k]) / a.bc2_sqrt + a.eps);
+        am = fmaxf(am, fabsf(mm[k]));
+        av = fmaxf(av, vv[k]);
+      }
+      store4(p + i, wt);
+    }
+    am = warp_max(am);
+    av = warp_max(av);
     __syncthreads();               // previous iteration's readers of red_* are done
     if (l == 0) { red_m[w] = am; red_v[w] = av; }
     __syncthreads();
-    am = red_m[0]; av = red_v[0];
-#pragma unroll
-    for (int k = 1; k < 8; ++k) { am = fmaxf(am, red_m[k]); av = fmaxf(av, red_v[k]); }
-    mq[i] = static_cast<uint8_t>(nearest_code(cs, mm / fmaxf(am, 1e-30f)));
-    vq[i] = static_cast<uint8_t>(nearest_code(cu, vv / fmaxf(av, 1e-30f)));
-    if (threadIdx.x == 0) { mabs[b] = am; vabs[b] = av; }
+    am = fmaxf(red_m[2 * grp], red_m[2 * grp + 1]);
+    av = fmaxf(red_v[2 * grp], red_v[2 * grp + 1]);
+    if (live) {
+      const float dm = fmaxf(am, 1e-30f), dv = fmaxf(av, 1e-30f);
+      uchar4 mc, vc;
+      mc.x = static_cast<uint8_t>(nearest_code(cs, mm[0] / dm));
+      mc.y = static_cast<uint8_t>(nearest_code(cs, mm[1] / dm));
+      mc.z = static_cast<uint8_t>(nearest_code(cs, mm[2] / dm));
+      mc.w = static_cast<uint8_t>(nearest_code(cs, mm[3] / dm));
+      vc.x = static_cast<uint8_t>(nearest_code(cu, vv[0] / dv));
+      vc.y = static_cast<uint8_t>(nearest_code(cu, vv[1] / dv));
+      vc.z = static_cast<uint8_t>(nearest_code(cu, vv[2] / dv));
+      vc.w = static_cast<uint8_t>(nearest_code(cu, vv[3] / dv));
+      *reinterpret_cast<uchar4*>(mq + i) = mc;
+      *reinterpret_cast<uchar4*>(vq + i) = vc;
+      if (t64 == 0) { mabs[b] = am; vabs[b] = av; }
+    }
   }
 }
 
@@ -282,7 +336,7 @@ extern "C" int nsa_adamw8bit_step(void* p, const void* g, uint8_t* mq, float* ma
   if (n % 256) return nsa::fail(NSA_ERR_SHAPE, "adamw8bit: element count must be a multiple of 256");
   const AdamArgs a = make_args(step, lr, b1, b2, eps, wd);
   const long nb = n / 256;
-  const int grid = grid_cap(nb, 16);
+  const int grid = grid_cap((nb + 3) / 4, 8);
   if (p_fp32 && g_fp32) adamw8bit_kernel<float, float><<<grid, 256, 0, st>>>((float*)p, (const float*)g, mq, mabs, vq, vabs, cb_signed, cb_unsigned, grad_scale, nb, a);
   else if (p_fp32) adamw8bit_kernel<float, bf16><<<grid, 256, 0, st>>>((float*)p, (const bf16*)g, mq, mabs, vq, vabs, cb_signed, cb_unsigned, grad_scale, nb, a);
   else if (g_fp32) adamw8bit_kernel<bf16, float><<<grid, 256, 0, st>>>((bf16*)p, (const float*)g, mq, mabs, vq, vabs, cb_signed, cb_unsigned, grad_scale, nb, a);

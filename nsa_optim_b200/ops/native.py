@@ -1010,6 +1010,20 @@ class _SSD(torch.autograd.Function):
         return (dx, ddt, dA, dB.view(Bsz, T, 1, N).to(torch.bfloat16), dC.view(Bsz, T, 1, N).to(torch.bfloat16), dD)
 
 
+def sumsq(tensors) -> Tensor:
+    """Sum of squares over a list of bf16 / fp32 CUDA tensors -> fp32 device scalar (no host sync)."""
+    lib = load()
+    dev = tensors[0].device
+    out = torch.zeros((), dtype=torch.float32, device=dev)
+    partial = torch.empty(int(lib.nsa_sumsq_parts()), dtype=torch.float32, device=dev)
+    for g in tensors:
+        if g.dtype not in (torch.bfloat16, torch.float32) or not g.is_contiguous():
+            g = g.float().contiguous()
+        _check(lib.nsa_sumsq(_p(g), c_long(g.numel()), c_int(int(g.dtype == torch.float32)), _p(partial), _p(out), c_int(1),
+                             _stream()))
+    return out
+
+
 def affine_quantize(t: Tensor, bits: int, q_block: int):
     """CUDA form of :func:`nsa_optim_b200.ops.quant.affine_quantize` for fp32 matrices."""
     rows, cols = t.shape

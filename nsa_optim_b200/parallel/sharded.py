@@ -43,6 +43,7 @@ import torch.distributed as dist
 import torch.nn as nn
 from torch import Tensor
 
+from .. import ops
 from . import dist as pdist
 
 ALIGN = 256
@@ -548,7 +549,10 @@ class ShardedModel(nn.Module):
         if not grads:
             z = torch.zeros((), device=self.info.device)
             return z, None
-        sq = torch.stack([g.float().pow(2).sum() for g in grads]).sum()
+        if self._cuda and ops.get_backend() != "torch":
+            sq = ops.native_module().sumsq(grads)            # one small kernel pair per tensor, fp32 accumulation
+        else:
+            sq = torch.stack([g.float().pow(2).sum() for g in grads]).sum()
         if self.world > 1 and not local_only:
             pdist.all_reduce_sum(sq, self.group)
         norm = sq.sqrt()
