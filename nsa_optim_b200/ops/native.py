@@ -94,10 +94,84 @@ def read_status(reset: bool = True) -> Tuple[int, int, int, int]:
     return tuple(int(v) for v in out)
 
 
+# --------------------------------------------------------------------------------------
+# Output allocation.  With NSA_B200_DEBUG_CANARY=1 every tensor a wrapper allocates for a kernel
+# sits between two 4 KB guard zones filled with a pattern; ``check_canaries()`` (also run by
+# ``check_status()``) verifies them, which catches a kernel writing past either end of its
+# output: the stand-in for a memory sanitizer on machines where none may be run.
+# --------------------------------------------------------------------------------------
+_CANARY = os.environ.get("NSA_B200_DEBUG_CANARY", "") not in ("", "0")
+_GUARD = 4096
+_GUARD_BYTE = 0xA5
+_guards: list = []
+
+
+def _shape_of(size) -> tuple:
+    if len(size) == 1 and isinstance(size[0], (tuple, list, torch.Size)):
+        return tuple(int(x) for x in size[0])
+    return tuple(int(x) for x in size)
+
+
+def _guarded(shape, dtype, device, zero: bool) -> Tensor:
+    dtype = dtype or torch.get_default_dtype()
+    n = 1
+    for d in shape:
+        n *= d
+    nbytes = n * torch.empty((), dtype=dtype).element_size()
+    pad = (-nbytes) % 256
+    buf = torch.empty(_GUARD + nbytes + pad + _GUARD, dtype=torch.uint8, device=device)
+    buf[:_GUARD].fill_(_GUARD_BYTE)
+    buf[_GUARD + nbytes:].fill_(_GUARD_BYTE)
+    _guards.append((buf, nbytes))
+    out = buf[_GUARD:_GUARD + nbytes].view(dtype).view(shape)
+    return out.zero_() if zero else out
+
+
+def _empty(*size, dtype=None, device=None) -> Tensor:
+    if _CANARY and device is not None and torch.device(device).type == "cuda":
+        return _guarded(_shape_of(size), dtype, device, False)
+    return torch.empty(*size, dtype=dtype, device=device)
+
+
+def _zeros(*size, dtype=None, device=None) -> Tensor:
+    if _CANARY and device is not None and torch.device(device).type == "cuda":
+        return _guarded(_shape_of(size), dtype, device, True)
+    return torch.zeros(*size, dtype=dtype, device=device)
+
+
+def _empty_like(t: Tensor, dtype=None) -> Tensor:
+    if _CANARY and t.is_cuda:
+        return _guarded(tuple(t.shape), dtype or t.dtype, t.device, False)
+    return torch.empty_like(t, dtype=dtype, memory_format=torch.contiguous_format)
+
+
+def _zeros_like(t: Tensor, dtype=None) -> Tensor:
+    if _CANARY and t.is_cuda:
+        return _guarded(tuple(t.shape), dtype or t.dtype, t.device, True)
+    return torch.zeros_like(t, dtype=dtype, memory_format=torch.contiguous_format)
+
+
+def check_canaries() -> int:
+    """Verify and release the guard zones recorded so far; returns how many buffers were checked."""
+    torch.cuda.synchronize()
+    n = len(_guards)
+    for k, (buf, nbytes) in enumerate(_guards):
+        head_ok = bool((buf[:_GUARD] == _GUARD_BYTE).all())
+        tail_ok = bool((buf[_GUARD + nbytes:] == _GUARD_BYTE).all())
+        if not (head_ok and tail_ok):
+            _guards.clear()
+            side = "before" if not head_ok else "after"
+            raise RuntimeError(f"guard zone {side} kernel output #{k} ({nbytes} bytes) was overwritten")
+    _guards.clear()
+    return n
+
+
 def check_status(sync: bool = True) -> None:
     """Raise if any kernel since the last check reported a failure."""
     if sync:
         torch.cuda.synchronize()
+    if _CANARY:
+        check_canaries()
     code, block, info, count = read_status(reset=True)
     if code != 0:
         raise RuntimeError(f"native kernel reported status {code} ({STATUS_NAMES.get(code, 'unknown')}); "
@@ -124,7 +198,7 @@ def gemm(a: Tensor, b: Tensor, a_mn: bool, b_mn: bool, out: Optional[Tensor] = N
     if K != Kb:
         raise ValueError(f"gemm: reduction sizes differ ({K} vs {Kb})")
     if out is None:
-        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+        out = _empty(M, N, dtype=out_dtype, device=a.device)
     _check(load().nsa_gemm_bf16(_p(a), _p(b), _p(out), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)),
                                 c_int(b.stride(0)), c_int(out.stride(0)), c_int(int(a_mn)), c_int(int(b_mn)),
                                 c_int(int(out.dtype == torch.float32)), c_int(int(accumulate)), c_int(max_ctas),
@@ -216,8 +290,8 @@ def linear(x: Tensor, w: Tensor) -> Tensor:
 # --------------------------------------------------------------------------------------
 def _rms_fwd(x2, gate2, w, eps, mode):
     rows, d = x2.shape
-    y = torch.empty_like(x2)
-    rstd = torch.empty(rows, dtype=torch.float32, device=x2.device)
+    y = _empty_like(x2)
+    rstd = _empty(rows, dtype=torch.float32, device=x2.device)
     _check(load().nsa_rmsnorm_fwd(_p(x2), _p(gate2), _p(w), _p(y), _p(rstd), c_long(rows), c_int(d),
                                   c_float(eps), c_int(mode), _stream()))
     return y, rstd
@@ -225,11 +299,11 @@ def _rms_fwd(x2, gate2, w, eps, mode):
 
 def _rms_bwd(x2, gate2, w, dy2, rstd, mode):
     rows, d = x2.shape
-    dx = torch.empty_like(x2)
-    dg = torch.empty_like(x2) if mode != 0 else None
-    dw = torch.empty(d, dtype=torch.bfloat16, device=x2.device)
+    dx = _empty_like(x2)
+    dg = _empty_like(x2) if mode != 0 else None
+    dw = _empty(d, dtype=torch.bfloat16, device=x2.device)
     parts = int(load().nsa_rmsnorm_bwd_parts(c_long(rows), c_int(d)))
-    partial = torch.empty(parts * d, dtype=torch.float32, device=x2.device)
+    partial = _empty(parts * d, dtype=torch.float32, device=x2.device)
     _check(load().nsa_rmsnorm_bwd(_p(x2), _p(gate2), _p(w), _p(dy2), _p(rstd), _p(dx), _p(dg), _p(dw), c_void_p(0),
                                   _p(partial), c_long(rows), c_int(d), c_int(mode), _stream()))
     return dx, dg, dw
@@ -290,8 +364,8 @@ class _L2Norm(torch.autograd.Function):
     def forward(ctx, x, eps):
         x2 = x.reshape(-1, x.shape[-1]).contiguous()
         rows, d = x2.shape
-        y = torch.empty_like(x2)
-        rinv = torch.empty(rows, dtype=torch.float32, device=x.device)
+        y = _empty_like(x2)
+        rinv = _empty(rows, dtype=torch.float32, device=x.device)
         _check(load().nsa_l2norm_fwd(_p(x2), _p(y), _p(rinv), c_long(rows), c_int(d), c_float(eps), _stream()))
         ctx.save_for_backward(y, rinv)
         return y.view(x.shape)
@@ -300,7 +374,7 @@ class _L2Norm(torch.autograd.Function):
     def backward(ctx, dy):
         y, rinv = ctx.saved_tensors
         dy2 = dy.reshape(y.shape).contiguous()
-        dx = torch.empty_like(y)
+        dx = _empty_like(y)
         _check(load().nsa_l2norm_bwd(_p(y), _p(dy2), _p(rinv), _p(dx), c_long(y.shape[0]), c_int(y.shape[1]), _stream()))
         return dx.view(dy.shape), None
 
@@ -327,7 +401,7 @@ class _SwiGLU(torch.autograd.Function):
     def forward(ctx, gate, up):
         g2, u2 = _rows_view(gate), _rows_view(up)
         rows, cols = g2.shape
-        y = torch.empty(rows, cols, dtype=gate.dtype, device=gate.device)
+        y = _empty(rows, cols, dtype=gate.dtype, device=gate.device)
         _check(load().nsa_swiglu_fwd(_p(g2), _p(u2), _p(y), c_long(rows), c_int(cols), c_long(g2.stride(0)),
                                      c_long(u2.stride(0)), _stream()))
         ctx.save_for_backward(g2, u2)
@@ -338,8 +412,8 @@ class _SwiGLU(torch.autograd.Function):
         g2, u2 = ctx.saved_tensors
         rows, cols = g2.shape
         dy2 = dy.reshape(rows, cols).contiguous()
-        dg = torch.empty(rows, cols, dtype=dy.dtype, device=dy.device)
-        du = torch.empty(rows, cols, dtype=dy.dtype, device=dy.device)
+        dg = _empty(rows, cols, dtype=dy.dtype, device=dy.device)
+        du = _empty(rows, cols, dtype=dy.dtype, device=dy.device)
         _check(load().nsa_swiglu_bwd(_p(g2), _p(u2), _p(dy2), _p(dg), _p(du), c_long(rows), c_int(cols),
                                      c_long(g2.stride(0)), c_long(u2.stride(0)), c_long(cols), _stream()))
         return dg.view(dy.shape), du.view(dy.shape)
@@ -354,7 +428,7 @@ def swiglu(gate, up):
 def _rope_call(x: Tensor, cos: Tensor, sin: Tensor, backward: bool) -> Tensor:
     B, T, H, D = x.shape
     xc = x.contiguous()
-    y = torch.empty_like(xc)
+    y = _empty_like(xc)
     _check(load().nsa_rope(_p(xc), _p(cos), _p(sin), _p(y), c_long(B), c_int(T), c_int(H), c_int(D),
                            c_int(int(backward)), _stream()))
     return y
@@ -391,7 +465,7 @@ class _Conv1d(torch.autograd.Function):
                    and x.data_ptr() % 16 == 0) else x.contiguous()
         wb = weight.to(torch.bfloat16).contiguous()
         bb = None if bias is None else bias.to(torch.bfloat16).contiguous()
-        y = torch.empty(B, T, C, dtype=x.dtype, device=x.device)
+        y = _empty(B, T, C, dtype=x.dtype, device=x.device)
         _check(load().nsa_conv1d_fwd(_p(xv), _p(wb), _p(bb), _p(y), c_int(B), c_int(T), c_int(C),
                                      c_long(xv.stride(1)), c_int(weight.shape[-1]), c_int(int(activation)), _stream()))
         ctx.save_for_backward(xv, wb, bb)
@@ -405,10 +479,10 @@ class _Conv1d(torch.autograd.Function):
         B, T, C = xv.shape
         W = wb.shape[-1]
         dyc = dy.contiguous()
-        dx = torch.empty(B, T, C, dtype=dy.dtype, device=dy.device)
+        dx = _empty(B, T, C, dtype=dy.dtype, device=dy.device)
         parts = int(load().nsa_conv1d_bwd_parts(c_int(B), c_int(T)))
-        partial = torch.empty(parts * (W + 1) * C, dtype=torch.float32, device=dy.device)
-        dwdb = torch.empty((W + 1) * C, dtype=torch.float32, device=dy.device)
+        partial = _empty(parts * (W + 1) * C, dtype=torch.float32, device=dy.device)
+        dwdb = _empty((W + 1) * C, dtype=torch.float32, device=dy.device)
         _check(load().nsa_conv1d_bwd(_p(xv), _p(wb), _p(bb), _p(dyc), _p(dx), _p(partial), _p(dwdb), c_int(B), c_int(T),
                                      c_int(C), c_long(xv.stride(1)), c_int(W), c_int(int(ctx.activation)), _stream()))
         dw = dwdb[: W * C].view(W, C).t().contiguous().to(ctx.wdtype)
@@ -430,7 +504,7 @@ class _Embedding(torch.autograd.Function):
     def forward(ctx, ids, weight):
         flat = ids.reshape(-1).contiguous()
         n, d = flat.numel(), weight.shape[1]
-        y = torch.empty(n, d, dtype=weight.dtype, device=weight.device)
+        y = _empty(n, d, dtype=weight.dtype, device=weight.device)
         _check(load().nsa_embedding_fwd(_p(flat), _p(weight), _p(y), c_long(n), c_int(d), c_long(weight.shape[0]), _stream()))
         ctx.save_for_backward(flat)
         ctx.wshape, ctx.wdtype = weight.shape, weight.dtype
@@ -441,7 +515,7 @@ class _Embedding(torch.autograd.Function):
         (flat,) = ctx.saved_tensors
         n, d = flat.numel(), ctx.wshape[1]
         sorted_ids, perm = torch.sort(flat, stable=True)
-        dw = torch.zeros(ctx.wshape, dtype=torch.float32, device=dy.device)
+        dw = _zeros(ctx.wshape, dtype=torch.float32, device=dy.device)
         dy2 = dy.reshape(n, d).contiguous()
         _check(load().nsa_embedding_bwd(_p(sorted_ids), _p(perm), _p(dy2), _p(dw), c_long(n), c_int(d), _stream()))
         return None, dw.to(ctx.wdtype)
@@ -469,10 +543,10 @@ class _LinearCE(torch.autograd.Function):
         need_h, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         n_valid = (labels != ignore_index).sum().clamp_min(1).float()
         inv = (1.0 / n_valid).reshape(1)
-        loss_rows = torch.empty(N, dtype=torch.float32, device=hidden.device)
-        dh = torch.empty_like(h) if need_h else None
-        dw = torch.zeros(V, d, dtype=torch.float32, device=hidden.device) if need_w else None
-        logits = torch.empty(min(chunk, N), V, dtype=torch.bfloat16, device=hidden.device)
+        loss_rows = _empty(N, dtype=torch.float32, device=hidden.device)
+        dh = _empty_like(h) if need_h else None
+        dw = _zeros(V, d, dtype=torch.float32, device=hidden.device) if need_w else None
+        logits = _empty(min(chunk, N), V, dtype=torch.bfloat16, device=hidden.device)
         for s0 in range(0, N, chunk):
             s1 = min(N, s0 + chunk)
             lg = logits[: s1 - s0]
@@ -534,9 +608,9 @@ class _GDNSeq(torch.autograd.Function):
     def forward(ctx, w, qd, kt, u, gamma):
         BH, NC, C, K = w.shape
         V = u.shape[-1]
-        v_new = torch.empty_like(u)
-        o_inter = torch.empty(BH, NC, C, V, dtype=torch.float32, device=u.device)
-        S_all = torch.empty(BH, NC, K, V, dtype=torch.bfloat16, device=u.device)
+        v_new = _empty_like(u)
+        o_inter = _empty(BH, NC, C, V, dtype=torch.float32, device=u.device)
+        S_all = _empty(BH, NC, K, V, dtype=torch.bfloat16, device=u.device)
         _check(load().nsa_gdn_seq_fwd(_p(w), _p(qd), _p(kt), _p(u), _p(gamma), _p(v_new), _p(o_inter), _p(S_all),
                                       c_int(BH), c_int(NC), c_int(K), c_int(V), _stream()))
         ctx.save_for_backward(w, qd, kt, gamma, S_all, v_new)
@@ -548,11 +622,11 @@ class _GDNSeq(torch.autograd.Function):
         BH, NC, C, K = w.shape
         V = v_new.shape[-1]
         nvt = V // 64
-        dv = torch.zeros_like(v_new) if dv_new is None else dv_new.to(torch.bfloat16).contiguous()
-        do = torch.zeros_like(v_new) if do_inter is None else do_inter.to(torch.bfloat16).contiguous()
-        du = torch.empty_like(v_new)
-        parts = torch.empty(3, nvt, BH, NC, C, K, dtype=torch.bfloat16, device=w.device)
-        dgp = torch.empty(nvt, BH, NC, dtype=torch.float32, device=w.device)
+        dv = _zeros_like(v_new) if dv_new is None else dv_new.to(torch.bfloat16).contiguous()
+        do = _zeros_like(v_new) if do_inter is None else do_inter.to(torch.bfloat16).contiguous()
+        du = _empty_like(v_new)
+        parts = _empty(3, nvt, BH, NC, C, K, dtype=torch.bfloat16, device=w.device)
+        dgp = _empty(nvt, BH, NC, dtype=torch.float32, device=w.device)
         _check(load().nsa_gdn_seq_bwd(_p(w), _p(qd), _p(kt), _p(S_all), _p(v_new), _p(dv), _p(do), _p(gamma), _p(du),
                                       _p(parts[0]), _p(parts[1]), _p(parts[2]), _p(dgp), c_int(BH), c_int(NC),
                                       c_int(K), c_int(V), _stream()))
@@ -571,7 +645,7 @@ class _GDNPack(torch.autograd.Function):
         B, T, H, K = q.shape
         V = v.shape[-1]
         Tp = sq.shape[-1]
-        mk = lambda w: torch.empty(B * H, Tp, w, dtype=torch.bfloat16, device=q.device)
+        mk = lambda w: _empty(B * H, Tp, w, dtype=torch.bfloat16, device=q.device)
         qh, kh, vh, qd, kt = mk(K), mk(K), mk(V), mk(K), mk(K)
         _check(load().nsa_gdn_pack_fwd(_p(q), _p(k), _p(v), _p(sq), _p(sk), _p(qh), _p(kh), _p(vh), _p(qd), _p(kt),
                                        c_int(B), c_int(T), c_int(Tp), c_int(H), c_int(K), c_int(V), _stream()))
@@ -586,9 +660,9 @@ class _GDNPack(torch.autograd.Function):
         V, Tp = ctx.V, sq.shape[-1]
         c = lambda t: None if t is None else t.to(torch.bfloat16).contiguous()
         dqh, dkh, dvh, dqd, dkt = c(dqh), c(dkh), c(dvh), c(dqd), c(dkt)
-        dq, dk = torch.empty_like(q), torch.empty_like(k)
-        dv = torch.empty(B, T, H, V, dtype=torch.bfloat16, device=q.device)
-        dsq, dsk = torch.empty_like(sq), torch.empty_like(sk)
+        dq, dk = _empty_like(q), _empty_like(k)
+        dv = _empty(B, T, H, V, dtype=torch.bfloat16, device=q.device)
+        dsq, dsk = _empty_like(sq), _empty_like(sk)
         _check(load().nsa_gdn_pack_bwd(_p(q), _p(k), _p(sq), _p(sk), _p(dqh), _p(dkh), _p(dvh), _p(dqd), _p(dkt), _p(dq), _p(dk),
                                        _p(dv), _p(dsq), _p(dsk), c_int(B), c_int(T), c_int(Tp), c_int(H), c_int(K), c_int(V),
                                        _stream()))
@@ -606,8 +680,8 @@ class _GDNTmat(torch.autograd.Function):
         kk, qkr = kk.contiguous(), qkr.contiguous()
         gc, bh = gc.float().contiguous(), bh.float().contiguous()
         n = gc.numel() // 64
-        Tu, Tw, qk = torch.empty_like(kk), torch.empty_like(kk), torch.empty_like(kk)
-        X = torch.empty(kk.shape, dtype=torch.float32, device=kk.device)
+        Tu, Tw, qk = _empty_like(kk), _empty_like(kk), _empty_like(kk)
+        X = _empty(kk.shape, dtype=torch.float32, device=kk.device)
         _check(load().nsa_gdn_tmat_fwd(_p(kk), _p(qkr), _p(gc), _p(bh), _p(Tu), _p(Tw), _p(qk), _p(X), c_long(n), c_float(scale),
                                        _stream()))
         ctx.save_for_backward(kk, qkr, gc, bh, X)
@@ -618,16 +692,16 @@ class _GDNTmat(torch.autograd.Function):
     def backward(ctx, dTu, dTw, dqk):
         kk, qkr, gc, bh, X = ctx.saved_tensors
         n = gc.numel() // 64
-        z = lambda t: torch.zeros_like(kk) if t is None else t.to(torch.bfloat16).contiguous()
+        z = lambda t: _zeros_like(kk) if t is None else t.to(torch.bfloat16).contiguous()
         dTu, dTw, dqk = z(dTu), z(dTw), z(dqk)
-        dX = torch.empty_like(X)
+        dX = _empty_like(X)
         lib = load()
         _check(lib.nsa_gdn_tmat_dx(_p(dTu), _p(dTw), _p(gc), _p(bh), _p(dX), c_long(n), _stream()))
         Xt = X.transpose(-1, -2)
         dA = -torch.matmul(torch.matmul(Xt, dX), Xt)
         del dX
-        dkk, dqkr = torch.empty_like(kk), torch.empty_like(kk)
-        dgc, dbh = torch.empty_like(gc), torch.empty_like(bh)
+        dkk, dqkr = _empty_like(kk), _empty_like(kk)
+        dgc, dbh = _empty_like(gc), _empty_like(bh)
         _check(lib.nsa_gdn_tmat_bwd(_p(dA.contiguous()), _p(kk), _p(qkr), _p(dqk), _p(dTu), _p(dTw), _p(X), _p(gc), _p(bh), _p(dkk),
                                     _p(dqkr), _p(dgc), _p(dbh), c_long(n), c_float(ctx.scale), _stream()))
         return dkk, dqkr, dgc, dbh, None
@@ -685,8 +759,8 @@ class _Attn(torch.autograd.Function):
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         B, T, Hq, D = q.shape
         S, Hkv = k.shape[1], k.shape[2]
-        o = torch.empty_like(q)
-        L = torch.empty(B, T, Hq, dtype=torch.float32, device=q.device)
+        o = _empty_like(q)
+        L = _empty(B, T, Hq, dtype=torch.float32, device=q.device)
         tb, tm, tc, mu = tiles[:4] if tiles is not None else (None, None, None, 0)
         _check(load().nsa_attn_fwd(_p(q), _p(k), _p(v), _p(o), _p(L), c_int(B), c_int(T), c_int(S), c_int(Hq),
                                    c_int(Hkv), c_int(D), c_float(scale), c_int(int(causal)), c_int(window),
@@ -704,10 +778,10 @@ class _Attn(torch.autograd.Function):
         B, T, Hq, D = q.shape
         S, Hkv = k.shape[1], k.shape[2]
         do = do.contiguous()
-        dq = torch.empty_like(q)
-        dk = torch.zeros(k.shape, dtype=torch.float32, device=q.device)
-        dv = torch.zeros(v.shape, dtype=torch.float32, device=q.device)
-        delta = torch.empty(B, T, Hq, dtype=torch.float32, device=q.device)
+        dq = _empty_like(q)
+        dk = _zeros(k.shape, dtype=torch.float32, device=q.device)
+        dv = _zeros(v.shape, dtype=torch.float32, device=q.device)
+        delta = _empty(B, T, Hq, dtype=torch.float32, device=q.device)
         tb, tm, tc, mu = ctx.tiles[:4] if ctx.tiles is not None else (None, None, None, 0)
         G = Hq // Hkv
         split = D == 128 and os.environ.get("NSA_B200_ATTN_BWD", "split") == "split" and (ctx.tiles is None or G >= 8)
@@ -754,9 +828,9 @@ def union_blocks(idx: Tensor, G: int, nS: int):
     nqt = -(-T // R)
     max_u = min(R * top_n, nS)
     max_u += max_u & 1
-    tb = torch.empty(B, Hkv, nqt, max_u, dtype=torch.int32, device=idx.device)
-    tm = torch.empty(B, Hkv, nqt, max_u, dtype=torch.int64, device=idx.device)
-    tc = torch.empty(B, Hkv, nqt, dtype=torch.int32, device=idx.device)
+    tb = _empty(B, Hkv, nqt, max_u, dtype=torch.int32, device=idx.device)
+    tm = _empty(B, Hkv, nqt, max_u, dtype=torch.int64, device=idx.device)
+    tc = _empty(B, Hkv, nqt, dtype=torch.int32, device=idx.device)
     _check(load().nsa_union_blocks(_p(idx), _p(tb), _p(tm), _p(tc), c_int(B), c_int(T), c_int(Hkv), c_int(G),
                                    c_int(top_n), c_int(nS), c_int(max_u), _stream()))
     return tb, tm, tc, max_u
@@ -782,7 +856,7 @@ def inverse_blocks(idx: Tensor, nS: int, R: int, visits_per_cta: int):
     list_start = torch.searchsorted(skey, torch.arange(lists + 1, device=dev, dtype=torch.int64)).to(torch.int32)
     cnt = list_start[1:] - list_start[:-1]
     items = (-(-cnt // R) + visits_per_cta - 1) // visits_per_cta
-    item_start = torch.zeros(lists + 1, dtype=torch.int32, device=dev)
+    item_start = _zeros(lists + 1, dtype=torch.int32, device=dev)
     item_start[1:] = items.cumsum(0)
     bound = (B * Hkv * T * n) // (R * visits_per_cta) + lists
     return tok, list_start, item_start, nS, bound
@@ -802,7 +876,7 @@ def selected_attention(q, k, v, idx, scale=None):
 def nsa_importance(q, k_cmp, L_cmp, nS, stride, block, scale):
     B, T, Hq, D = q.shape
     Hkv = k_cmp.shape[2]
-    imp = torch.zeros(B, Hkv, T, nS, dtype=torch.float32, device=q.device)
+    imp = _zeros(B, Hkv, T, nS, dtype=torch.float32, device=q.device)
     _check(load().nsa_attn_importance(_p(q.contiguous()), _p(k_cmp.contiguous()), _p(L_cmp), _p(imp), c_int(B), c_int(T),
                                       c_int(k_cmp.shape[1]), c_int(Hq), c_int(Hkv), c_int(D), c_float(scale),
                                       c_int(stride), c_int(block - 1), c_int(nS), _stream()))
@@ -816,7 +890,7 @@ def nsa_select(imp: Tensor, sel_block: int, top_n: int) -> Tensor:
     B, H, T, nS = imp.shape
     if imp.is_cuda and nS <= 2048 and imp.dtype == torch.float32:
         imp = imp.contiguous()
-        idx = torch.empty(B, H, T, top_n, dtype=torch.int32, device=imp.device)
+        idx = _empty(B, H, T, top_n, dtype=torch.int32, device=imp.device)
         _check(load().nsa_select_blocks(_p(imp), _p(idx), c_long(B * H * T), c_int(T), c_int(nS), c_int(sel_block),
                                         c_int(top_n), _stream()))
         return idx
@@ -847,7 +921,7 @@ class _GateCombine(torch.autograd.Function):
         g1, g2, g3 = (g.to(torch.bfloat16).contiguous() for g in (g1, g2, g3))
         D = o1.shape[-1]
         rows = o1.numel() // D
-        o = torch.empty_like(o1)
+        o = _empty_like(o1)
         _check(load().nsa_gate_combine_fwd(_p(o1), _p(o2), _p(o3), _p(g1), _p(g2), _p(g3), _p(o), c_long(rows), c_int(D),
                                            _stream()))
         ctx.save_for_backward(o1, o2, o3, g1, g2, g3)
@@ -859,8 +933,8 @@ class _GateCombine(torch.autograd.Function):
         do = do.contiguous()
         D = o1.shape[-1]
         rows = o1.numel() // D
-        d1, d2, d3 = torch.empty_like(o1), torch.empty_like(o1), torch.empty_like(o1)
-        e1, e2, e3 = torch.empty_like(g1), torch.empty_like(g1), torch.empty_like(g1)
+        d1, d2, d3 = _empty_like(o1), _empty_like(o1), _empty_like(o1)
+        e1, e2, e3 = _empty_like(g1), _empty_like(g1), _empty_like(g1)
         _check(load().nsa_gate_combine_bwd(_p(o1), _p(o2), _p(o3), _p(g1), _p(g2), _p(g3), _p(do), _p(d1), _p(d2), _p(d3),
                                            _p(e1), _p(e2), _p(e3), c_long(rows), c_int(D), _stream()))
         return d1, d2, d3, e1, e2, e3
@@ -904,7 +978,7 @@ class _SSDStatePass(torch.autograd.Function):
         S, gamma = S.contiguous(), gamma.contiguous()
         B, nc, H = gamma.shape
         E = S[0, 0, 0].numel()
-        Hprev = torch.empty_like(S)
+        Hprev = _empty_like(S)
         _check(load().nsa_ssd_state_fwd(_p(S), _p(gamma), _p(Hprev), c_void_p(0), c_void_p(0), c_int(B), c_int(nc),
                                         c_int(H), c_long(E), _stream()))
         ctx.save_for_backward(gamma, Hprev)
@@ -916,7 +990,7 @@ class _SSDStatePass(torch.autograd.Function):
         B, nc, H = gamma.shape
         E = Hprev[0, 0, 0].numel()
         dHprev = dHprev.contiguous().float()
-        dS = torch.empty_like(Hprev)
+        dS = _empty_like(Hprev)
         _check(load().nsa_ssd_state_bwd(_p(dHprev), _p(gamma), _p(dS), c_void_p(0), c_int(B), c_int(nc), c_int(H), c_long(E),
                                         _stream()))
         dgamma = (Hprev * dS).sum((-1, -2))
@@ -951,19 +1025,19 @@ class _SSD(torch.autograd.Function):
         A = A.float().contiguous()
         Df = None if D is None else D.float().contiguous()
         dev = x.device
-        S_loc = torch.empty(Bsz, nc, H, N, P, dtype=torch.float32, device=dev)
-        gamma = torch.empty(Bsz, nc, H, dtype=torch.float32, device=dev)
+        S_loc = _empty(Bsz, nc, H, N, P, dtype=torch.float32, device=dev)
+        gamma = _empty(Bsz, nc, H, dtype=torch.float32, device=dev)
         lib = load()
         _check(lib.nsa_ssd_chunk_state(c_int(0), _p(Bm), c_long(ldb), _p(x), c_long(ldx), _p(dt), _p(A), _p(S_loc), _p(gamma),
                                        c_int(Bsz), c_int(T), c_int(H), c_int(N), c_int(P), _stream()))
-        Hb = torch.empty(Bsz, nc, H, N, P, dtype=torch.bfloat16, device=dev)
+        Hb = _empty(Bsz, nc, H, N, P, dtype=torch.bfloat16, device=dev)
         _check(lib.nsa_ssd_state_fwd(_p(S_loc), _p(gamma), c_void_p(0), _p(Hb), c_void_p(0), c_int(Bsz), c_int(nc), c_int(H),
                                      c_long(N * P), _stream()))
         del S_loc
-        y = torch.empty(Bsz, T, H, P, dtype=torch.bfloat16, device=dev)
+        y = _empty(Bsz, T, H, P, dtype=torch.bfloat16, device=dev)
         _check(lib.nsa_ssd_chunk_out(_p(Cm), c_long(ldc), _p(Bm), c_long(ldb), _p(x), c_long(ldx), _p(Hb), _p(dt), _p(A),
                                      _p(Df), _p(y), c_int(Bsz), c_int(T), c_int(H), c_int(N), c_int(P), _stream()))
-        ctx.save_for_backward(x, dt, A, Bm, Cm, Df if Df is not None else torch.empty(0, device=dev), y, gamma, Hb)
+        ctx.save_for_backward(x, dt, A, Bm, Cm, Df if Df is not None else _empty(0, device=dev), y, gamma, Hb)
         ctx.lds = (ldx, ldb, ldc)
         ctx.has_D = D is not None
         return y
@@ -979,20 +1053,20 @@ class _SSD(torch.autograd.Function):
         dev = y.device
         dy = dy.contiguous()
         lib = load()
-        G = torch.empty(Bsz, nc, H, N, P, dtype=torch.float32, device=dev)
+        G = _empty(Bsz, nc, H, N, P, dtype=torch.float32, device=dev)
         _check(lib.nsa_ssd_chunk_state(c_int(1), _p(Cm), c_long(ldc), _p(dy), c_long(H * P), _p(dt), _p(A), _p(G), c_void_p(0),
                                        c_int(Bsz), c_int(T), c_int(H), c_int(N), c_int(P), _stream()))
-        dHn = torch.empty(Bsz, nc, H, N, P, dtype=torch.bfloat16, device=dev)
+        dHn = _empty(Bsz, nc, H, N, P, dtype=torch.bfloat16, device=dev)
         _check(lib.nsa_ssd_state_bwd(_p(G), _p(gamma), c_void_p(0), _p(dHn), c_int(Bsz), c_int(nc), c_int(H), c_long(N * P),
                                      _stream()))
         del G
-        dx = torch.empty(Bsz, T, H, P, dtype=torch.bfloat16, device=dev)
+        dx = _empty(Bsz, T, H, P, dtype=torch.bfloat16, device=dev)
         # dB / dC: every head writes its own bf16 rows, summed afterwards (64 heads reducing into the
         # same fp32 rows with vector atomics was the slowest part of the kernel)
-        dBh = torch.empty(Bsz, T, H, N, dtype=torch.bfloat16, device=dev)
-        dCh = torch.empty(Bsz, T, H, N, dtype=torch.bfloat16, device=dev)
-        q = torch.empty(Bsz, T, H, dtype=torch.float32, device=dev)
-        k = torch.empty(Bsz, T, H, dtype=torch.float32, device=dev)
+        dBh = _empty(Bsz, T, H, N, dtype=torch.bfloat16, device=dev)
+        dCh = _empty(Bsz, T, H, N, dtype=torch.bfloat16, device=dev)
+        q = _empty(Bsz, T, H, dtype=torch.float32, device=dev)
+        k = _empty(Bsz, T, H, dtype=torch.float32, device=dev)
         _check(lib.nsa_ssd_chunk_grad_heads(_p(Cm), c_long(ldc), _p(Bm), c_long(ldb), _p(x), c_long(ldx), _p(dy), _p(y), _p(Hb),
                                             _p(dHn), _p(dt), _p(A), _p(Df), _p(dx), _p(dBh), _p(dCh), _p(q), _p(k), c_int(Bsz),
                                             c_int(T), c_int(H), c_int(N), c_int(P), _stream()))
@@ -1014,8 +1088,8 @@ def sumsq(tensors) -> Tensor:
     """Sum of squares over a list of bf16 / fp32 CUDA tensors -> fp32 device scalar (no host sync)."""
     lib = load()
     dev = tensors[0].device
-    out = torch.zeros((), dtype=torch.float32, device=dev)
-    partial = torch.empty(int(lib.nsa_sumsq_parts()), dtype=torch.float32, device=dev)
+    out = _zeros((), dtype=torch.float32, device=dev)
+    partial = _empty(int(lib.nsa_sumsq_parts()), dtype=torch.float32, device=dev)
     for g in tensors:
         if g.dtype not in (torch.bfloat16, torch.float32) or not g.is_contiguous():
             g = g.float().contiguous()
@@ -1029,9 +1103,9 @@ def affine_quantize(t: Tensor, bits: int, q_block: int):
     rows, cols = t.shape
     nblk = -(-cols // q_block)
     t = t.float().contiguous()
-    q = torch.empty(rows, nblk * q_block, dtype=torch.uint8, device=t.device)
-    scale = torch.empty(rows, nblk, dtype=torch.float32, device=t.device)
-    zero = torch.empty(rows, nblk, dtype=torch.float32, device=t.device)
+    q = _empty(rows, nblk * q_block, dtype=torch.uint8, device=t.device)
+    scale = _empty(rows, nblk, dtype=torch.float32, device=t.device)
+    zero = _empty(rows, nblk, dtype=torch.float32, device=t.device)
     _check(load().nsa_affine_quant(_p(t), _p(q), _p(scale), _p(zero), c_long(rows), c_int(cols), c_int(q_block), c_int(bits),
                                    _stream()))
     return q, scale, zero, cols
@@ -1040,7 +1114,7 @@ def affine_quantize(t: Tensor, bits: int, q_block: int):
 def affine_dequantize(q: Tensor, scale: Tensor, zero: Tensor, orig_cols: int) -> Tensor:
     rows = q.shape[0]
     q_block = q.shape[1] // scale.shape[1]
-    out = torch.empty(rows, orig_cols, dtype=torch.float32, device=q.device)
+    out = _empty(rows, orig_cols, dtype=torch.float32, device=q.device)
     _check(load().nsa_affine_dequant(_p(q.contiguous()), _p(scale.contiguous()), _p(zero.contiguous()), _p(out), c_long(rows),
                                      c_int(orig_cols), c_int(q_block), _stream()))
     return out
@@ -1054,7 +1128,7 @@ def mamba3_gate(u: Tensor, dt: Tensor, A: Tensor, Bc: Tensor, Cc: Tensor, D: Ten
     N = A.shape[1]
     f = lambda t: t.detach().float().contiguous()
     u, dt, A, Bc, Cc, D = f(u), f(dt), f(A), f(Bc), f(Cc), f(D)
-    gate = torch.empty(B, L, H, dtype=torch.float32, device=u.device)
+    gate = _empty(B, L, H, dtype=torch.float32, device=u.device)
     _check(load().nsa_mamba3_scan(_p(u), _p(dt), _p(A), _p(Bc), _p(Cc), _p(D), _p(gate), c_int(B), c_int(L), c_int(H),
                                   c_int(N), _stream()))
     return gate

@@ -187,3 +187,22 @@ def test_affine_block_quant_matches_torch_form(native, cols, q_block, bits):
     back = quant.affine_dequantize(q, sc, zp, oc)
     assert back.shape == (37, cols) and torch.allclose(back, back2, atol=float(sc.max()) * 1.01)
     assert (back - t).abs().max() <= float(sc.max()) * 1.01 + 1e-6
+
+
+def test_canary_mode_catches_a_write_past_the_output(native, monkeypatch):
+    """Debug allocation mode: outputs sit between guard zones; an intact run verifies clean, a byte
+    written just past an output is reported."""
+    monkeypatch.setattr(native, "_CANARY", True)
+    native._guards.clear()
+    x = torch.randn(64, 256, device="cuda").bfloat16()
+    w = torch.ones(256, device="cuda").bfloat16()
+    from nsa_optim_b200 import ops
+    y = ops.rms_norm(x, w, 1e-6)
+    assert torch.allclose(y.float(), oracle.rms_norm(x.float(), w.float(), 1e-6), atol=3e-2, rtol=3e-2)
+    assert native.check_canaries() >= 1
+    out = native._empty(16, dtype=torch.float32, device=x.device)
+    buf, nbytes = native._guards[-1]
+    buf[native._GUARD + nbytes] = 0                 # what a kernel writing one element too far would do
+    with pytest.raises(RuntimeError, match="guard zone after"):
+        native.check_canaries()
+    assert out.numel() == 16
