@@ -167,3 +167,20 @@ def test_loss_helpers():
     none, l2 = compute_cross_entropy_loss(h, head, y, create_cross_entropy_loss(head, "liger"))
     assert logits.shape == (2, 6, 11) and none is None and torch.allclose(l1, l2, atol=1e-5)
     assert create_cross_entropy_loss(head, "baseline") is None
+
+
+def test_split_last_backward_equals_torch_split():
+    """The column split used by the Mamba mixer: same values and the same gradient as torch.split,
+    including a group that receives no gradient."""
+    from nsa_optim_b200.models.kernels import split_last
+    torch.manual_seed(0)
+    x = torch.randn(3, 5, 12, requires_grad=True)
+    a, b, c = split_last(x, [4, 6, 2])
+    ra, rb, rc = torch.split(x.detach().clone().requires_grad_(True), [4, 6, 2], dim=-1)
+    assert torch.equal(a, ra) and torch.equal(b, rb) and torch.equal(c, rc)
+    w = torch.randn(3, 5, 4)
+    (g,) = torch.autograd.grad((a * w).sum() + (c ** 2).sum(), x)
+    want = torch.zeros_like(x)
+    want[..., :4] = w
+    want[..., 10:] = 2 * x.detach()[..., 10:]
+    assert torch.allclose(g, want)
