@@ -27,7 +27,8 @@ from .. import ops
 from ..config import AttentionType, resolve_attention_type
 from .base import CausalLMBase, default_loss_fn, init_linear_embedding_
 from .deltanet import GatedDeltaNetMixer
-from .kernels import Embedding, Linear, RotaryEmbedding, apply_rotary_pos_emb, create_mlp, create_rms_norm
+from .kernels import (Embedding, Linear, RotaryEmbedding, apply_rotary_pos_emb, create_mlp, create_rms_norm,
+                      resolve_kv_heads)
 from .mamba import Mamba2Mixer
 
 
@@ -133,7 +134,8 @@ class AttentionBlock(nn.Module):
     def __init__(self, config: HybridConfig, layer_idx: int):
         super().__init__()
         self.layer_idx = layer_idx
-        self.num_heads, self.num_kv_heads = config.num_attention_heads, config.num_key_value_heads
+        self.num_heads = config.num_attention_heads
+        self.num_kv_heads = resolve_kv_heads(self.num_heads, config.num_key_value_heads)
         self.head_dim = config.head_dim
         self.sparse = config.attention_type != AttentionType.DENSE
         d = config.d_model

@@ -215,3 +215,14 @@ def split_last(x: Tensor, sizes) -> tuple:
     if not (x.requires_grad and torch.is_grad_enabled()):
         return torch.split(x, list(sizes), dim=-1)
     return _SplitLast.apply(x, *sizes)
+
+
+def resolve_kv_heads(num_heads: int, num_kv_heads: int) -> int:
+    """KV head count usable for grouped-query attention: the largest divisor of ``num_heads`` not
+    above ``num_kv_heads``.  The size table gives the smallest models more KV heads than query
+    heads (100M: 4 query / 8 KV heads, config.py:145), which no attention path can run; those
+    shapes get one KV head per query head."""
+    kv = max(1, min(num_kv_heads, num_heads))
+    while num_heads % kv:
+        kv -= 1
+    return kv

@@ -25,7 +25,7 @@ from torch import Tensor
 from .. import ops
 from ..config import AttentionType, ModelConfig
 from .base import CausalLMBase, default_loss_fn, init_linear_embedding_
-from .kernels import (Embedding, KernelType, Linear, RotaryEmbedding, apply_rotary_pos_emb,
+from .kernels import (Embedding, KernelType, Linear, RotaryEmbedding, apply_rotary_pos_emb, resolve_kv_heads,
                       create_mlp, create_rms_norm)
 
 FSA_AVAILABLE = True  # the sparse kernels are built in; kept for import compatibility
@@ -47,7 +47,7 @@ class DenseAttention(nn.Module):
         self.layer_idx = layer_idx
         self.hidden_size = config.hidden_size
         self.num_heads = config.num_attention_heads
-        self.num_kv_heads = config.num_key_value_heads
+        self.num_kv_heads = resolve_kv_heads(config.num_attention_heads, config.num_key_value_heads)
         self.head_dim = config.head_dim
         self.num_kv_groups = self.num_heads // self.num_kv_heads
         self.q_proj = Linear(self.hidden_size, self.num_heads * self.head_dim)

@@ -184,3 +184,17 @@ def test_split_last_backward_equals_torch_split():
     want[..., :4] = w
     want[..., 10:] = 2 * x.detach()[..., 10:]
     assert torch.allclose(g, want)
+
+
+def test_kv_heads_resolve_to_a_divisor_of_the_query_heads():
+    """The size table gives 100M models 4 query and 8 KV heads; attention modules fall back to a
+    usable grouping, and the 100M hybrid (the smoke-test size) runs a step."""
+    from nsa_optim_b200.models.kernels import resolve_kv_heads
+    assert resolve_kv_heads(4, 8) == 4 and resolve_kv_heads(32, 8) == 8 and resolve_kv_heads(6, 4) == 3
+    cfg = HybridConfig(d_model=64, vocab_size=64, block_pattern="A", block_repeats=1, num_attention_heads=4,
+                       num_key_value_heads=8, head_dim=16, intermediate_size=64)
+    m = create_hybrid_model(cfg)
+    ids = torch.randint(0, 64, (1, 16))
+    _, loss, _ = m(input_ids=ids, labels=ids)
+    loss.backward()
+    assert m.layers[0].k_proj.weight.shape[0] == 4 * 16
