@@ -205,7 +205,12 @@ class _SplitLast(torch.autograd.Function):
             if g is None:
                 out[..., o:o + n].zero_()
             else:
-                out[..., o:o + n].copy_(g)
+                dst = out[..., o:o + n]
+                done = False
+                if dst.is_cuda and ops.get_backend() != "torch":
+                    done = ops.native_module().copy_columns(dst, g)
+                if not done:
+                    dst.copy_(g)
             o += n
         return (out,) + (None,) * len(ctx.sizes)
 

@@ -129,3 +129,12 @@ extern "C" int nsa_status_read(int* out, int reset) {
   return 0;
 }
 extern "C" int nsa_sm_count() { return nsa::sm_count(); }
+
+// Row-pitched device-to-device copy (column slices of row-major matrices) on `st`.
+extern "C" int nsa_copy2d(void* dst, long dst_pitch_bytes, const void* src, long src_pitch_bytes, long width_bytes, long rows,
+                          cudaStream_t st) {
+  if (rows <= 0 || width_bytes <= 0) return 0;
+  cudaError_t e = cudaMemcpy2DAsync(dst, static_cast<size_t>(dst_pitch_bytes), src, static_cast<size_t>(src_pitch_bytes),
+                                    static_cast<size_t>(width_bytes), static_cast<size_t>(rows), cudaMemcpyDeviceToDevice, st);
+  return e == cudaSuccess ? 0 : nsa::fail_cuda(e, "nsa_copy2d");
+}

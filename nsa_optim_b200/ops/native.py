@@ -1084,6 +1084,34 @@ class _SSD(torch.autograd.Function):
         return (dx, ddt, dA, dB.view(Bsz, T, 1, N).to(torch.bfloat16), dC.view(Bsz, T, 1, N).to(torch.bfloat16), dD)
 
 
+def copy_columns(dst: Tensor, src: Tensor) -> bool:
+    """dst[...] = src for two tensors that are column slices of row-major matrices (last dimension
+    contiguous, one uniform row pitch): a pitched device copy instead of a generic strided kernel.
+    Returns False (nothing done) when the layouts do not qualify."""
+    if dst.shape != src.shape or dst.dtype != src.dtype or not (dst.is_cuda and src.is_cuda) or dst.dim() < 2:
+        return False
+    def pitch(t):
+        if t.stride(-1) != 1:
+            return None
+        p = t.stride(-2)
+        if p < t.shape[-1]:
+            return None
+        exp = p
+        for d in range(t.dim() - 2, -1, -1):           # leading dims must fold into rows of pitch p
+            if t.shape[d] != 1 and t.stride(d) != exp:
+                return None
+            exp *= t.shape[d]
+        return p
+    dp, sp = pitch(dst), pitch(src)
+    if dp is None or sp is None:
+        return False
+    es = dst.element_size()
+    rows = dst.numel() // dst.shape[-1]
+    _check(load().nsa_copy2d(_p(dst), c_long(dp * es), _p(src), c_long(sp * es), c_long(dst.shape[-1] * es), c_long(rows),
+                             _stream()))
+    return True
+
+
 def sumsq(tensors) -> Tensor:
     """Sum of squares over a list of bf16 / fp32 CUDA tensors -> fp32 device scalar (no host sync)."""
     lib = load()

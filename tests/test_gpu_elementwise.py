@@ -206,3 +206,13 @@ def test_canary_mode_catches_a_write_past_the_output(native, monkeypatch):
     with pytest.raises(RuntimeError, match="guard zone after"):
         native.check_canaries()
     assert out.numel() == 16
+
+
+def test_pitched_column_copy(native):
+    out = torch.zeros(3, 50, 40, device="cuda").bfloat16()
+    g = torch.randn(3, 50, 16, device="cuda").bfloat16()
+    assert native.copy_columns(out[..., 8:24], g)
+    ref = torch.zeros_like(out)
+    ref[..., 8:24] = g
+    assert torch.equal(out, ref)
+    assert not native.copy_columns(out[..., 8:24], g[:, :, :1].expand(3, 50, 16))     # broadcast source: not a pitched layout
