@@ -139,6 +139,40 @@ int nsa_ssd_chunk_grad(const void* Cm, long ld_c, const void* Bm, long ld_b, con
     void* dx, float* dB_acc, float* dC_acc, float* q_out, float* k_out, int B, int T, int H, int N, int P, cudaStream_t
     st);
 
+/* ---- further entry points of attention.cu ---- */
+int nsa_select_blocks(const float* imp, int* idx, long rows, int T, int nS, int sel_block, int top_n, cudaStream_t
+    st);
+
+/* ---- further entry points of elementwise.cu ---- */
+int nsa_gdn_pack_fwd(const void* q, const void* k, const void* v, const float* sq, const float* sk, void* qh, void*
+    kh, void* vh, void* qd, void* kt, int B, int T, int Tp, int H, int K, int V, cudaStream_t st);
+int nsa_gdn_pack_bwd(const void* q, const void* k, const float* sq, const float* sk, const void* dqh, const void*
+    dkh, const void* dvh, const void* dqd, const void* dkt, void* dq, void* dk, void* dv, float* dsq, float* dsk, int B,
+    int T, int Tp, int H, int K, int V, cudaStream_t st);
+int nsa_gdn_tmat_fwd(const void* kk, const void* qkr, const float* gc, const float* beta, void* Tu, void* Tw, void*
+    qk, float* X, long n_chunks, float scale, cudaStream_t st);
+int nsa_gdn_tmat_dx(const void* dTu, const void* dTw, const float* gc, const float* beta, float* dX, long n_chunks,
+    cudaStream_t st);
+int nsa_gdn_tmat_bwd(const float* dA, const void* kk, const void* qkr, const void* dqk, const void* dTu, const void*
+    dTw, const float* X, const float* gc, const float* beta, void* dkk, void* dqkr, float* dgc, float* dbeta, long
+    n_chunks, float scale, cudaStream_t st);
+
+/* ---- further entry points of optim.cu ---- */
+int nsa_affine_quant(const float* t, uint8_t* q, float* scale, float* zero, long rows, int cols, int q_block, int
+    bits, cudaStream_t st);
+int nsa_affine_dequant(const uint8_t* q, const float* scale, const float* zero, float* out, long rows, int cols, int
+    q_block, cudaStream_t st);
+
+/* ---- further entry points of runtime.cu ---- */
+int nsa_copy2d(void* dst, long dst_pitch_bytes, const void* src, long src_pitch_bytes, long width_bytes, long rows,
+    cudaStream_t st);
+
+/* ---- further entry points of ssd.cu ---- */
+int nsa_ssd_chunk_grad_heads(const void* Cm, long ld_c, const void* Bm, long ld_b, const void* x, long ld_x, const
+    void* dy, const void* y, const void* Hprev_bf16, const void* dHn_bf16, const float* dt, const float* A, const float*
+    Dskip, void* dx, void* dB_heads, void* dC_heads, float* q_out, float* k_out, float* r_out, int B, int T, int H, int
+    N, int P, cudaStream_t st);
+
 #ifdef __cplusplus
 }
 #endif

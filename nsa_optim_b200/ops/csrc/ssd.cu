@@ -98,6 +98,7 @@ struct SsdParams {
   bf16* dC_heads;      //   the caller sums over heads: 64 heads adding into one row contend for the same L2 lines otherwise
   float* q_out;        // [B, T, H]  dy . (y - D x)
   float* k_out;        // [B, T, H]  x . dx (without the D term)
+  float* r_out;        // [B, T, H]  dy . x (gradient of the skip weight D before the sum over tokens), or null
   KernelStatus* status;
 };
 
@@ -490,7 +491,7 @@ ssd_chunk_grad_kernel(const __grid_constant__ CUtensorMap tm_c, const __grid_con
         const bf16* xr = p.x_raw + tok * p.ldx + h * PD;
         const bf16* dyr = p.dy_raw + (tok * p.H + h) * PD;
         uint4* dst = reinterpret_cast<uint4*>(p.dx + (tok * p.H + h) * PD);
-        float kacc = 0.f;
+        float kacc = 0.f, racc = 0.f;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const uint4 xv = reinterpret_cast<const uint4*>(xr)[j];
@@ -504,11 +505,13 @@ ssd_chunk_grad_kernel(const __grid_constant__ CUtensorMap tm_c, const __grid_con
             const int i0 = 8 * j + 2 * k;
             const float g0 = dxa[i0] + s_row * dxi[i0], g1 = dxa[i0 + 1] + s_row * dxi[i0 + 1];
             kacc += xf.x * g0 + xf.y * g1;
+            racc += xf.x * df.x + xf.y * df.y;
             o[k] = tc5::pack_bf16(g0 + dsk * df.x, g1 + dsk * df.y);
           }
           dst[j] = make_uint4(o[0], o[1], o[2], o[3]);
         }
         p.k_out[tok * p.H + h] = kacc;
+        if (p.r_out) p.r_out[tok * p.H + h] = racc;
       }
     }
     float q_inter = 0.f;    // C_i . (dy_i H^T): the state-path part of dy.(y - D x), before exp(cum_i)
@@ -690,8 +693,8 @@ extern "C" int nsa_ssd_chunk_out(const void* Cm, long ld_c, const void* Bm, long
 static int ssd_chunk_grad_impl(const void* Cm, long ld_c, const void* Bm, long ld_b, const void* x, long ld_x,
                                const void* dy, const void* y, const void* Hprev_bf16, const void* dHn_bf16,
                                const float* dt, const float* A, const float* Dskip, void* dx, float* dB_acc,
-                               float* dC_acc, void* dB_heads, void* dC_heads, float* q_out, float* k_out, int B, int T,
-                               int H, int N, int P, cudaStream_t st) {
+                               float* dC_acc, void* dB_heads, void* dC_heads, float* q_out, float* k_out, float* r_out,
+                               int B, int T, int H, int N, int P, cudaStream_t st) {
   int rc = check_dims(N, P, ld_c | ld_b, ld_x);
   if (rc) return rc;
   const int nc = (T + L - 1) / L;
@@ -707,7 +710,7 @@ static int ssd_chunk_grad_impl(const void* Cm, long ld_c, const void* Bm, long l
   p.dt = dt; p.A = A; p.Dskip = Dskip; p.B = B; p.T = T; p.H = H; p.nc = nc;
   p.x_raw = (const bf16*)x; p.ldx = ld_x; p.y_in = (const bf16*)y; p.dy_raw = (const bf16*)dy; p.dx = (bf16*)dx;
   p.dB_acc = dB_acc; p.dC_acc = dC_acc; p.q_out = q_out; p.k_out = k_out; p.status = nsa::status_ptr();
-  p.dB_heads = (bf16*)dB_heads; p.dC_heads = (bf16*)dC_heads;
+  p.dB_heads = (bf16*)dB_heads; p.dC_heads = (bf16*)dC_heads; p.r_out = r_out;
   const int smem = 13 * BOXB + 1024 + 2048;
   static bool cfg = false;
   if (!cfg) { if ((rc = smem_attr(ssd_chunk_grad_kernel, smem))) return rc; cfg = true; }
@@ -723,15 +726,16 @@ extern "C" int nsa_ssd_chunk_grad(const void* Cm, long ld_c, const void* Bm, lon
                                   float* dC_acc, float* q_out, float* k_out, int B, int T, int H, int N, int P,
                                   cudaStream_t st) {
   return ssd_chunk_grad_impl(Cm, ld_c, Bm, ld_b, x, ld_x, dy, y, Hprev_bf16, dHn_bf16, dt, A, Dskip, dx, dB_acc, dC_acc,
-                             nullptr, nullptr, q_out, k_out, B, T, H, N, P, st);
+                             nullptr, nullptr, q_out, k_out, nullptr, B, T, H, N, P, st);
 }
 // Same, with dB / dC written per head as bf16 [B, T, H, N] (plain stores); the caller sums over heads.
+// r_out (optional, fp32 [B, T, H]) receives dy . x per token and head.
 extern "C" int nsa_ssd_chunk_grad_heads(const void* Cm, long ld_c, const void* Bm, long ld_b, const void* x, long ld_x,
                                         const void* dy, const void* y, const void* Hprev_bf16, const void* dHn_bf16,
                                         const float* dt, const float* A, const float* Dskip, void* dx, void* dB_heads,
-                                        void* dC_heads, float* q_out, float* k_out, int B, int T, int H, int N, int P,
-                                        cudaStream_t st) {
+                                        void* dC_heads, float* q_out, float* k_out, float* r_out, int B, int T, int H,
+                                        int N, int P, cudaStream_t st) {
   if (dB_heads == nullptr || dC_heads == nullptr) return nsa::fail(NSA_ERR_SHAPE, "ssd_chunk_grad_heads: null output");
   return ssd_chunk_grad_impl(Cm, ld_c, Bm, ld_b, x, ld_x, dy, y, Hprev_bf16, dHn_bf16, dt, A, Dskip, dx, nullptr, nullptr,
-                             dB_heads, dC_heads, q_out, k_out, B, T, H, N, P, st);
+                             dB_heads, dC_heads, q_out, k_out, r_out, B, T, H, N, P, st);
 }

@@ -1067,9 +1067,10 @@ class _SSD(torch.autograd.Function):
         dCh = _empty(Bsz, T, H, N, dtype=torch.bfloat16, device=dev)
         q = _empty(Bsz, T, H, dtype=torch.float32, device=dev)
         k = _empty(Bsz, T, H, dtype=torch.float32, device=dev)
+        rdx = _empty(Bsz, T, H, dtype=torch.float32, device=dev) if ctx.has_D else None
         _check(lib.nsa_ssd_chunk_grad_heads(_p(Cm), c_long(ldc), _p(Bm), c_long(ldb), _p(x), c_long(ldx), _p(dy), _p(y), _p(Hb),
-                                            _p(dHn), _p(dt), _p(A), _p(Df), _p(dx), _p(dBh), _p(dCh), _p(q), _p(k), c_int(Bsz),
-                                            c_int(T), c_int(H), c_int(N), c_int(P), _stream()))
+                                            _p(dHn), _p(dt), _p(A), _p(Df), _p(dx), _p(dBh), _p(dCh), _p(q), _p(k), _p(rdx),
+                                            c_int(Bsz), c_int(T), c_int(H), c_int(N), c_int(P), _stream()))
         dB = dBh.sum(2, dtype=torch.float32)
         dC = dCh.sum(2, dtype=torch.float32)
         del dBh, dCh
@@ -1080,7 +1081,7 @@ class _SSD(torch.autograd.Function):
         da = (pre[..., -1:] - pre + dcum).transpose(1, 2)
         ddt = da * A[None, None, :] + k / dt.clamp_min(1e-20)
         dA = (da * dt).sum((0, 1))
-        dD = (dy.float() * x.float()).sum((0, 1, 3)) if ctx.has_D else None
+        dD = rdx.sum((0, 1)) if ctx.has_D else None
         return (dx, ddt, dA, dB.view(Bsz, T, 1, N).to(torch.bfloat16), dC.view(Bsz, T, 1, N).to(torch.bfloat16), dD)
 
 
