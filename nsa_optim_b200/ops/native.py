@@ -614,7 +614,9 @@ class _GDNSeq(torch.autograd.Function):
         _check(load().nsa_gdn_seq_fwd(_p(w), _p(qd), _p(kt), _p(u), _p(gamma), _p(v_new), _p(o_inter), _p(S_all),
                                       c_int(BH), c_int(NC), c_int(K), c_int(V), _stream()))
         ctx.save_for_backward(w, qd, kt, gamma, S_all, v_new)
-        return v_new, o_inter
+        # handed on as bf16 (it is added to a bf16 matmul result next), so its gradient also arrives
+        # as bf16 instead of making an fp32 round trip
+        return v_new, o_inter.to(torch.bfloat16)
 
     @staticmethod
     def backward(ctx, dv_new, do_inter):
@@ -740,7 +742,7 @@ def gated_delta_rule(q, k, v, g, beta, scale=None, chunk=64):
     gamma = eg[..., -1].contiguous()
     v_new, o_inter = _GDNSeq.apply(w, qd, kt, u, gamma)
     # o = o_inter + qk v_new in one batched GEMM with fp32 accumulation
-    o = torch.baddbmm(o_inter.to(bf).view(-1, C, V), qk.view(-1, C, C), v_new.view(-1, C, V))
+    o = torch.baddbmm(o_inter.view(-1, C, V), qk.view(-1, C, C), v_new.view(-1, C, V))
     o = o.view(B, H, Tp, V).permute(0, 2, 1, 3)[:, :T]
     return o.to(v.dtype)
 
