@@ -791,10 +791,10 @@ class _Attn(torch.autograd.Function):
             # dQ from the query-tile-outer kernel, dK / dV from the key-block-stationary kernel
             R = 128 // G
             inv = (None, None, None, 0, 0)
-            visits = 128
+            visits = int(os.environ.get('NSA_B200_KV_VISITS', '128'))
             if ctx.tiles is not None:
                 idx, nS = ctx.tiles[4], ctx.tiles[5]
-                visits = 64
+                visits = int(os.environ.get('NSA_B200_KV_VISITS_SEL', '64'))
                 inv = inverse_blocks(idx, nS, R, visits)
             _check(load().nsa_attn_bwd_split(_p(q), _p(k), _p(v), _p(o), _p(do), _p(L), _p(delta), _p(dq), _p(dk), _p(dv),
                                              c_int(B), c_int(T), c_int(S), c_int(Hq), c_int(Hkv), c_int(D), c_float(scale),
