@@ -310,6 +310,11 @@ class ShardedModel(nn.Module):
 
             def run(x, weight, _u=unit):
                 native.clear_pending_gather()
+                # The per-chunk flags hold the epoch of the last gather.  Within one optimizer step the
+                # epoch does not change, so a second gather of the same unit (next micro-batch under
+                # gradient accumulation, after the buffer was freed and re-allocated) would find them
+                # already set and let the GEMM read rows the copy CTAs have not written yet.
+                _u.chunk_flags.zero_()
                 y = symm.gemm_all_gather(self.arena, x, _u.full, _u.off_shard, _u.shard_size,
                                          (weight.data_ptr() - lo_ptr) // es, weight.shape[0], _u.chunk_flags,
                                          _u.chunks_per_shard, _u.ch_shard, epoch)

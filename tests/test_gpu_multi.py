@@ -25,7 +25,7 @@ WORKER = textwrap.dedent("""
                        "--deltanet_num_heads", "2", "--nsa_window_size", "64", "--nsa_num_selected_blocks", "4",
                        "--context_length", "512", "--batch_size", "1", "--gradient_accumulation_steps", "2",
                        "--optimizer_type", "adamw8bit", "--synthetic_data", "--num_train_steps", "4", "--warmup_steps", "0",
-                       "-lr", "1e-3", "--comm", comm, "--gradient_checkpointing"])
+                       "-lr", "1e-3", "--comm", comm] + sys.argv[3:])
     tr = Trainer(args, verbose=False)
     losses = []
     for i in range(4):
@@ -41,12 +41,12 @@ WORKER = textwrap.dedent("""
 """)
 
 
-def _run(tmp_path, comm, port):
+def _run(tmp_path, comm, port, extra=("--gradient_checkpointing",)):
     script = tmp_path / "worker.py"
     script.write_text(WORKER.format(root=ROOT))
     env = dict(os.environ, WANDB_MODE="disabled", NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-           "127.0.0.1", "--master-port", str(port), str(script), str(tmp_path), comm]
+           "127.0.0.1", "--master-port", str(port), str(script), str(tmp_path), comm, *extra]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
     return json.load(open(tmp_path / f"res_{comm}.json"))
@@ -60,3 +60,16 @@ def test_fused_comm_matches_nccl(tmp_path):
     for x, y in zip(a["losses"], b["losses"]):
         assert abs(x - y) < 3e-2, (a, b)
     assert abs(a["norm"] - b["norm"]) < 5e-2 * max(1.0, a["norm"])
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_comm_under_gradient_accumulation_without_recompute(tmp_path):
+    """Two micro-batches per step, fully sharded, nothing recomputed: every block is gathered by its
+    first GEMM twice within one epoch, so the per-chunk flags of the first gather must not satisfy
+    the second one (which reads a freshly allocated buffer)."""
+    import math
+    a = _run(tmp_path, "nccl", 29815, extra=("--block_pattern", "DADA"))
+    b = _run(tmp_path, "fused", 29817, extra=("--block_pattern", "DADA"))
+    assert b["comm"] == "fused" and all(math.isfinite(x) for x in b["losses"])
+    for x, y in zip(a["losses"], b["losses"]):
+        assert abs(x - y) < 3e-2, (a, b)
