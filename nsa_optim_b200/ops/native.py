@@ -578,7 +578,19 @@ def linear_cross_entropy(hidden, weight, labels, ignore_index=-100, chunk=4096):
 # --------------------------------------------------------------------------------------
 # optimizer steps
 # --------------------------------------------------------------------------------------
+def _require_numel(what: str, t: Optional[Tensor], n: int) -> None:
+    """The update kernels index every state tensor with the parameter's element count; a state
+    restored from a checkpoint of another sharding would make them run past its end."""
+    if t is not None and t.numel() != n:
+        raise ValueError(f"optimizer state '{what}' has {t.numel()} elements, the kernel needs {n}")
+
+
 def adamw_step(p, g, m, v, master, step, lr, b1, b2, eps, wd, grad_scale):
+    n = p.numel()
+    _require_numel("grad", g, n)
+    _require_numel("exp_avg", m, n)
+    _require_numel("exp_avg_sq", v, n)
+    _require_numel("master", master, n)
     gs = None if grad_scale is None else grad_scale.reshape(1).float()
     _check(load().nsa_adamw_step(_p(p), _p(g), _p(m), _p(v), _p(master), _p(gs), c_long(p.numel()),
                                  c_int(int(p.dtype == torch.float32)), c_int(int(g.dtype == torch.float32)),
@@ -588,6 +600,14 @@ def adamw_step(p, g, m, v, master, step, lr, b1, b2, eps, wd, grad_scale):
 def adamw8bit_step(p, g, mq, mabs, vq, vabs, step, lr, b1, b2, eps, wd, grad_scale, block):
     if block != 256:
         raise ValueError("the native 8-bit AdamW kernel uses 256-element blocks")
+    n = p.numel()
+    if n % block:
+        raise ValueError(f"8-bit AdamW needs a multiple of {block} elements, got {n}")
+    _require_numel("grad", g, n)
+    _require_numel("exp_avg", mq, n)
+    _require_numel("exp_avg_sq", vq, n)
+    _require_numel("exp_avg_absmax", mabs, n // block)
+    _require_numel("exp_avg_sq_absmax", vabs, n // block)
     gs = None if grad_scale is None else grad_scale.reshape(1).float()
     cs = quant.codebook(8, True, p.device)
     cu = quant.codebook(8, False, p.device)

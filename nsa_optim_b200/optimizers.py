@@ -42,10 +42,17 @@ from .ops import quant
 # parameter groups
 # --------------------------------------------------------------------------------------
 def is_no_decay(name: str, param: Tensor) -> bool:
-    """1-D tensors, biases, and anything whose name mentions layernorm or embed skip decay."""
+    """1-D tensors, biases, and anything whose name mentions layernorm or embed skip decay.
+
+    A shard piece handed out by the sharded runtime is always 1-D, whatever the parameter it was
+    cut from; it carries ``_is_matrix`` / ``_no_weight_decay`` describing the original parameter,
+    and those decide instead of ``ndim`` (otherwise every weight matrix would lose its decay as
+    soon as the world size exceeds one)."""
     lname = name.lower()
-    return (param.ndim == 1 or name.endswith(".bias") or "layernorm" in lname or "embed" in lname
-            or getattr(param, "_no_weight_decay", False))
+    by_name = name.endswith(".bias") or "layernorm" in lname or "embed" in lname
+    if hasattr(param, "_is_matrix"):
+        return by_name or bool(getattr(param, "_no_weight_decay", False)) or not param._is_matrix
+    return param.ndim == 1 or by_name or bool(getattr(param, "_no_weight_decay", False))
 
 
 def get_param_groups(model_or_named, weight_decay: float) -> List[Dict[str, Any]]:
@@ -548,6 +555,99 @@ class SOAPLowBit(Optimizer):
                 self._store_moment(st, "exp_avg_sq", False, V)
                 p.copy_(W.view_as(p))
         return loss
+
+
+# --------------------------------------------------------------------------------------
+# sharding-independent view of elementwise state (used by checkpoints)
+# --------------------------------------------------------------------------------------
+_NOT_ELEMENTWISE = ("L", "R", "L_inv", "QL", "L_blocks", "orig_2d_shape")
+
+
+def _moment_codec(optimizer: Optimizer) -> Tuple[int, int]:
+    """(bits, block) of the blockwise moment codec of ``optimizer`` (0, 0 when moments are fp32)."""
+    if isinstance(optimizer, AdamWLowBit):
+        return optimizer.bits, optimizer.block_size
+    if isinstance(optimizer, SOAPLowBit):
+        return optimizer.bits, optimizer.moment_block
+    return 0, 0
+
+
+def state_moments(state: Dict[str, Any], bits: int, block: int) -> Optional[Tuple[int, Tensor, Optional[Tensor]]]:
+    """``(step, exp_avg, exp_avg_sq)`` of one state entry as flat fp32 tensors, dequantised when
+    they are stored as codes; ``None`` for an entry that is not purely elementwise (Kronecker
+    factors, eigenbases) or has no first moment."""
+    if "exp_avg" not in state or any(k in state for k in _NOT_ELEMENTWISE):
+        return None
+
+    def load(key: str, signed: bool) -> Optional[Tensor]:
+        t = state.get(key)
+        if t is None:
+            return None
+        if t.dtype == torch.uint8:
+            return quant.dequantize_blockwise(t, state[key + "_absmax"], bits, signed, block).float().reshape(-1)
+        return t.float().reshape(-1)
+
+    return int(state.get("step", 0)), load("exp_avg", True), load("exp_avg_sq", False)
+
+
+def fresh_state(optimizer: Optimizer, p: Tensor) -> Optional[Dict[str, Any]]:
+    """The state ``optimizer`` would create for ``p`` on its first step (``None`` for the
+    optimizers that build it inline)."""
+    st: Dict[str, Any] = {}
+    if isinstance(optimizer, (AdamW, AdamWLowBit)):
+        optimizer._init(p, st)
+    elif isinstance(optimizer, SOAPLowBit):
+        group = next(g for g in optimizer.param_groups if any(q is p for q in g["params"]))
+        optimizer._init_state(p, st, group["max_precond_dim"])
+    else:
+        return None
+    return st
+
+
+def install_moments(optimizer: Optimizer, p: Tensor, step: int, m: Tensor, v: Optional[Tensor]) -> bool:
+    """Gives ``p`` a state whose moments are ``m`` / ``v`` (flat fp32, ``p.numel()`` long), in the
+    storage format this optimizer uses for ``p``.  False when ``p`` does not take elementwise
+    state here (a preconditioned matrix) and was left untouched."""
+    st = fresh_state(optimizer, p)
+    if st is None or any(k in st for k in _NOT_ELEMENTWISE) or m.numel() != p.numel():
+        return False
+    bits, block = _moment_codec(optimizer)
+    for key, val, signed in (("exp_avg", m, True), ("exp_avg_sq", v, False)):
+        if key not in st or val is None:
+            continue
+        val = val.to(p.device, torch.float32)
+        if st[key].dtype == torch.uint8:
+            st[key], st[key + "_absmax"] = quant.quantize_blockwise(val, bits, signed, block)
+        else:
+            st[key].copy_(val.view_as(st[key]))
+    st["step"] = int(step)
+    optimizer.state[p] = st
+    return True
+
+
+def state_fits(optimizer: Optimizer, p: Tensor, state: Dict[str, Any]) -> bool:
+    """Whether a saved state entry has the tensor sizes this optimizer's kernels will index for
+    ``p``.  Guards a resume against a checkpoint written under another sharding."""
+    bits, block = _moment_codec(optimizer)
+    n = p.numel()
+    for key in ("exp_avg", "exp_avg_sq", "master"):
+        t = state.get(key)
+        if not torch.is_tensor(t):
+            continue
+        want = n // 2 if (t.dtype == torch.uint8 and bits == 4) else n
+        if t.numel() != want:
+            return False
+        am = state.get(key + "_absmax")
+        if t.dtype == torch.uint8 and (not torch.is_tensor(am) or block == 0 or am.numel() != n // block):
+            return False
+    shape = state.get("orig_2d_shape")
+    if shape is not None and int(shape[0]) * int(shape[1]) != n:
+        return False
+    for key in ("L", "R", "QL", "QR", "L_inv", "R_inv"):
+        t = state.get(key)
+        if torch.is_tensor(t) and p.ndim == 2 and t.shape[0] not in p.shape:
+            return False
+    return True
 
 
 # --------------------------------------------------------------------------------------

@@ -96,8 +96,28 @@ WORKER = textwrap.dedent("""
             if world > 1:
                 torch.distributed.all_reduce(l); l /= world
             losses.append(float(l))
+        wsq = sum(float(v.double().pow(2).sum()) for v in tr.model.state_dict(rank0_only=False).values())
         if rank == 0:
-            json.dump({{"losses": losses, "norm": float(o["grad_norm"])}}, open(os.path.join(out, f"res_w{{world}}.json"), "w"))
+            json.dump({{"losses": losses, "norm": float(o["grad_norm"]), "wsq": wsq}},
+                      open(os.path.join(out, f"res_w{{world}}.json"), "w"))
+    elif mode == "save2":
+        tr.cfg.batch_size = 4 // world
+        for i in range(2):
+            tr.step([mine(full[i])])
+        tr.save()
+    elif mode == "continue":
+        tr.cfg.batch_size = 4 // world
+        ckpt = os.path.join(out, tr.cfg.run_name, "checkpoint-2")
+        assert tr.resume(ckpt) == 2
+        n_state = sum(1 for p in tr.optimizer.state.values() if p)
+        for i in range(2, 4):
+            o = tr.step([mine(full[i])])
+            l = o["loss"].detach().clone()
+            if world > 1:
+                torch.distributed.all_reduce(l); l /= world
+            losses.append(float(l))
+        if rank == 0:
+            json.dump({{"losses": losses, "n_state": n_state}}, open(os.path.join(out, f"cont_w{{world}}.json"), "w"))
     elif mode == "resume":
         for i in range(2):
             tr.step([mine(full[i])])
@@ -144,6 +164,52 @@ def test_two_ranks_match_one_rank(tmp_path, opt, extra):
     for a, b in zip(r1["losses"], r2["losses"]):
         assert abs(a - b) < tol, (r1, r2)
     assert abs(r1["norm"] - r2["norm"]) < 1e-2 * max(1.0, r1["norm"])
+
+
+def test_weight_decay_reaches_matrices_under_sharding(tmp_path):
+    """Shard pieces are 1-D views; the decay / no-decay split must follow the original parameter."""
+    from nsa_optim_b200.optimizers import get_param_groups
+    ps = [("w", torch.nn.Parameter(torch.randn(512, 512))), ("norm.weight", torch.nn.Parameter(torch.ones(512)))]
+    for world in (1, 2):
+        u = FlatUnit("u", None, [(n, torch.nn.Parameter(p.detach().clone())) for n, p in ps], world, 0,
+                     torch.device("cpu"), torch.float32)
+        decay, no_decay = get_param_groups(u.pieces, 0.1)
+        assert decay["param_names"] == ["w"] and no_decay["param_names"] == ["norm.weight"], world
+    # and end to end: with a large decay the weights of a 2-rank run shrink as in the 1-rank run
+    args = ("--optimizer_type", "adamw", "-wd", "3.0")
+    run_ranks(tmp_path, 1, "train", args)
+    run_ranks(tmp_path, 2, "train", args, port=29747)
+    r1 = json.load(open(tmp_path / "res_w1.json"))
+    r2 = json.load(open(tmp_path / "res_w2.json"))
+    assert abs(r1["wsq"] - r2["wsq"]) < 1e-3 * r1["wsq"], (r1["wsq"], r2["wsq"])
+
+
+@pytest.mark.parametrize("opt,save_world,load_world", [("adamw", 2, 1), ("adamw8bit", 2, 1), ("adamw8bit", 1, 2)])
+def test_resume_at_another_world_size(tmp_path, opt, save_world, load_world):
+    """optimizer.pt is sharding-independent: a run saved at one world size continues at another
+    with the moments it had (compared against an uninterrupted run)."""
+    args = ("--optimizer_type", opt)
+    run_ranks(tmp_path, 1, "train", args)
+    run_ranks(tmp_path, save_world, "save2", args, port=29751)
+    run_ranks(tmp_path, load_world, "continue", args, port=29753)
+    ref = json.load(open(tmp_path / "res_w1.json"))["losses"]
+    got = json.load(open(tmp_path / f"cont_w{load_world}.json"))
+    assert got["n_state"] > 0
+    tol = 3e-3 if opt == "adamw8bit" else 3e-4
+    for a, b in zip(ref[2:], got["losses"]):
+        assert abs(a - b) < tol, (ref, got)
+
+
+def test_checkpoint_of_another_layout_is_not_attached(tmp_path):
+    """A state whose tensors do not have the size the kernels will index is refused."""
+    from nsa_optim_b200.optimizers import AdamWLowBit, state_fits
+    p = torch.nn.Parameter(torch.zeros(8192))
+    opt = AdamWLowBit([p])
+    good = {}
+    opt._init(p, good)
+    assert state_fits(opt, p, good)
+    half = {k: (v[: v.numel() // 2] if torch.is_tensor(v) else v) for k, v in good.items()}
+    assert not state_fits(opt, p, half)
 
 
 @pytest.mark.parametrize("world", [1, 2])
