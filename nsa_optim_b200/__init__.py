@@ -4,6 +4,6 @@ Mamba-2 / Gated DeltaNet / (native sparse) attention language models with low-bi
 Layout: ``config`` (sizes, flags, grid), ``models`` (four families + factories), ``ops``
 (dispatch, PyTorch implementations, sm_100a CUDA kernels), ``optimizers``, ``parallel``
 (sharded-parameter runtime and the NVLink peer-memory kernels), ``data``, ``checkpoint``,
-``train`` (CLI), ``utils``.
+``train`` (CLI), ``profiling``, ``benchmarks``, ``analysis``.
 """
 __version__ = "0.1.0"

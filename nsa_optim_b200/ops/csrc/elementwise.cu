@@ -1015,7 +1015,8 @@ static __device__ __align__(256) float g_noalloc_scratch[NSA_NOALLOC_SCRATCH_FLO
 
 // Device address of g_noalloc_scratch per device.  In host code the array's name is only a
 // handle for the runtime, not an address a kernel can use, so the address is looked up once
-// per device with that device current.
+// per device with that device current.  The cache is filled without a lock: host threads that
+// race on a device's first call all store the same value.
 static float* g_noalloc_scratch_addr[64] = {nullptr};
 
 static int noalloc_scratch_for_current_device(float** out) {
@@ -1038,7 +1039,8 @@ static int noalloc_scratch_for_current_device(float** out) {
 //  * The first call on each device looks up the scratch address (a synchronous runtime
 //    query); make that first call before any stream capture begins on that device.
 //  * Limit: nsa_rmsnorm_bwd_parts(rows, d) * d must not exceed NSA_NOALLOC_SCRATCH_FLOATS
-//    (always true for d <= 4096); larger problems are rejected with NSA_ERR_LIMIT and
+//    (true whenever sm_count * 4 * d <= 592 * 4096, e.g. d <= 4096 on a 148-SM part); larger
+//    problems are rejected with NSA_ERR_LIMIT and
 //    nothing is launched.
 //  * All calls on a device share the one scratch array, which keeps whatever the previous
 //    call left in it.  Nothing in it has to start at zero: the backward kernel overwrites

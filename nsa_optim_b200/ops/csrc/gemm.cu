@@ -174,6 +174,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int tiles_n = (p.N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int k_blocks = (p.K + BK - 1) / BK;
+  // With the fused all-gather the TMA producer may wait up to ag.max_cycles for a peer's shard, so
+  // everything downstream of it (MMA issuer, epilogue) must be at least that patient: otherwise
+  // ordinary rank skew would make a consumer give up while the producer is still within budget.
+  const long long wait_cycles = tc5::kMaxWaitCycles + (p.ag.enabled ? p.ag.max_cycles : 0ll);
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -268,13 +272,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       for (int t = cta; t < num_tiles && ok; t += n_ctas, ++tile_i) {
         const uint32_t acc = tile_i & 1;
         const uint32_t acc_ph = (tile_i >> 1) & 1;
-        if (!tc5::mbar_wait(&tempty_bar[acc], acc_ph ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+        if (!tc5::mbar_wait_cycles(&tempty_bar[acc], acc_ph ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY, wait_cycles)) { ok = false; break; }
         tc5::fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          if (!tc5::mbar_wait(&full_bar[s], ph, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL)) { ok = false; break; }
+          if (!tc5::mbar_wait_cycles(&full_bar[s], ph, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL, wait_cycles)) { ok = false; break; }
           tc5::fence_after_sync();
           const uint32_t sa = tc5::smem_u32(smem + s * STAGE_BYTES);
           const uint32_t sb = sa + A_BYTES;
@@ -300,7 +304,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       if (p.ag.enabled) nb = (nb + p.ag.n_rot) % tiles_n;
       const uint32_t acc = tile_i & 1;
       const uint32_t acc_ph = (tile_i >> 1) & 1;
-      if (!tc5::mbar_wait(&tfull_bar[acc], acc_ph, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      if (!tc5::mbar_wait_cycles(&tfull_bar[acc], acc_ph, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL, wait_cycles)) { ok = false; break; }
       tc5::fence_after_sync();
       const int row = mb * BM + quarter * 32 + lane;
       const int col0 = nb * BN;

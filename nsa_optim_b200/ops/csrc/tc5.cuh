@@ -87,6 +87,24 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return false;
 }
 
+// The same wait with a caller-chosen cycle budget (no poll-count limit): for consumers whose
+// producer may itself legitimately wait on another GPU for up to `max_cycles`.
+__device__ __forceinline__ bool mbar_wait_cycles(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                 KernelStatus* status, int code, long long max_cycles) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t i = 0;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 255u) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > max_cycles) break;
+    }
+  }
+  *abort_flag = 1;
+  status_report(status, code, blockIdx.x, parity);
+  return false;
+}
+
 // ---------------------------------------------------------------------------------------
 // TMA (tile mode; every load targets the issuing CTA's own shared memory only)
 // ---------------------------------------------------------------------------------------

@@ -41,6 +41,26 @@ STATUS_NAMES = {
 }
 
 
+# Shapes a native kernel does not cover are computed by the PyTorch implementation of the same op.
+# Every such call is counted per op, so that a benchmark or a test can show that none of its work
+# took that route (``fallback_counts()``; ``NSA_B200_STRICT=1`` turns a fallback into an error).
+_fallbacks: dict = {}
+_STRICT = os.environ.get("NSA_B200_STRICT", "") not in ("", "0")
+
+
+def _fallback(op: str, why: str = "") -> None:
+    _fallbacks[op] = _fallbacks.get(op, 0) + 1
+    if _STRICT:
+        raise RuntimeError(f"native op '{op}' does not cover this call ({why}) and NSA_B200_STRICT is set")
+
+
+def fallback_counts(reset: bool = False) -> dict:
+    out = dict(_fallbacks)
+    if reset:
+        _fallbacks.clear()
+    return out
+
+
 def lib_path() -> str:
     return _LIB_PATH
 
@@ -168,7 +188,7 @@ def check_canaries() -> int:
 
 def check_status(sync: bool = True) -> None:
     """Raise if any kernel since the last check reported a failure."""
-    if sync:
+    if sync and torch.cuda.is_available():
         torch.cuda.synchronize()
     if _CANARY:
         check_canaries()
@@ -276,6 +296,7 @@ class _LinearGather(torch.autograd.Function):
 def linear(x: Tensor, w: Tensor) -> Tensor:
     if (x.shape[-1] % 8) or (w.shape[0] % 8):
         flush_pending_gather()
+        _fallback("linear")
         return torch_impl.linear(x, w)
     pg = _pending_gather
     if pg is not None:
@@ -348,6 +369,7 @@ class _GatedRMSNorm(torch.autograd.Function):
 def rms_norm(x, w, eps=1e-6):
     d = x.shape[-1]
     if d % 8 or d > 8192:
+        _fallback("rms_norm")
         return torch_impl.rms_norm(x, w, eps)
     return _RMSNorm.apply(x, w, eps)
 
@@ -355,6 +377,7 @@ def rms_norm(x, w, eps=1e-6):
 def gated_rms_norm(x, gate, w, eps=1e-6, norm_before_gate=True):
     d = x.shape[-1]
     if d % 8 or d > 8192:
+        _fallback("gated_rms_norm")
         return torch_impl.gated_rms_norm(x, gate, w, eps, norm_before_gate)
     return _GatedRMSNorm.apply(x, gate, w, eps, norm_before_gate)
 
@@ -382,6 +405,7 @@ class _L2Norm(torch.autograd.Function):
 def l2_norm(x, eps=1e-6):
     d = x.shape[-1]
     if d % 8 or d > 512:
+        _fallback("l2_norm")
         return torch_impl.l2_norm(x, eps)
     return _L2Norm.apply(x, eps)
 
@@ -421,6 +445,7 @@ class _SwiGLU(torch.autograd.Function):
 
 def swiglu(gate, up):
     if gate.shape[-1] % 8:
+        _fallback("swiglu")
         return torch_impl.swiglu(gate, up)
     return _SwiGLU.apply(gate, up)
 
@@ -450,6 +475,7 @@ class _RoPE(torch.autograd.Function):
 
 def rope(x, cos, sin):
     if x.shape[-1] % 16 or cos.shape[0] != x.shape[1]:
+        _fallback("rope")
         return torch_impl.rope(x, cos, sin)
     return _RoPE.apply(x, cos, sin)
 
@@ -492,6 +518,7 @@ class _Conv1d(torch.autograd.Function):
 
 def causal_conv1d(x, weight, bias, activation=True):
     if x.shape[-1] % 8 or weight.shape[-1] != 4:
+        _fallback("causal_conv1d")
         return torch_impl.causal_conv1d(x, weight, bias, activation)
     return _Conv1d.apply(x, weight, bias, activation)
 
@@ -523,6 +550,7 @@ class _Embedding(torch.autograd.Function):
 
 def embedding(ids, weight):
     if weight.shape[1] % 8 or ids.dtype != torch.long:
+        _fallback("embedding")
         return torch_impl.embedding(ids, weight)
     return _Embedding.apply(ids, weight)
 
@@ -571,6 +599,7 @@ class _LinearCE(torch.autograd.Function):
 
 def linear_cross_entropy(hidden, weight, labels, ignore_index=-100, chunk=4096):
     if hidden.shape[-1] % 8 or weight.shape[0] % 8:
+        _fallback("linear_cross_entropy")
         return torch_impl.linear_cross_entropy(hidden, weight, labels, ignore_index, chunk)
     return _LinearCE.apply(hidden, weight, labels, ignore_index, chunk)
 
@@ -738,6 +767,7 @@ def gated_delta_rule(q, k, v, g, beta, scale=None, chunk=64):
     B, T, H, K = q.shape
     V = v.shape[-1]
     if K != 128 or V % 64 or chunk != 64 or q.dtype != torch.bfloat16:
+        _fallback("gated_delta_rule")
         return torch_impl.gated_delta_rule(q, k, v, g, beta, scale, chunk)
     scale = K ** -0.5 if scale is None else scale
     C = 64
@@ -837,6 +867,7 @@ def _attn_ok(q, k) -> bool:
 
 def attention(q, k, v, causal=True, window=0, scale=None):
     if not _attn_ok(q, k) or q.shape[1] != k.shape[1]:
+        _fallback("attention")
         return torch_impl.attention(q, k, v, causal, window, scale)
     scale = q.shape[-1] ** -0.5 if scale is None else scale
     return _Attn.apply(q, k, v, causal, int(window), float(scale), 1, 0, None)[0]
@@ -969,6 +1000,7 @@ def nsa_attention(q, k, v, g_cmp, g_slc, g_swa, cmp_block=32, cmp_stride=16, sel
     G = Hq // Hkv
     if (not _attn_ok(q, k) or sel_block != 64 or sel_block != 4 * cmp_stride or cmp_block != 2 * cmp_stride
             or G < 2 or G > 32 or T < cmp_block):
+        _fallback("nsa_attention")
         return torch_impl.nsa_attention(q, k, v, g_cmp, g_slc, g_swa, cmp_block, cmp_stride, sel_block, top_n,
                                         window, scale)
     scale = D ** -0.5 if scale is None else scale

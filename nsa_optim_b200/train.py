@@ -31,6 +31,7 @@ import torch
 import torch.nn as nn
 
 from . import checkpoint as ckpt
+from . import ops
 from .config import (AttentionType, MambaType, ModelConfig, OptimizerConfig, OptimizerType, TrainingConfig,
                      resolve_attention_type)
 from .data import DataConfig, create_dataloader, create_synthetic_loader, get_tokenizer
@@ -231,6 +232,41 @@ def evaluate(model, dataloader, device, max_batches: int = 50) -> Dict[str, floa
     return {"loss": mean, "perplexity": math.exp(min(mean, 50.0)), "tokens": count}
 
 
+class LossScaler:
+    """Dynamic loss scaling for float16 training (the reference wraps its step in
+    ``torch.cuda.amp.GradScaler``: train.py:255-283, 645-647).  The loss is multiplied by
+    ``scale`` before backward; gradients are unscaled inside the optimizer update through its
+    ``grad_scale`` argument.  A step whose gradient norm is not finite is skipped and the scale is
+    halved; after ``growth_interval`` good steps in a row it is doubled."""
+
+    def __init__(self, init_scale: float = 65536.0, growth_factor: float = 2.0, backoff_factor: float = 0.5,
+                 growth_interval: int = 2000, min_scale: float = 1.0):
+        self.scale = float(init_scale)
+        self.growth_factor, self.backoff_factor = growth_factor, backoff_factor
+        self.growth_interval, self.min_scale = growth_interval, min_scale
+        self.good_steps = 0
+        self.overflows = 0
+
+    def update(self, found_inf: bool) -> None:
+        if found_inf:
+            self.scale = max(self.min_scale, self.scale * self.backoff_factor)
+            self.good_steps = 0
+            self.overflows += 1
+        else:
+            self.good_steps += 1
+            if self.good_steps >= self.growth_interval:
+                self.scale *= self.growth_factor
+                self.good_steps = 0
+
+    def state_dict(self) -> Dict[str, Any]:
+        return {"scale": self.scale, "good_steps": self.good_steps, "overflows": self.overflows}
+
+    def load_state_dict(self, sd: Dict[str, Any]) -> None:
+        self.scale = float(sd.get("scale", self.scale))
+        self.good_steps = int(sd.get("good_steps", 0))
+        self.overflows = int(sd.get("overflows", 0))
+
+
 class Trainer:
     """Builds model, runtime, optimizer, schedule and data from parsed flags; :meth:`step` is
     one optimizer step (all accumulation micro-batches)."""
@@ -269,7 +305,13 @@ class Trainer:
                                           self.info.world_size)
         self.scheduler = get_lr_scheduler(self.optimizer, self.cfg.lr_scheduler_type,
                                           self.cfg.num_train_steps, self.cfg.warmup_steps, self.cfg.min_lr_ratio)
-        self.scaler_scale = 65536.0 if self.dtype == torch.float16 else None
+        self.scaler = LossScaler() if self.dtype == torch.float16 else None
+        # Kernels never trap: a wait that ran out (a peer that stopped, a flag never set) leaves a
+        # record in a host-mapped status block and the kernel returns without touching its output.
+        # The step reads that block before it lets the optimizer consume the data.
+        self._kernel_check = None
+        if self.device.type == "cuda" and ops.get_backend() != "torch":
+            self._kernel_check = ops.native_module().check_status
         self.step_count = 0
         self.total_tokens = 0
         self.skipped_steps = 0
@@ -308,12 +350,12 @@ class Trainer:
     def micro_step(self, batch: Dict[str, torch.Tensor]) -> torch.Tensor:
         ids = batch["input_ids"].to(self.device, non_blocking=True)
         labels = batch["labels"].to(self.device, non_blocking=True)
-        ctx = torch.autocast(self.device.type, dtype=torch.float16) if self.scaler_scale else contextlib.nullcontext()
+        ctx = torch.autocast(self.device.type, dtype=torch.float16) if self.scaler else contextlib.nullcontext()
         with ctx:
             _, loss, _ = self.model(input_ids=ids, labels=labels)
         scaled = loss / self.cfg.gradient_accumulation_steps
-        if self.scaler_scale:
-            scaled = scaled * self.scaler_scale
+        if self.scaler:
+            scaled = scaled * self.scaler.scale
         self.model.backward(scaled)
         return loss.detach()
 
@@ -327,12 +369,18 @@ class Trainer:
             losses.append(self.micro_step(batch))
         loss = torch.stack(losses).mean()
         norm, coef = self.model.clip_grad_norm(self.cfg.max_grad_norm, local_only=self.args.local_clip)
-        if self.scaler_scale:
-            inv = torch.tensor(1.0 / self.scaler_scale, device=self.device)
+        self.check_kernels(sync=False)
+        do_step = True
+        if self.scaler:
+            # gradients carry the loss scale: unscale the norm, fold 1/scale into the update, and let
+            # an overflow (non-finite norm, agreed by every rank because the norm is global) skip it
+            inv = torch.tensor(1.0 / self.scaler.scale, device=self.device)
             norm = norm * inv
             coef = inv if coef is None else (self.cfg.max_grad_norm / (norm + 1e-6)).clamp(max=1.0) * inv
-        do_step = True
-        if self.args.skip_nonfinite:
+            do_step = bool(torch.isfinite(norm))
+            self.scaler.update(not do_step)
+        if self.args.skip_nonfinite and do_step:
+            # one host read per step: the price of the flag (off by default)
             do_step = bool(torch.isfinite(loss) & torch.isfinite(norm))
         if do_step:
             self.optimizer.step(grad_scale=coef)
@@ -345,6 +393,14 @@ class Trainer:
         self.total_tokens += accum * self.cfg.batch_size * self.cfg.max_seq_length * self.info.world_size
         return {"loss": loss, "grad_norm": norm, "lr": self.scheduler.get_last_lr()[0]}
 
+    def check_kernels(self, sync: bool = False) -> None:
+        """Raises if a native kernel has reported a failure (see ``ops/native.py::check_status``).
+        Without ``sync`` this is one read of host memory and sees reports of kernels that have
+        finished so far; the training loop calls it with ``sync`` at every log point and before a
+        checkpoint is written, so a failed collective never reaches a saved state."""
+        if self._kernel_check is not None:
+            self._kernel_check(sync)
+
     # ---- checkpointing
     def meta(self) -> Dict[str, Any]:
         return {"model_type": self.model_type, "model_size": self.cfg.model_size,
@@ -354,7 +410,10 @@ class Trainer:
 
     def save(self, step: Optional[int] = None) -> str:
         step = self.step_count if step is None else step
+        self.check_kernels(sync=True)
         ts = {"total_tokens": self.total_tokens, "skipped_steps": self.skipped_steps}
+        if self.scaler:
+            ts["loss_scaler"] = self.scaler.state_dict()
         if hasattr(self.data, "state_dict"):
             ts["data"] = self.data.state_dict()
         return ckpt.save_checkpoint(self.model, self.optimizer, self.scheduler, step, self.cfg.output_dir,
@@ -365,6 +424,8 @@ class Trainer:
         self.step_count = int(st.get("step", 0))
         self.total_tokens = int(st.get("total_tokens", self.step_count * self.cfg.gradient_accumulation_steps
                                        * self.cfg.batch_size * self.cfg.max_seq_length * self.info.world_size))
+        if self.scaler and "loss_scaler" in st:
+            self.scaler.load_state_dict(st["loss_scaler"])
         if self.data is None:
             self.make_data()
         if "data" in st and hasattr(self.data, "load_state_dict"):
@@ -443,6 +504,7 @@ def train(args: argparse.Namespace) -> Dict[str, Any]:
             t_end = mark()
             if use_events:
                 torch.cuda.synchronize()
+                trainer.check_kernels(sync=False)
                 dt = t_start.elapsed_time(t_end) / 1e3
             else:
                 dt = t_end - t_start

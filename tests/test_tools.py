@@ -148,3 +148,83 @@ def test_flop_model():
                      attention_type="nsa")
     f = hybrid_flops_per_token(h, 65536, training=True, recompute=True)
     assert 5.5e9 < f["model_flops"] < 9e9 and f["total"] > f["model_flops"]
+
+
+def _tiny_trainer(tmp_path, *extra):
+    from nsa_optim_b200.parallel.dist import DistInfo
+    from nsa_optim_b200.train import Trainer, parse_args
+    args = parse_args(["--block_pattern", "MDA", "--block_repeats", "1", "--model_size", "100M", "--hidden_size", "64",
+                       "--vocab_size", "128", "--num_heads", "4", "--num_kv_heads", "2", "--mamba_d_state", "16",
+                       "--mamba_headdim", "16", "--deltanet_head_dim", "16", "--intermediate_size", "128",
+                       "--rope_theta", "1e4", "--context_length", "32", "--batch_size", "2", "--num_train_steps", "4",
+                       "--warmup_steps", "0", "--dtype", "float32", "--synthetic_data", "--device", "cpu",
+                       "--output_dir", str(tmp_path), *extra])
+    return Trainer(args, info=DistInfo(), verbose=False)
+
+
+def test_skip_nonfinite_leaves_parameters_and_optimizer_untouched(tmp_path):
+    tr = _tiny_trainer(tmp_path, "--skip_nonfinite")
+    tr.step()
+    assert tr.skipped_steps == 0
+    before = {n: p.detach().clone() for n, p in tr.model.module.named_parameters()}
+    steps_before = [int(st["step"]) for st in tr.optimizer.state.values() if st]
+    head = next(p for n, p in tr.model.module.named_parameters() if "norm" in n)
+    poisoned = head.detach().clone()
+    with torch.no_grad():
+        head.fill_(float("inf"))
+    out = tr.step()
+    assert tr.skipped_steps == 1 and not torch.isfinite(out["loss"])
+    with torch.no_grad():
+        head.copy_(poisoned)
+    for n, p in tr.model.module.named_parameters():
+        assert torch.equal(p, before[n]), n
+    assert [int(st["step"]) for st in tr.optimizer.state.values() if st] == steps_before
+    tr.step()                                   # training goes on afterwards
+    assert tr.skipped_steps == 1 and tr.step_count == 3
+
+
+def test_loss_scaler_backs_off_on_overflow_and_grows_back():
+    from nsa_optim_b200.train import LossScaler
+    s = LossScaler(init_scale=1024.0, growth_interval=3)
+    s.update(True)
+    assert s.scale == 512.0 and s.overflows == 1
+    for _ in range(3):
+        s.update(False)
+    assert s.scale == 1024.0 and s.good_steps == 0
+    s.update(False)
+    s.update(True)
+    assert s.scale == 512.0 and s.good_steps == 0
+    t = LossScaler()
+    t.load_state_dict(s.state_dict())
+    assert t.scale == 512.0 and t.overflows == 2
+
+
+def test_overflow_under_loss_scaling_skips_the_step(tmp_path):
+    from nsa_optim_b200.train import LossScaler
+    tr = _tiny_trainer(tmp_path)
+    tr.scaler = LossScaler(init_scale=float(2 ** 126))       # fp32 gradients overflow at this scale
+    before = {n: p.detach().clone() for n, p in tr.model.module.named_parameters()}
+    tr.step()
+    assert tr.skipped_steps == 1 and tr.scaler.scale == float(2 ** 125)
+    assert all(torch.equal(p, before[n]) for n, p in tr.model.module.named_parameters())
+    tr.scaler = LossScaler(init_scale=64.0)
+    out = tr.step()
+    assert tr.skipped_steps == 1 and torch.isfinite(out["grad_norm"])
+    assert any(not torch.equal(p, before[n]) for n, p in tr.model.module.named_parameters())
+
+
+def test_a_recorded_kernel_status_aborts_the_step(tmp_path, monkeypatch):
+    """The trainer reads the kernels' status block before the optimizer consumes a step's
+    gradients; a recorded time-out (faked here: no GPU involved) must stop it."""
+    import functools
+    from nsa_optim_b200.ops import native
+    tr = _tiny_trainer(tmp_path)
+    monkeypatch.setattr(native, "read_status", lambda reset=True: (201, 3, 7, 1))
+    monkeypatch.setattr(native, "_CANARY", False)
+    tr._kernel_check = functools.partial(native.check_status)
+    before = {n: p.detach().clone() for n, p in tr.model.module.named_parameters()}
+    with pytest.raises(RuntimeError, match="status 201"):
+        tr.step()
+    assert all(torch.equal(p, before[n]) for n, p in tr.model.module.named_parameters())
+    with pytest.raises(RuntimeError, match="status 201"):
+        tr.save()
