@@ -78,6 +78,38 @@ def bench_gemm(m: int, n: int, k: int, a_mn: bool, b_mn: bool, backend: str, ite
             "tflops": tf, "frac_of_peak": tf / pk["bf16_tflops"], "peak": f"{pk['bf16_tflops']} TFLOP/s of {pk['source']}"}
 
 
+MODEL_GEMMS = [(8192, 8192, 8192, False, False), (65536, 8512, 2048, False, False),
+               (65536, 2048, 5632, False, False), (65536, 2048, 8512, False, True),
+               (8512, 2048, 65536, True, True), (4096, 32000, 2048, False, False)]
+
+
+def bench_gemm_compare(iters: int) -> List[Dict]:
+    """The flagship model's GEMM shapes on the CTA-pair kernel, the single-CTA kernel and the
+    library (cuBLAS through torch.matmul), in one process on the same tensors."""
+    nat = ops.native_module()
+    out = []
+    for (m, n, k, a_mn, b_mn) in MODEL_GEMMS:
+        a = torch.randn((k, m) if a_mn else (m, k), device="cuda").bfloat16()
+        b = torch.randn((k, n) if b_mn else (n, k), device="cuda").bfloat16()
+        c = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+        A, B = (a.t() if a_mn else a), (b if b_mn else b.t())
+        row = {"op": f"gemm[{'mn' if a_mn else 'k'}{'mn' if b_mn else 'k'}] {m}x{n}x{k}"}
+        flops = 2.0 * m * n * k
+        for name in ("pair", "single"):
+            nat.gemm_select(name)
+            try:
+                ms = time_ms(lambda: nat.gemm(a, b, a_mn, b_mn, out=c), iters)
+            finally:
+                nat.gemm_select("default")
+            row[f"{name}_ms"], row[f"{name}_tflops"] = ms, flops / (ms * 1e-3) / 1e12
+        ms = time_ms(lambda: torch.matmul(A, B, out=c), iters)
+        row["library_ms"], row["library_tflops"] = ms, flops / (ms * 1e-3) / 1e12
+        row["pair_over_library"] = row["pair_tflops"] / row["library_tflops"]
+        out.append(row)
+        del a, b, c
+    return out
+
+
 def _bw_row(name: str, backend: str, ms: float, nbytes: float) -> Dict:
     pk = peaks()
     gbs = nbytes / (ms * 1e-3) / 1e9
@@ -225,7 +257,7 @@ def bench_comm(iters: int, world: int = 4, shard_mb: int = 32) -> List[Dict]:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["all", "gemm", "elementwise", "attention", "mixers", "nsa", "comm"])
+    ap.add_argument("--op", default="all", choices=["all", "gemm", "gemm_compare", "elementwise", "attention", "mixers", "nsa", "comm"])
     ap.add_argument("--backend", default="native", choices=["native", "torch"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
@@ -242,10 +274,10 @@ def main() -> None:
         if a.op == "gemm":
             rows.append(bench_gemm(a.m, a.n, a.k, a.a_mn, a.b_mn, a.backend, a.iters))
         else:
-            for (m, n, k, am, bm) in [(8192, 8192, 8192, False, False), (65536, 8512, 2048, False, False),
-                                      (65536, 2048, 5632, False, False), (65536, 2048, 8512, False, True),
-                                      (8512, 2048, 65536, True, True), (4096, 32000, 2048, False, False)]:
+            for (m, n, k, am, bm) in MODEL_GEMMS:
                 rows.append(bench_gemm(m, n, k, am, bm, a.backend, a.iters))
+    if a.op == "gemm_compare":
+        rows += bench_gemm_compare(a.iters)
     if a.op in ("all", "elementwise"):
         rows += bench_elementwise(a.backend, a.rows, 2048, 5632, a.iters)
     if a.op in ("all", "attention"):

@@ -14,6 +14,8 @@
 //   a_mn = 0: A is [M, K] (K contiguous)      a_mn = 1: A is [K, M] (M contiguous)
 //   b_mn = 0: B is [N, K] (K contiguous)      b_mn = 1: B is [K, N] (N contiguous)
 // Requirements: base pointers 16-byte aligned, leading dimensions multiples of 8 elements.
+#include <cstdlib>
+#include <cstring>
 #include "host.cuh"
 #include "tc5.cuh"
 
@@ -134,6 +136,49 @@ __device__ void ag_copy_role(const AgFuse& ag, int cta, KernelStatus* status) {
     if (threadIdx.x == 0) {
       __threadfence();
       asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(ag.chunk_flags + pr * ag.chunks_per_shard + c), "r"(ag.epoch) : "memory");
+    }
+  }
+}
+
+// One thread stores 32 consecutive accumulator columns of its row straight to global memory
+// (fp32 or bf16 output, optional accumulation into C, any alignment).
+__device__ __forceinline__ void store_direct(const uint32_t (&r)[32], int row, int col, const GemmParams& p) {
+  const bool full = (col + 32 <= p.N);
+  if (p.out_fp32) {
+    float* dst = reinterpret_cast<float*>(p.C) + static_cast<size_t>(row) * p.ldc + col;
+    if (full && (p.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                               __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+        float4* q = reinterpret_cast<float4*>(dst) + j;
+        if (p.accumulate) { float4 o = *q; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+        *q = v;
+      }
+    } else {
+      for (int j = 0; j < 32 && col + j < p.N; ++j) {
+        float v = __uint_as_float(r[j]);
+        dst[j] = p.accumulate ? dst[j] + v : v;
+      }
+    }
+  } else {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col;
+    if (full && (p.ldc & 7) == 0 && !p.accumulate && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint4 v;
+        v.x = tc5::pack_bf16(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+        v.y = tc5::pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+        v.z = tc5::pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+        v.w = tc5::pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+        reinterpret_cast<uint4*>(dst)[j] = v;
+      }
+    } else {
+      for (int j = 0; j < 32 && col + j < p.N; ++j) {
+        float v = __uint_as_float(r[j]);
+        if (p.accumulate) v += __bfloat162float(dst[j]);
+        dst[j] = __float2bfloat16(v);
+      }
     }
   }
 }
@@ -318,44 +363,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tc5::tmem_ld_x32(taddr + c * 32, r);
         tc5::tmem_ld_wait();
         if (!row_ok) continue;
-        const bool full = (col + 32 <= p.N);
-        if (p.out_fp32) {
-          float* dst = reinterpret_cast<float*>(p.C) + static_cast<size_t>(row) * p.ldc + col;
-          if (full && (p.ldc & 3) == 0) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                     __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-              float4* q = reinterpret_cast<float4*>(dst) + j;
-              if (p.accumulate) { float4 o = *q; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
-              *q = v;
-            }
-          } else {
-            for (int j = 0; j < 32 && col + j < p.N; ++j) {
-              float v = __uint_as_float(r[j]);
-              dst[j] = p.accumulate ? dst[j] + v : v;
-            }
-          }
-        } else {
-          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col;
-          if (full && (p.ldc & 7) == 0 && !p.accumulate) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              uint4 v;
-              v.x = tc5::pack_bf16(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
-              v.y = tc5::pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
-              v.z = tc5::pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
-              v.w = tc5::pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
-              reinterpret_cast<uint4*>(dst)[j] = v;
-            }
-          } else {
-            for (int j = 0; j < 32 && col + j < p.N; ++j) {
-              float v = __uint_as_float(r[j]);
-              if (p.accumulate) v += __bfloat162float(dst[j]);
-              dst[j] = __float2bfloat16(v);
-            }
-          }
-        }
+        store_direct(r, row, col, p);
       }
       tc5::fence_before_sync();
       __syncwarp();
@@ -385,7 +393,334 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParam
   return cudaGetLastError();
 }
 
+
+// =========================================================================================
+// CTA-pair GEMM: the default kernel for plain C = op(A) op(B).
+//
+// A cluster of two CTAs (the two SMs of one TPC) owns a 256 x 256 output tile and executes
+// tcgen05.mma.cta_group::2 with M = 256: CTA r of the pair stages A rows [128 r, 128 r + 128) and
+// B rows [128 r, 128 r + 128) of the tile in its own shared memory (plain TMA loads, no
+// multicast), so per MMA each SM reads 128 x 16 of A and 128 x 16 of B instead of 128 x 16 and
+// 256 x 16: the shared-memory read traffic that bounds the single-CTA kernel drops by a third
+// and the operand bytes fetched per FLOP by a quarter.  The even CTA's MMA thread issues for
+// both; its commits arrive on the barriers of both CTAs.  Each CTA drains its own 128
+// accumulator rows: registers -> swizzled shared memory -> TMA store (bf16 output), so global
+// writes are full 128-byte lines; fp32 output and accumulation into C use direct stores.
+// Six 32 KB stages, two 256-column accumulators per CTA (epilogue of tile i under the MMAs of
+// tile i + 1).  Every wait is bounded; all threads of both CTAs reach the final cluster barrier
+// on every path, after which tensor memory is released.
+// =========================================================================================
+namespace pair {
+constexpr int BM = 128;                        // rows of A (and of the accumulator) per CTA
+constexpr int BN = 256;                        // tile width; each CTA stages BN / 2 rows of B
+constexpr int BNH = BN / 2;
+constexpr int BK = 64;
+constexpr int STAGES = 6;
+constexpr int A_BYTES = BM * BK * 2;           // 16 KB
+constexpr int B_BYTES = BNH * BK * 2;          // 16 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int EPI_BOX_BYTES = 32 * 64 * 2;     // one warp's staging box: 32 rows x 64 bf16
+constexpr int EPI_BYTES = 4 * 2 * EPI_BOX_BYTES;
+constexpr int THREADS = 192;
+constexpr int GROUP_M = 8;                     // in 256-row tiles
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 + 256;
+static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB a CTA may use");
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& mb, int& nb) {
+  const int per_group = GROUP_M * tiles_n;
+  const int g = t / per_group;
+  const int first_m = g * GROUP_M;
+  const int gm = min(GROUP_M, tiles_m - first_m);
+  const int local = t - g * per_group;
+  mb = first_m + local % gm;
+  nb = local / gm;
+}
+}  // namespace pair
+
+template <int A_MN, int B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::THREADS, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                      const __grid_constant__ CUtensorMap tmap_c, const GemmParams p, const int tma_store) {
+  // the pair kernel's tile constants hide the single-CTA kernel's of the same names
+  constexpr int BM = pair::BM, BN = pair::BN, BNH = pair::BNH, BK = pair::BK, STAGES = pair::STAGES;
+  constexpr int A_BYTES = pair::A_BYTES, STAGE_BYTES = pair::STAGE_BYTES;
+  constexpr int EPI_BOX_BYTES = pair::EPI_BOX_BYTES, EPI_BYTES = pair::EPI_BYTES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* epi = smem + STAGES * STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi + EPI_BYTES);
+  uint64_t* full_bar = bars;                     // [STAGES]  TMA (both CTAs) -> MMA; used in the leader only
+  uint64_t* empty_bar = bars + STAGES;           // [STAGES]  MMA -> TMA producer of each CTA
+  uint64_t* tfull_bar = bars + 2 * STAGES;       // [2]       MMA -> epilogue of each CTA
+  uint64_t* tempty_bar = bars + 2 * STAGES + 2;  // [2]       epilogues of both CTAs -> MMA; leader only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const uint32_t rank = tc5::cluster_ctarank();  // 0 = leader
+  const int cluster = blockIdx.x >> 1;
+  const int n_clusters = gridDim.x >> 1;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int k_blocks = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      tc5::mbar_init(&full_bar[s], 1);           // the leader's expect_tx arrival
+      tc5::mbar_init(&empty_bar[s], 1);          // one commit
+    }
+    for (int a = 0; a < 2; ++a) {
+      tc5::mbar_init(&tfull_bar[a], 1);          // one commit
+      tc5::mbar_init(&tempty_bar[a], 8);         // four epilogue warps of each CTA
+    }
+    tc5::fence_barrier_init();
+    tc5::prefetch_tensormap(&tmap_a);
+    tc5::prefetch_tensormap(&tmap_b);
+    if (tma_store) tc5::prefetch_tensormap(&tmap_c);
+  }
+  if (warp == 1) {
+    tc5::tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tc5::tmem_relinquish_pair();
+  }
+  tc5::fence_before_sync();
+  tc5::cluster_sync();                           // barriers of both CTAs are initialised past this point
+  tc5::fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (each CTA)
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = cluster; t < num_tiles && ok; t += n_clusters) {
+        int mb, nb;
+        pair::tile_coords(t, tiles_m, tiles_n, mb, nb);
+        const int m0 = mb * 2 * BM + static_cast<int>(rank) * BM;
+        const int n0 = nb * BN + static_cast<int>(rank) * BNH;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!tc5::mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_EMPTY)) { ok = false; break; }
+          uint8_t* sa = smem + s * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          if (rank == 0) tc5::mbar_expect_tx(&full_bar[s], 2 * STAGE_BYTES);   // bytes of both CTAs
+          const uint32_t bar = tc5::mapa(tc5::smem_u32(&full_bar[s]), 0);
+          const int k0 = kb * BK;
+          if (A_MN == 0) {
+            tc5::tma_load_2d_pair(sa, &tmap_a, bar, k0, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c) tc5::tma_load_2d_pair(sa + c * CHUNK_BYTES, &tmap_a, bar, m0 + 64 * c, k0);
+          }
+          if (B_MN == 0) {
+            tc5::tma_load_2d_pair(sb, &tmap_b, bar, k0, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BNH / 64; ++c) tc5::tma_load_2d_pair(sb + c * CHUNK_BYTES, &tmap_b, bar, n0 + 64 * c, k0);
+          }
+        }
+      }
+      if (ok) {
+        // The MMA thread's last commits arrive on this CTA's empty barriers asynchronously; wait for
+        // them, so that no arrival is still on its way to this CTA's shared memory when it exits.
+        const uint32_t used = it < (uint32_t)STAGES ? it : (uint32_t)STAGES;
+        for (uint32_t j = 0; j < used && ok; ++j) {
+          const uint32_t q = it - 1 - j;
+          ok = tc5::mbar_wait(&empty_bar[q % STAGES], (q / STAGES) & 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_EMPTY);
+        }
+      }
+      if (!ok && rank == 0) {
+        // let the leader's copies already issued land before shared memory is released
+        const uint32_t pending = it < (uint32_t)STAGES ? it : (uint32_t)STAGES;
+        for (uint32_t j = 0; j < pending; ++j) {
+          const uint32_t q = it - 1 - j;
+          const long long t0 = clock64();
+          for (uint32_t i = 0; i < tc5::kMaxPolls; ++i) {
+            if (tc5::mbar_try_wait(&full_bar[q % STAGES], (q / STAGES) & 1)) break;
+            if ((i & 255u) == 255u && clock64() - t0 > tc5::kMaxWaitCycles) break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = tc5::make_idesc_bf16(2 * BM, BN, A_MN, B_MN);
+      uint32_t it = 0;
+      uint32_t tile_i = 0;
+      bool ok = true;
+      for (int t = cluster; t < num_tiles && ok; t += n_clusters, ++tile_i) {
+        const uint32_t acc = tile_i & 1;
+        const uint32_t acc_ph = (tile_i >> 1) & 1;
+        if (!tc5::mbar_wait(&tempty_bar[acc], acc_ph ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+        tc5::fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!tc5::mbar_wait(&full_bar[s], ph, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL)) { ok = false; break; }
+          tc5::fence_after_sync();
+          const uint32_t sa = tc5::smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t ad = A_MN ? tc5::desc_mnmajor(sa + k * 2048, CHUNK_BYTES) : tc5::desc_kmajor(sa + k * 32);
+            const uint64_t bd = B_MN ? tc5::desc_mnmajor(sb + k * 2048, CHUNK_BYTES) : tc5::desc_kmajor(sb + k * 32);
+            tc5::mma_ss_pair(d_tmem, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tc5::mma_commit_pair(&empty_bar[s], 3);      // both producers may refill the stage
+        }
+        if (ok) tc5::mma_commit_pair(&tfull_bar[acc], 3);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (4 warps, each CTA)
+    const int quarter = warp & 3;                 // TMEM lanes [32*quarter, 32*quarter+32)
+    uint8_t* my_epi = epi + quarter * 2 * EPI_BOX_BYTES;
+    const uint32_t tempty_leader0 = tc5::mapa(tc5::smem_u32(&tempty_bar[0]), 0);
+    const uint32_t tempty_leader1 = tc5::mapa(tc5::smem_u32(&tempty_bar[1]), 0);
+    uint32_t tile_i = 0;
+    uint32_t boxes = 0;                           // TMA stores issued by this warp's lane 0
+    bool ok = true;
+    for (int t = cluster; t < num_tiles && ok; t += n_clusters, ++tile_i) {
+      int mb, nb;
+      pair::tile_coords(t, tiles_m, tiles_n, mb, nb);
+      const uint32_t acc = tile_i & 1;
+      const uint32_t acc_ph = (tile_i >> 1) & 1;
+      if (!tc5::mbar_wait(&tfull_bar[acc], acc_ph, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc5::fence_after_sync();
+      const int row0 = mb * 2 * BM + static_cast<int>(rank) * BM + quarter * 32;
+      const int row = row0 + lane;
+      const int col0 = nb * BN;
+      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+      if (tma_store) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          const int col = col0 + c * 64;
+          if (col >= p.N || row0 >= p.M) break;    // uniform across the warp
+          uint32_t r0[32], r1[32];
+          tc5::tmem_ld_x32(taddr + c * 64, r0);
+          tc5::tmem_ld_x32(taddr + c * 64 + 32, r1);
+          tc5::tmem_ld_wait();
+          uint8_t* box = my_epi + (boxes & 1) * EPI_BOX_BYTES;
+          if (boxes >= 2) {                        // the store that last read this box must be done with it
+            if (lane == 0) tc5::tma_store_wait_read<1>();
+            __syncwarp();
+          }
+          // row `lane` of the box: eight 16-byte chunks, chunk j at slot j ^ (lane % 8) (128-byte swizzle)
+          uint8_t* rowp = box + lane * 128;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 v;
+            v.x = tc5::pack_bf16(__uint_as_float(r0[8 * j + 0]), __uint_as_float(r0[8 * j + 1]));
+            v.y = tc5::pack_bf16(__uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3]));
+            v.z = tc5::pack_bf16(__uint_as_float(r0[8 * j + 4]), __uint_as_float(r0[8 * j + 5]));
+            v.w = tc5::pack_bf16(__uint_as_float(r0[8 * j + 6]), __uint_as_float(r0[8 * j + 7]));
+            *reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4)) = v;
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 v;
+            v.x = tc5::pack_bf16(__uint_as_float(r1[8 * j + 0]), __uint_as_float(r1[8 * j + 1]));
+            v.y = tc5::pack_bf16(__uint_as_float(r1[8 * j + 2]), __uint_as_float(r1[8 * j + 3]));
+            v.z = tc5::pack_bf16(__uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5]));
+            v.w = tc5::pack_bf16(__uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
+            *reinterpret_cast<uint4*>(rowp + (((j + 4) ^ (lane & 7)) << 4)) = v;
+          }
+          tc5::fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) {
+            tc5::tma_store_2d(&tmap_c, box, col, row0);   // rows past M and columns past N are clipped
+            tc5::tma_store_commit();
+          }
+          ++boxes;
+        }
+      } else {
+        const bool row_ok = row < p.M;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col = col0 + c * 32;
+          if (col >= p.N) break;
+          uint32_t r[32];
+          tc5::tmem_ld_x32(taddr + c * 32, r);
+          tc5::tmem_ld_wait();
+          if (!row_ok) continue;
+          store_direct(r, row, col, p);
+        }
+      }
+      tc5::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc5::mbar_arrive_cluster(acc ? tempty_leader1 : tempty_leader0);
+    }
+    if (tma_store && lane == 0) tc5::tma_store_wait<0>();
+  }
+
+  // Both CTAs meet here on every path: the leader's MMAs read the peer's shared memory and the
+  // commits arrive on the peer's barriers, so neither CTA may leave, or release tensor memory,
+  // before both are done.
+  tc5::fence_before_sync();
+  tc5::cluster_sync();
+  if (warp == 1) {
+    tc5::fence_after_sync();
+    tc5::tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int A_MN, int B_MN>
+cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
+                        int tma_store, int max_ctas, cudaStream_t st) {
+  auto kern = gemm_bf16_pair_kernel<A_MN, B_MN>;
+  static int clusters[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (clusters[dev] == 0) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    // how many CTA pairs the device can hold at once (all of its TPCs, normally sm_count / 2)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(nsa::sm_count() & ~1), 1, 1);
+    cfg.blockDim = dim3(pair::THREADS, 1, 1);
+    cfg.dynamicSmemBytes = pair::SMEM_BYTES;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr; cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+      (void)cudaGetLastError();
+      n = nsa::sm_count() / 2;
+    }
+    clusters[dev] = n;
+  }
+  const int tiles = ((p.M + 2 * pair::BM - 1) / (2 * pair::BM)) * ((p.N + pair::BN - 1) / pair::BN);
+  int n = clusters[dev];
+  if (max_ctas > 0 && max_ctas / 2 < n) n = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
+  if (tiles < n) n = tiles;
+  kern<<<2 * n, pair::THREADS, pair::SMEM_BYTES, st>>>(ta, tb, tc, p, tma_store);
+  nsa::count_launch();
+  return cudaGetLastError();
+}
+
 }  // namespace
+
+// Which kernel plain GEMMs use: the CTA-pair kernel unless NSA_B200_GEMM=single is set in the
+// environment (read once) or the problem has fewer than 128 rows.
+static int g_gemm_select = 0;                   // 0 = environment default, 1 = single-CTA kernel, 2 = pair kernel
+static bool use_pair_kernel() {
+  if (g_gemm_select) return g_gemm_select == 2;
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("NSA_B200_GEMM");
+    v = (e != nullptr && strcmp(e, "single") == 0) ? 0 : 1;
+  }
+  return v == 1;
+}
+// Overrides the kernel choice for the calls that follow (benchmarks and tests compare the two).
+extern "C" void nsa_gemm_select(int which) { g_gemm_select = (which == 1 || which == 2) ? which : 0; }
 
 extern "C" int nsa_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb,
                              int ldc, int a_mn, int b_mn, int out_fp32, int accumulate, int max_ctas,
@@ -393,24 +728,40 @@ extern "C" int nsa_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7))
     return nsa::fail(NSA_ERR_ALIGNMENT, "nsa_gemm_bf16: operands need 16-byte aligned bases and leading dimensions that are multiples of 8");
-  CUtensorMap ta, tb;
+  const bool pairk = use_pair_kernel() && M > 128;
+  CUtensorMap ta, tb, tc;
   int rc;
-  // tensor maps: innermost dimension first
+  // tensor maps: innermost dimension first.  Both kernels stage 128 rows of A per CTA; the pair
+  // kernel stages 128 rows of B per CTA, the single-CTA kernel 256.
   if (!a_mn) rc = nsa::make_tmap_2d_bf16(&ta, A, /*inner*/ K, /*outer*/ M, lda, /*box*/ BK, BM);
   else       rc = nsa::make_tmap_2d_bf16(&ta, A, M, K, lda, 64, BK);
   if (rc) return rc;
-  if (!b_mn) rc = nsa::make_tmap_2d_bf16(&tb, B, K, N, ldb, BK, BN);
+  if (!b_mn) rc = nsa::make_tmap_2d_bf16(&tb, B, K, N, ldb, BK, pairk ? pair::BNH : BN);
   else       rc = nsa::make_tmap_2d_bf16(&tb, B, N, K, ldb, 64, BK);
   if (rc) return rc;
   GemmParams p;
   p.ag = AgFuse{};
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldb = ldb; p.a_mn = a_mn; p.b_mn = b_mn;
   p.out_fp32 = out_fp32; p.accumulate = accumulate; p.C = C; p.status = nsa::status_ptr();
+  cudaError_t e;
+  if (pairk) {
+    // bf16 output without accumulation leaves through TMA stores when C allows a tensor map
+    const int tma_store = (!out_fp32 && !accumulate && (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (ldc & 7) == 0) ? 1 : 0;
+    if (tma_store) {
+      if ((rc = nsa::make_tmap_2d_bf16(&tc, C, N, M, ldc, 64, 32))) return rc;
+    } else {
+      tc = ta;                                   // unused by the kernel
+    }
+    if (!a_mn && !b_mn) e = launch_pair<0, 0>(ta, tb, tc, p, tma_store, max_ctas, stream);
+    else if (!a_mn && b_mn) e = launch_pair<0, 1>(ta, tb, tc, p, tma_store, max_ctas, stream);
+    else if (a_mn && !b_mn) e = launch_pair<1, 0>(ta, tb, tc, p, tma_store, max_ctas, stream);
+    else e = launch_pair<1, 1>(ta, tb, tc, p, tma_store, max_ctas, stream);
+    return e == cudaSuccess ? 0 : nsa::fail_cuda(e, "nsa_gemm_bf16 launch (pair kernel)");
+  }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int sms = nsa::sm_count();
   if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
   const int grid = tiles < sms ? tiles : sms;
-  cudaError_t e;
   if (!a_mn && !b_mn) e = launch<0, 0>(ta, tb, p, grid, stream);
   else if (!a_mn && b_mn) e = launch<0, 1>(ta, tb, p, grid, stream);
   else if (a_mn && !b_mn) e = launch<1, 0>(ta, tb, p, grid, stream);

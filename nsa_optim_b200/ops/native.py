@@ -226,6 +226,12 @@ def gemm(a: Tensor, b: Tensor, a_mn: bool, b_mn: bool, out: Optional[Tensor] = N
     return out
 
 
+def gemm_select(which: str = "default") -> None:
+    """Kernel used by plain GEMMs from now on: "pair" (two CTAs per 256 x 256 tile), "single"
+    (one CTA per 128 x 256 tile) or "default" (pair unless NSA_B200_GEMM=single)."""
+    load().nsa_gemm_select(c_int({"default": 0, "single": 1, "pair": 2}[which]))
+
+
 class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x: Tensor, w: Tensor):

@@ -18,7 +18,8 @@ def _mk(M, N, K, a_mn, b_mn):
 
 
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
-@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 256), (1000, 264, 72), (4096, 2048, 1024)])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 256), (1000, 264, 72), (4096, 2048, 1024),
+                                   (136, 320, 200), (2048, 8512, 2048), (8512, 2048, 4096)])
 def test_gemm_matches_fp32(native, shape, a_mn, b_mn):
     M, N, K = shape
     if (a_mn and M % 8) or (b_mn and N % 8):
@@ -29,6 +30,47 @@ def test_gemm_matches_fp32(native, shape, a_mn, b_mn):
     err = (c.float() - ref).abs().max().item()
     scale = ref.abs().max().item()
     assert err <= 1e-2 * scale + 1e-2, (err, scale)
+
+
+@pytest.mark.parametrize("which", ["single", "pair"])
+def test_both_gemm_kernels_agree_with_fp32(native, which):
+    """The CTA-pair kernel is the default; the single-CTA kernel stays selectable (and is the one the
+    fused all-gather GEMM is built on).  Ragged M, N and K on both."""
+    try:
+        native.gemm_select(which)
+        for (M, N, K) in [(777, 1096, 328), (4096, 5632, 2048)]:
+            for a_mn, b_mn in [(False, False), (False, True), (True, True)]:
+                if (a_mn and M % 8) or (b_mn and N % 8):
+                    continue
+                a, b = _mk(M, N, K, a_mn, b_mn)
+                c = native.gemm(a, b, a_mn, b_mn)
+                ref = _ref(a, b, a_mn, b_mn)
+                assert (c.float() - ref).abs().max().item() <= 1e-2 * ref.abs().max().item() + 1e-2, (which, M, N, K)
+    finally:
+        native.gemm_select("default")
+
+
+def test_gemm_is_deterministic(native):
+    a, b = _mk(3000, 2048, 1536, False, False)
+    c1 = native.gemm(a, b, False, False)
+    c2 = native.gemm(a, b, False, False)
+    assert torch.equal(c1, c2)
+
+
+def test_gemm_output_with_odd_pitch_and_bf16_accumulate(native):
+    """Outputs a TMA store cannot address (row pitch not a multiple of 16 bytes) or that accumulate
+    take the direct-store epilogue."""
+    M, N, K = 520, 264, 192
+    a, b = _mk(M, N, K, False, False)
+    ref = _ref(a, b, False, False)
+    base = torch.zeros(M, N + 3, device="cuda", dtype=torch.bfloat16)
+    out = base[:, :N]
+    native.gemm(a, b, False, False, out=out)
+    assert (out.float() - ref).abs().max().item() <= 1e-2 * ref.abs().max().item() + 1e-2
+    assert float(base[:, N:].abs().max()) == 0.0
+    acc = torch.ones(M, N, device="cuda", dtype=torch.bfloat16)
+    native.gemm(a, b, False, False, out=acc, accumulate=True)
+    assert (acc.float() - (ref + 1)).abs().max().item() <= 2e-2 * ref.abs().max().item() + 2e-2
 
 
 def test_gemm_fp32_accumulate(native):
