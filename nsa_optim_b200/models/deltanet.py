@@ -23,7 +23,7 @@ import torch.nn.functional as F
 from torch import Tensor
 
 from .. import ops
-from .kernels import Linear, create_mlp, create_rms_norm
+from .kernels import Linear, create_mlp, create_rms_norm, residual_block
 from .mamba import _SSMModel, _inv_softplus_dt, _mlp_width
 
 
@@ -114,8 +114,7 @@ class GatedDeltaNetBlock(nn.Module):
         self.mlp = create_mlp(config.d_model, _mlp_width(config.d_model))
 
     def forward(self, hidden_states: Tensor, attention_mask=None, position_ids=None) -> Tensor:
-        h = hidden_states + self.mixer(self.input_layernorm(hidden_states))
-        return h + self.mlp(self.post_attention_layernorm(h))
+        return residual_block(hidden_states, self.input_layernorm, self.mixer, self.post_attention_layernorm, self.mlp)
 
 
 class GatedDeltaNetModel(_SSMModel):

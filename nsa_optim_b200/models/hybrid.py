@@ -28,7 +28,7 @@ from ..config import AttentionType, resolve_attention_type
 from .base import CausalLMBase, default_loss_fn, init_linear_embedding_
 from .deltanet import GatedDeltaNetMixer
 from .kernels import (Embedding, Linear, RotaryEmbedding, apply_rotary_pos_emb, create_mlp, create_rms_norm,
-                      resolve_kv_heads)
+                      residual_block, resolve_kv_heads)
 from .mamba import Mamba2Mixer
 
 
@@ -106,8 +106,7 @@ class MambaBlock(nn.Module):
         self.mlp = create_mlp(config.d_model, config.intermediate_size)
 
     def forward(self, hidden_states: Tensor, attention_mask=None, position_ids=None) -> Tensor:
-        h = hidden_states + self.mixer(self.norm(hidden_states))
-        return h + self.mlp(self.post_mixer_norm(h))
+        return residual_block(hidden_states, self.norm, self.mixer, self.post_mixer_norm, self.mlp)
 
 
 class DeltaNetBlock(nn.Module):
@@ -125,8 +124,7 @@ class DeltaNetBlock(nn.Module):
         self.mlp = create_mlp(config.d_model, config.intermediate_size)
 
     def forward(self, hidden_states: Tensor, attention_mask=None, position_ids=None) -> Tensor:
-        h = hidden_states + self.mixer(self.norm(hidden_states))
-        return h + self.mlp(self.post_mixer_norm(h))
+        return residual_block(hidden_states, self.norm, self.mixer, self.post_mixer_norm, self.mlp)
 
 
 class AttentionBlock(nn.Module):
@@ -156,8 +154,12 @@ class AttentionBlock(nn.Module):
         self.mlp = create_mlp(d, config.intermediate_size)
 
     def forward(self, hidden_states: Tensor, attention_mask=None, position_ids=None) -> Tensor:
-        B, T, _ = hidden_states.shape
-        x = self.norm(hidden_states)
+        return residual_block(hidden_states, self.norm, lambda x: self.attend(x, position_ids),
+                              self.post_attn_norm, self.mlp)
+
+    def attend(self, x: Tensor, position_ids=None) -> Tensor:
+        """The attention mixer on the normed input: projections, RoPE, attention, output projection."""
+        B, T, _ = x.shape
         q = self.q_proj(x).view(B, T, self.num_heads, self.head_dim)
         k = self.k_proj(x).view(B, T, self.num_kv_heads, self.head_dim)
         v = self.v_proj(x).view(B, T, self.num_kv_heads, self.head_dim)
@@ -170,8 +172,7 @@ class AttentionBlock(nn.Module):
             o = ops.nsa_attention(q, k, v, g_cmp, g_slc, g_swa, **self.nsa)
         else:
             o = ops.attention(q, k, v, causal=True)
-        h = hidden_states + self.o_proj(o.reshape(B, T, self.num_heads * self.head_dim))
-        return h + self.mlp(self.post_attn_norm(h))
+        return self.o_proj(o.reshape(B, T, self.num_heads * self.head_dim))
 
 
 _BLOCKS = {"M": MambaBlock, "D": DeltaNetBlock, "A": AttentionBlock}

@@ -72,6 +72,28 @@ class RMSNorm(nn.Module):
         with _ctx(self.kernel_type):
             return ops.rms_norm(x, self.weight, self.variance_epsilon)
 
+    def forward_skip(self, x: Tensor) -> Tuple[Tensor, Tensor]:
+        """(norm(x), x): take the residual branch from the second value."""
+        with _ctx(self.kernel_type):
+            return ops.rms_norm_skip(x, self.weight, self.variance_epsilon)
+
+    def forward_add(self, x: Tensor, r: Tensor) -> Tuple[Tensor, Tensor]:
+        """(x + r, norm(x + r)) in one pass."""
+        with _ctx(self.kernel_type):
+            return ops.add_rms_norm(x, r, self.weight, self.variance_epsilon)
+
+
+def residual_block(hidden: Tensor, norm1: nn.Module, mixer, norm2: nn.Module, mlp) -> Tensor:
+    """``h = hidden + mixer(norm1(hidden)); return h + mlp(norm2(h))`` with the residual adds
+    folded into the norm kernels where the norms support it (reference block structure:
+    models/hybrid.py:221-236)."""
+    if hasattr(norm1, "forward_skip") and hasattr(norm2, "forward_add"):
+        x1, skip = norm1.forward_skip(hidden)
+        h, x2 = norm2.forward_add(skip, mixer(x1))
+        return h + mlp(x2)
+    h = hidden + mixer(norm1(hidden))
+    return h + mlp(norm2(h))
+
 
 class RotaryEmbedding(nn.Module):
     """cos/sin cache of shape (T, D/2) in fp32; grows on demand.  ``forward`` returns the

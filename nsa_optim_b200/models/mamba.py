@@ -25,7 +25,7 @@ from torch import Tensor
 
 from .. import ops
 from .base import CausalLMBase, default_loss_fn, init_linear_embedding_
-from .kernels import Embedding, Linear, create_mlp, create_rms_norm, split_last
+from .kernels import Embedding, Linear, create_mlp, create_rms_norm, residual_block, split_last
 
 
 def _inv_softplus_dt(n: int, dt_min: float = 1e-3, dt_max: float = 1e-1, floor: float = 1e-4) -> Tensor:
@@ -110,8 +110,7 @@ class Mamba2Block(nn.Module):
         self.mlp = create_mlp(config.d_model, _mlp_width(config.d_model))
 
     def forward(self, hidden_states: Tensor, attention_mask=None, position_ids=None) -> Tensor:
-        h = hidden_states + self.mixer(self.norm(hidden_states))
-        return h + self.mlp(self.post_mixer_norm(h))
+        return residual_block(hidden_states, self.norm, self.mixer, self.post_mixer_norm, self.mlp)
 
 
 class _SSMModel(CausalLMBase):
@@ -260,8 +259,7 @@ class _Mamba3Layer(nn.Module):
         self.mlp = create_mlp(config.d_model, _mlp_width(config.d_model))
 
     def forward(self, x: Tensor, inference_params=None) -> Tensor:
-        h = x + self.mixer(self.norm(x))
-        return h + self.mlp(self.post_mixer_norm(h))
+        return residual_block(x, self.norm, self.mixer, self.post_mixer_norm, self.mlp)
 
 
 class Mamba3Model(_SSMModel):

@@ -26,7 +26,7 @@ from .. import ops
 from ..config import AttentionType, ModelConfig
 from .base import CausalLMBase, default_loss_fn, init_linear_embedding_
 from .kernels import (Embedding, KernelType, Linear, RotaryEmbedding, apply_rotary_pos_emb, resolve_kv_heads,
-                      create_mlp, create_rms_norm)
+                      create_mlp, create_rms_norm, residual_block)
 
 FSA_AVAILABLE = True  # the sparse kernels are built in; kept for import compatibility
 
@@ -146,11 +146,14 @@ class TransformerBlock(nn.Module):
 
     def forward(self, hidden_states: Tensor, attention_mask: Optional[Tensor] = None,
                 position_ids: Optional[Tensor] = None, past_key_value=None, use_cache: bool = False):
-        a, cache = self.self_attn(self.input_layernorm(hidden_states), attention_mask, position_ids,
-                                  past_key_value, use_cache)
-        h = hidden_states + a
-        h = h + self.mlp(self.post_attention_layernorm(h))
-        return (h, cache) if use_cache else h
+        cache = [None]
+
+        def attend(x: Tensor) -> Tensor:
+            a, cache[0] = self.self_attn(x, attention_mask, position_ids, past_key_value, use_cache)
+            return a
+
+        h = residual_block(hidden_states, self.input_layernorm, attend, self.post_attention_layernorm, self.mlp)
+        return (h, cache[0]) if use_cache else h
 
 
 class TransformerModel(CausalLMBase):

@@ -100,6 +100,21 @@ def rms_norm(x: Tensor, weight: Tensor, eps: float = 1e-6) -> Tensor:
     return torch_impl.rms_norm(x, weight, eps)
 
 
+def rms_norm_skip(x: Tensor, weight: Tensor, eps: float = 1e-6):
+    """(rmsnorm(x) * weight, x).  Use the second value, not ``x``, for the residual branch: the
+    native backward then adds the residual gradient inside the norm's backward kernel."""
+    if _use_native(x, "rms_norm"):
+        return native_module().rms_norm_skip(x, weight, eps)
+    return torch_impl.rms_norm_skip(x, weight, eps)
+
+
+def add_rms_norm(x: Tensor, r: Tensor, weight: Tensor, eps: float = 1e-6):
+    """(h, rmsnorm(h) * weight) with h = x + r, one kernel each way on the native path."""
+    if _use_native(x, "rms_norm"):
+        return native_module().add_rms_norm(x, r, weight, eps)
+    return torch_impl.add_rms_norm(x, r, weight, eps)
+
+
 def gated_rms_norm(x: Tensor, gate: Tensor, weight: Tensor, eps: float = 1e-6,
                    norm_before_gate: bool = True) -> Tensor:
     if _use_native(x, "gated_rms_norm"):

@@ -120,14 +120,61 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const bf16* __restrict
   }
 }
 
+// Residual add fused into the plain norm: h = x + r (rounded to bf16, written out because the
+// residual stream continues from it) and y = h * rstd(h) * w, one read of x and r, one write of
+// h and y.  The statistics use the rounded h, so the result equals add-then-norm to the bit.
+template <int TPR, int NV>
+__global__ void __launch_bounds__(256) rmsnorm_add_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ r,
+                                                              const bf16* __restrict__ w, bf16* __restrict__ h,
+                                                              bf16* __restrict__ y, float* __restrict__ rstd_out,
+                                                              long rows, int d, float eps) {
+  __shared__ float red[8];
+  const int rows_per_cta = 256 / TPR;
+  const long row = static_cast<long>(blockIdx.x) * rows_per_cta + threadIdx.x / TPR;
+  const int t = threadIdx.x % TPR;
+  const bool active = row < rows;
+  float hv[NV][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (t + i * TPR) * 8;
+    if (active && c < d) {
+      float rv[8];
+      load8(x + row * d + c, hv[i]);
+      load8(r + row * d + c, rv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) hv[i][j] = __bfloat162float(__float2bfloat16(hv[i][j] + rv[j]));
+      store8(h + row * d + c, hv[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += hv[i][j] * hv[i][j];
+    }
+  }
+  ss = row_sum<TPR>(ss, red);
+  const float rstd = rsqrtf(ss / d + eps);
+  if (active && t == 0 && rstd_out) rstd_out[row] = rstd;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (t + i * TPR) * 8;
+    if (active && c < d) {
+      float wv[8], o[8];
+      load8(w + c, wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = hv[i][j] * rstd * wv[j];
+      store8(y + row * d + c, o);
+    }
+  }
+}
+
 // Backward.  Persistent over rows; writes dx (and dg for gated modes) and per-CTA partial
-// dw into `partial[gridDim.x][d]`.
+// dw into `partial[gridDim.x][d]`.  `dres` (may be null) is a gradient that reaches the norm's
+// input by another route (the residual stream); it is added into dx here instead of by a
+// separate pass over both tensors.
 template <int TPR, int NV, int MODE>
 __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ g,
                                                           const bf16* __restrict__ w, const bf16* __restrict__ dy,
                                                           const float* __restrict__ rstd_in, bf16* __restrict__ dx,
                                                           bf16* __restrict__ dg, float* __restrict__ partial,
-                                                          long rows, int d) {
+                                                          long rows, int d, const bf16* __restrict__ dres = nullptr) {
   __shared__ float red[8];
   __shared__ float dw_sh[(TPR == 32) ? 512 : 1];
   const int rows_per_cta = 256 / TPR;
@@ -194,6 +241,12 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const bf16* __restrict
           store8(dg + row * d + c, og);
         } else if (MODE == 1) {
           store8(dg + row * d + c, sg[i]);
+        }
+        if (dres != nullptr) {
+          float rv[8];
+          load8(dres + row * d + c, rv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += rv[j];
         }
         store8(dx + row * d + c, o);
       }
@@ -948,14 +1001,29 @@ int launch_rms_fwd(const void* x, const void* g, const void* w, void* y, float* 
 
 template <int MODE>
 int launch_rms_bwd(const void* x, const void* g, const void* w, const void* dy, const float* rstd, void* dx, void* dg,
-                   float* partial, int grid, long rows, int d, cudaStream_t st) {
-  const bf16 *X = (const bf16*)x, *G = (const bf16*)g, *Wt = (const bf16*)w, *DY = (const bf16*)dy;
+                   float* partial, int grid, long rows, int d, cudaStream_t st, const void* dres = nullptr) {
+  const bf16 *X = (const bf16*)x, *G = (const bf16*)g, *Wt = (const bf16*)w, *DY = (const bf16*)dy, *DR = (const bf16*)dres;
   bf16 *DX = (bf16*)dx, *DG = (bf16*)dg;
-  if (d <= 256) rmsnorm_bwd_kernel<32, 1, MODE><<<grid, 256, 0, st>>>(X, G, Wt, DY, rstd, DX, DG, partial, rows, d);
-  else if (d <= 512) rmsnorm_bwd_kernel<32, 2, MODE><<<grid, 256, 0, st>>>(X, G, Wt, DY, rstd, DX, DG, partial, rows, d);
-  else if (d <= 2048) rmsnorm_bwd_kernel<256, 1, MODE><<<grid, 256, 0, st>>>(X, G, Wt, DY, rstd, DX, DG, partial, rows, d);
-  else if (d <= 4096) rmsnorm_bwd_kernel<256, 2, MODE><<<grid, 256, 0, st>>>(X, G, Wt, DY, rstd, DX, DG, partial, rows, d);
-  else if (d <= 8192) rmsnorm_bwd_kernel<256, 4, MODE><<<grid, 256, 0, st>>>(X, G, Wt, DY, rstd, DX, DG, partial, rows, d);
+  if (d <= 256) rmsnorm_bwd_kernel<32, 1, MODE><<<grid, 256, 0, st>>>(X, G, Wt, DY, rstd, DX, DG, partial, rows, d, DR);
+  else if (d <= 512) rmsnorm_bwd_kernel<32, 2, MODE><<<grid, 256, 0, st>>>(X, G, Wt, DY, rstd, DX, DG, partial, rows, d, DR);
+  else if (d <= 2048) rmsnorm_bwd_kernel<256, 1, MODE><<<grid, 256, 0, st>>>(X, G, Wt, DY, rstd, DX, DG, partial, rows, d, DR);
+  else if (d <= 4096) rmsnorm_bwd_kernel<256, 2, MODE><<<grid, 256, 0, st>>>(X, G, Wt, DY, rstd, DX, DG, partial, rows, d, DR);
+  else if (d <= 8192) rmsnorm_bwd_kernel<256, 4, MODE><<<grid, 256, 0, st>>>(X, G, Wt, DY, rstd, DX, DG, partial, rows, d, DR);
+  else return nsa::fail(NSA_ERR_SHAPE, "rmsnorm: width above 8192 is not supported");
+  nsa::count_launch();
+  return 0;
+}
+
+int launch_rms_add_fwd(const void* x, const void* r, const void* w, void* h, void* y, float* rstd, long rows, int d, float eps,
+                       cudaStream_t st) {
+  const bf16 *X = (const bf16*)x, *R = (const bf16*)r, *Wt = (const bf16*)w;
+  bf16 *H = (bf16*)h, *Y = (bf16*)y;
+  if (d % 8) return nsa::fail(NSA_ERR_SHAPE, "rmsnorm: width must be a multiple of 8");
+  if (d <= 256) rmsnorm_add_fwd_kernel<32, 1><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(X, R, Wt, H, Y, rstd, rows, d, eps);
+  else if (d <= 512) rmsnorm_add_fwd_kernel<32, 2><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(X, R, Wt, H, Y, rstd, rows, d, eps);
+  else if (d <= 2048) rmsnorm_add_fwd_kernel<256, 1><<<(unsigned)rows, 256, 0, st>>>(X, R, Wt, H, Y, rstd, rows, d, eps);
+  else if (d <= 4096) rmsnorm_add_fwd_kernel<256, 2><<<(unsigned)rows, 256, 0, st>>>(X, R, Wt, H, Y, rstd, rows, d, eps);
+  else if (d <= 8192) rmsnorm_add_fwd_kernel<256, 4><<<(unsigned)rows, 256, 0, st>>>(X, R, Wt, H, Y, rstd, rows, d, eps);
   else return nsa::fail(NSA_ERR_SHAPE, "rmsnorm: width above 8192 is not supported");
   nsa::count_launch();
   return 0;
@@ -990,6 +1058,26 @@ extern "C" int nsa_rmsnorm_bwd(const void* x, const void* gate, const void* w, c
   if (mode == 0) rc = launch_rms_bwd<0>(x, gate, w, dy, rstd, dx, dgate, partial, parts, rows, d, st);
   else if (mode == 1) rc = launch_rms_bwd<1>(x, gate, w, dy, rstd, dx, dgate, partial, parts, rows, d, st);
   else rc = launch_rms_bwd<2>(x, gate, w, dy, rstd, dx, dgate, partial, parts, rows, d, st);
+  if (rc) return rc;
+  reduce_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(partial, parts, d, (bf16*)dw_bf16, dw_f32);
+  nsa::count_launch();
+  return 0;
+}
+
+// h = x + r and y = rmsnorm(h) * w in one pass (plain mode).  x, r, h, y: [rows, d] bf16 contiguous.
+extern "C" int nsa_rmsnorm_add_fwd(const void* x, const void* r, const void* w, void* h, void* y, float* rstd, long rows,
+                                   int d, float eps, cudaStream_t st) {
+  return launch_rms_add_fwd(x, r, w, h, y, rstd, rows, d, eps, st);
+}
+
+// Plain-mode backward that also adds `dres` (the gradient arriving at the norm's input through the
+// residual stream, [rows, d] bf16) into dx.  `partial` as for nsa_rmsnorm_bwd.
+extern "C" int nsa_rmsnorm_bwd_res(const void* x, const void* w, const void* dy, const float* rstd, const void* dres,
+                                   void* dx, void* dw_bf16, float* dw_f32, float* partial, long rows, int d,
+                                   cudaStream_t st) {
+  if (d % 8) return nsa::fail(NSA_ERR_SHAPE, "rmsnorm: width must be a multiple of 8");
+  const int parts = nsa_rmsnorm_bwd_parts(rows, d);
+  const int rc = launch_rms_bwd<0>(x, nullptr, w, dy, rstd, dx, nullptr, partial, parts, rows, d, st, dres);
   if (rc) return rc;
   reduce_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(partial, parts, d, (bf16*)dw_bf16, dw_f32);
   nsa::count_launch();

@@ -353,6 +353,90 @@ class _RMSNorm(torch.autograd.Function):
         return dx.view(dy.shape), dw.to(ctx.wdtype), None
 
 
+def _rms_bwd_res(x2, w, dy2, rstd, dres2):
+    rows, d = x2.shape
+    dx = _empty_like(x2)
+    dw = _empty(d, dtype=torch.bfloat16, device=x2.device)
+    parts = int(load().nsa_rmsnorm_bwd_parts(c_long(rows), c_int(d)))
+    partial = _empty(parts * d, dtype=torch.float32, device=x2.device)
+    _check(load().nsa_rmsnorm_bwd_res(_p(x2), _p(w), _p(dy2), _p(rstd), _p(dres2), _p(dx), _p(dw), c_void_p(0),
+                                      _p(partial), c_long(rows), c_int(d), _stream()))
+    return dx, dw
+
+
+def _norm_grads(ctx, h2, wb, rstd, dres, dy):
+    """Gradient at the input of a plain norm that also receives `dres` by the residual route."""
+    if dy is None:
+        return (dres, None)
+    dy2 = dy.reshape(h2.shape).contiguous()
+    if dres is None:
+        dx, _, dw = _rms_bwd(h2, None, wb, dy2, rstd, 0)
+    else:
+        dx, dw = _rms_bwd_res(h2, wb, dy2, rstd, dres.reshape(h2.shape).contiguous())
+    return dx.view(dy.shape), dw.to(ctx.wdtype)
+
+
+class _RMSNormSkip(torch.autograd.Function):
+    """(y, x) with y = rmsnorm(x) * w.  The second output is the input itself, handed on to the
+    residual stream; in backward its gradient and the norm's gradient meet in one kernel instead
+    of two kernels and an add."""
+
+    @staticmethod
+    def forward(ctx, x, w, eps):
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        wb = w.to(torch.bfloat16)
+        y, rstd = _rms_fwd(x2, None, wb, eps, 0)
+        ctx.save_for_backward(x2, wb, rstd)
+        ctx.wdtype = w.dtype
+        return y.view(x.shape), x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, dy, dskip):
+        x2, wb, rstd = ctx.saved_tensors
+        dx, dw = _norm_grads(ctx, x2, wb, rstd, dskip, dy)
+        return dx, dw, None
+
+
+class _AddRMSNorm(torch.autograd.Function):
+    """(h, y) with h = x + r and y = rmsnorm(h) * w in one pass; backward adds the gradient that
+    reaches h directly to the norm's gradient in the same kernel, and x and r share the result."""
+
+    @staticmethod
+    def forward(ctx, x, r, w, eps):
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        r2 = r.reshape(-1, r.shape[-1]).contiguous()
+        wb = w.to(torch.bfloat16)
+        rows, d = x2.shape
+        h = _empty_like(x2)
+        y = _empty_like(x2)
+        rstd = _empty(rows, dtype=torch.float32, device=x2.device)
+        _check(load().nsa_rmsnorm_add_fwd(_p(x2), _p(r2), _p(wb), _p(h), _p(y), _p(rstd), c_long(rows), c_int(d),
+                                          c_float(eps), _stream()))
+        ctx.save_for_backward(h, wb, rstd)
+        ctx.wdtype = w.dtype
+        return h.view(x.shape), y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dh, dy):
+        h2, wb, rstd = ctx.saved_tensors
+        dx, dw = _norm_grads(ctx, h2, wb, rstd, dh, dy)
+        return dx, dx, dw, None
+
+
+def rms_norm_skip(x, w, eps=1e-6):
+    if x.shape[-1] % 8 or x.shape[-1] > 8192:
+        _fallback("rms_norm_skip")
+        return torch_impl.rms_norm_skip(x, w, eps)
+    return _RMSNormSkip.apply(x, w, eps)
+
+
+def add_rms_norm(x, r, w, eps=1e-6):
+    if x.shape[-1] % 8 or x.shape[-1] > 8192 or x.shape != r.shape:
+        _fallback("add_rms_norm")
+        return torch_impl.add_rms_norm(x, r, w, eps)
+    return _AddRMSNorm.apply(x, r, w, eps)
+
+
 class _GatedRMSNorm(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, gate, w, eps, norm_before_gate):

@@ -29,6 +29,17 @@ from . import oracle
 # ------------------------------------------------------------------ simple ops
 rms_norm = oracle.rms_norm
 gated_rms_norm = oracle.gated_rms_norm
+
+
+def rms_norm_skip(x: Tensor, weight: Tensor, eps: float = 1e-6):
+    """(rmsnorm(x) * weight, x): the second value continues the residual stream."""
+    return rms_norm(x, weight, eps), x
+
+
+def add_rms_norm(x: Tensor, r: Tensor, weight: Tensor, eps: float = 1e-6):
+    """(h, rmsnorm(h) * weight) with h = x + r."""
+    h = x + r
+    return h, rms_norm(h, weight, eps)
 swiglu = oracle.swiglu
 l2_norm = oracle.l2_norm
 rope = oracle.rope

@@ -32,6 +32,31 @@ def test_rmsnorm(native, rows, d):
     close(y, yr); close(x.grad, xr.grad); close(w.grad, wr.grad, atol=5e-2)
 
 
+@pytest.mark.parametrize("rows,d", [(37, 256), (9, 512), (300, 2048), (3, 4096)])
+def test_residual_fused_norms_match_the_unfused_block(native, rows, d):
+    """norm -> branch -> (add + norm) -> branch -> add, with the adds folded into the norm kernels,
+    against the same chain written with plain adds in fp32."""
+    x = bf(rows, d).requires_grad_()
+    w1 = (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16().requires_grad_()
+    w2 = (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16().requires_grad_()
+    a, b = bf(d, scale=0.5), bf(d, scale=0.5)             # stand-ins for the mixer and the MLP
+    y1, skip = native.rms_norm_skip(x, w1, 1e-6)
+    h, y2 = native.add_rms_norm(skip, y1 * a, w2, 1e-6)
+    out = h + y2 * b
+    g = bf(rows, d)
+    out.backward(g)
+    xr, w1r, w2r = (t.detach().float().requires_grad_() for t in (x, w1, w2))
+    y1r = oracle.rms_norm(xr, w1r, 1e-6)
+    hr = xr + y1r * a.float()
+    outr = hr + oracle.rms_norm(hr, w2r, 1e-6) * b.float()
+    outr.backward(g.float())
+    close(out, outr); close(x.grad, xr.grad, rtol=3e-2); close(w1.grad, w1r.grad, atol=5e-2, rtol=3e-2)
+    close(w2.grad, w2r.grad, atol=5e-2, rtol=3e-2)
+    # the fused forward equals add-then-norm to the bit
+    h2 = (x.detach() + (y1 * a).detach())
+    assert torch.equal(h.detach(), h2) and torch.equal(y2.detach(), native.rms_norm(h2, w2.detach(), 1e-6))
+
+
 @pytest.mark.parametrize("nbg", [True, False])
 @pytest.mark.parametrize("rows,d", [(40, 256), (6, 4096)])
 def test_gated_rmsnorm(native, rows, d, nbg):
