@@ -18,6 +18,7 @@
 //   reduce_scatter_adamw8bit: the same reduction feeding the blockwise 8-bit AdamW update of
 //              the owned parameter shard in one pass (no gradient shard round trip).
 // Peer memory is only ever accessed with plain loads and stores issued by these kernels.
+#include "codebook.cuh"
 #include "host.cuh"
 #include <cuda_bf16.h>
 #include <cstring>
@@ -162,15 +163,6 @@ __global__ void __launch_bounds__(256) reduce_scatter_kernel(const float* const*
 
 struct AdamArgs { float lr, beta1, beta2, eps, wd, bc1, bc2_sqrt; };
 
-__device__ __forceinline__ int nearest_code(const float* cb, float x) {
-  int lo = 0, hi = 255;
-  while (hi - lo > 1) {
-    const int mid = (lo + hi) >> 1;
-    if (cb[mid] <= x) lo = mid; else hi = mid;
-  }
-  return (x - cb[lo] <= cb[hi] - x) ? lo : hi;
-}
-
 // One CTA per 256-element block of the owned shard.  wd_mask[b] != 0 -> weight decay applies.
 template <typename PT>
 __global__ void __launch_bounds__(256) rs_adamw8bit_kernel(const float* const* grads, PT* p_shard, uint8_t* mq, float* mabs,
@@ -181,8 +173,12 @@ __global__ void __launch_bounds__(256) rs_adamw8bit_kernel(const float* const* g
                                                            KernelStatus* status) {
   __shared__ int sh_ok;
   __shared__ float cs[256], cu[256], red_m[8], red_v[8];
+  __shared__ uint8_t ts[cbk::kTable], tu[cbk::kTable];
   cs[threadIdx.x] = cb_signed[threadIdx.x];
   cu[threadIdx.x] = cb_unsigned[threadIdx.x];
+  __syncthreads();
+  cbk::build_table(cs, ts);
+  cbk::build_table(cu, tu);
   if (!cta_wait_peers(flags, W, rank, epoch, max_cycles, status, &sh_ok)) return;
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
   for (long b = blockIdx.x; b < nblocks; b += gridDim.x) {
@@ -205,8 +201,8 @@ __global__ void __launch_bounds__(256) rs_adamw8bit_kernel(const float* const* g
     am = red_m[0]; av = red_v[0];
 #pragma unroll
     for (int k = 1; k < 8; ++k) { am = fmaxf(am, red_m[k]); av = fmaxf(av, red_v[k]); }
-    mq[i] = static_cast<uint8_t>(nearest_code(cs, mm / fmaxf(am, 1e-30f)));
-    vq[i] = static_cast<uint8_t>(nearest_code(cu, vv / fmaxf(av, 1e-30f)));
+    mq[i] = static_cast<uint8_t>(cbk::nearest_code(cs, ts, mm / fmaxf(am, 1e-30f)));
+    vq[i] = static_cast<uint8_t>(cbk::nearest_code(cu, tu, vv / fmaxf(av, 1e-30f)));
     if (threadIdx.x == 0) { mabs[b] = am; vabs[b] = av; }
   }
 }

@@ -10,6 +10,7 @@
 // (clip coefficient), so no host synchronisation is needed between norm and update.
 #include <algorithm>
 
+#include "codebook.cuh"
 #include "host.cuh"
 #include <cuda_bf16.h>
 
@@ -50,16 +51,6 @@ __global__ void __launch_bounds__(256) adamw_kernel(PT* __restrict__ p, const GT
   }
 }
 
-// Index of the code-book entry nearest to x; `cb` sorted ascending, 256 entries, in shared memory.
-__device__ __forceinline__ int nearest_code(const float* cb, float x) {
-  int lo = 0, hi = 255;
-  while (hi - lo > 1) {
-    const int mid = (lo + hi) >> 1;
-    if (cb[mid] <= x) lo = mid; else hi = mid;
-  }
-  return (x - cb[lo] <= cb[hi] - x) ? lo : hi;
-}
-
 __device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
   const float4 x = *reinterpret_cast<const float4*>(p);
   v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
@@ -91,9 +82,13 @@ __global__ void __launch_bounds__(256) adamw8bit_kernel(PT* __restrict__ p, cons
                                                         const float* __restrict__ cb_unsigned,
                                                         const float* __restrict__ grad_scale, long nblocks, AdamArgs a) {
   __shared__ float cs[256], cu[256];
+  __shared__ uint8_t ts[cbk::kTable], tu[cbk::kTable];
   __shared__ float red_m[8], red_v[8];
   cs[threadIdx.x] = cb_signed[threadIdx.x];
   cu[threadIdx.x] = cb_unsigned[threadIdx.x];
+  __syncthreads();
+  cbk::build_table(cs, ts);
+  cbk::build_table(cu, tu);
   __syncthreads();
   const float gs = grad_scale ? *grad_scale : 1.f;
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
@@ -136,14 +131,14 @@ __global__ void __launch_bounds__(256) adamw8bit_kernel(PT* __restrict__ p, cons
     if (live) {
       const float dm = fmaxf(am, 1e-30f), dv = fmaxf(av, 1e-30f);
       uchar4 mc, vc;
-      mc.x = static_cast<uint8_t>(nearest_code(cs, mm[0] / dm));
-      mc.y = static_cast<uint8_t>(nearest_code(cs, mm[1] / dm));
-      mc.z = static_cast<uint8_t>(nearest_code(cs, mm[2] / dm));
-      mc.w = static_cast<uint8_t>(nearest_code(cs, mm[3] / dm));
-      vc.x = static_cast<uint8_t>(nearest_code(cu, vv[0] / dv));
-      vc.y = static_cast<uint8_t>(nearest_code(cu, vv[1] / dv));
-      vc.z = static_cast<uint8_t>(nearest_code(cu, vv[2] / dv));
-      vc.w = static_cast<uint8_t>(nearest_code(cu, vv[3] / dv));
+      mc.x = static_cast<uint8_t>(cbk::nearest_code(cs, ts, mm[0] / dm));
+      mc.y = static_cast<uint8_t>(cbk::nearest_code(cs, ts, mm[1] / dm));
+      mc.z = static_cast<uint8_t>(cbk::nearest_code(cs, ts, mm[2] / dm));
+      mc.w = static_cast<uint8_t>(cbk::nearest_code(cs, ts, mm[3] / dm));
+      vc.x = static_cast<uint8_t>(cbk::nearest_code(cu, tu, vv[0] / dv));
+      vc.y = static_cast<uint8_t>(cbk::nearest_code(cu, tu, vv[1] / dv));
+      vc.z = static_cast<uint8_t>(cbk::nearest_code(cu, tu, vv[2] / dv));
+      vc.w = static_cast<uint8_t>(cbk::nearest_code(cu, tu, vv[3] / dv));
       *reinterpret_cast<uchar4*>(mq + i) = mc;
       *reinterpret_cast<uchar4*>(vq + i) = vc;
       if (t64 == 0) { mabs[b] = am; vabs[b] = av; }

@@ -135,3 +135,64 @@ def test_inverse_selection_map_lists_tokens_per_block():
                 want = [t for t in range(T) if blk in idx[b, h, t].tolist()]
                 assert tok[ls[l]:ls[l + 1]].tolist() == want
                 assert int(its[l + 1] - its[l]) == -(-(-(-len(want) // R)) // C)
+
+
+def test_bracket_table_lookup_equals_binary_search():
+    """The 8-bit optimizer kernels find the nearest code through a bracket table indexed by the
+    value's sign, exponent and top mantissa bits (csrc/codebook.cuh).  This restates that
+    arithmetic with numpy integers and checks it against the plain binary search on both code
+    books, on random values, every code, every midpoint and the edge cases."""
+    import numpy as np
+    from nsa_optim_b200.ops import quant
+    K_BINS = 386
+
+    def bin_index(x):
+        b = x.astype(np.float32).view(np.uint32).astype(np.int64)
+        k = ((b & 0x7FFFFFFF) >> 19) - (103 << 4)
+        k = np.clip(k, -1, 384)
+        return (b >> 31) * K_BINS + k + 1
+
+    def bin_floor(e):
+        sign, kk = (e >= K_BINS), (e - K_BINS if e >= K_BINS else e)
+        if kk == 0:
+            return -2.0 ** -24 if sign else 0.0
+        k = kk - 1
+        if k == 384:
+            return -np.inf if sign else 1.0
+        lower = np.array([(k + (103 << 4)) << 19], dtype=np.uint32).view(np.float32)[0]
+        upper = np.array([(k + 1 + (103 << 4)) << 19], dtype=np.uint32).view(np.float32)[0]
+        return -float(upper) if sign else float(lower)
+
+    def binary(cb, x):
+        lo, hi = 0, 255
+        while hi - lo > 1:
+            mid = (lo + hi) >> 1
+            if cb[mid] <= x:
+                lo = mid
+            else:
+                hi = mid
+        return lo, hi
+
+    rng = np.random.default_rng(0)
+    for signed in (True, False):
+        cb = quant.codebook(8, signed, "cpu").numpy().astype(np.float32)
+        table = np.array([binary(cb, np.float32(bin_floor(e)))[0] if cb[0] <= bin_floor(e) else 0
+                          for e in range(2 * K_BINS)])
+        mids = ((cb[:-1].astype(np.float64) + cb[1:]) / 2).astype(np.float32)
+        xs = np.concatenate([rng.uniform(-1, 1, 20000), 10.0 ** rng.uniform(-9, 0, 20000) * rng.choice([-1, 1], 20000),
+                             cb, mids, np.nextafter(mids, 2), np.nextafter(mids, -2),
+                             [0.0, -0.0, 1.0, -1.0, 1e-30, -1e-30, 2.0 ** -24, -2.0 ** -24]]).astype(np.float32)
+        if not signed:
+            xs = np.abs(xs)
+        worst = 0
+        for x, e in zip(xs, bin_index(xs)):
+            lo, steps = int(table[e]), 0
+            assert cb[lo] <= x or lo == 0
+            while lo < 254 and cb[lo + 1] <= x:
+                lo, steps = lo + 1, steps + 1
+            worst = max(worst, steps)
+            got = lo if (x - cb[lo] <= cb[lo + 1] - x) else lo + 1
+            blo, bhi = binary(cb, x)
+            want = blo if (x - cb[blo] <= cb[bhi] - x) else bhi
+            assert got == want, (signed, float(x), got, want)
+        assert worst <= 8, worst            # the scan stays short where the code book is densest
