@@ -5,10 +5,12 @@ at 64K context, AdamW8bit, bf16, sharded data parallel (one rank per GPU).
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         --master-port P bench.py --gpus N --steps K --warmup W
 
-Prints ONE JSON line on rank 0.  Two timed regions of exactly K steps each:
+Prints ONE JSON line on rank 0.  Timed regions of exactly K steps each, run alternately
+(device, end to end, device, end to end); each kind reports the mean of its two repeats and both:
   * ``value``: device-timed (CUDA events), inputs already resident, max over ranks;
   * ``e2e``: the same steps through ``Trainer.step`` including, every step, the host->device
     copy of that step's token batch from pinned memory and a device->host read of the loss.
+``gpu_launches`` is the number of this library's kernel launches in one region of K steps.
 Model: 16 layers (MDMA x 4), d_model 2048, FFN 5632, vocab 32000; A blocks: 32 q / 2 kv heads of
 128, compression 32/16, selection 64 x top-16, window 512; M blocks: d_state 128, headdim 64,
 expand 2, chunk 256; D blocks: 16 heads of 128.  Random-init weights, uniform random tokens.
@@ -103,21 +105,43 @@ class ClockSampler:
 
 
 def reference_arm(a) -> None:
+    """Runs the reference's own training step when it can be imported; otherwise prints why not.
+
+    ``baseline/_ref`` holds the offline install of the reference (pip ``--no-deps --target``) plus
+    its top-level modules ``config.py``, ``train.py``, ``optimizers.py``, ``data.py``, which its
+    ``pyproject.toml`` does not package.  The import is attempted for real and the deepest frame
+    inside the reference that failed is reported with file and line."""
+    import traceback
     ref = os.path.join(ROOT, "baseline", "_ref")
     why = None
     if not os.path.isdir(ref):
-        why = "baseline/_ref is absent (offline install of the reference was not possible)"
+        why = "baseline/_ref is absent (the offline install of the reference was not made)"
     else:
         sys.path.insert(0, ref)
         try:
             import models  # noqa: F401  (the reference's package)
+            import train  # noqa: F401   (the reference's entry point)
         except Exception as exc:  # noqa: BLE001
-            why = (f"reference installs only with --no-deps and cannot be imported offline: "
-                   f"{type(exc).__name__}: {exc}")
+            where = ""
+            for fr in reversed(traceback.extract_tb(exc.__traceback__)):
+                if ref in fr.filename:
+                    where = f" at {os.path.relpath(fr.filename, ref)}:{fr.lineno} ({fr.line})"
+                    break
+            why = f"the reference cannot be imported offline: {type(exc).__name__}: {exc}{where}"
+            if "mamba_ssm" in str(exc):
+                # The only importable Mamba-2 layer here is fla.layers.mamba2.Mamba2, and without the
+                # mamba_ssm / causal_conv1d kernels it runs its PyTorch path, whose intermediate
+                # C[:, :, :, None] * B[:, :, None] has shape (batch, chunks, 256, 256, heads, d_state).
+                chunks, heads, d_state = a.seq_len // 256, 64, 128
+                gb = chunks * 256 * 256 * heads * d_state * 4 / 1e9
+                why += (f"; mamba_ssm has no wheel here (torchao, causal_conv1d, native_sparse_attention are "
+                        f"missing too), and fla's Mamba2 as a stand-in has only its PyTorch path, which needs a "
+                        f"{gb:.0f} GB intermediate per layer at {a.seq_len} tokens")
     if why is None:
-        why = "reference imported but its train.py/config.py are not packaged by its pyproject"
+        why = ("the reference imports, but its --attn_type nsa hybrid trains dense attention blocks at 12 layers and "
+               "vocabulary 151936 (models/hybrid.py:292-394): not the named config; not run")
     if int(os.environ.get("RANK", 0)) == 0:
-        print(json.dumps({"impl": "reference", "unavailable": why.replace("\n", " ")[:300]}))
+        print(json.dumps({"impl": "reference", "unavailable": why.replace("\n", " ")[:700]}))
 
 
 def main() -> None:
@@ -125,7 +149,11 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", type=str, default="native", choices=["native", "reference", "torch"])
+    ap.add_argument("--impl", type=str, default="native", choices=["native", "reference", "torch", "library"],
+                    help="native: this framework's kernels (the product); reference: the unmodified reference from "
+                         "baseline/_ref; library: a diagnostic arm, this framework with third-party library kernels "
+                         "(cuBLAS, flash_attn, fla, Liger) and NCCL collectives in place of its own; torch: the eager "
+                         "PyTorch oracle")
     ap.add_argument("--seq_len", type=int, default=65536)
     ap.add_argument("--comm", type=str, default="auto")
     ap.add_argument("--skip_e2e", action="store_true")
@@ -145,6 +173,9 @@ def main() -> None:
 
     if a.impl == "torch":
         ops.set_backend("torch")
+    if a.impl == "library":
+        ops.set_backend("library")
+        a.comm = "nccl"
     world = int(os.environ.get("WORLD_SIZE", 1))
     if world != a.gpus:
         raise SystemExit(f"--gpus {a.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
@@ -160,7 +191,7 @@ def main() -> None:
         args.gradient_checkpointing = False
     tr = Trainer(args, verbose=False)
     info, dev = tr.info, tr.device
-    native = ops.native_module() if a.impl == "native" else None
+    native = ops.native_module() if a.impl in ("native", "library") else None
     K, W = a.steps, max(a.warmup, 3)
     tokens_per_step = args.batch_size * args.context_length * world
 
@@ -180,48 +211,72 @@ def main() -> None:
     if native is not None:
         native.check_status()
 
-    # ---- region 1: device-timed, inputs resident on the device
-    resident = [{k: v.to(dev) for k, v in b.items()} for b in host[W:W + K]]
-    sampler = ClockSampler(info.local_rank)
-    sync_all()
-    sampler.start()
-    l0 = native.launch_count() if native is not None else 0
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(K):
-        out = tr.step([resident[i]])
-    e1.record()
-    sync_all()
-    launches = (native.launch_count() - l0) if native is not None else 0
-    clocks = sampler.stop()
-    ms = e0.elapsed_time(e1)
-    t = torch.tensor([ms], dtype=torch.float64, device=dev)
-    pdist.all_reduce_max(t)
-    ms = float(t)
-    value = tokens_per_step * K / (ms / 1e3)
-    final_loss = float(out["loss"])
-    del resident
-
-    # ---- region 2: end to end through the public API: H2D of the batch + D2H of the loss every step
-    e2e = None
-    if not a.skip_e2e:
+    # ---- two kinds of timed region, run alternately (device, end to end, device, end to end) so that
+    # a slow drift of the clocks shows up as a difference between the repeats instead of between the
+    # kinds.  "value" and "e2e.value" are the means of their two repeats; both repeats are printed.
+    #   device: CUDA events around K steps, inputs already resident on the device;
+    #   e2e:    the same K steps through Trainer.step from pinned host batches, with the host->device
+    #           copy of each batch and a device->host read of each step's loss inside the region.
+    def device_region(batches):
+        resident = [{k: v.to(dev) for k, v in b.items()} for b in batches]
         sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for b in resident:
+            o = tr.step([b])
+        e1.record()
+        sync_all()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        pdist.all_reduce_max(t)
+        return float(t), o
+
+    def e2e_region(batches):
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         w0 = time.perf_counter()
         e0.record()
-        d2h = 0
-        for i in range(K):
-            out = tr.step([host[W + K + i]])          # pinned host tensors; Trainer copies them in
-            loss_host = out["loss"].float().cpu()      # device -> host read of the step's result
-            d2h = loss_host.numel() * loss_host.element_size()
+        nbytes = 0
+        for b in batches:
+            o = tr.step([b])                          # pinned host tensors; Trainer copies them in
+            loss_host = o["loss"].float().cpu()       # device -> host read of the step's result
+            nbytes = loss_host.numel() * loss_host.element_size()
         e1.record()
         sync_all()
         wall_ms = (time.perf_counter() - w0) * 1e3
         t = torch.tensor([max(e0.elapsed_time(e1), wall_ms)], dtype=torch.float64, device=dev)
         pdist.all_reduce_max(t)
-        e2e = {"value": tokens_per_step * K / (float(t) / 1e3), "unit": "tokens/s", "ms_per_step": float(t) / K,
-               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+        return float(t), nbytes
+
+    repeats = 1 if a.skip_e2e else 2
+    half = [host[W:W + K], host[W + K:W + 2 * K]]
+    sampler = ClockSampler(info.local_rank)
+    sync_all()
+    sampler.start()
+    l0 = native.launch_count() if native is not None else 0
+    dev_ms, e2e_ms, d2h = [], [], 0
+    steps_run = 0
+    for r in range(repeats):
+        ms_r, out = device_region(half[r % 2])
+        dev_ms.append(ms_r)
+        steps_run += K
+        if not a.skip_e2e:
+            ms_e, d2h = e2e_region(half[(r + 1) % 2])
+            e2e_ms.append(ms_e)
+            steps_run += K
+    launches = ((native.launch_count() - l0) * K // steps_run) if native is not None else 0
+    clocks = sampler.stop()
+    ms = sum(dev_ms) / len(dev_ms)
+    value = tokens_per_step * K / (ms / 1e3)
+    final_loss = float(out["loss"])
+    e2e = None
+    if e2e_ms:
+        em = sum(e2e_ms) / len(e2e_ms)
+        e2e = {"value": tokens_per_step * K / (em / 1e3), "unit": "tokens/s", "ms_per_step": em / K,
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "repeats_ms_per_step": [round(x / K, 3) for x in e2e_ms]}
     if native is not None:
         native.check_status()
+    fallbacks = native.fallback_counts() if native is not None else {}
 
     if info.is_main:
         line = {
@@ -242,10 +297,16 @@ def main() -> None:
                        "baseline_note": "vs_baseline divides by the reference's only published number (11589 tok/s, 0.5B MDMA, "
                                         "8K context, unnamed 32 GB GPU); it is not the same config"},
             "clocks": clocks, "gpu_launches": launches, "final_loss": final_loss,
+            "repeats_ms_per_step": [round(x / K, 3) for x in dev_ms], "region_order": "device, e2e, device, e2e",
+            "torch_fallback_calls": fallbacks,
             "native_ops": sorted(native.SUPPORTED) if native is not None else [],
         }
         if e2e is not None:
             line["e2e"] = e2e
+        if a.impl == "library":
+            from nsa_optim_b200.ops import library_impl
+            line["impl"] = "library (diagnostic: third-party kernels inside this framework; not the reference)"
+            line["library_ops"] = library_impl.report()
         print(json.dumps(line), flush=True)
     pdist.cleanup_distributed()
 

@@ -28,7 +28,7 @@ _native_err: Optional[BaseException] = None
 
 def set_backend(name: str) -> None:
     global _BACKEND
-    if name not in ("auto", "native", "torch"):
+    if name not in ("auto", "native", "torch", "library"):
         raise ValueError(name)
     _BACKEND = name
 
@@ -86,15 +86,31 @@ def native_op_names():
     return sorted(native_module().SUPPORTED)
 
 
+def _library(t: Tensor):
+    """The third-party-library implementations, when the diagnostic "library" backend is selected
+    (see ``library_impl``); each returns None when its library cannot serve the call, and the op then
+    runs on the native kernel."""
+    if _BACKEND == "library" and t.is_cuda:
+        from . import library_impl
+        return library_impl
+    return None
+
+
 # ------------------------------------------------------------------ ops
 def linear(x: Tensor, weight: Tensor) -> Tensor:
     """y = x @ weight^T (weight (out, in), no bias)."""
+    if _library(x) is not None:
+        return _library(x).linear(x, weight)
     if _use_native(x, "linear"):
         return native_module().linear(x, weight)
     return torch_impl.linear(x, weight)
 
 
 def rms_norm(x: Tensor, weight: Tensor, eps: float = 1e-6) -> Tensor:
+    if _library(x) is not None:
+        y = _library(x).rms_norm(x, weight, eps)
+        if y is not None:
+            return y
     if _use_native(x, "rms_norm"):
         return native_module().rms_norm(x, weight, eps)
     return torch_impl.rms_norm(x, weight, eps)
@@ -103,6 +119,8 @@ def rms_norm(x: Tensor, weight: Tensor, eps: float = 1e-6) -> Tensor:
 def rms_norm_skip(x: Tensor, weight: Tensor, eps: float = 1e-6):
     """(rmsnorm(x) * weight, x).  Use the second value, not ``x``, for the residual branch: the
     native backward then adds the residual gradient inside the norm's backward kernel."""
+    if _library(x) is not None:
+        return rms_norm(x, weight, eps), x
     if _use_native(x, "rms_norm"):
         return native_module().rms_norm_skip(x, weight, eps)
     return torch_impl.rms_norm_skip(x, weight, eps)
@@ -110,6 +128,9 @@ def rms_norm_skip(x: Tensor, weight: Tensor, eps: float = 1e-6):
 
 def add_rms_norm(x: Tensor, r: Tensor, weight: Tensor, eps: float = 1e-6):
     """(h, rmsnorm(h) * weight) with h = x + r, one kernel each way on the native path."""
+    if _library(x) is not None:
+        h = x + r
+        return h, rms_norm(h, weight, eps)
     if _use_native(x, "rms_norm"):
         return native_module().add_rms_norm(x, r, weight, eps)
     return torch_impl.add_rms_norm(x, r, weight, eps)
@@ -123,6 +144,10 @@ def gated_rms_norm(x: Tensor, gate: Tensor, weight: Tensor, eps: float = 1e-6,
 
 
 def swiglu(gate: Tensor, up: Tensor) -> Tensor:
+    if _library(gate) is not None:
+        y = _library(gate).swiglu(gate, up)
+        if y is not None:
+            return y
     if _use_native(gate, "swiglu"):
         return native_module().swiglu(gate, up)
     return torch_impl.swiglu(gate, up)
@@ -149,6 +174,10 @@ def embedding(ids: Tensor, weight: Tensor) -> Tensor:
 
 def attention(q: Tensor, k: Tensor, v: Tensor, causal: bool = True, window: int = 0,
               scale: Optional[float] = None) -> Tensor:
+    if _library(q) is not None:
+        o = _library(q).attention(q, k, v, causal, window, scale)
+        if o is not None:
+            return o
     if _use_native(q, "attention") and q.shape[1] == k.shape[1]:
         return native_module().attention(q, k, v, causal, window, scale)
     return torch_impl.attention(q, k, v, causal, window, scale)
@@ -156,6 +185,10 @@ def attention(q: Tensor, k: Tensor, v: Tensor, causal: bool = True, window: int 
 
 def nsa_attention(q, k, v, g_cmp, g_slc, g_swa, cmp_block=32, cmp_stride=16, sel_block=64,
                   top_n=16, window=512, scale=None) -> Tensor:
+    if _library(q) is not None:
+        o = _library(q).nsa_attention(q, k, v, g_cmp, g_slc, g_swa, sel_block, top_n, window, scale)
+        if o is not None:
+            return o
     if _use_native(q, "nsa_attention"):
         return native_module().nsa_attention(q, k, v, g_cmp, g_slc, g_swa, cmp_block, cmp_stride,
                                              sel_block, top_n, window, scale)
@@ -176,6 +209,10 @@ def ssd_scan(x, dt, A, Bm, Cm, D=None, chunk: int = 256) -> Tensor:
 
 
 def gated_delta_rule(q, k, v, g, beta, scale=None, chunk: int = 64) -> Tensor:
+    if _library(q) is not None:
+        o = _library(q).gated_delta_rule(q, k, v, g, beta, scale)
+        if o is not None:
+            return o
     if _use_native(q, "gated_delta_rule"):
         return native_module().gated_delta_rule(q, k, v, g, beta, scale, chunk)
     return torch_impl.gated_delta_rule(q, k, v, g, beta, scale, chunk)
@@ -183,6 +220,10 @@ def gated_delta_rule(q, k, v, g, beta, scale=None, chunk: int = 64) -> Tensor:
 
 def linear_cross_entropy(hidden: Tensor, weight: Tensor, labels: Tensor, ignore_index: int = -100,
                          chunk: int = 4096) -> Tensor:
+    if _library(hidden) is not None:
+        loss = _library(hidden).linear_cross_entropy(hidden, weight, labels, ignore_index)
+        if loss is not None:
+            return loss
     if _use_native(hidden, "linear_cross_entropy"):
         return native_module().linear_cross_entropy(hidden, weight, labels, ignore_index, chunk)
     return torch_impl.linear_cross_entropy(hidden, weight, labels, ignore_index, chunk)
