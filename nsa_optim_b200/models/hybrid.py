@@ -167,9 +167,7 @@ class AttentionBlock(nn.Module):
         q, k = apply_rotary_pos_emb(q, k, cos, sin)
         if self.sparse:
             w = torch.cat([self.gate_cmp.weight, self.gate_slc.weight, self.gate_swa.weight], 0)
-            g = torch.sigmoid(ops.linear(x, w).float()).to(x.dtype)
-            g_cmp, g_slc, g_swa = g.split(self.num_heads, dim=-1)
-            o = ops.nsa_attention(q, k, v, g_cmp, g_slc, g_swa, **self.nsa)
+            o = ops.nsa_attention(q, k, v, None, None, None, gate_logits=ops.linear(x, w), **self.nsa)
         else:
             o = ops.attention(q, k, v, causal=True)
         return self.o_proj(o.reshape(B, T, self.num_heads * self.head_dim))

@@ -184,14 +184,22 @@ def attention(q: Tensor, k: Tensor, v: Tensor, causal: bool = True, window: int 
 
 
 def nsa_attention(q, k, v, g_cmp, g_slc, g_swa, cmp_block=32, cmp_stride=16, sel_block=64,
-                  top_n=16, window=512, scale=None) -> Tensor:
+                  top_n=16, window=512, scale=None, gate_logits: Optional[Tensor] = None) -> Tensor:
+    """Native sparse attention: compressed, selected and sliding-window branches combined with
+    per-(token, head) gates.  The gates are either three tensors (B, T, Hq) already in (0, 1), or
+    ``gate_logits`` (B, T, 3*Hq) in the order compressed, selected, window, whose sigmoid the native
+    combine kernel takes itself."""
+    if gate_logits is not None and not (_use_native(q, "nsa_attention") and _library(q) is None):
+        Hq = q.shape[2]
+        g_cmp, g_slc, g_swa = torch.sigmoid(gate_logits.float()).to(q.dtype)[..., :3 * Hq].split(Hq, dim=-1)
+        gate_logits = None
     if _library(q) is not None:
         o = _library(q).nsa_attention(q, k, v, g_cmp, g_slc, g_swa, sel_block, top_n, window, scale)
         if o is not None:
             return o
     if _use_native(q, "nsa_attention"):
         return native_module().nsa_attention(q, k, v, g_cmp, g_slc, g_swa, cmp_block, cmp_stride,
-                                             sel_block, top_n, window, scale)
+                                             sel_block, top_n, window, scale, gate_logits)
     return torch_impl.nsa_attention(q, k, v, g_cmp, g_slc, g_swa, cmp_block, cmp_stride,
                                     sel_block, top_n, window, scale)
 

@@ -75,7 +75,8 @@ __device__ __forceinline__ float row_sum(float v, float* red) {
 template <int TPR, int NV, int MODE>
 __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ g,
                                                           const bf16* __restrict__ w, bf16* __restrict__ y,
-                                                          float* __restrict__ rstd_out, long rows, int d, float eps) {
+                                                          float* __restrict__ rstd_out, long rows, int d, float eps,
+                                                          long ldg) {
   __shared__ float red[8];
   const int rows_per_cta = 256 / TPR;
   const long row = static_cast<long>(blockIdx.x) * rows_per_cta + threadIdx.x / TPR;
@@ -90,7 +91,7 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const bf16* __restrict
       load8(x + row * d + c, xv[i]);
       if (MODE == 2) {
         float gv[8];
-        load8(g + row * d + c, gv);
+        load8(g + row * ldg + c, gv);
 #pragma unroll
         for (int j = 0; j < 8; ++j) xv[i][j] *= silu_f(gv[j]);
       }
@@ -111,7 +112,7 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const bf16* __restrict
       for (int j = 0; j < 8; ++j) o[j] = xv[i][j] * rstd * wv[j];
       if (MODE == 1) {
         float gv[8];
-        load8(g + row * d + c, gv);
+        load8(g + row * ldg + c, gv);
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] *= silu_f(gv[j]);
       }
@@ -174,7 +175,8 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const bf16* __restrict
                                                           const bf16* __restrict__ w, const bf16* __restrict__ dy,
                                                           const float* __restrict__ rstd_in, bf16* __restrict__ dx,
                                                           bf16* __restrict__ dg, float* __restrict__ partial,
-                                                          long rows, int d, const bf16* __restrict__ dres = nullptr) {
+                                                          long rows, int d, const bf16* __restrict__ dres = nullptr,
+                                                          long ldg = 0) {
   __shared__ float red[8];
   __shared__ float dw_sh[(TPR == 32) ? 512 : 1];
   const int rows_per_cta = 256 / TPR;
@@ -202,7 +204,7 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const bf16* __restrict
         float xv[8], dv[8];
         load8(x + row * d + c, xv);
         load8(dy + row * d + c, dv);
-        if (MODE != 0) load8(g + row * d + c, gv[i]);
+        if (MODE != 0) load8(g + row * (ldg ? ldg : d) + c, gv[i]);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           float xin = xv[j];
@@ -401,10 +403,12 @@ template <int LANES>
 __global__ void __launch_bounds__(256) gate_combine_fwd_kernel(const bf16* __restrict__ o1, const bf16* __restrict__ o2,
                                                                const bf16* __restrict__ o3, const bf16* __restrict__ g1,
                                                                const bf16* __restrict__ g2, const bf16* __restrict__ g3,
-                                                               bf16* __restrict__ o, long n8) {
+                                                               bf16* __restrict__ o, long n8, int Hq, long ldg, int sig) {
   for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += static_cast<long>(gridDim.x) * blockDim.x) {
     const long row = i / LANES;
-    const float a = __bfloat162float(g1[row]), b = __bfloat162float(g2[row]), c = __bfloat162float(g3[row]);
+    const long gi = (row / Hq) * ldg + row % Hq;           // gates: [tokens, Hq] with row pitch ldg
+    float a = __bfloat162float(g1[gi]), b = __bfloat162float(g2[gi]), c = __bfloat162float(g3[gi]);
+    if (sig) { a = sigmoid_f(a); b = sigmoid_f(b); c = sigmoid_f(c); }   // gates given as logits
     float x[8], y[8], z[8], r[8];
     load8(o1 + i * 8, x);
     load8(o2 + i * 8, y);
@@ -421,14 +425,17 @@ __global__ void __launch_bounds__(256) gate_combine_bwd_kernel(const bf16* __res
                                                                const bf16* __restrict__ d_o, bf16* __restrict__ do1,
                                                                bf16* __restrict__ do2, bf16* __restrict__ do3,
                                                                bf16* __restrict__ dg1, bf16* __restrict__ dg2,
-                                                               bf16* __restrict__ dg3, long n8) {
+                                                               bf16* __restrict__ dg3, long n8, int Hq, long ldg, int sig) {
   // the grid is sized so that every thread handles exactly one vector (rows stay inside a warp)
   const long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const bool live = i < n8;
   const long row = (live ? i : 0) / LANES;
   float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  const long gi = (row / Hq) * ldg + row % Hq;
+  float a = 0.f, b = 0.f, c = 0.f;
   if (live) {
-    const float a = __bfloat162float(g1[row]), b = __bfloat162float(g2[row]), c = __bfloat162float(g3[row]);
+    a = __bfloat162float(g1[gi]); b = __bfloat162float(g2[gi]); c = __bfloat162float(g3[gi]);
+    if (sig) { a = sigmoid_f(a); b = sigmoid_f(b); c = sigmoid_f(c); }
     float x[8], y[8], z[8], d[8], r[8];
     load8(o1 + i * 8, x);
     load8(o2 + i * 8, y);
@@ -453,9 +460,68 @@ __global__ void __launch_bounds__(256) gate_combine_bwd_kernel(const bf16* __res
     s3 += __shfl_xor_sync(0xffffffffu, s3, o);
   }
   if (live && (threadIdx.x % LANES) == 0) {
-    dg1[row] = __float2bfloat16(s1);
-    dg2[row] = __float2bfloat16(s2);
-    dg3[row] = __float2bfloat16(s3);
+    // gates given as logits: the gradient goes back through the sigmoid here
+    if (sig) { s1 *= a * (1.f - a); s2 *= b * (1.f - b); s3 *= c * (1.f - c); }
+    dg1[gi] = __float2bfloat16(s1);
+    dg2[gi] = __float2bfloat16(s2);
+    dg3[gi] = __float2bfloat16(s3);
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// Mean pooling of keys / values into compressed blocks (native sparse attention):
+//   y[b, i, :] = mean over t in [i*stride, i*stride + block) of x[b, t, :]
+// x rows are `width` = Hkv * D elements with row pitch ldx; y is contiguous [B, nC, width].
+// Backward: dx[b, t, :] = (1/block) * sum of dy[b, i, :] over the windows i that contain t.
+// One thread per 8 elements; fp32 accumulation in a fixed order.
+// ------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) nsa_pool_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, int T, int nC,
+                                                           int width8, long ldx, int block, int stride, long n) {
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const int c8 = static_cast<int>(i % width8);
+    const long r = i / width8;
+    const int ci = static_cast<int>(r % nC);
+    const long b = r / nC;
+    const bf16* src = x + (b * T + static_cast<long>(ci) * stride) * ldx + c8 * 8;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int t = 0; t < block; ++t) {
+      float v[8];
+      load8(src + t * ldx, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += v[j];
+    }
+    const float inv = 1.f / block;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] *= inv;
+    store8(y + i * 8, acc);
+  }
+}
+__global__ void __launch_bounds__(256) nsa_pool_bwd_kernel(const bf16* __restrict__ dy, bf16* __restrict__ dx, int T, int nC,
+                                                           int width8, int block, int stride, long n) {
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const int c8 = static_cast<int>(i % width8);
+    const long r = i / width8;
+    const int t = static_cast<int>(r % T);
+    const long b = r / T;
+    int lo = t - block + 1;
+    lo = lo <= 0 ? 0 : (lo + stride - 1) / stride;
+    int hi = t / stride;
+    hi = hi < nC - 1 ? hi : nC - 1;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int ci = lo; ci <= hi; ++ci) {
+      float v[8];
+      load8(dy + ((b * nC + ci) * width8 + c8) * 8, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += v[j];
+    }
+    const float inv = 1.f / block;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] *= inv;
+    store8(dx + i * 8, acc);
   }
 }
 
@@ -985,15 +1051,18 @@ inline int grid_for(long n, int block, int per_sm = 8) {
 }
 
 template <int MODE>
-int launch_rms_fwd(const void* x, const void* g, const void* w, void* y, float* rstd, long rows, int d, float eps, cudaStream_t st) {
+int launch_rms_fwd(const void* x, const void* g, const void* w, void* y, float* rstd, long rows, int d, float eps, cudaStream_t st,
+                   long ldg = 0) {
+  if (ldg == 0) ldg = d;
+  if (ldg % 8 || (reinterpret_cast<uintptr_t>(g) & 15)) return nsa::fail(NSA_ERR_ALIGNMENT, "rmsnorm: gate rows must be 16-byte aligned");
   const bf16 *X = (const bf16*)x, *G = (const bf16*)g, *Wt = (const bf16*)w;
   bf16* Y = (bf16*)y;
   if (d % 8) return nsa::fail(NSA_ERR_SHAPE, "rmsnorm: width must be a multiple of 8");
-  if (d <= 256) rmsnorm_fwd_kernel<32, 1, MODE><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(X, G, Wt, Y, rstd, rows, d, eps);
-  else if (d <= 512) rmsnorm_fwd_kernel<32, 2, MODE><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(X, G, Wt, Y, rstd, rows, d, eps);
-  else if (d <= 2048) rmsnorm_fwd_kernel<256, 1, MODE><<<(unsigned)rows, 256, 0, st>>>(X, G, Wt, Y, rstd, rows, d, eps);
-  else if (d <= 4096) rmsnorm_fwd_kernel<256, 2, MODE><<<(unsigned)rows, 256, 0, st>>>(X, G, Wt, Y, rstd, rows, d, eps);
-  else if (d <= 8192) rmsnorm_fwd_kernel<256, 4, MODE><<<(unsigned)rows, 256, 0, st>>>(X, G, Wt, Y, rstd, rows, d, eps);
+  if (d <= 256) rmsnorm_fwd_kernel<32, 1, MODE><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(X, G, Wt, Y, rstd, rows, d, eps, ldg);
+  else if (d <= 512) rmsnorm_fwd_kernel<32, 2, MODE><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(X, G, Wt, Y, rstd, rows, d, eps, ldg);
+  else if (d <= 2048) rmsnorm_fwd_kernel<256, 1, MODE><<<(unsigned)rows, 256, 0, st>>>(X, G, Wt, Y, rstd, rows, d, eps, ldg);
+  else if (d <= 4096) rmsnorm_fwd_kernel<256, 2, MODE><<<(unsigned)rows, 256, 0, st>>>(X, G, Wt, Y, rstd, rows, d, eps, ldg);
+  else if (d <= 8192) rmsnorm_fwd_kernel<256, 4, MODE><<<(unsigned)rows, 256, 0, st>>>(X, G, Wt, Y, rstd, rows, d, eps, ldg);
   else return nsa::fail(NSA_ERR_SHAPE, "rmsnorm: width above 8192 is not supported");
   nsa::count_launch();
   return 0;
@@ -1001,14 +1070,14 @@ int launch_rms_fwd(const void* x, const void* g, const void* w, void* y, float* 
 
 template <int MODE>
 int launch_rms_bwd(const void* x, const void* g, const void* w, const void* dy, const float* rstd, void* dx, void* dg,
-                   float* partial, int grid, long rows, int d, cudaStream_t st, const void* dres = nullptr) {
+                   float* partial, int grid, long rows, int d, cudaStream_t st, const void* dres = nullptr, long ldg = 0) {
   const bf16 *X = (const bf16*)x, *G = (const bf16*)g, *Wt = (const bf16*)w, *DY = (const bf16*)dy, *DR = (const bf16*)dres;
   bf16 *DX = (bf16*)dx, *DG = (bf16*)dg;
-  if (d <= 256) rmsnorm_bwd_kernel<32, 1, MODE><<<grid, 256, 0, st>>>(X, G, Wt, DY, rstd, DX, DG, partial, rows, d, DR);
-  else if (d <= 512) rmsnorm_bwd_kernel<32, 2, MODE><<<grid, 256, 0, st>>>(X, G, Wt, DY, rstd, DX, DG, partial, rows, d, DR);
-  else if (d <= 2048) rmsnorm_bwd_kernel<256, 1, MODE><<<grid, 256, 0, st>>>(X, G, Wt, DY, rstd, DX, DG, partial, rows, d, DR);
-  else if (d <= 4096) rmsnorm_bwd_kernel<256, 2, MODE><<<grid, 256, 0, st>>>(X, G, Wt, DY, rstd, DX, DG, partial, rows, d, DR);
-  else if (d <= 8192) rmsnorm_bwd_kernel<256, 4, MODE><<<grid, 256, 0, st>>>(X, G, Wt, DY, rstd, DX, DG, partial, rows, d, DR);
+  if (d <= 256) rmsnorm_bwd_kernel<32, 1, MODE><<<grid, 256, 0, st>>>(X, G, Wt, DY, rstd, DX, DG, partial, rows, d, DR, ldg);
+  else if (d <= 512) rmsnorm_bwd_kernel<32, 2, MODE><<<grid, 256, 0, st>>>(X, G, Wt, DY, rstd, DX, DG, partial, rows, d, DR, ldg);
+  else if (d <= 2048) rmsnorm_bwd_kernel<256, 1, MODE><<<grid, 256, 0, st>>>(X, G, Wt, DY, rstd, DX, DG, partial, rows, d, DR, ldg);
+  else if (d <= 4096) rmsnorm_bwd_kernel<256, 2, MODE><<<grid, 256, 0, st>>>(X, G, Wt, DY, rstd, DX, DG, partial, rows, d, DR, ldg);
+  else if (d <= 8192) rmsnorm_bwd_kernel<256, 4, MODE><<<grid, 256, 0, st>>>(X, G, Wt, DY, rstd, DX, DG, partial, rows, d, DR, ldg);
   else return nsa::fail(NSA_ERR_SHAPE, "rmsnorm: width above 8192 is not supported");
   nsa::count_launch();
   return 0;
@@ -1058,6 +1127,31 @@ extern "C" int nsa_rmsnorm_bwd(const void* x, const void* gate, const void* w, c
   if (mode == 0) rc = launch_rms_bwd<0>(x, gate, w, dy, rstd, dx, dgate, partial, parts, rows, d, st);
   else if (mode == 1) rc = launch_rms_bwd<1>(x, gate, w, dy, rstd, dx, dgate, partial, parts, rows, d, st);
   else rc = launch_rms_bwd<2>(x, gate, w, dy, rstd, dx, dgate, partial, parts, rows, d, st);
+  if (rc) return rc;
+  reduce_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(partial, parts, d, (bf16*)dw_bf16, dw_f32);
+  nsa::count_launch();
+  return 0;
+}
+
+// Gated modes with the gate given as a column slice of a wider row-major matrix: `ldg` is the
+// gate's row pitch in elements (a multiple of 8; the slice must start 16-byte aligned).  x, y, dx
+// and dgate stay contiguous [rows, d].
+extern "C" int nsa_rmsnorm_fwd_ldg(const void* x, const void* gate, long ldg, const void* w, void* y, float* rstd, long rows,
+                                   int d, float eps, int mode, cudaStream_t st) {
+  if (mode == 1) return launch_rms_fwd<1>(x, gate, w, y, rstd, rows, d, eps, st, ldg);
+  if (mode == 2) return launch_rms_fwd<2>(x, gate, w, y, rstd, rows, d, eps, st, ldg);
+  return nsa::fail(NSA_ERR_SHAPE, "nsa_rmsnorm_fwd_ldg: gated modes only");
+}
+extern "C" int nsa_rmsnorm_bwd_ldg(const void* x, const void* gate, long ldg, const void* w, const void* dy, const float* rstd,
+                                   void* dx, void* dgate, void* dw_bf16, float* dw_f32, float* partial, long rows, int d,
+                                   int mode, cudaStream_t st) {
+  if (d % 8 || ldg % 8 || (reinterpret_cast<uintptr_t>(gate) & 15))
+    return nsa::fail(NSA_ERR_ALIGNMENT, "rmsnorm: widths multiples of 8 and 16-byte aligned gate rows required");
+  const int parts = nsa_rmsnorm_bwd_parts(rows, d);
+  int rc;
+  if (mode == 1) rc = launch_rms_bwd<1>(x, gate, w, dy, rstd, dx, dgate, partial, parts, rows, d, st, nullptr, ldg);
+  else if (mode == 2) rc = launch_rms_bwd<2>(x, gate, w, dy, rstd, dx, dgate, partial, parts, rows, d, st, nullptr, ldg);
+  else return nsa::fail(NSA_ERR_SHAPE, "nsa_rmsnorm_bwd_ldg: gated modes only");
   if (rc) return rc;
   reduce_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(partial, parts, d, (bf16*)dw_bf16, dw_f32);
   nsa::count_launch();
@@ -1192,7 +1286,7 @@ extern "C" int nsa_gate_combine_fwd(const void* o1, const void* o2, const void* 
   const long n8 = rows * (D / 8);
   const int grid = grid_for(n8, 256);
 #define NSA_GC_FWD(L) gate_combine_fwd_kernel<L><<<grid, 256, 0, st>>>((const bf16*)o1, (const bf16*)o2, (const bf16*)o3, \
-    (const bf16*)g1, (const bf16*)g2, (const bf16*)g3, (bf16*)o, n8)
+    (const bf16*)g1, (const bf16*)g2, (const bf16*)g3, (bf16*)o, n8, 1, 1L, 0)
   if (D == 64) NSA_GC_FWD(8); else if (D == 128) NSA_GC_FWD(16); else NSA_GC_FWD(32);
 #undef NSA_GC_FWD
   nsa::count_launch();
@@ -1207,9 +1301,63 @@ extern "C" int nsa_gate_combine_bwd(const void* o1, const void* o2, const void* 
   if (blocks > 2147483647L) return nsa::fail(NSA_ERR_SHAPE, "gate_combine: problem too large for one launch");
 #define NSA_GC_BWD(L) gate_combine_bwd_kernel<L><<<(unsigned)blocks, 256, 0, st>>>((const bf16*)o1, (const bf16*)o2, \
     (const bf16*)o3, (const bf16*)g1, (const bf16*)g2, (const bf16*)g3, (const bf16*)d_o, (bf16*)do1, (bf16*)do2, (bf16*)do3, \
-    (bf16*)dg1, (bf16*)dg2, (bf16*)dg3, n8)
+    (bf16*)dg1, (bf16*)dg2, (bf16*)dg3, n8, 1, 1L, 0)
   if (D == 64) NSA_GC_BWD(8); else if (D == 128) NSA_GC_BWD(16); else NSA_GC_BWD(32);
 #undef NSA_GC_BWD
+  nsa::count_launch();
+  return 0;
+}
+
+// The same with the three gates as columns of one [tokens, >= 3*Hq] bf16 matrix (row pitch ldg, the
+// gate projection's output as it stands) and, with sig != 0, given as logits: the sigmoid and its
+// derivative are applied here.  rows = tokens * Hq.  dg1..dg3 use the same pitch.
+extern "C" int nsa_gate_combine_fwd_ex(const void* o1, const void* o2, const void* o3, const void* g1, const void* g2,
+                                       const void* g3, long ldg, int Hq, int sig, void* o, long rows, int D, cudaStream_t st) {
+  if (D != 64 && D != 128 && D != 256) return nsa::fail(NSA_ERR_SHAPE, "gate_combine: head_dim must be 64, 128 or 256");
+  if (Hq <= 0 || rows % Hq) return nsa::fail(NSA_ERR_SHAPE, "gate_combine: rows must be tokens * heads");
+  const long n8 = rows * (D / 8);
+  const int grid = grid_for(n8, 256);
+#define NSA_GC_FWD(L) gate_combine_fwd_kernel<L><<<grid, 256, 0, st>>>((const bf16*)o1, (const bf16*)o2, (const bf16*)o3, \
+    (const bf16*)g1, (const bf16*)g2, (const bf16*)g3, (bf16*)o, n8, Hq, ldg, sig)
+  if (D == 64) NSA_GC_FWD(8); else if (D == 128) NSA_GC_FWD(16); else NSA_GC_FWD(32);
+#undef NSA_GC_FWD
+  nsa::count_launch();
+  return 0;
+}
+extern "C" int nsa_gate_combine_bwd_ex(const void* o1, const void* o2, const void* o3, const void* g1, const void* g2,
+                                       const void* g3, long ldg, int Hq, int sig, const void* d_o, void* do1, void* do2,
+                                       void* do3, void* dg1, void* dg2, void* dg3, long rows, int D, cudaStream_t st) {
+  if (D != 64 && D != 128 && D != 256) return nsa::fail(NSA_ERR_SHAPE, "gate_combine: head_dim must be 64, 128 or 256");
+  if (Hq <= 0 || rows % Hq) return nsa::fail(NSA_ERR_SHAPE, "gate_combine: rows must be tokens * heads");
+  const long n8 = rows * (D / 8);
+  const long blocks = (n8 + 255) / 256;
+  if (blocks > 2147483647L) return nsa::fail(NSA_ERR_SHAPE, "gate_combine: problem too large for one launch");
+#define NSA_GC_BWD(L) gate_combine_bwd_kernel<L><<<(unsigned)blocks, 256, 0, st>>>((const bf16*)o1, (const bf16*)o2, \
+    (const bf16*)o3, (const bf16*)g1, (const bf16*)g2, (const bf16*)g3, (const bf16*)d_o, (bf16*)do1, (bf16*)do2, (bf16*)do3, \
+    (bf16*)dg1, (bf16*)dg2, (bf16*)dg3, n8, Hq, ldg, sig)
+  if (D == 64) NSA_GC_BWD(8); else if (D == 128) NSA_GC_BWD(16); else NSA_GC_BWD(32);
+#undef NSA_GC_BWD
+  nsa::count_launch();
+  return 0;
+}
+
+// Block mean pooling (see nsa_pool_fwd_kernel).  x: [B, T, width] bf16 with row pitch ldx; y: [B, nC, width]
+// contiguous, nC = (T - block) / stride + 1.  dx is contiguous [B, T, width].
+extern "C" int nsa_pool_fwd(const void* x, void* y, int B, int T, int width, long ldx, int block, int stride, cudaStream_t st) {
+  if (width % 8 || ldx % 8 || T < block || block <= 0 || stride <= 0)
+    return nsa::fail(NSA_ERR_SHAPE, "nsa_pool: width and pitch multiples of 8, T >= block required");
+  const int nC = (T - block) / stride + 1;
+  const long n = static_cast<long>(B) * nC * (width / 8);
+  nsa_pool_fwd_kernel<<<grid_for(n, 256), 256, 0, st>>>((const bf16*)x, (bf16*)y, T, nC, width / 8, ldx, block, stride, n);
+  nsa::count_launch();
+  return 0;
+}
+extern "C" int nsa_pool_bwd(const void* dy, void* dx, int B, int T, int width, int block, int stride, cudaStream_t st) {
+  if (width % 8 || T < block || block <= 0 || stride <= 0)
+    return nsa::fail(NSA_ERR_SHAPE, "nsa_pool: width multiple of 8, T >= block required");
+  const int nC = (T - block) / stride + 1;
+  const long n = static_cast<long>(B) * T * (width / 8);
+  nsa_pool_bwd_kernel<<<grid_for(n, 256), 256, 0, st>>>((const bf16*)dy, (bf16*)dx, T, nC, width / 8, block, stride, n);
   nsa::count_launch();
   return 0;
 }

@@ -437,22 +437,51 @@ def add_rms_norm(x, r, w, eps=1e-6):
     return _AddRMSNorm.apply(x, r, w, eps)
 
 
+def _gate_rows(gate: Tensor):
+    """(2-D gate, row pitch): a column slice of a wider row-major matrix is used in place when its
+    rows are 16-byte aligned; anything else is made contiguous."""
+    d = gate.shape[-1]
+    if gate.dim() >= 2 and gate.stride(-1) == 1 and gate.data_ptr() % 16 == 0:
+        pitch = gate.stride(-2)
+        exp, ok = pitch, pitch % 8 == 0 and pitch >= d
+        for k in range(gate.dim() - 2, -1, -1):
+            if gate.shape[k] != 1 and gate.stride(k) != exp:
+                ok = False
+            exp *= gate.shape[k]
+        if ok:
+            rows = gate.numel() // d
+            return torch.as_strided(gate, (rows, d), (pitch, 1)), pitch
+    g2 = gate.reshape(-1, d).contiguous()
+    return g2, d
+
+
 class _GatedRMSNorm(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, gate, w, eps, norm_before_gate):
         mode = 1 if norm_before_gate else 2
         x2 = x.reshape(-1, x.shape[-1]).contiguous()
-        g2 = gate.reshape(-1, gate.shape[-1]).contiguous()
+        g2, ldg = _gate_rows(gate)
         wb = w.to(torch.bfloat16)
-        y, rstd = _rms_fwd(x2, g2, wb, eps, mode)
+        rows, d = x2.shape
+        y = _empty_like(x2)
+        rstd = _empty(rows, dtype=torch.float32, device=x2.device)
+        _check(load().nsa_rmsnorm_fwd_ldg(_p(x2), _p(g2), c_long(ldg), _p(wb), _p(y), _p(rstd), c_long(rows), c_int(d),
+                                          c_float(eps), c_int(mode), _stream()))
         ctx.save_for_backward(x2, g2, wb, rstd)
-        ctx.mode, ctx.wdtype, ctx.gshape = mode, w.dtype, gate.shape
+        ctx.mode, ctx.wdtype, ctx.gshape, ctx.ldg = mode, w.dtype, gate.shape, ldg
         return y.view(x.shape)
 
     @staticmethod
     def backward(ctx, dy):
         x2, g2, wb, rstd = ctx.saved_tensors
-        dx, dg, dw = _rms_bwd(x2, g2, wb, dy.reshape(x2.shape).contiguous(), rstd, ctx.mode)
+        rows, d = x2.shape
+        dy2 = dy.reshape(x2.shape).contiguous()
+        dx, dg = _empty_like(x2), _empty_like(x2)
+        dw = _empty(d, dtype=torch.bfloat16, device=x2.device)
+        parts = int(load().nsa_rmsnorm_bwd_parts(c_long(rows), c_int(d)))
+        partial = _empty(parts * d, dtype=torch.float32, device=x2.device)
+        _check(load().nsa_rmsnorm_bwd_ldg(_p(x2), _p(g2), c_long(ctx.ldg), _p(wb), _p(dy2), _p(rstd), _p(dx), _p(dg), _p(dw),
+                                          c_void_p(0), _p(partial), c_long(rows), c_int(d), c_int(ctx.mode), _stream()))
         return dx.view(dy.shape), dg.view(ctx.gshape), dw.to(ctx.wdtype), None, None
 
 
@@ -1083,19 +1112,101 @@ class _GateCombine(torch.autograd.Function):
         return d1, d2, d3, e1, e2, e3
 
 
+class _GateCombineLogits(torch.autograd.Function):
+    """The same combine with the three gates taken as logits straight from the gate projection:
+    ``gates`` is (B, T, 3*Hq) (or wider; columns [0, Hq) compressed, [Hq, 2Hq) selected, [2Hq, 3Hq)
+    window).  The sigmoid runs inside the combine kernel and its derivative inside the backward
+    kernel, which writes d(logits) in the projection's own layout."""
+
+    @staticmethod
+    def forward(ctx, o1, o2, o3, gates):
+        o1, o2, o3 = o1.contiguous(), o2.contiguous(), o3.contiguous()
+        Hq, D = o1.shape[-2], o1.shape[-1]
+        gl = gates.to(torch.bfloat16)
+        if gl.stride(-1) != 1 or not gl.is_contiguous():
+            gl = gl.contiguous()
+        ldg = gl.shape[-1]
+        rows = o1.numel() // D
+        o = _empty_like(o1)
+        es = gl.element_size()
+        _check(load().nsa_gate_combine_fwd_ex(_p(o1), _p(o2), _p(o3), c_void_p(gl.data_ptr()), c_void_p(gl.data_ptr() + Hq * es),
+                                              c_void_p(gl.data_ptr() + 2 * Hq * es), c_long(ldg), c_int(Hq), c_int(1), _p(o),
+                                              c_long(rows), c_int(D), _stream()))
+        ctx.save_for_backward(o1, o2, o3, gl)
+        ctx.gdtype = gates.dtype
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        o1, o2, o3, gl = ctx.saved_tensors
+        do = do.contiguous()
+        Hq, D = o1.shape[-2], o1.shape[-1]
+        ldg = gl.shape[-1]
+        rows = o1.numel() // D
+        es = gl.element_size()
+        d1, d2, d3 = _empty_like(o1), _empty_like(o1), _empty_like(o1)
+        dgl = _zeros_like(gl) if ldg > 3 * Hq else _empty_like(gl)
+        g0, dg0 = gl.data_ptr(), dgl.data_ptr()
+        _check(load().nsa_gate_combine_bwd_ex(_p(o1), _p(o2), _p(o3), c_void_p(g0), c_void_p(g0 + Hq * es),
+                                              c_void_p(g0 + 2 * Hq * es), c_long(ldg), c_int(Hq), c_int(1), _p(do), _p(d1), _p(d2),
+                                              _p(d3), c_void_p(dg0), c_void_p(dg0 + Hq * es), c_void_p(dg0 + 2 * Hq * es),
+                                              c_long(rows), c_int(D), _stream()))
+        return d1, d2, d3, dgl.to(ctx.gdtype)
+
+
+class _Pool(torch.autograd.Function):
+    """Mean pooling of (B, T, H, D) keys / values over windows [i*stride, i*stride + block) ->
+    (B, nC, H, D), forward and backward in ``csrc/elementwise.cu`` (fla's ``mean_pooling`` in the
+    reference's NSA stack)."""
+
+    @staticmethod
+    def forward(ctx, x, block, stride):
+        B, T, H, D = x.shape
+        width = H * D
+        ok = (x.stride(3) == 1 and x.stride(2) == D and x.stride(1) % 8 == 0 and x.stride(0) == T * x.stride(1)
+              and x.data_ptr() % 16 == 0)
+        xv = x if ok else x.contiguous()
+        nC = (T - block) // stride + 1
+        y = _empty(B, nC, H, D, dtype=x.dtype, device=x.device)
+        _check(load().nsa_pool_fwd(_p(xv), _p(y), c_int(B), c_int(T), c_int(width), c_long(xv.stride(1)), c_int(block),
+                                   c_int(stride), _stream()))
+        ctx.shape, ctx.block, ctx.stride = (B, T, H, D), block, stride
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        B, T, H, D = ctx.shape
+        dy = dy.contiguous()
+        dx = _empty(B, T, H, D, dtype=dy.dtype, device=dy.device)
+        _check(load().nsa_pool_bwd(_p(dy), _p(dx), c_int(B), c_int(T), c_int(H * D), c_int(ctx.block), c_int(ctx.stride),
+                                   _stream()))
+        return dx, None, None
+
+
+def nsa_compress(x, block, stride):
+    if x.dtype != torch.bfloat16 or (x.shape[2] * x.shape[3]) % 8 or x.shape[1] < block:
+        _fallback("nsa_compress")
+        return torch_impl.nsa_compress(x, block, stride)
+    return _Pool.apply(x, int(block), int(stride))
+
+
 def nsa_attention(q, k, v, g_cmp, g_slc, g_swa, cmp_block=32, cmp_stride=16, sel_block=64, top_n=16,
-                  window=512, scale=None):
+                  window=512, scale=None, gate_logits=None):
+    """``gate_logits`` (B, T, 3*Hq), when given, replaces the three gate tensors: the sigmoid is taken
+    inside the combine kernel."""
     B, T, Hq, D = q.shape
     Hkv = k.shape[2]
     G = Hq // Hkv
     if (not _attn_ok(q, k) or sel_block != 64 or sel_block != 4 * cmp_stride or cmp_block != 2 * cmp_stride
             or G < 2 or G > 32 or T < cmp_block):
         _fallback("nsa_attention")
+        if gate_logits is not None:
+            g_cmp, g_slc, g_swa = torch.sigmoid(gate_logits.float()).to(q.dtype)[..., :3 * Hq].split(Hq, dim=-1)
         return torch_impl.nsa_attention(q, k, v, g_cmp, g_slc, g_swa, cmp_block, cmp_stride, sel_block, top_n,
                                         window, scale)
     scale = D ** -0.5 if scale is None else scale
-    kc = torch_impl.nsa_compress(k, cmp_block, cmp_stride)
-    vc = torch_impl.nsa_compress(v, cmp_block, cmp_stride)
+    kc = nsa_compress(k, cmp_block, cmp_stride)
+    vc = nsa_compress(v, cmp_block, cmp_stride)
     o_cmp, L_cmp = _Attn.apply(q, kc, vc, True, 0, float(scale), cmp_stride, cmp_block - 1, None)
     nS = -(-T // sel_block)
     with torch.no_grad():
@@ -1105,6 +1216,10 @@ def nsa_attention(q, k, v, g_cmp, g_slc, g_swa, cmp_block=32, cmp_stride=16, sel
         tiles = union_blocks(idx, G, nS) + (idx, nS)
     o_slc = _Attn.apply(q, k, v, True, 0, float(scale), 1, 0, tiles)[0]
     o_swa = _Attn.apply(q, k, v, True, int(window), float(scale), 1, 0, None)[0]
+    if gate_logits is not None:
+        if q.dtype == torch.bfloat16 and D in (64, 128, 256):
+            return _GateCombineLogits.apply(o_cmp, o_slc, o_swa, gate_logits)
+        g_cmp, g_slc, g_swa = torch.sigmoid(gate_logits.float()).to(q.dtype)[..., :3 * Hq].split(Hq, dim=-1)
     if q.dtype == torch.bfloat16 and D in (64, 128, 256):
         return _GateCombine.apply(o_cmp, o_slc, o_swa, g_cmp, g_slc, g_swa)
     return g_cmp.unsqueeze(-1) * o_cmp + g_slc.unsqueeze(-1) * o_slc + g_swa.unsqueeze(-1) * o_swa

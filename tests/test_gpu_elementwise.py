@@ -71,6 +71,23 @@ def test_gated_rmsnorm(native, rows, d, nbg):
     close(y, yr); close(x.grad, xr.grad); close(gt.grad, gr.grad); close(w.grad, wr.grad, atol=5e-2)
 
 
+@pytest.mark.parametrize("nbg", [True, False])
+def test_gated_rmsnorm_with_gate_as_column_slice(native, nbg):
+    """The gate is read in place from a slice of a wider matrix (as the Mamba-2 mixer hands it over)."""
+    rows, d = 70, 512
+    wide = bf(2, rows // 2, 3 * d + 64)
+    gate = wide[..., d:2 * d].detach().requires_grad_()
+    x = bf(2, rows // 2, d).requires_grad_()
+    w = (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16().requires_grad_()
+    y = native.gated_rms_norm(x, gate, w, 1e-5, nbg)
+    g = bf(2, rows // 2, d)
+    y.backward(g)
+    xr, gr, wr = (t.detach().float().requires_grad_() for t in (x, gate, w))
+    yr = oracle.gated_rms_norm(xr, gr, wr, 1e-5, nbg)
+    yr.backward(g.float())
+    close(y, yr); close(x.grad, xr.grad); close(gate.grad, gr.grad); close(w.grad, wr.grad, atol=5e-2)
+
+
 def test_l2norm(native):
     x = bf(2, 33, 4, 128).requires_grad_()
     y = native.l2_norm(x)
