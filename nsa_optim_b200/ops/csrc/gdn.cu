@@ -172,10 +172,21 @@ gdn_seq_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   constexpr uint32_t idesc1 = tc5::make_idesc_bf16(128, VT, 0, 1);   // A K-major, B MN-major
   constexpr uint32_t idesc2 = tc5::make_idesc_bf16(128, VT, 1, 1);   // A MN-major (k_tail^T), B MN-major
   bool ok = true;
+  // The chunk loop is one dependent chain, so every global load in it would add its full latency to
+  // every chunk: the u row and the decay of the next chunk are fetched one chunk ahead instead.
+  uint32_t upk_next[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) upk_next[j] = 0u;
+  if (r < CH) load_row_global(p.u + (static_cast<long>(bh * NC) * CH + r) * V + vt * VT, upk_next);
+  float g_next = NC > 1 ? p.gamma[bh * NC + 1] : 0.f;
   for (int c = 0; c < NC && ok; ++c) {
     const int s = c & 1;
     uint8_t* st = smem + s * FWD_STAGE;
     const long row0 = static_cast<long>(bh * NC + c) * CH;
+    uint32_t upk[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) upk[j] = upk_next[j];
+    const float g = g_next;                        // decay applied to the state that enters chunk c + 1
     if (r == 0) {
       if (tc5::mbar_wait(&full[s], (c >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL)) {
         tc5::fence_after_sync();
@@ -190,9 +201,9 @@ gdn_seq_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         if (c + 1 < NC) issue_loads(c + 1);
       }
     }
-    // u row (rows 0..63 only) while the MMA runs
-    uint32_t upk[32];
-    if (r < CH) load_row_global(p.u + (row0 + r) * V + vt * VT, upk);
+    // next chunk's u row (rows 0..63 only) and the decay after it, in flight while this chunk computes
+    if (c + 1 < NC && r < CH) load_row_global(p.u + (row0 + CH + r) * V + vt * VT, upk_next);
+    if (c + 2 < NC) g_next = p.gamma[bh * NC + c + 2];
     if (!tc5::mbar_wait(m1, c & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; }
     if (__syncthreads_or(!ok)) { ok = false; break; }
     tc5::fence_after_sync();
@@ -238,7 +249,6 @@ gdn_seq_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       pack_row(sv, pk);
       write_row_swz(Sb, r, pk);
       store_row_global(p.S_all + (static_cast<long>(bh * NC + c + 1) * KD + r) * V + vt * VT, pk);
-      const float g = p.gamma[bh * NC + c + 1];
 #pragma unroll
       for (int j = 0; j < 64; ++j) sv[j] *= g;
       tmem_st_row64(tS, sv);
@@ -361,23 +371,38 @@ gdn_seq_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   constexpr uint32_t id_dn = tc5::make_idesc_bf16(128, VT, 1, 1, 1);    // (-w)^T x dv_tot
   const long part_stride = static_cast<long>(p.BH) * NC * CH * KD;
   bool ok = true;
+  // The chunk loop is one dependent chain: the rows that come straight from global memory (v_new and
+  // dv_new for rows 0..63, do for rows 64..127) and the decay are fetched one chunk ahead, so their
+  // latency is not paid once per chunk.
+  uint32_t row_next[32], dv_next[32];
+  auto fetch_rows = [&](int cc) {
+    const long rr = static_cast<long>(bh * NC + cc) * CH;
+    if (r < CH) {
+      load_row_global(p.v_new + (rr + r) * V + vt * VT, row_next);
+      load_row_global(p.dv_new + (rr + r) * V + vt * VT, dv_next);
+    } else {
+      load_row_global(p.d_o + (rr + r - CH) * V + vt * VT, row_next);
+    }
+  };
+#pragma unroll
+  for (int j = 0; j < 32; ++j) dv_next[j] = 0u;
+  fetch_rows(NC - 1);
+  float g_next = p.gamma[bh * NC + NC - 1];
   for (int it = 0; it < NC && ok; ++it) {
     const int c = NC - 1 - it;
     const int s = it & 1;
     uint8_t* st = smem + s * BWD_STAGE;
     const long row0 = static_cast<long>(bh * NC + c) * CH;
-    // stage the per-chunk activations/gradients that come straight from global memory
+    // stage this chunk's rows (already in registers) and start the next chunk's loads
     uint32_t dvin[32];
-    if (r < CH) {
-      uint32_t pk[32];
-      load_row_global(p.v_new + (row0 + r) * V + vt * VT, pk);
-      write_row_swz(AV, r, pk);
-      load_row_global(p.dv_new + (row0 + r) * V + vt * VT, dvin);
-    } else {
-      uint32_t pk[32];
-      load_row_global(p.d_o + (row0 + r - CH) * V + vt * VT, pk);
-      write_row_swz(AV, r, pk);
-      write_row_swz(AD, r, pk);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) dvin[j] = dv_next[j];
+    write_row_swz(AV, r, row_next);
+    if (r >= CH) write_row_swz(AD, r, row_next);
+    const float g = g_next;
+    if (c > 0) {
+      fetch_rows(c - 1);
+      g_next = p.gamma[bh * NC + c - 1];
     }
     tc5::fence_proxy_async();
     tc5::fence_before_sync();
@@ -400,7 +425,6 @@ gdn_seq_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     if (!tc5::mbar_wait(m1, it & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; }
     if (__syncthreads_or(!ok)) { ok = false; break; }
     tc5::fence_after_sync();
-    const float g = p.gamma[bh * NC + c];
     float part_dg = 0.f;
     {
       // dS (entering from chunk c+1): dgamma partial with S_prev, then scale by gamma in place
