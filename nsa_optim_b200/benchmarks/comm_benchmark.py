@@ -61,7 +61,7 @@ def main() -> None:
     gfull = arena.view(off_g, W * S, torch.float32)
     parts = torch.zeros(symm.reduce_scatter_parts(), device=dev)
     x = (torch.randn(a.m, a.k, device=dev) * 0.1).bfloat16()
-    cps = max(1, min(16, (S * 2) // (1 << 20)))
+    cps = max(1, min(1024, (S * 2) // (256 << 10)))
     flags = torch.zeros(W * cps, dtype=torch.int32, device=dev)
     epoch = [0]
     torch.cuda.synchronize()
@@ -136,7 +136,9 @@ def main() -> None:
     ms = timed(lambda: (dist.all_gather_into_tensor(full, shard), native.gemm(x, w_view, False, False)))
     row("NCCL all_gather, then GEMM", ms, None, flops, roofline_ms=round(target, 4), frac_of_roofline=round(target / ms, 3))
     ok_fused = True
-    for cc in (4, 8, 16, 32):
+    for cc, which in ((0, "pair"), (16, "single"), (32, "single")):
+        native.gemm_select(which)
+
         def pre():
             publish()
             flags.zero_()
@@ -147,8 +149,11 @@ def main() -> None:
         y = fused()
         torch.cuda.synchronize()
         ok_fused = ok_fused and bool(torch.equal(y, y_ref)) and bool(torch.equal(full, ref))
-        row(f"GEMM with the all-gather inside, {cc} copy CTAs", ms, None, flops, roofline_ms=round(target, 4),
+        name = ("CTA-pair kernel, copy role in the idle MMA warps" if which == "pair"
+                else f"single-CTA kernel, {cc} copy CTAs")
+        row(f"GEMM with the all-gather inside: {name}", ms, None, flops, roofline_ms=round(target, 4),
             frac_of_roofline=round(target / ms, 3))
+    native.gemm_select("default")
     native.check_status()
     dist.barrier()
     if rank == 0:

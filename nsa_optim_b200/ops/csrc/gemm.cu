@@ -435,7 +435,69 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   mb = first_m + local % gm;
   nb = local / gm;
 }
+// Tile order of the GEMM that gathers its own B operand: N-major, so that the sweep passes through
+// the unit's shards one after the other in the order in which they are pulled (the local shard
+// first); inside a group of GROUP_N tile columns the rows run fastest, which keeps that B panel in
+// L2 while A streams by.  The caller rotates nb by ag.n_rot.
+constexpr int GROUP_N = 8;
+__device__ __forceinline__ void tile_coords_nmajor(int t, int tiles_m, int tiles_n, int& mb, int& nb) {
+  const int per_group = GROUP_N * tiles_m;
+  const int g = t / per_group;
+  const int first_n = g * GROUP_N;
+  const int gn = min(GROUP_N, tiles_n - first_n);
+  const int local = t - g * per_group;
+  nb = first_n + local % gn;
+  mb = local / gn;
+}
 }  // namespace pair
+
+// Copy role of the fused all-gather in the CTA-pair kernel: the MMA warp of the odd CTA of each pair
+// has nothing else to do (the even CTA issues for both), so it pulls the peers' shards, 16 loads of
+// 16 bytes in flight per lane, into the local gathered buffer and publishes one flag per chunk.
+// Jobs are numbered shard-major in pull order, so the shards complete in the order in which the
+// tile sweep needs them.  No SM is taken away from the GEMM.
+__device__ void ag_copy_warp(const AgFuse& ag, int cluster, int n_clusters, KernelStatus* status) {
+  const int lane = threadIdx.x & 31;
+  const int jobs = ag.W * ag.chunks_per_shard;
+  int ready_peer = -1;
+  for (int q = cluster; q < jobs; q += n_clusters) {
+    const int k = q / ag.chunks_per_shard, c = q - k * ag.chunks_per_shard;
+    const int pr = (ag.rank + k) % ag.W;
+    if (pr != ag.rank && pr != ready_peer) {
+      int ok = 1;
+      if (lane == 0 && ag.peer_flags != nullptr && !spin_until(ag.peer_flags + pr, ag.epoch, ag.max_cycles, true)) {
+        status_report(status, STATUS_TIMEOUT_PEER_FLAG, pr, (int)ag.epoch);
+        ok = 0;
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) return;
+      ready_peer = pr;
+    }
+    const long lo = static_cast<long>(c) * ag.chunk_vec;
+    const long hi = lo + ag.chunk_vec < ag.shard_vec ? lo + ag.chunk_vec : ag.shard_vec;
+    const uint4* src = ag.shards[pr];
+    uint4* dst = ag.full + static_cast<long>(pr) * ag.shard_vec;
+    constexpr int U = 16;
+    for (long i0 = lo + lane; i0 < hi; i0 += 32L * U) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long i = i0 + 32L * u;
+        if (i < hi) v[u] = src[i];
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long i = i0 + 32L * u;
+        if (i < hi) dst[i] = v[u];
+      }
+    }
+    __syncwarp();
+    if (lane == 0) {
+      __threadfence();
+      asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(ag.chunk_flags + pr * ag.chunks_per_shard + c), "r"(ag.epoch) : "memory");
+    }
+  }
+}
 
 template <int A_MN, int B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::THREADS, 1)
@@ -465,6 +527,16 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   const int tiles_n = (p.N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int k_blocks = (p.K + BK - 1) / BK;
+  // with the gather inside, the producers may wait for a peer; everything downstream waits as long
+  const long long wait_cycles = tc5::kMaxWaitCycles + (p.ag.enabled ? p.ag.max_cycles : 0ll);
+  auto coords = [&](int t, int& mb, int& nb) {
+    if (p.ag.enabled) {
+      pair::tile_coords_nmajor(t, tiles_m, tiles_n, mb, nb);
+      nb = (nb + p.ag.n_rot) % tiles_n;
+    } else {
+      pair::tile_coords(t, tiles_m, tiles_n, mb, nb);
+    }
+  };
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -497,13 +569,28 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       bool ok = true;
       for (int t = cluster; t < num_tiles && ok; t += n_clusters) {
         int mb, nb;
-        pair::tile_coords(t, tiles_m, tiles_n, mb, nb);
+        coords(t, mb, nb);
         const int m0 = mb * 2 * BM + static_cast<int>(rank) * BM;
         const int n0 = nb * BN + static_cast<int>(rank) * BNH;
+        if (p.ag.enabled && n0 < p.N) {
+          // this CTA's B rows [n0, n1) live at 16-byte units [g_lo, g_hi] of the gathered buffer
+          const int n1 = n0 + BNH < p.N ? n0 + BNH : p.N;
+          const long g_lo = p.ag.b_vec_offset + static_cast<long>(n0) * p.ldb / 8;
+          const long g_hi = p.ag.b_vec_offset + static_cast<long>(n1) * p.ldb / 8 - 1;
+          const int id_lo = ag_chunk_id(p.ag, g_lo), id_hi = ag_chunk_id(p.ag, g_hi);
+          for (int id = id_lo; id <= id_hi && ok; ++id)
+            if (!spin_until(p.ag.chunk_flags + id, p.ag.epoch, p.ag.max_cycles, false)) {
+              *abort_flag = 1;
+              status_report(p.status, STATUS_TIMEOUT_LOCAL_FLAG, blockIdx.x, id);
+              ok = false;
+            }
+          if (!ok) break;
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          if (!tc5::mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_EMPTY)) { ok = false; break; }
+          if (!tc5::mbar_wait_cycles(&empty_bar[s], ph ^ 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_EMPTY, wait_cycles)) { ok = false; break; }
           uint8_t* sa = smem + s * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
           if (rank == 0) tc5::mbar_expect_tx(&full_bar[s], 2 * STAGE_BYTES);   // bytes of both CTAs
@@ -547,6 +634,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (rank == 1 && p.ag.enabled) ag_copy_warp(p.ag, cluster, n_clusters, p.status);
     if (lane == 0 && rank == 0) {
       constexpr uint32_t idesc = tc5::make_idesc_bf16(2 * BM, BN, A_MN, B_MN);
       uint32_t it = 0;
@@ -555,13 +643,13 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       for (int t = cluster; t < num_tiles && ok; t += n_clusters, ++tile_i) {
         const uint32_t acc = tile_i & 1;
         const uint32_t acc_ph = (tile_i >> 1) & 1;
-        if (!tc5::mbar_wait(&tempty_bar[acc], acc_ph ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+        if (!tc5::mbar_wait_cycles(&tempty_bar[acc], acc_ph ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY, wait_cycles)) { ok = false; break; }
         tc5::fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          if (!tc5::mbar_wait(&full_bar[s], ph, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL)) { ok = false; break; }
+          if (!tc5::mbar_wait_cycles(&full_bar[s], ph, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL, wait_cycles)) { ok = false; break; }
           tc5::fence_after_sync();
           const uint32_t sa = tc5::smem_u32(smem + s * STAGE_BYTES);
           const uint32_t sb = sa + A_BYTES;
@@ -587,10 +675,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     bool ok = true;
     for (int t = cluster; t < num_tiles && ok; t += n_clusters, ++tile_i) {
       int mb, nb;
-      pair::tile_coords(t, tiles_m, tiles_n, mb, nb);
+      coords(t, mb, nb);
       const uint32_t acc = tile_i & 1;
       const uint32_t acc_ph = (tile_i >> 1) & 1;
-      if (!tc5::mbar_wait(&tfull_bar[acc], acc_ph, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      if (!tc5::mbar_wait_cycles(&tfull_bar[acc], acc_ph, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL, wait_cycles)) { ok = false; break; }
       tc5::fence_after_sync();
       const int row0 = mb * 2 * BM + static_cast<int>(rank) * BM + quarter * 32;
       const int row = row0 + lane;
@@ -771,7 +859,10 @@ extern "C" int nsa_gemm_bf16(const void* A, const void* B, void* C, int M, int N
 
 // y[M,N] = x[M,K] * W[N,K]^T where W lives at element offset `b_elem_offset` of the sharded
 // unit's gathered buffer `full`, which this same kernel assembles from the W ranks' shards
-// (see AgFuse).  After the kernel the whole unit (not only W) is gathered.
+// (see AgFuse).  After the kernel the whole unit (not only W) is gathered.  With the CTA-pair
+// kernel (the default above 128 rows) no SM is set aside for copying; the single-CTA kernel
+// reserves `copy_ctas` CTAs for it.  Use chunks of a few hundred KB (chunks_per_shard) so that
+// every copy warp has work: there is one per CTA pair.
 //   shards      device array of W pointers to the ranks' shards (shard_elems bf16 each)
 //   chunk_flags local scratch, W * chunks_per_shard words, values < epoch on entry
 //   peer_flags  local flag row, peer p's shard is final once peer_flags[p] >= epoch (may be null)
@@ -784,10 +875,11 @@ extern "C" int nsa_gemm_bf16_ag(const void* A, void* C, int M, int N, int K, int
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(Bp) & 15) || (lda & 7) || (K & 7) ||
       (shard_elems & 7) || (b_elem_offset & 7))
     return nsa::fail(NSA_ERR_ALIGNMENT, "nsa_gemm_bf16_ag: operands need 16-byte alignment");
-  CUtensorMap ta, tb;
+  const bool pairk = use_pair_kernel() && M > 128;
+  CUtensorMap ta, tb, tc;
   int rc;
   if ((rc = nsa::make_tmap_2d_bf16(&ta, A, K, M, lda, BK, BM))) return rc;
-  if ((rc = nsa::make_tmap_2d_bf16(&tb, Bp, K, N, K, BK, BN))) return rc;
+  if ((rc = nsa::make_tmap_2d_bf16(&tb, Bp, K, N, K, BK, pairk ? pair::BNH : BN))) return rc;
   GemmParams p;
   p.ag = AgFuse{};
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldb = K; p.a_mn = 0; p.b_mn = 0;
@@ -820,6 +912,18 @@ extern "C" int nsa_gemm_bf16_ag(const void* A, void* C, int M, int N, int K, int
       ag.n_rot = static_cast<int>((row + BN - 1) / BN) % tiles_n;
       break;
     }
+  }
+  if (pairk) {
+    // CTA-pair kernel: the copy role runs in the otherwise idle MMA warp of every odd CTA, the tile
+    // sweep follows the shards (see ag_copy_warp and tile_coords_nmajor); `copy_ctas` is not used
+    const int tma_store = ((reinterpret_cast<uintptr_t>(C) & 15) == 0 && (ldc & 7) == 0) ? 1 : 0;
+    if (tma_store) {
+      if ((rc = nsa::make_tmap_2d_bf16(&tc, C, N, M, ldc, 64, 32))) return rc;
+    } else {
+      tc = ta;
+    }
+    cudaError_t e = launch_pair<0, 0>(ta, tb, tc, p, tma_store, 0, stream);
+    return e == cudaSuccess ? 0 : nsa::fail_cuda(e, "nsa_gemm_bf16_ag launch (pair kernel)");
   }
   const int tiles = ((M + BM - 1) / BM) * tiles_n;
   int gemm_ctas = sms - copy_ctas;

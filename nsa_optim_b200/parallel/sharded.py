@@ -274,7 +274,7 @@ class ShardedModel(nn.Module):
             u.shard = new_shard
             u.grad_stage = arena.view(u.off_grad, W * u.shard_size, torch.float32)
             u.ch_shard, u.ch_grad, u.ch_done = 3 * i, 3 * i + 1, 3 * i + 2
-            u.chunks_per_shard = max(1, min(16, (u.shard_size * es) // (1 << 20)))
+            u.chunks_per_shard = max(1, min(1024, (u.shard_size * es) // (256 << 10)))
             u.chunk_flags = torch.zeros(W * u.chunks_per_shard, dtype=torch.int32, device=u.device)
             u.rs_partial = torch.zeros(symm.reduce_scatter_parts(), dtype=torch.float32, device=u.device)
             u._build_pieces()

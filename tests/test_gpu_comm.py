@@ -82,9 +82,14 @@ def test_rs_adamw8bit_matches_unfused(native):
     assert (sa[0] == sb[0]).float().mean() > 0.99 and (sa[2] == sb[2]).float().mean() > 0.99
 
 
-def test_gemm_fused_allgather(native):
+@pytest.mark.parametrize("which,M", [("pair", 700), ("pair", 4096), ("single", 700)])
+def test_gemm_fused_allgather(native, which, M):
+    """Both GEMM kernels can gather their own B operand: the CTA-pair kernel copies with the idle
+    MMA warp of every odd CTA and sweeps the tiles shard by shard, the single-CTA kernel sets copy
+    CTAs aside.  Ranks are emulated inside ONE launch here (copy role and consumers are parts of the
+    same resident grid), so nothing waits on another launch."""
     from nsa_optim_b200.parallel import symm
-    K, N, M = 256, 1000 - 1000 % 8, 700
+    K, N = 256, 1000 - 1000 % 8
     w_off = 4096                                  # weight starts inside shard 0, spans several shards
     total = 4096 + N * K + 8192
     S = -(-total // (W * 256)) * 256
@@ -98,12 +103,16 @@ def test_gemm_fused_allgather(native):
     x = torch.randn(M, K, device="cuda").bfloat16()
     ref = x.float() @ unit[w_off:w_off + N * K].view(N, K).float().t()
     cps = 3
-    for r, a in enumerate(arenas):
-        full = torch.zeros(W * S, dtype=torch.bfloat16, device="cuda")
-        flags = torch.zeros(W * cps, dtype=torch.int32, device="cuda")
-        y = symm.gemm_all_gather(a, x, full, off_sh, S, w_off, N, flags, cps, None, 1, copy_ctas=8)
-        assert torch.equal(full, unit)
-        assert (y.float() - ref).abs().max().item() <= 1e-2 * ref.abs().max().item() + 1e-2
+    native.gemm_select(which)
+    try:
+        for r, a in enumerate(arenas):
+            full = torch.zeros(W * S, dtype=torch.bfloat16, device="cuda")
+            flags = torch.zeros(W * cps, dtype=torch.int32, device="cuda")
+            y = symm.gemm_all_gather(a, x, full, off_sh, S, w_off, N, flags, cps, None, 1, copy_ctas=8)
+            assert torch.equal(full, unit)
+            assert (y.float() - ref).abs().max().item() <= 1e-2 * ref.abs().max().item() + 1e-2
+    finally:
+        native.gemm_select("default")
 
 
 def test_wait_times_out_with_status_not_hang(native):
