@@ -238,20 +238,30 @@ def bench_comm(iters: int, world: int = 4, shard_mb: int = 32) -> List[Dict]:
     parts = torch.zeros(symm.reduce_scatter_parts(), device="cuda")
     ms = time_ms(lambda: symm.reduce_scatter(a0, off_g, gs, 1.0 / W, True, 0, 1, parts), iters)
     rows.append(_bw_row(f"p2p reduce_scatter+scale+sumsq W={W} (emulated)", "native", ms, (W + 2.0) * S * 4))
-    M, K = 16384, 2048
+    M, K = 65536, 2048
     N = (W * S - 4096) // K // 8 * 8
     N = min(N, 8512)
-    cps = 16
+    cps = max(1, min(1024, (S * 2) // (256 << 10)))
     x = torch.randn(M, K, device="cuda").bfloat16()
-    epoch = [1]
+    nat = ops.native_module()
+    symm.all_gather(a0, off_sh, S * 2, full, 0, 1)
+    w_view = full[4096:4096 + N * K].view(N, K)
+    flops = 2.0 * M * N * K
+    ms = time_ms(lambda: nat.gemm(x, w_view, False, False), iters)
+    rows.append({"op": f"plain gemm {M}x{N}x{K} (unit already gathered)", "backend": "native", "ms": ms, "tflops": flops / ms / 1e9})
+    for which in ("pair", "single"):
+        nat.gemm_select(which)
 
-    def fused():
-        flags = torch.zeros(W * cps, dtype=torch.int32, device="cuda")
-        symm.gemm_all_gather(a0, x, full, off_sh, S, 4096, N, flags, cps, 0, 1)
-    ms = time_ms(fused, iters)
-    rows.append({"op": f"gemm + fused all_gather {M}x{N}x{K} W={W} (emulated)", "backend": "native", "ms": ms,
-                 "tflops": 2.0 * M * N * K / ms / 1e9, "frac_of_peak": 2.0 * M * N * K / ms / 1e9 / pk["bf16_tflops"],
-                 "gathered_mb": W * S * 2 / 2**20})
+        def fused():
+            flags = torch.zeros(W * cps, dtype=torch.int32, device="cuda")
+            symm.gemm_all_gather(a0, x, full, off_sh, S, 4096, N, flags, cps, 0, 1)
+        try:
+            ms = time_ms(fused, iters)
+        finally:
+            nat.gemm_select("default")
+        rows.append({"op": f"gemm + fused all_gather {M}x{N}x{K} W={W} (emulated, {which} kernel)", "backend": "native", "ms": ms,
+                     "tflops": flops / ms / 1e9, "frac_of_peak": flops / ms / 1e9 / pk["bf16_tflops"],
+                     "gathered_mb": W * S * 2 / 2**20})
     return rows
 
 

@@ -54,6 +54,7 @@ struct AgFuse {
   long long max_cycles;
   int copy_ctas;
   int n_rot;                    // rotation of the N-block order
+  int w_lo, w_hi, w_start;      // chunk ids (shard-major numbering) that hold B, and the one the sweep needs first
 };
 
 struct GemmParams {
@@ -452,18 +453,23 @@ __device__ __forceinline__ void tile_coords_nmajor(int t, int tiles_m, int tiles
 }  // namespace pair
 
 // Copy role of the fused all-gather in the CTA-pair kernel: the MMA warp of the odd CTA of each pair
-// has nothing else to do (the even CTA issues for both), so it pulls the peers' shards, 16 loads of
+// has nothing else to do (the even CTA issues for both), so it pulls the peers' shards, 32 loads of
 // 16 bytes in flight per lane, into the local gathered buffer and publishes one flag per chunk.
-// Jobs are numbered shard-major in pull order, so the shards complete in the order in which the
-// tile sweep needs them.  No SM is taken away from the GEMM.
+// No SM is taken away from the GEMM.
 __device__ void ag_copy_warp(const AgFuse& ag, int cluster, int n_clusters, KernelStatus* status) {
   const int lane = threadIdx.x & 31;
   const int jobs = ag.W * ag.chunks_per_shard;
-  int ready_peer = -1;
+  const int n_w = ag.w_hi - ag.w_lo + 1;
+  unsigned ready_mask = 1u << ag.rank;          // peers whose "shard ready" flag has been seen
   for (int q = cluster; q < jobs; q += n_clusters) {
-    const int k = q / ag.chunks_per_shard, c = q - k * ag.chunks_per_shard;
-    const int pr = (ag.rank + k) % ag.W;
-    if (pr != ag.rank && pr != ready_peer) {
+    // Order: first the chunks that hold B, starting with the one the tile sweep needs first and
+    // wrapping around inside B's range; then the rest of the unit.  (On a rank whose own shard
+    // holds none of B, the GEMM can only start once B's first rows have crossed the link.)
+    int id;
+    if (q < n_w) id = ag.w_lo + (ag.w_start - ag.w_lo + q) % n_w;
+    else id = (ag.w_hi + 1 + (q - n_w)) % jobs;
+    const int pr = id / ag.chunks_per_shard, c = id - pr * ag.chunks_per_shard;
+    if (!((ready_mask >> pr) & 1u)) {
       int ok = 1;
       if (lane == 0 && ag.peer_flags != nullptr && !spin_until(ag.peer_flags + pr, ag.epoch, ag.max_cycles, true)) {
         status_report(status, STATUS_TIMEOUT_PEER_FLAG, pr, (int)ag.epoch);
@@ -471,13 +477,13 @@ __device__ void ag_copy_warp(const AgFuse& ag, int cluster, int n_clusters, Kern
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) return;
-      ready_peer = pr;
+      ready_mask |= 1u << pr;
     }
     const long lo = static_cast<long>(c) * ag.chunk_vec;
     const long hi = lo + ag.chunk_vec < ag.shard_vec ? lo + ag.chunk_vec : ag.shard_vec;
     const uint4* src = ag.shards[pr];
     uint4* dst = ag.full + static_cast<long>(pr) * ag.shard_vec;
-    constexpr int U = 16;
+    constexpr int U = 32;
     for (long i0 = lo + lane; i0 < hi; i0 += 32L * U) {
       uint4 v[U];
 #pragma unroll
@@ -567,25 +573,39 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
+      int seen_group = -1;                         // tile-column group whose chunk flags have been awaited
       for (int t = cluster; t < num_tiles && ok; t += n_clusters) {
         int mb, nb;
         coords(t, mb, nb);
         const int m0 = mb * 2 * BM + static_cast<int>(rank) * BM;
         const int n0 = nb * BN + static_cast<int>(rank) * BNH;
-        if (p.ag.enabled && n0 < p.N) {
-          // this CTA's B rows [n0, n1) live at 16-byte units [g_lo, g_hi] of the gathered buffer
-          const int n1 = n0 + BNH < p.N ? n0 + BNH : p.N;
-          const long g_lo = p.ag.b_vec_offset + static_cast<long>(n0) * p.ldb / 8;
-          const long g_hi = p.ag.b_vec_offset + static_cast<long>(n1) * p.ldb / 8 - 1;
-          const int id_lo = ag_chunk_id(p.ag, g_lo), id_hi = ag_chunk_id(p.ag, g_hi);
-          for (int id = id_lo; id <= id_hi && ok; ++id)
-            if (!spin_until(p.ag.chunk_flags + id, p.ag.epoch, p.ag.max_cycles, false)) {
-              *abort_flag = 1;
-              status_report(p.status, STATUS_TIMEOUT_LOCAL_FLAG, blockIdx.x, id);
-              ok = false;
+        if (p.ag.enabled) {
+          // The sweep stays inside one group of GROUP_N tile columns for tiles_m tile rows, so the
+          // flags of the chunks that hold this CTA's B rows of the whole group are awaited once,
+          // when the group is entered: an acquire load is an L2 round trip on the producer's
+          // critical path, far too slow to repeat for every tile.
+          const int group = t / (pair::GROUP_N * tiles_m);
+          if (group != seen_group) {
+            const int first_n = group * pair::GROUP_N;
+            const int gn = min(pair::GROUP_N, tiles_n - first_n);
+            for (int j = 0; j < gn && ok; ++j) {
+              const int r0 = ((first_n + j + p.ag.n_rot) % tiles_n) * BN + static_cast<int>(rank) * BNH;
+              if (r0 >= p.N) continue;
+              const int r1 = r0 + BNH < p.N ? r0 + BNH : p.N;
+              const long g_lo = p.ag.b_vec_offset + static_cast<long>(r0) * p.ldb / 8;
+              const long g_hi = p.ag.b_vec_offset + static_cast<long>(r1) * p.ldb / 8 - 1;
+              const int id_lo = ag_chunk_id(p.ag, g_lo), id_hi = ag_chunk_id(p.ag, g_hi);
+              for (int id = id_lo; id <= id_hi && ok; ++id)
+                if (!spin_until(p.ag.chunk_flags + id, p.ag.epoch, p.ag.max_cycles, false)) {
+                  *abort_flag = 1;
+                  status_report(p.status, STATUS_TIMEOUT_LOCAL_FLAG, blockIdx.x, id);
+                  ok = false;
+                }
             }
-          if (!ok) break;
-          asm volatile("fence.proxy.async;" ::: "memory");
+            if (!ok) break;
+            asm volatile("fence.proxy.async;" ::: "memory");
+            seen_group = group;
+          }
         }
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
@@ -875,6 +895,7 @@ extern "C" int nsa_gemm_bf16_ag(const void* A, void* C, int M, int N, int K, int
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(Bp) & 15) || (lda & 7) || (K & 7) ||
       (shard_elems & 7) || (b_elem_offset & 7))
     return nsa::fail(NSA_ERR_ALIGNMENT, "nsa_gemm_bf16_ag: operands need 16-byte alignment");
+  if (W < 1 || W > 32 || chunks_per_shard < 1) return nsa::fail(NSA_ERR_SHAPE, "nsa_gemm_bf16_ag: 1 to 32 ranks, at least one chunk per shard");
   const bool pairk = use_pair_kernel() && M > 128;
   CUtensorMap ta, tb, tc;
   int rc;
@@ -912,6 +933,14 @@ extern "C" int nsa_gemm_bf16_ag(const void* A, void* C, int M, int N, int K, int
       ag.n_rot = static_cast<int>((row + BN - 1) / BN) % tiles_n;
       break;
     }
+  }
+  {
+    const long cv = ag.chunk_vec;
+    auto chunk_of = [&](long g) { const long pidx = g / shard_vec; return static_cast<int>(pidx * chunks_per_shard + (g - pidx * shard_vec) / cv); };
+    ag.w_lo = chunk_of(b_lo);
+    ag.w_hi = chunk_of(b_hi - 1);
+    const long first_row = static_cast<long>(ag.n_rot) * BN;                  // the sweep starts at this row of B
+    ag.w_start = chunk_of(b_lo + (first_row < N ? first_row : 0) * K / 8);
   }
   if (pairk) {
     // CTA-pair kernel: the copy role runs in the otherwise idle MMA warp of every odd CTA, the tile

@@ -177,12 +177,14 @@ class _UnitFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_out: Tensor):
         runtime, unit = ctx.runtime, ctx.unit
-        runtime._pre_backward(unit)
-        if ctx.local is None:
+        recompute = ctx.local is None
+        runtime._pre_backward(unit, recompute)
+        if recompute:
             (hidden,) = ctx.saved_tensors
             with torch.enable_grad():
                 h = hidden.detach().requires_grad_(True)
                 out_g = unit.module(h, *ctx.args)
+            runtime._after_recompute(unit)
         else:
             h, out_g = ctx.local
             ctx.local = None
@@ -455,12 +457,25 @@ class ShardedModel(nn.Module):
         if self.strategy == ShardingStrategy.FULL_SHARD:
             unit.free_full()
 
-    def _pre_backward(self, unit: FlatUnit) -> None:
-        self._gather(unit)
+    def _pre_backward(self, unit: FlatUnit, recompute: bool = False) -> None:
+        """Re-gather for the backward pass.  A block that recomputes its forward first lets the
+        recompute's first matmul gather the unit (the same fused kernel as in the forward pass); a
+        block that kept its activations needs the weights for dX = dY W, where a shard covers a slice
+        of the reduction dimension and no tile can start on local data alone, so its gather runs as
+        the stand-alone kernel on the communication stream, issued one block ahead."""
+        if recompute and self._lazy():
+            self._gather(unit, lazy=True)
+        else:
+            self._gather(unit)
         prv = self._neighbour(unit, -1)
-        if prv is not None and self.strategy == ShardingStrategy.FULL_SHARD:
+        if prv is not None and self.strategy == ShardingStrategy.FULL_SHARD and not (self._lazy() and self._checkpointed(prv)):
             self._gather(prv)
         self._wait_ready(unit)
+
+    def _after_recompute(self, unit: FlatUnit) -> None:
+        if self.arena is not None:
+            from ..ops import native
+            native.flush_pending_gather()        # nothing in the recompute consumed the deferred gather
 
     def _post_backward(self, unit: FlatUnit) -> None:
         self._reduce_grads(unit)
