@@ -89,6 +89,10 @@ class ModelConfig:
     # additions: compressed branch geometry and an explicit head width
     nsa_compress_block: int = 32
     nsa_compress_stride: int = 16
+    # how the selected branch picks its blocks: "compressed" = from the compressed branch's
+    # attention probabilities (three branches); "learned" = the reference module's scorer, a
+    # projection k_compress of queries and block-mean keys (two branches: selected + window)
+    nsa_block_scorer: str = "compressed"
     head_dim: Optional[int] = None
     gradient_checkpointing: bool = False
 

@@ -16,6 +16,8 @@ attention, plus sliding window, combined by per-head sigmoid gates) runs end to 
 """
 from __future__ import annotations
 
+import math
+
 from typing import Optional, Tuple
 
 import torch
@@ -90,9 +92,15 @@ class NativeSparseAttention(DenseAttention):
         self.num_selected_blocks = config.nsa_num_selected_blocks
         self.compress_block = config.nsa_compress_block
         self.compress_stride = config.nsa_compress_stride
-        # reference-compatible parameter: kept so its checkpoints load; the compressed branch
-        # pools keys directly and does not use it.
+        # The reference module's block scorer (models/transformer.py:172-214): a head_dim -> head_dim/4
+        # projection applied to queries and to block-mean keys.  Its output only feeds a top-k, so it
+        # receives no gradient there either: a persistent buffer, loaded from reference checkpoints.
+        # With ``nsa_block_scorer="learned"`` it chooses the blocks (two branches, as the reference
+        # module); by default the compressed branch's probabilities choose them (three branches).
         self.k_compress = _FrozenWeight(max(1, self.head_dim // 4), self.head_dim)
+        self.block_scorer = getattr(config, "nsa_block_scorer", "compressed")
+        if self.block_scorer == "learned":
+            nn.init.normal_(self.k_compress.weight, std=self.head_dim ** -0.5)
         self.gate_cmp = Linear(self.hidden_size, self.num_heads)
         self.gate_slc = Linear(self.hidden_size, self.num_heads)
         self.gate_swa = Linear(self.hidden_size, self.num_heads)
@@ -101,6 +109,38 @@ class NativeSparseAttention(DenseAttention):
         w = torch.cat([self.gate_cmp.weight, self.gate_slc.weight, self.gate_swa.weight], 0)
         g = torch.sigmoid(ops.linear(x, w).float()).to(x.dtype)
         return g.split(self.num_heads, dim=-1)
+
+    @torch.no_grad()
+    def learned_block_indices(self, q: Tensor, k: Tensor) -> Tensor:
+        """(B, Hkv, T, n) int32 block lists from the learned scorer: score(t, block) = sum over the
+        GQA group's heads of k_compress(q_t) . mean over the block of k_compress(k), divided by
+        sqrt(head_dim / 4); blocks after the query's own are masked; top-n, ascending, -1 where a
+        query sees fewer blocks.  (The reference scores per query head after repeating K; its kernel
+        shares one list per KV head, so the group's scores are summed here.)"""
+        B, T, Hq, D = q.shape
+        Hkv, G, bs = self.num_kv_heads, self.num_kv_groups, self.block_size
+        w = self.k_compress.weight.to(q.dtype)
+        qc = torch.matmul(q, w.t()).view(B, T, Hkv, G, -1).sum(3).float()                 # B,T,Hkv,d4
+        kc = torch.matmul(k, w.t()).float()
+        nS = -(-T // bs)
+        pad = nS * bs - T
+        if pad:
+            kc = torch.nn.functional.pad(kc, (0, 0, 0, 0, 0, pad))
+        kbm = kc.view(B, nS, bs, Hkv, -1).mean(2)                                         # B,nS,Hkv,d4
+        n = min(self.num_selected_blocks, nS)
+        own = torch.arange(T, device=q.device) // bs
+        out = torch.empty(B, Hkv, T, self.num_selected_blocks, dtype=torch.int32, device=q.device)
+        for s0 in range(0, T, 8192):                                                      # bound the score matrix
+            s1 = min(T, s0 + 8192)
+            sc = torch.einsum("bthd,bnhd->bhtn", qc[:, s0:s1], kbm) / math.sqrt(kbm.shape[-1])
+            vis = torch.arange(nS, device=q.device)[None, :] <= own[s0:s1, None]
+            sc = sc.masked_fill(~vis, float("-inf"))
+            top, ind = torch.topk(sc, n, dim=-1)
+            ind = ind.masked_fill(top == float("-inf"), nS + 1).sort(-1).values
+            ind = ind.masked_fill(ind > nS, -1)
+            out[:, :, s0:s1, :n] = ind.to(torch.int32)
+            out[:, :, s0:s1, n:] = -1
+        return out
 
     def forward(self, hidden_states, attention_mask=None, position_ids=None,
                 past_key_value=None, use_cache: bool = False):
@@ -111,6 +151,11 @@ class NativeSparseAttention(DenseAttention):
             k = torch.cat([past_key_value[0], k], dim=1)
             v = torch.cat([past_key_value[1], v], dim=1)
             o = ops.attention(q, k, v, causal=True)
+        elif self.block_scorer == "learned":
+            _, g_slc, g_swa = self.gates(hidden_states)
+            idx = self.learned_block_indices(q, k)
+            o = ops.nsa_attention_indexed(q, k, v, idx, g_slc, g_swa, sel_block=self.block_size,
+                                          window=self.window_size)
         else:
             g_cmp, g_slc, g_swa = self.gates(hidden_states)
             o = ops.nsa_attention(q, k, v, g_cmp, g_slc, g_swa,

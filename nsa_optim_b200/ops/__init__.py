@@ -204,6 +204,13 @@ def nsa_attention(q, k, v, g_cmp, g_slc, g_swa, cmp_block=32, cmp_stride=16, sel
                                     sel_block, top_n, window, scale)
 
 
+def nsa_attention_indexed(q, k, v, idx, g_slc, g_swa, sel_block=64, window=512, scale=None) -> Tensor:
+    """Two-branch sparse attention (selected blocks ``idx`` (B, Hkv, T, n) + sliding window)."""
+    if _use_native(q, "nsa_attention") and _library(q) is None:
+        return native_module().nsa_attention_indexed(q, k, v, idx, g_slc, g_swa, sel_block, window, scale)
+    return torch_impl.nsa_attention_indexed(q, k, v, idx, g_slc, g_swa, sel_block, window, scale)
+
+
 def causal_conv1d(x: Tensor, weight: Tensor, bias: Optional[Tensor], activation: bool = True) -> Tensor:
     if _use_native(x, "causal_conv1d"):
         return native_module().causal_conv1d(x, weight, bias, activation)

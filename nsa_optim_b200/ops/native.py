@@ -1045,6 +1045,20 @@ def selected_attention(q, k, v, idx, scale=None):
     return _Attn.apply(q, k, v, True, 0, float(scale), 1, 0, tiles)[0]
 
 
+def nsa_attention_indexed(q, k, v, idx, g_slc, g_swa, sel_block=64, window=512, scale=None):
+    """Selected-block attention over caller-given block lists ``idx`` (B, Hkv, T, n) plus the sliding
+    window, gated: both branches on the tcgen05 attention kernels."""
+    B, T, Hq, D = q.shape
+    G = Hq // k.shape[2]
+    if not _attn_ok(q, k) or sel_block != 64 or G < 2 or G > 32:
+        _fallback("nsa_attention_indexed")
+        return torch_impl.nsa_attention_indexed(q, k, v, idx, g_slc, g_swa, sel_block, window, scale)
+    scale = D ** -0.5 if scale is None else scale
+    o_slc = selected_attention(q, k, v, idx, scale)
+    o_swa = _Attn.apply(q, k, v, True, int(window), float(scale), 1, 0, None)[0]
+    return g_slc.unsqueeze(-1) * o_slc + g_swa.unsqueeze(-1) * o_swa
+
+
 def nsa_importance(q, k_cmp, L_cmp, nS, stride, block, scale):
     B, T, Hq, D = q.shape
     Hkv = k_cmp.shape[2]

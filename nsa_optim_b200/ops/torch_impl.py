@@ -104,6 +104,38 @@ def nsa_compress(x: Tensor, block: int, stride: int) -> Tensor:
     return y.to(x.dtype).reshape(B, H, D, -1).permute(0, 3, 1, 2)
 
 
+def selected_attention(q: Tensor, k: Tensor, v: Tensor, idx: Tensor, sel_block: int = 64,
+                       scale: Optional[float] = None, q_chunk: int = 1024) -> Tensor:
+    """Causal attention of every query over its own list of key blocks.  q (B,T,Hq,D), k/v (B,T,Hkv,D),
+    idx (B,Hkv,T,n) block numbers (-1 = unused); the heads of a GQA group share a list."""
+    B, T, Hq, D = q.shape
+    Hkv = k.shape[2]
+    G = Hq // Hkv
+    scale = D ** -0.5 if scale is None else scale
+    kh, vh = k.permute(0, 2, 1, 3).float(), v.permute(0, 2, 1, 3).float()
+    blk = torch.arange(T, device=q.device) // sel_block
+    outs = []
+    for s0 in range(0, T, q_chunk):
+        s1 = min(T, s0 + q_chunk)
+        qc = q[:, s0:s1].reshape(B, s1 - s0, Hkv, G, D).permute(0, 2, 3, 1, 4).float()      # B,Hkv,G,tq,D
+        sc = torch.matmul(qc, kh[:, :, None].transpose(-1, -2)) * scale                     # B,Hkv,G,tq,T
+        chosen = (idx[:, :, s0:s1, :, None] == blk[None, None, None, None, :]).any(3)       # B,Hkv,tq,T
+        causal = torch.arange(T, device=q.device)[None, :] <= torch.arange(s0, s1, device=q.device)[:, None]
+        sc = sc.masked_fill(~(chosen & causal)[:, :, None], float("-inf"))
+        p = torch.nan_to_num(torch.softmax(sc, -1), nan=0.0)
+        outs.append(torch.matmul(p, vh[:, :, None]).permute(0, 3, 1, 2, 4).reshape(B, s1 - s0, Hq, D))
+    return torch.cat(outs, 1).to(q.dtype)
+
+
+def nsa_attention_indexed(q: Tensor, k: Tensor, v: Tensor, idx: Tensor, g_slc: Tensor, g_swa: Tensor,
+                          sel_block: int = 64, window: int = 512, scale: Optional[float] = None) -> Tensor:
+    """Selected-block attention over given block lists plus sliding-window attention, combined by
+    per-(token, head) gates: the two-branch form of the reference's NativeSparseAttention module."""
+    o_slc = selected_attention(q, k, v, idx, sel_block, scale)
+    o_swa = attention(q, k, v, True, window, scale)
+    return g_slc.unsqueeze(-1) * o_slc + g_swa.unsqueeze(-1) * o_swa
+
+
 def _importance_band(cmp_block: int, cmp_stride: int, sel_block: int):
     """Offsets and weights of the compressed blocks that overlap selection block j, relative
     to ``j * sel_block / cmp_stride``."""

@@ -106,6 +106,9 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--deltanet_num_heads", type=int, default=None)
     g.add_argument("--nsa_compress_block", type=int, default=32)
     g.add_argument("--nsa_compress_stride", type=int, default=16)
+    g.add_argument("--nsa_block_scorer", type=str, default="compressed", choices=["compressed", "learned"],
+                   help="block selection of sparse attention: from the compressed branch (default) or the "
+                        "reference module's learned k_compress scorer (selected + window branches only)")
     g = p.add_argument_group("runtime")
     g.add_argument("--synthetic_data", action="store_true", help="uniform random token ids (seeded)")
     g.add_argument("--seed", type=int, default=0)
@@ -202,7 +205,8 @@ def build_model(cfg: TrainingConfig, args: argparse.Namespace, verbose: bool = T
                               num_attention_heads=args.num_heads, num_key_value_heads=args.num_kv_heads,
                               head_dim=args.head_dim, tie_word_embeddings=args.tie_embeddings or None,
                               nsa_compress_block=args.nsa_compress_block,
-                              nsa_compress_stride=args.nsa_compress_stride)
+                              nsa_compress_stride=args.nsa_compress_stride,
+                              nsa_block_scorer=args.nsa_block_scorer)
         model = create_model(mc, kernel_type)
     if args.ce_kernel_type is not None:
         from .models.kernels import create_cross_entropy_loss

@@ -151,3 +151,80 @@ def test_block_selection_kernel_matches_topk(native, T, top_n):
     # forced blocks first, never a future block
     t = torch.arange(T, device="cuda")
     assert (got[..., 0] == 0).all() and (got.max(-1).values <= (t // 64)).all()
+
+
+def _chunked_fp32_attention(q, k, v, causal=True, q_chunk=2048):
+    """fp32 softmax attention evaluated per query chunk (no T x T matrix at once)."""
+    B, T, Hq, D = q.shape
+    G = Hq // k.shape[2]
+    kh = k.float().permute(0, 2, 1, 3)[:, :, None]            # B,Hkv,1,T,D
+    vh = v.float().permute(0, 2, 1, 3)[:, :, None]
+    outs = []
+    for s0 in range(0, T, q_chunk):
+        s1 = min(T, s0 + q_chunk)
+        qc = q[:, s0:s1].float().reshape(B, s1 - s0, -1, G, D).permute(0, 2, 3, 1, 4)
+        sc = torch.matmul(qc, kh[:, :, :, :s1].transpose(-1, -2)) * D ** -0.5
+        vis = torch.arange(s1, device=q.device)[None, :] <= torch.arange(s0, s1, device=q.device)[:, None]
+        sc = sc.masked_fill(~vis, float("-inf"))
+        outs.append(torch.matmul(torch.softmax(sc, -1), vh[:, :, :, :s1]).permute(0, 3, 1, 2, 4).reshape(B, s1 - s0, Hq, D))
+    return torch.cat(outs, 1)
+
+
+def test_dense_causal_at_16k_against_chunked_fp32(native):
+    """Long rows: the online-softmax rescale chain is 256 visits long at T = 16384."""
+    B, T, Hq, Hkv, D = 1, 16384, 32, 2, 128
+    q, k, v = mk(B, T, Hq, Hkv, D)
+    ql, kl, vl = (t.clone().requires_grad_() for t in (q, k, v))
+    o = native.attention(ql, kl, vl, True, 0)
+    do = torch.randn_like(o)
+    o.backward(do)
+    qr, kr, vr = (t.float().clone().requires_grad_() for t in (q, k, v))
+    o_ref = _chunked_fp32_attention(qr, kr, vr)
+    o_ref.backward(do.float())
+    close(o, o_ref, "out", rtol=2e-2, atol=1e-2)
+    # late rows average over thousands of keys: compare them on their own scale as well
+    close(o[:, -2048:], o_ref[:, -2048:], "late rows", rtol=3e-2, atol=2e-3)
+    for name, a, b in (("dq", ql, qr), ("dk", kl, kr), ("dv", vl, vr)):
+        close(a.grad, b.grad, name)
+
+
+def test_attention_forward_and_backward_repeat_bit_for_bit(native):
+    """Same inputs twice -> the same bits, forward and the split (dQ pass + key-stationary dK/dV pass)
+    backward: no reduction in these kernels depends on scheduling order."""
+    q, k, v = mk(1, 2048, 32, 2, 128)
+    do = torch.randn(1, 2048, 32, 128, device="cuda").bfloat16()
+    results = []
+    for _ in range(2):
+        ql, kl, vl = (t.clone().requires_grad_() for t in (q, k, v))
+        o = native.attention(ql, kl, vl, True, 0)
+        o.backward(do)
+        results.append((o.detach(), ql.grad, kl.grad, vl.grad))
+    for a, b in zip(*results):
+        assert torch.equal(a, b)
+    nS = 2048 // 64
+    t = torch.arange(2048, device="cuda")
+    own = (t // 64)[None, None, :, None]
+    rnd = torch.randint(0, nS, (1, 2, 2048, 7), device="cuda")
+    idx = torch.cat([own.expand(1, 2, 2048, 1), torch.where(rnd <= own, rnd, -torch.ones_like(rnd))], -1).to(torch.int32)
+    results = []
+    for _ in range(2):
+        ql, kl, vl = (t_.clone().requires_grad_() for t_ in (q, k, v))
+        o = native.selected_attention(ql, kl, vl, idx)
+        o.backward(do)
+        results.append((o.detach(), ql.grad, kl.grad, vl.grad))
+    for a, b in zip(*results):
+        assert torch.equal(a, b)
+
+
+def test_two_branch_nsa_over_given_block_lists(native):
+    """The reference module's form: selected blocks chosen outside the attention op + sliding window."""
+    B, T, Hq, Hkv, D, top_n = 1, 700, 32, 2, 128, 6
+    q, k, v = mk(B, T, Hq, Hkv, D)
+    nS = -(-T // 64)
+    own = (torch.arange(T, device="cuda") // 64)[None, None, :, None]
+    rnd = torch.randint(0, nS, (B, Hkv, T, top_n - 1), device="cuda")
+    idx = torch.cat([own.expand(B, Hkv, T, 1), torch.where(rnd <= own, rnd, -torch.ones_like(rnd))], -1).to(torch.int32)
+    g1 = torch.rand(B, T, Hq, device="cuda").bfloat16()
+    g2 = torch.rand(B, T, Hq, device="cuda").bfloat16()
+    run_pair(lambda q, k, v: native.nsa_attention_indexed(q, k, v, idx, g1, g2, 64, 128),
+             lambda q, k, v: torch_impl.nsa_attention_indexed(q, k, v, idx, g1.float(), g2.float(), 64, 128), (q, k, v))

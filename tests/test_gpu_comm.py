@@ -44,6 +44,11 @@ def test_signal_allgather_reduce_scatter(native):
         want = 1.0 + 0.25 * gsum[r * S:(r + 1) * S]
         assert torch.allclose(gs, want, atol=1e-5)
         assert torch.allclose(parts.sum(), want.pow(2).sum(), rtol=1e-4)
+        # fixed rank order inside the kernel: a repeat gives the same bits, shard and partial sums alike
+        gs2 = torch.ones(S, device="cuda")
+        parts2 = torch.zeros(symm.reduce_scatter_parts(), device="cuda")
+        symm.reduce_scatter(a, off_g, gs2, 0.25, True, 0, 7, parts2)
+        assert torch.equal(gs, gs2) and torch.equal(parts, parts2)
 
 
 def test_rs_adamw8bit_matches_unfused(native):

@@ -198,3 +198,35 @@ def test_kv_heads_resolve_to_a_divisor_of_the_query_heads():
     _, loss, _ = m(input_ids=ids, labels=ids)
     loss.backward()
     assert m.layers[0].k_proj.weight.shape[0] == 4 * 16
+
+
+def test_learned_block_scorer_mode_selects_causal_blocks_and_trains():
+    """``nsa_block_scorer="learned"``: the reference module's k_compress scorer picks the blocks and
+    the selected + window branches run on them (reference: models/transformer.py:172-268)."""
+    from nsa_optim_b200.ops import torch_impl
+    cfg = small_cfg(AttentionType.NSA, nsa_block_scorer="learned")
+    m = create_model(cfg)
+    attn = m.layers[0].self_attn
+    assert attn.block_scorer == "learned" and float(attn.k_compress.weight.abs().sum()) > 0
+    assert "layers.0.self_attn.k_compress.weight" in m.state_dict()
+    B, T = 2, 40
+    q = torch.randn(B, T, attn.num_heads, attn.head_dim)
+    k = torch.randn(B, T, attn.num_kv_heads, attn.head_dim)
+    idx = attn.learned_block_indices(q, k)
+    assert idx.shape == (B, attn.num_kv_heads, T, cfg.nsa_num_selected_blocks) and idx.dtype == torch.int32
+    own = (torch.arange(T) // cfg.nsa_block_size)[None, None, :, None]
+    assert bool(((idx <= own) & (idx >= -1)).all())                         # never a block after the query's own
+    first = idx[:, :, : cfg.nsa_block_size]                                 # queries of block 0 see exactly one block
+    assert bool((first[..., 0] == 0).all()) and bool((first[..., 1:] == -1).all())
+    srt = idx.masked_fill(idx < 0, 10 ** 6).sort(-1).values
+    assert bool((srt[..., 1:] > srt[..., :-1]).logical_or(srt[..., 1:] == 10 ** 6).all())   # ascending, no repeats
+    # with every visible block selected the selected branch is plain causal attention
+    nS = -(-T // cfg.nsa_block_size)
+    every = torch.arange(nS, dtype=torch.int32).expand(B, attn.num_kv_heads, T, nS)
+    v = torch.randn(B, T, attn.num_kv_heads, attn.head_dim)
+    full = torch_impl.selected_attention(q, k, v, every, cfg.nsa_block_size)
+    assert torch.allclose(full, torch_impl.attention(q, k, v, True, 0, None), atol=1e-5)
+    ids = torch.randint(0, 100, (2, 32))
+    _, loss, _ = m(ids, labels=ids)
+    loss.backward()
+    assert all(p.grad is not None for n, p in m.named_parameters() if "gate_cmp" not in n)
