@@ -5,8 +5,11 @@
 Each ``.cu`` file is one translation unit (no relocatable device code is needed: kernels
 receive every pointer they use as an argument).  Objects go to ``ops/_build/``; the shared
 library is written beside this file so that it is found by ``ops/native.py``.  nvcc
-cross-compiles without a GPU.  ``--debug`` adds ``-DNSA_DEBUG_BOUNDS`` (kernels check
-indices against extents and record a status code instead of accessing out of range).
+cross-compiles without a GPU.  ``--debug`` builds ``libnsa_b200_debug.so`` with
+``-DNSA_DEBUG_BOUNDS``: indices that kernels read from tensors (token ids, labels, selected block
+numbers) are checked where they are used and a bad one is recorded in the status block
+(code 302) while the kernel continues with the clamped value; set ``NSA_B200_LIB`` to that file to
+run a program on it.
 """
 from __future__ import annotations
 
@@ -43,9 +46,9 @@ def _newest_header() -> float:
                 if f.endswith((".cuh", ".h"))), default=0.0)
 
 
-def _compile(nvcc: str, name: str, extra: List[str], verbose: bool) -> str:
+def _compile(nvcc: str, name: str, extra: List[str], verbose: bool, obj_dir: str = OBJ) -> str:
     src = os.path.join(SRC, name)
-    obj = os.path.join(OBJ, name[:-3] + ".o")
+    obj = os.path.join(obj_dir, name[:-3] + ".o")
     cmd = [nvcc] + ARCH + COMMON + extra + ["-I", SRC, "-c", src, "-o", obj]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
@@ -58,14 +61,22 @@ def _compile(nvcc: str, name: str, extra: List[str], verbose: bool) -> str:
     return obj
 
 
-def build(force: bool = False, verbose: bool = False, debug: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, debug: bool = False, out: str = None,
+          only: List[str] = None) -> str:
+    """Builds the library.  ``debug`` adds -DNSA_DEBUG_BOUNDS; a debug build goes to its own object
+    directory and, unless ``out`` names another file, to ``libnsa_b200_debug.so`` beside the release
+    library (which stays in place).  ``only`` restricts the build to some translation units (a
+    partial library for a test that needs few entry points; ``runtime.cu`` is always included)."""
     nvcc = nvcc_path()
-    os.makedirs(OBJ, exist_ok=True)
+    obj_dir = os.path.join(OBJ, "debug") if debug else OBJ
+    lib = out or (os.path.join(HERE, "libnsa_b200_debug.so") if debug else LIB)
+    os.makedirs(obj_dir, exist_ok=True)
     extra = ["-DNSA_DEBUG_BOUNDS"] if debug else []
     hdr = _newest_header()
     todo, objs = [], []
-    for name in sources():
-        obj = os.path.join(OBJ, name[:-3] + ".o")
+    names = sources() if only is None else sorted(set(only) | {"runtime.cu"})
+    for name in names:
+        obj = os.path.join(obj_dir, name[:-3] + ".o")
         objs.append(obj)
         stale = (force or not os.path.exists(obj)
                  or os.path.getmtime(obj) < max(os.path.getmtime(os.path.join(SRC, name)), hdr))
@@ -73,13 +84,13 @@ def build(force: bool = False, verbose: bool = False, debug: bool = False) -> st
             todo.append(name)
     if todo:
         with cf.ThreadPoolExecutor(max_workers=min(8, len(todo))) as ex:
-            list(ex.map(lambda n: _compile(nvcc, n, extra, verbose), todo))
-    if todo or not os.path.exists(LIB):
-        cmd = [nvcc, "-shared", "-o", LIB] + objs + ["-lcudart"]
+            list(ex.map(lambda n: _compile(nvcc, n, extra, verbose, obj_dir), todo))
+    if todo or not os.path.exists(lib):
+        cmd = [nvcc, "-shared", "-o", lib] + objs + ["-lcudart"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    return LIB
+    return lib
 
 
 def main() -> None:

@@ -2508,7 +2508,7 @@ __global__ void __launch_bounds__(256) attn_delta_kernel(const bf16* __restrict_
 __global__ void __launch_bounds__(128) nsa_union_kernel(const int* __restrict__ idx, int* __restrict__ tile_blocks,
                                                         unsigned long long* __restrict__ tile_masks,
                                                         int* __restrict__ tile_counts, int T, int R, int top_n,
-                                                        int nS, int max_u) {
+                                                        int nS, int max_u, KernelStatus* status) {
   extern __shared__ unsigned int sh[];          // bitmap words, then per-word prefix counts
   const int words = (nS + 31) / 32;
   unsigned int* bitmap = sh;
@@ -2527,6 +2527,7 @@ __global__ void __launch_bounds__(128) nsa_union_kernel(const int* __restrict__ 
     const int tl = i / top_n, t = q0 + tl;
     if (t >= T) continue;
     const int blk = idx[(bh * T + t) * top_n + (i - tl * top_n)];
+    NSA_CHECK_INDEX(blk >= -1 && blk < nS && blk * 64 <= t, status, blk);     // in range and not after the query
     if (blk >= 0 && blk < nS) atomicOr(&bitmap[blk >> 5], 1u << (blk & 31));
   }
   __syncthreads();
@@ -2801,7 +2802,7 @@ extern "C" int nsa_union_blocks(const int* idx, int* tile_blocks, unsigned long 
   if (R > 64) return nsa::fail(NSA_ERR_SHAPE, "union: more than 64 tokens per tile");
   const int words = (nS + 31) / 32;
   const dim3 grid((T + R - 1) / R, B * Hkv);
-  nsa_union_kernel<<<grid, 128, words * 8, st>>>(idx, tile_blocks, tile_masks, tile_counts, T, R, top_n, nS, max_u);
+  nsa_union_kernel<<<grid, 128, words * 8, st>>>(idx, tile_blocks, tile_masks, tile_counts, T, R, top_n, nS, max_u, nsa::status_ptr());
   nsa::count_launch();
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : nsa::fail_cuda(e, "nsa_union_blocks launch");

@@ -1011,12 +1011,14 @@ __global__ void __launch_bounds__(128) conv1d_bwd_kernel(const bf16* __restrict_
 // Embedding
 // ------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) embedding_fwd_kernel(const long* __restrict__ ids, const bf16* __restrict__ w,
-                                                            bf16* __restrict__ y, long n, int d, long vocab) {
+                                                            bf16* __restrict__ y, long n, int d, long vocab,
+                                                            KernelStatus* status) {
   const int d8 = d / 8;
   for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n * d8; i += static_cast<long>(gridDim.x) * blockDim.x) {
     const long tok = i / d8;
     const int v = static_cast<int>(i - tok * d8);
     long id = ids[tok];
+    if (v == 0) NSA_CHECK_INDEX(id >= 0 && id < vocab, status, id);
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
     *reinterpret_cast<uint4*>(y + tok * d + v * 8) = *reinterpret_cast<const uint4*>(w + id * d + v * 8);
   }
@@ -1446,7 +1448,7 @@ extern "C" int nsa_conv1d_bwd(const void* x, const void* w, const void* bias, co
 
 extern "C" int nsa_embedding_fwd(const long* ids, const void* w, void* y, long n, int d, long vocab, cudaStream_t st) {
   if (d % 8) return nsa::fail(NSA_ERR_SHAPE, "embedding: width must be a multiple of 8");
-  embedding_fwd_kernel<<<grid_for(n * (d / 8), 256), 256, 0, st>>>(ids, (const bf16*)w, (bf16*)y, n, d, vocab);
+  embedding_fwd_kernel<<<grid_for(n * (d / 8), 256), 256, 0, st>>>(ids, (const bf16*)w, (bf16*)y, n, d, vocab, nsa::status_ptr());
   nsa::count_launch();
   return 0;
 }

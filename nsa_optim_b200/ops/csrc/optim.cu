@@ -175,12 +175,14 @@ __global__ void sumsq_final_kernel(const float* __restrict__ partial, int parts,
 // overwritten with (softmax - onehot) * (*inv_count) (zeros for ignored rows).
 __global__ void __launch_bounds__(256) cross_entropy_kernel(bf16* __restrict__ logits, const long* __restrict__ labels,
                                                             float* __restrict__ loss_out, const float* __restrict__ inv_count,
-                                                            int V, long ld, long ignore_index, int write_grad) {
+                                                            int V, long ld, long ignore_index, int write_grad,
+                                                            KernelStatus* status) {
   __shared__ float red[8], red2[8];
   const long row = blockIdx.x;
   bf16* lp = logits + row * ld;
   const long label = labels[row];
   const bool ignored = (label == ignore_index) || label < 0 || label >= V;
+  if (threadIdx.x == 0) NSA_CHECK_INDEX(label == ignore_index || (label >= 0 && label < V), status, label);
   const int V8 = V / 8;
   // pass 1: online max / sum-exp
   float mx = -INFINITY, sum = 0.f;
@@ -355,7 +357,8 @@ extern "C" int nsa_cross_entropy(void* logits, const long* labels, float* loss_r
                                  int V, long ld, long ignore_index, int write_grad, cudaStream_t st) {
   if (rows <= 0) return 0;
   if (ld % 8) return nsa::fail(NSA_ERR_SHAPE, "cross_entropy: row pitch must be a multiple of 8");
-  cross_entropy_kernel<<<(unsigned)rows, 256, 0, st>>>((bf16*)logits, labels, loss_rows, inv_count, V, ld, ignore_index, write_grad);
+  cross_entropy_kernel<<<(unsigned)rows, 256, 0, st>>>((bf16*)logits, labels, loss_rows, inv_count, V, ld, ignore_index, write_grad,
+                                                       nsa::status_ptr());
   nsa::count_launch();
   return 0;
 }

@@ -21,6 +21,7 @@ enum : int {
   STATUS_TIMEOUT_PEER_FLAG = 201,    // a flag written by another GPU never reached its value
   STATUS_TIMEOUT_LOCAL_FLAG = 202,   // a flag written by another CTA of this GPU never did
   STATUS_BAD_ARGUMENT = 301,
+  STATUS_BAD_INDEX = 302,            // debug builds: an index read from a tensor was outside its range
 };
 
 #ifdef __CUDACC__
@@ -33,4 +34,15 @@ __device__ __forceinline__ void status_report(KernelStatus* st, int code, int bl
   atomicAdd(&st->count, 1);
   __threadfence_system();
 }
+
+// Debug builds (-DNSA_DEBUG_BOUNDS, `python -m nsa_optim_b200.ops.build --debug`): indices that
+// kernels read from tensors (token ids, labels, selected-block numbers) are checked against their
+// range where they are used.  A bad one is recorded (STATUS_BAD_INDEX, info = the index) and the
+// kernel goes on with the clamped or skipped value it uses in release builds, so nothing faults;
+// release builds compile the check away and clamp or skip silently.
+#ifdef NSA_DEBUG_BOUNDS
+#define NSA_CHECK_INDEX(ok, st, info) do { if (!(ok)) status_report((st), STATUS_BAD_INDEX, blockIdx.x, static_cast<int>(info)); } while (0)
+#else
+#define NSA_CHECK_INDEX(ok, st, info) do { } while (0)
+#endif
 #endif

@@ -21,7 +21,7 @@ from torch import Tensor
 
 from . import quant, torch_impl
 
-_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libnsa_b200.so")
+_LIB_PATH = os.environ.get("NSA_B200_LIB") or os.path.join(os.path.dirname(os.path.abspath(__file__)), "libnsa_b200.so")
 _lib: Optional[ctypes.CDLL] = None
 
 SUPPORTED = {
@@ -38,6 +38,7 @@ STATUS_NAMES = {
     201: "timeout waiting for a flag written by a peer GPU",
     202: "timeout waiting for a flag written by another CTA",
     301: "bad argument",
+    302: "an index read from a tensor was out of range (debug build)",
 }
 
 

@@ -240,6 +240,9 @@ class ShardedModel(nn.Module):
         self._cuda = device.type == "cuda"
         self.comm_stream = torch.cuda.Stream(device=device) if (self._cuda and self.world > 1) else None
         self._order: List[FlatUnit] = []
+        self._exposed: list = []
+        self.measure_exposed = False
+        self.nvtx = False
         self._micro_steps = 0
         self.launch_counter = 0
         self.arena = None
@@ -402,8 +405,40 @@ class ShardedModel(nn.Module):
 
     def _wait_ready(self, unit: FlatUnit) -> None:
         if unit.ready_event is not None:
-            torch.cuda.current_stream().wait_event(unit.ready_event)
+            with self._exposed_wait():
+                torch.cuda.current_stream().wait_event(unit.ready_event)
             unit.ready_event = None
+
+    # ---- exposed communication: how long the compute stream stood still waiting for the
+    # communication stream.  Each wait is bracketed by two events on the compute stream; the time
+    # between them is the part of the collective that compute did not hide.  (A gather that runs
+    # inside the consuming GEMM has no such wait; its stall, if any, is inside that kernel's time.)
+    class _ExposedWait:
+        def __init__(self, owner):
+            self.owner = owner
+
+        def __enter__(self):
+            o = self.owner
+            self.e0 = None
+            if o.measure_exposed and o._cuda:
+                self.e0 = torch.cuda.Event(enable_timing=True)
+                self.e0.record()
+
+        def __exit__(self, *exc):
+            if self.e0 is not None:
+                e1 = torch.cuda.Event(enable_timing=True)
+                e1.record()
+                self.owner._exposed.append((self.e0, e1))
+            return False
+
+    def _exposed_wait(self):
+        return ShardedModel._ExposedWait(self)
+
+    def pop_exposed_comm_ms(self) -> float:
+        """Sum of the exposed waits recorded since the last call (call after a synchronize)."""
+        total = sum(a.elapsed_time(b) for a, b in self._exposed)
+        self._exposed = []
+        return float(total)
 
     def _reduce_grads(self, unit: FlatUnit) -> None:
         """Pack parameter gradients, reduce-scatter, accumulate 1/world of the sum."""
@@ -490,6 +525,12 @@ class ShardedModel(nn.Module):
         return getattr(unit.module, "block_kind", "A") in self.checkpoint_kinds
 
     def _run_layer(self, layer: nn.Module, hidden: Tensor, *args) -> Tensor:
+        if self.nvtx:
+            with torch.cuda.nvtx.range(f"{self._unit_of[id(layer)].name} {getattr(layer, 'block_kind', '')}"):
+                return self._run_layer_impl(layer, hidden, *args)
+        return self._run_layer_impl(layer, hidden, *args)
+
+    def _run_layer_impl(self, layer: nn.Module, hidden: Tensor, *args) -> Tensor:
         unit = self._unit_of[id(layer)]
         if not (torch.is_grad_enabled() and self.module.training):
             self._pre_forward(unit)
@@ -536,7 +577,8 @@ class ShardedModel(nn.Module):
 
     def wait_reductions(self) -> None:
         if self.comm_stream is not None:
-            torch.cuda.current_stream().wait_stream(self.comm_stream)
+            with self._exposed_wait():
+                torch.cuda.current_stream().wait_stream(self.comm_stream)
 
     def zero_grad(self, set_to_none: bool = True) -> None:
         if self.world == 1:

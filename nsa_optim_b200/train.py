@@ -111,6 +111,9 @@ def build_parser() -> argparse.ArgumentParser:
                         "reference module's learned k_compress scorer (selected + window branches only)")
     g = p.add_argument_group("runtime")
     g.add_argument("--synthetic_data", action="store_true", help="uniform random token ids (seeded)")
+    g.add_argument("--nvtx", action="store_true",
+                   help="NVTX ranges around the phases of a step (forward+backward per micro-batch, clip, optimizer) "
+                        "and around every block, for timeline profilers")
     g.add_argument("--seed", type=int, default=0)
     g.add_argument("--dist_backend", type=str, default=None, choices=["nccl", "gloo"])
     g.add_argument("--comm", type=str, default="auto", choices=["auto", "fused", "nccl", "gloo"])
@@ -296,6 +299,7 @@ class Trainer:
         self.model = ShardedModel(model, self.info, strategy=sharding, param_dtype=self.dtype,
                                   activation_checkpointing=self.cfg.gradient_checkpointing, comm=comm,
                                   checkpoint_blocks=getattr(args, "checkpoint_blocks", None))
+        self.model.nvtx = bool(getattr(args, "nvtx", False)) and self.device.type == "cuda"
         self.n_params = sum(p.numel() for p in model.parameters())
         if self.verbose:
             print(f"Model dtype: {self.cfg.dtype}")
@@ -363,6 +367,12 @@ class Trainer:
         self.model.backward(scaled)
         return loss.detach()
 
+    def _range(self, name: str):
+        """NVTX range when ``--nvtx`` is on (a no-op context otherwise)."""
+        if getattr(self.args, "nvtx", False) and self.device.type == "cuda":
+            return torch.cuda.nvtx.range(name)
+        return contextlib.nullcontext()
+
     def step(self, batches: Optional[List[Dict[str, torch.Tensor]]] = None) -> Dict[str, Any]:
         """Runs ``gradient_accumulation_steps`` micro-batches and one optimizer update.
         Returned tensors (``loss``, ``grad_norm``) stay on the device."""
@@ -370,9 +380,11 @@ class Trainer:
         losses = []
         for i in range(accum):
             batch = batches[i] if batches is not None else self.next_batch()
-            losses.append(self.micro_step(batch))
+            with self._range(f"micro_step {i}"):
+                losses.append(self.micro_step(batch))
         loss = torch.stack(losses).mean()
-        norm, coef = self.model.clip_grad_norm(self.cfg.max_grad_norm, local_only=self.args.local_clip)
+        with self._range("clip"):
+            norm, coef = self.model.clip_grad_norm(self.cfg.max_grad_norm, local_only=self.args.local_clip)
         self.check_kernels(sync=False)
         do_step = True
         if self.scaler:
@@ -387,9 +399,10 @@ class Trainer:
             # one host read per step: the price of the flag (off by default)
             do_step = bool(torch.isfinite(loss) & torch.isfinite(norm))
         if do_step:
-            self.optimizer.step(grad_scale=coef)
-            self.scheduler.step()
-            self.model.regather_all()
+            with self._range("optimizer"):
+                self.optimizer.step(grad_scale=coef)
+                self.scheduler.step()
+                self.model.regather_all()
         else:
             self.skipped_steps += 1
         self.model.zero_grad(set_to_none=True)
@@ -485,6 +498,7 @@ def train(args: argparse.Namespace) -> Dict[str, Any]:
         print(f"Effective batch: {eff} sequences x {cfg.max_seq_length} tokens "
               f"({cfg.batch_size} per GPU x {cfg.gradient_accumulation_steps} accumulation x {info.world_size} ranks)")
     use_events = trainer.device.type == "cuda"
+    trainer.model.measure_exposed = use_events and info.world_size > 1
     flops_per_token = _model_flops_per_token(trainer)
     window_losses: List[torch.Tensor] = []
     window_tokens = 0
@@ -527,6 +541,11 @@ def train(args: argparse.Namespace) -> Dict[str, Any]:
                 if flops_per_token:
                     from .profiling import model_flops_utilisation
                     rec["mfu"] = model_flops_utilisation(flops_per_token, tok_s, info.world_size)
+                if trainer.model.measure_exposed:
+                    # time the compute stream waited for the communication stream in this window
+                    ms = trainer.model.pop_exposed_comm_ms()
+                    rec["exposed_comm_ms_per_step"] = ms / max(1, cfg.log_interval)
+                    rec["exposed_comm_frac"] = ms / max(dt * 1e3, 1e-9)
                 history.append(rec)
                 log_f.write(json.dumps(rec) + "\n")
                 log_f.flush()

@@ -258,3 +258,32 @@ def test_pitched_column_copy(native):
     ref[..., 8:24] = g
     assert torch.equal(out, ref)
     assert not native.copy_columns(out[..., 8:24], g[:, :, :1].expand(3, 50, 16))     # broadcast source: not a pitched layout
+
+
+def test_debug_build_reports_out_of_range_indices(tmp_path):
+    """-DNSA_DEBUG_BOUNDS: a token id outside the vocabulary is recorded (status 302, the id as detail)
+    and the gather continues with the clamped row; nothing faults.  Builds a small debug library
+    (two translation units) beside the test and talks to it through ctypes."""
+    import ctypes
+    from ctypes import c_int, c_long, c_void_p
+    from nsa_optim_b200.ops import build
+    lib_file = build.build(debug=True, out=str(tmp_path / "libdebug.so"), only=["elementwise.cu"])
+    lib = ctypes.CDLL(lib_file)
+    vocab, d = 50, 64
+    w = bf(vocab, d)
+    ids = torch.tensor([3, 49, 77, 0], device="cuda", dtype=torch.long)       # 77 is out of range
+    y = torch.empty(4, d, device="cuda", dtype=torch.bfloat16)
+    st = c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert lib.nsa_embedding_fwd(c_void_p(ids.data_ptr()), c_void_p(w.data_ptr()), c_void_p(y.data_ptr()), c_long(4), c_int(d),
+                                 c_long(vocab), st) == 0
+    torch.cuda.synchronize()
+    out = (c_int * 4)()
+    assert lib.nsa_status_read(out, c_int(1)) == 0
+    assert out[0] == 302 and out[2] == 77 and out[3] == 1
+    assert torch.equal(y[2], w[49]) and torch.equal(y[0], w[3])               # clamped, and the rest untouched by it
+    ids[2] = 5
+    lib.nsa_embedding_fwd(c_void_p(ids.data_ptr()), c_void_p(w.data_ptr()), c_void_p(y.data_ptr()), c_long(4), c_int(d),
+                          c_long(vocab), st)
+    torch.cuda.synchronize()
+    lib.nsa_status_read(out, c_int(1))
+    assert out[0] == 0
