@@ -528,14 +528,27 @@ class SOAPLowBit(Optimizer):
                 V = self._load_moment(st, "exp_avg_sq", False, (rows, cols)).clone()
                 bs, nbc = st["block_size"], st["num_blocks_col"]
                 refresh = t % freq == 0
+                nat = _native_for(p) if (cols % 8 == 0 and rows % 8 == 0 and bs % 8 == 0) else None
+                # native path: every product below is a tcgen05 GEMM on bf16 operands with fp32
+                # accumulation (the gradient is scaled once so that G G^T and G^T G accumulate straight
+                # into the EMA factors); PyTorch fp32 matmuls otherwise
+                Gs = (G * math.sqrt(1 - sb)).to(torch.bfloat16) if nat is not None else None
+                Gh = G.to(torch.bfloat16) if nat is not None else None
                 for bi in range(len(st["block_shapes"])):
                     i, j = divmod(bi, nbc)
                     r, c = st["block_shapes"][bi]
                     rs, cs = slice(i * bs, i * bs + r), slice(j * bs, j * bs + c)
                     Gb = G[rs, cs]
                     L, R = st["L_blocks"][bi], st["R_blocks"][bi]
-                    L.mul_(sb).add_(Gb @ Gb.T, alpha=1 - sb)
-                    R.mul_(sb).add_(Gb.T @ Gb, alpha=1 - sb)
+                    if nat is not None:
+                        gsb = Gs[rs, cs]
+                        L.mul_(sb)
+                        R.mul_(sb)
+                        nat.gemm(gsb, gsb, False, False, out=L, accumulate=True)       # L += (1-sb) G G^T
+                        nat.gemm(gsb, gsb, True, True, out=R, accumulate=True)         # R += (1-sb) G^T G
+                    else:
+                        L.mul_(sb).add_(Gb @ Gb.T, alpha=1 - sb)
+                        R.mul_(sb).add_(Gb.T @ Gb, alpha=1 - sb)
                     QL = self._dequantize_block(*st["QL_q_blocks"][bi])
                     QR = self._dequantize_block(*st["QR_q_blocks"][bi])
                     if refresh:
@@ -546,11 +559,21 @@ class SOAPLowBit(Optimizer):
                         # use what will be read back next step, so projection and storage agree
                         QL = self._dequantize_block(*st["QL_q_blocks"][bi])
                         QR = self._dequantize_block(*st["QR_q_blocks"][bi])
-                    Gp = QL.T @ Gb @ QR
+                    if nat is not None:
+                        QLh, QRh = QL.to(torch.bfloat16), QR.to(torch.bfloat16)
+                        T1 = nat.gemm(QLh, Gh[rs, cs], True, True)                                 # QL^T G
+                        Gp = nat.gemm(T1, QRh, False, True, out_dtype=torch.float32)               # (QL^T G) QR
+                    else:
+                        Gp = QL.T @ Gb @ QR
                     Mb = M[rs, cs].mul_(b1).add_(Gp, alpha=1 - b1)
                     Vb = V[rs, cs].mul_(b2).addcmul_(Gp, Gp, value=1 - b2)
                     upd = Mb / ((Vb.sqrt() / math.sqrt(bc2)).add_(eps))
-                    W[rs, cs].add_(QL @ upd @ QR.T, alpha=-lr / bc1)
+                    if nat is not None:
+                        U1 = nat.gemm(QLh, upd.to(torch.bfloat16), False, True)                    # QL upd
+                        U = nat.gemm(U1, QRh, False, False, out_dtype=torch.float32)               # (QL upd) QR^T
+                        W[rs, cs].add_(U, alpha=-lr / bc1)
+                    else:
+                        W[rs, cs].add_(QL @ upd @ QR.T, alpha=-lr / bc1)
                 self._store_moment(st, "exp_avg", True, M)
                 self._store_moment(st, "exp_avg_sq", False, V)
                 p.copy_(W.view_as(p))
