@@ -68,6 +68,19 @@ def _round_up(x: int, m: int) -> int:
     return -(-x // m) * m
 
 
+@dataclass
+class OwnedParam:
+    """A 2-D parameter whose flat range is cut by shard boundaries, given as a whole to one rank
+    (the owner) for optimizers that need whole matrices.  ``holders``: (rank, start, end) of every
+    rank's piece in the parameter's own element coordinates."""
+    unit: "FlatUnit"
+    slot: ParamSlot
+    owner: int
+    holders: List[Tuple[int, int, int]]
+    param: Optional[nn.Parameter] = None      # on the owner: the whole weight, compute dtype
+    grad: Optional[Tensor] = None             # on the owner: the whole reduced gradient, fp32
+
+
 class FlatUnit:
     """One communication unit: layout, owned shard, gathered buffer, gradient shard."""
 
@@ -590,11 +603,119 @@ class ShardedModel(nn.Module):
             for s in u.slots:
                 s.param.grad = None
 
+    # ------------------------------------------------------------------ whole-matrix ownership
+    def enable_owner_preconditioning(self) -> int:
+        """For optimizers that precondition whole matrices (SOAP, Shampoo).  Shards are contiguous
+        ranges of a unit's flat buffer, so most large matrices are cut by a shard boundary and no rank
+        sees their whole gradient.  Every such matrix gets one owner among the ranks that hold a piece
+        (round robin, so the owners' work is spread): before the optimizer step the holders send
+        their reduced gradient pieces to the owner, the owner updates the whole matrix with its whole
+        state, and afterwards sends every holder its piece of the new weight.  The pieces leave the
+        holders' optimizer lists, so nothing is updated twice and no matrix falls back to an
+        elementwise rule.  (The reference keeps SOAP under FSDP by all-reducing Kronecker factors of
+        flat shards, optimizers.py:873-905, and degrades to Adam where shapes are lost.)
+        A matrix that lies whole inside one shard stays with that rank and is handed to the optimizer
+        as a 2-D view of the shard.  Returns the number of matrices handled.  Call before building the
+        optimizer, and again (rebuilding the optimizer's parameter list) if the shard storage moves."""
+        self.owned: List[OwnedParam] = []
+        if self.world == 1:
+            return 0
+        k = 0
+        for u in self.all_units():
+            full = None
+            for s in u.slots:
+                if len(s.shape) != 2:
+                    continue
+                holders = []
+                for r in range(self.world):
+                    lo, hi = r * u.shard_size, (r + 1) * u.shard_size
+                    a, b = max(lo, s.offset), min(hi, s.offset + s.numel)
+                    if b > a:
+                        holders.append((r, a - s.offset, b - s.offset))
+                if len(holders) == 1:
+                    # whole inside one shard: that rank updates it in place, as a matrix, through 2-D
+                    # views of its shard and gradient shard (no copy, nothing to exchange)
+                    op = OwnedParam(u, s, holders[0][0], [])
+                    if op.owner == self.rank:
+                        base = s.offset - self.rank * u.shard_size
+                        op.param = nn.Parameter(u.shard[base:base + s.numel].view(s.shape), requires_grad=True)
+                        op.grad = u.grad_shard[base:base + s.numel].view(s.shape)
+                        if op.param.dtype == torch.float32:
+                            op.param.grad = op.grad
+                        else:
+                            op.param._fp32_grad = op.grad
+                        op.param._logical_numel = s.numel
+                        op.param._no_weight_decay = getattr(s.param, "_no_weight_decay", False)
+                    self.owned.append(op)
+                    continue
+                owner = holders[k % len(holders)][0]
+                k += 1
+                op = OwnedParam(u, s, owner, holders)
+                if owner == self.rank:
+                    if full is None:
+                        full = u.full if u.gathered else self._full_unit_tensor(u)
+                    w = full[s.offset:s.offset + s.numel].view(s.shape).detach().clone()
+                    op.param = nn.Parameter(w, requires_grad=True)
+                    op.grad = torch.zeros(s.shape, dtype=torch.float32, device=u.device)
+                    if w.dtype == torch.float32:
+                        op.param.grad = op.grad
+                    else:
+                        op.param._fp32_grad = op.grad
+                    op.param._logical_numel = s.numel
+                    op.param._no_weight_decay = getattr(s.param, "_no_weight_decay", False)
+                self.owned.append(op)
+            if full is not None and full is not u.full:
+                del full
+        moved = {op.slot.name for op in self.owned}
+        for u in self.all_units():
+            u.pieces = [(n, p) for n, p in u.pieces if n not in moved]
+        return len(self.owned)
+
+    def _exchange_owned(self, to_owner: bool) -> None:
+        """Moves every owned matrix's pieces between holders and owner: reduced gradients to the owner
+        (``to_owner``) or updated weights back to the holders."""
+        if not getattr(self, "owned", None):
+            return
+        p2p = []
+        for op in self.owned:
+            u, s = op.unit, op.slot
+            base = s.offset - self.rank * u.shard_size          # slot coordinate -> index into this rank's shard
+            for r, a, b in op.holders:
+                mine = r == self.rank
+                own = op.owner == self.rank
+                if to_owner:
+                    if mine and own:
+                        op.grad.view(-1)[a:b].copy_(u.grad_shard[base + a:base + b])
+                    elif mine:
+                        p2p.append(dist.P2POp(dist.isend, u.grad_shard[base + a:base + b], op.owner, self.group))
+                    elif own:
+                        p2p.append(dist.P2POp(dist.irecv, op.grad.view(-1)[a:b], r, self.group))
+                else:
+                    if mine and own:
+                        u.shard[base + a:base + b].copy_(op.param.data.view(-1)[a:b])
+                    elif own:
+                        p2p.append(dist.P2POp(dist.isend, op.param.data.view(-1)[a:b], r, self.group))
+                    elif mine:
+                        p2p.append(dist.P2POp(dist.irecv, u.shard[base + a:base + b], op.owner, self.group))
+        if p2p:
+            for req in dist.batch_isend_irecv(p2p):
+                req.wait()
+
+    def collect_owned_grads(self) -> None:
+        self.wait_reductions()
+        self._exchange_owned(True)
+
+    def publish_owned_weights(self) -> None:
+        self._exchange_owned(False)
+
     # ------------------------------------------------------------------ optimizer view
     def named_optimizer_parameters(self) -> List[Tuple[str, nn.Parameter]]:
         out = []
         for u in self.all_units():
             out.extend(u.pieces)
+        for op in getattr(self, "owned", []):
+            if op.param is not None:
+                out.append((op.slot.name, op.param))
         return out
 
     def local_grads(self) -> List[Tensor]:
@@ -677,6 +798,9 @@ class ShardedModel(nn.Module):
     def piece_map(self) -> Dict[int, Tuple[FlatUnit, ParamSlot, int, int]]:
         """id(piece) -> (unit, slot, start offset of the piece inside the parameter, length)."""
         out = {}
+        for op in getattr(self, "owned", []):
+            if op.param is not None:
+                out[id(op.param)] = (op.unit, op.slot, 0, op.slot.numel)
         for u in self.all_units():
             lo = u.rank * u.shard_size
             by_name = {s.name: s for s in u.slots}

@@ -309,6 +309,12 @@ class Trainer:
             if self.cfg.optimizer_type in (OptimizerType.SOAP, OptimizerType.SOAP_4BIT,
                                            OptimizerType.SOAP_8BIT, OptimizerType.SHAMPOO):
                 print_preconditioning_stats(model, self.cfg.optimizer_config.max_precond_dim)
+        self.whole_matrix_optimizer = self.cfg.optimizer_type in (OptimizerType.SOAP, OptimizerType.SOAP_4BIT,
+                                                                  OptimizerType.SOAP_8BIT, OptimizerType.SHAMPOO)
+        if self.whole_matrix_optimizer and self.info.world_size > 1:
+            n = self.model.enable_owner_preconditioning()
+            if self.verbose:
+                print(f"Whole-matrix optimizer under sharding: {n} matrices cut by shard boundaries are each updated by one owner rank")
         self.optimizer = create_optimizer(self.model.named_optimizer_parameters(), self.cfg.optimizer_config,
                                           self.info.world_size)
         self.scheduler = get_lr_scheduler(self.optimizer, self.cfg.lr_scheduler_type,
@@ -400,8 +406,10 @@ class Trainer:
             do_step = bool(torch.isfinite(loss) & torch.isfinite(norm))
         if do_step:
             with self._range("optimizer"):
+                self.model.collect_owned_grads()         # whole-matrix optimizers: gradient pieces to their owners
                 self.optimizer.step(grad_scale=coef)
                 self.scheduler.step()
+                self.model.publish_owned_weights()       # and the updated pieces back to their holders
                 self.model.regather_all()
         else:
             self.skipped_steps += 1
