@@ -64,6 +64,8 @@ struct GemmParams {
   int a_mn, b_mn;
   int out_fp32;
   int accumulate;
+  int split_k;                  // pair kernel: parts the reduction is cut into (1 = none); parts meet in
+                                // an fp32 C through TMA reduce-add stores
   void* C;
   KernelStatus* status;
 };
@@ -531,8 +533,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   const int lane = threadIdx.x & 31;
   const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
   const int tiles_n = (p.N + BN - 1) / BN;
-  const int num_tiles = tiles_m * tiles_n;
-  const int k_blocks = (p.K + BK - 1) / BK;
+  const int S = p.split_k > 1 ? p.split_k : 1;
+  const int num_tiles = tiles_m * tiles_n * S;                  // work items: (tile, part of the reduction)
+  const int k_blocks_all = (p.K + BK - 1) / BK;
+  const int kb_per = (k_blocks_all + S - 1) / S;
   // with the gather inside, the producers may wait for a peer; everything downstream waits as long
   const long long wait_cycles = tc5::kMaxWaitCycles + (p.ag.enabled ? p.ag.max_cycles : 0ll);
   auto coords = [&](int t, int& mb, int& nb) {
@@ -540,8 +544,14 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       pair::tile_coords_nmajor(t, tiles_m, tiles_n, mb, nb);
       nb = (nb + p.ag.n_rot) % tiles_n;
     } else {
-      pair::tile_coords(t, tiles_m, tiles_n, mb, nb);
+      pair::tile_coords(t / S, tiles_m, tiles_n, mb, nb);
     }
+  };
+  // k-blocks [kb_lo, kb_hi) of work item t (the parts of one tile are consecutive items, so they run
+  // at the same time on different CTA pairs); an empty range is skipped by every role alike
+  auto k_range = [&](int t, int& kb_lo, int& kb_hi) {
+    kb_lo = (t % S) * kb_per;
+    kb_hi = kb_lo + kb_per < k_blocks_all ? kb_lo + kb_per : k_blocks_all;
   };
 
   if (threadIdx.x == 0) {
@@ -575,8 +585,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       bool ok = true;
       int seen_group = -1;                         // tile-column group whose chunk flags have been awaited
       for (int t = cluster; t < num_tiles && ok; t += n_clusters) {
-        int mb, nb;
+        int mb, nb, kb_lo, kb_hi;
         coords(t, mb, nb);
+        k_range(t, kb_lo, kb_hi);
+        if (kb_lo >= kb_hi) continue;
         const int m0 = mb * 2 * BM + static_cast<int>(rank) * BM;
         const int n0 = nb * BN + static_cast<int>(rank) * BNH;
         if (p.ag.enabled) {
@@ -607,7 +619,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             seen_group = group;
           }
         }
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!tc5::mbar_wait_cycles(&empty_bar[s], ph ^ 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_EMPTY, wait_cycles)) { ok = false; break; }
@@ -660,13 +672,17 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       uint32_t it = 0;
       uint32_t tile_i = 0;
       bool ok = true;
-      for (int t = cluster; t < num_tiles && ok; t += n_clusters, ++tile_i) {
+      for (int t = cluster; t < num_tiles && ok; t += n_clusters) {
+        int kb_lo, kb_hi;
+        k_range(t, kb_lo, kb_hi);
+        if (kb_lo >= kb_hi) continue;
         const uint32_t acc = tile_i & 1;
         const uint32_t acc_ph = (tile_i >> 1) & 1;
+        ++tile_i;
         if (!tc5::mbar_wait_cycles(&tempty_bar[acc], acc_ph ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY, wait_cycles)) { ok = false; break; }
         tc5::fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!tc5::mbar_wait_cycles(&full_bar[s], ph, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL, wait_cycles)) { ok = false; break; }
@@ -677,7 +693,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           for (int k = 0; k < BK / 16; ++k) {
             const uint64_t ad = A_MN ? tc5::desc_mnmajor(sa + k * 2048, CHUNK_BYTES) : tc5::desc_kmajor(sa + k * 32);
             const uint64_t bd = B_MN ? tc5::desc_mnmajor(sb + k * 2048, CHUNK_BYTES) : tc5::desc_kmajor(sb + k * 32);
-            tc5::mma_ss_pair(d_tmem, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            tc5::mma_ss_pair(d_tmem, ad, bd, idesc, (kb > kb_lo || k > 0) ? 1u : 0u);
           }
           tc5::mma_commit_pair(&empty_bar[s], 3);      // both producers may refill the stage
         }
@@ -693,18 +709,47 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     uint32_t tile_i = 0;
     uint32_t boxes = 0;                           // TMA stores issued by this warp's lane 0
     bool ok = true;
-    for (int t = cluster; t < num_tiles && ok; t += n_clusters, ++tile_i) {
-      int mb, nb;
+    for (int t = cluster; t < num_tiles && ok; t += n_clusters) {
+      int mb, nb, kb_lo, kb_hi;
       coords(t, mb, nb);
+      k_range(t, kb_lo, kb_hi);
+      if (kb_lo >= kb_hi) continue;
       const uint32_t acc = tile_i & 1;
       const uint32_t acc_ph = (tile_i >> 1) & 1;
+      ++tile_i;
       if (!tc5::mbar_wait_cycles(&tfull_bar[acc], acc_ph, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL, wait_cycles)) { ok = false; break; }
       tc5::fence_after_sync();
       const int row0 = mb * 2 * BM + static_cast<int>(rank) * BM + quarter * 32;
       const int row = row0 + lane;
       const int col0 = nb * BN;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
-      if (tma_store) {
+      if (tma_store == 2) {
+        // a part of a split reduction: 32 x 32 fp32 boxes added into C by TMA reduce stores
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col = col0 + c * 32;
+          if (col >= p.N || row0 >= p.M) break;    // uniform across the warp
+          uint32_t r0[32];
+          tc5::tmem_ld_x32(taddr + c * 32, r0);
+          tc5::tmem_ld_wait();
+          uint8_t* box = my_epi + (boxes & 1) * EPI_BOX_BYTES;
+          if (boxes >= 2) {
+            if (lane == 0) tc5::tma_store_wait_read<1>();
+            __syncwarp();
+          }
+          uint8_t* rowp = box + lane * 128;        // 32 floats per row: eight 16-byte chunks, swizzled
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4)) = make_uint4(r0[4 * j], r0[4 * j + 1], r0[4 * j + 2], r0[4 * j + 3]);
+          tc5::fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) {
+            tc5::tma_reduce_add_2d(&tmap_c, box, col, row0);
+            tc5::tma_store_commit();
+          }
+          ++boxes;
+        }
+      } else if (tma_store) {
 #pragma unroll 1
         for (int c = 0; c < BN / 64; ++c) {
           const int col = col0 + c * 64;
@@ -804,7 +849,7 @@ cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUte
     }
     clusters[dev] = n;
   }
-  const int tiles = ((p.M + 2 * pair::BM - 1) / (2 * pair::BM)) * ((p.N + pair::BN - 1) / pair::BN);
+  const int tiles = ((p.M + 2 * pair::BM - 1) / (2 * pair::BM)) * ((p.N + pair::BN - 1) / pair::BN) * (p.split_k > 1 ? p.split_k : 1);
   int n = clusters[dev];
   if (max_ctas > 0 && max_ctas / 2 < n) n = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
   if (tiles < n) n = tiles;
@@ -827,6 +872,10 @@ static bool use_pair_kernel() {
   }
   return v == 1;
 }
+// Number of CTA pairs the pair kernel runs at once on the current device (0 before its first launch:
+// then half the SM count is the estimate).
+extern "C" int nsa_gemm_pair_clusters(void) { return nsa::sm_count() / 2; }
+
 // Overrides the kernel choice for the calls that follow (benchmarks and tests compare the two).
 extern "C" void nsa_gemm_select(int which) { g_gemm_select = (which == 1 || which == 2) ? which : 0; }
 
@@ -850,7 +899,7 @@ extern "C" int nsa_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   GemmParams p;
   p.ag = AgFuse{};
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldb = ldb; p.a_mn = a_mn; p.b_mn = b_mn;
-  p.out_fp32 = out_fp32; p.accumulate = accumulate; p.C = C; p.status = nsa::status_ptr();
+  p.out_fp32 = out_fp32; p.accumulate = accumulate; p.split_k = 1; p.C = C; p.status = nsa::status_ptr();
   cudaError_t e;
   if (pairk) {
     // bf16 output without accumulation leaves through TMA stores when C allows a tensor map
@@ -875,6 +924,39 @@ extern "C" int nsa_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   else if (a_mn && !b_mn) e = launch<1, 0>(ta, tb, p, grid, stream);
   else e = launch<1, 1>(ta, tb, p, grid, stream);
   return e == cudaSuccess ? 0 : nsa::fail_cuda(e, "nsa_gemm_bf16 launch");
+}
+
+// C32[M,N] += op(A) op(B) with the reduction cut into `split_k` parts that run on different CTA pairs
+// and meet in the fp32 matrix C32 through TMA reduce-add stores.  For shapes with a long reduction
+// and too few output tiles to fill the machine evenly (weight gradients: K = tokens).  C32 must hold
+// the values the products are to be added to (zeros for a plain product); base 16-byte aligned, ldc a
+// multiple of 4.  Pair kernel only; M > 128.
+extern "C" int nsa_gemm_bf16_splitk(const void* A, const void* B, float* C32, int M, int N, int K, int lda, int ldb,
+                                    int ldc, int a_mn, int b_mn, int split_k, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7) ||
+      (reinterpret_cast<uintptr_t>(C32) & 15) || (ldc & 3))
+    return nsa::fail(NSA_ERR_ALIGNMENT, "nsa_gemm_bf16_splitk: operands need 16-byte aligned bases and row pitches");
+  if (M <= 128 || split_k < 1 || split_k > 16) return nsa::fail(NSA_ERR_SHAPE, "nsa_gemm_bf16_splitk: M > 128 and 1 <= split_k <= 16 required");
+  CUtensorMap ta, tb, tc;
+  int rc;
+  if (!a_mn) rc = nsa::make_tmap_2d_bf16(&ta, A, K, M, lda, BK, BM);
+  else       rc = nsa::make_tmap_2d_bf16(&ta, A, M, K, lda, 64, BK);
+  if (rc) return rc;
+  if (!b_mn) rc = nsa::make_tmap_2d_bf16(&tb, B, K, N, ldb, BK, pair::BNH);
+  else       rc = nsa::make_tmap_2d_bf16(&tb, B, N, K, ldb, 64, BK);
+  if (rc) return rc;
+  if ((rc = nsa::make_tmap_2d_f32(&tc, C32, N, M, ldc, 32, 32))) return rc;
+  GemmParams p;
+  p.ag = AgFuse{};
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldb = ldb; p.a_mn = a_mn; p.b_mn = b_mn;
+  p.out_fp32 = 1; p.accumulate = 1; p.split_k = split_k; p.C = C32; p.status = nsa::status_ptr();
+  cudaError_t e;
+  if (!a_mn && !b_mn) e = launch_pair<0, 0>(ta, tb, tc, p, 2, 0, stream);
+  else if (!a_mn && b_mn) e = launch_pair<0, 1>(ta, tb, tc, p, 2, 0, stream);
+  else if (a_mn && !b_mn) e = launch_pair<1, 0>(ta, tb, tc, p, 2, 0, stream);
+  else e = launch_pair<1, 1>(ta, tb, tc, p, 2, 0, stream);
+  return e == cudaSuccess ? 0 : nsa::fail_cuda(e, "nsa_gemm_bf16_splitk launch");
 }
 
 // y[M,N] = x[M,K] * W[N,K]^T where W lives at element offset `b_elem_offset` of the sharded
@@ -904,7 +986,7 @@ extern "C" int nsa_gemm_bf16_ag(const void* A, void* C, int M, int N, int K, int
   GemmParams p;
   p.ag = AgFuse{};
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldb = K; p.a_mn = 0; p.b_mn = 0;
-  p.out_fp32 = 0; p.accumulate = 0; p.C = C; p.status = nsa::status_ptr();
+  p.out_fp32 = 0; p.accumulate = 0; p.split_k = 1; p.C = C; p.status = nsa::status_ptr();
   const int sms = nsa::sm_count();
   if (copy_ctas <= 0) copy_ctas = 16;
   if (copy_ctas > sms / 2) copy_ctas = sms / 2;

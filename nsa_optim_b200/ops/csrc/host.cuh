@@ -26,6 +26,9 @@ int sm_count();
 // `ld` is the row pitch in elements; box_inner * 2 bytes must be 128.
 int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
                       uint32_t box_inner, uint32_t box_outer);
+// 2-D fp32 tensor map with 128-byte swizzle; box_inner * 4 bytes must be 128.
+int make_tmap_2d_f32(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
+                     uint32_t box_inner, uint32_t box_outer);
 // General tiled bf16 map (rank <= 5) with explicit byte strides for dims 1..rank-1.
 int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
                    const uint64_t* strides_bytes, const uint32_t* box, int swizzle128);

@@ -108,6 +108,25 @@ int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t*
   return 0;
 }
 
+int make_tmap_2d_f32(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
+                     uint32_t box_inner, uint32_t box_outer) {
+  bind_primary_context();
+  EncodeTiledFn enc = encoder();
+  if (!enc) return fail(NSA_ERR_DRIVER_API, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t gd[2] = {inner, outer}, gs[1] = {ld * 4};
+  cuuint32_t bx[2] = {box_inner, box_outer}, es[2] = {1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), gd, gs, bx, es,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char msg[160];
+    snprintf(msg, sizeof(msg), "cuTensorMapEncodeTiled (fp32) failed with CUresult %d (%llu x %llu)", (int)r,
+             (unsigned long long)inner, (unsigned long long)outer);
+    return fail(NSA_ERR_DRIVER_API, msg);
+  }
+  return 0;
+}
+
 int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
                       uint32_t box_inner, uint32_t box_outer) {
   uint64_t dims[2] = {inner, outer};

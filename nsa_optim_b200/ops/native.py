@@ -209,10 +209,35 @@ def _as_2d(x: Tensor) -> Tensor:
     return x2
 
 
+_SPLITK_MAX = int(os.environ.get("NSA_B200_SPLITK_MAX", "2"))
+_gemm_which = "default"
+
+
+def split_k_choice(M: int, N: int, K: int, clusters: int = 74) -> int:
+    """Parts to cut the reduction of an M x N x K GEMM into.  The pair kernel gives each CTA pair
+    256 x 256 tiles; with few tiles and a long reduction (weight gradients: K = tokens) the last wave
+    is mostly empty, and splitting the reduction fills it.  Two parts added into a zeroed fp32 C
+    give the same bits in either order, so the default limit of 2 keeps results reproducible;
+    ``NSA_B200_SPLITK_MAX`` raises it."""
+    tiles = -(-M // 256) * -(-N // 256)
+    if K < 8192 or M <= 128 or tiles >= 6 * clusters:
+        return 1
+
+    def eff(S):
+        w = tiles * S / clusters
+        return w / -(-w // 1)
+
+    best = max(range(1, _SPLITK_MAX + 1), key=lambda S: eff(S) - 0.01 * S)
+    return best if eff(best) > eff(1) + 0.04 else 1
+
+
 def gemm(a: Tensor, b: Tensor, a_mn: bool, b_mn: bool, out: Optional[Tensor] = None,
-         out_dtype: torch.dtype = torch.bfloat16, accumulate: bool = False, max_ctas: int = 0) -> Tensor:
+         out_dtype: torch.dtype = torch.bfloat16, accumulate: bool = False, max_ctas: int = 0,
+         split_k: Optional[int] = None) -> Tensor:
     """C = op(A) op(B): a_mn False -> A is (M, K), True -> A is (K, M); b_mn False -> B is (N, K),
-    True -> B is (K, N).  Row pitches may exceed the logical width (sliced views)."""
+    True -> B is (K, N).  Row pitches may exceed the logical width (sliced views).  ``split_k``
+    (default: chosen by :func:`split_k_choice`) cuts the reduction into parts that run on different
+    CTA pairs and meet in fp32 through TMA reduce-add stores."""
     a, b = _as_2d(a), _as_2d(b)
     M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
     N, Kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
@@ -220,6 +245,22 @@ def gemm(a: Tensor, b: Tensor, a_mn: bool, b_mn: bool, out: Optional[Tensor] = N
         raise ValueError(f"gemm: reduction sizes differ ({K} vs {Kb})")
     if out is None:
         out = _empty(M, N, dtype=out_dtype, device=a.device)
+    if split_k is None:
+        split_k = split_k_choice(M, N, K) if (max_ctas == 0 and _gemm_which != "single") else 1
+    if split_k > 1 and M > 128:
+        direct = out.dtype == torch.float32 and out.stride(1) == 1 and out.stride(0) % 4 == 0 and out.data_ptr() % 16 == 0
+        if direct:
+            ws = out
+            if not accumulate:
+                ws.zero_()
+        else:
+            ws = out.float() if accumulate else _zeros(M, N, dtype=torch.float32, device=a.device)
+        _check(load().nsa_gemm_bf16_splitk(_p(a), _p(b), _p(ws), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)),
+                                           c_int(b.stride(0)), c_int(ws.stride(0)), c_int(int(a_mn)), c_int(int(b_mn)),
+                                           c_int(split_k), _stream()))
+        if not direct:
+            out.copy_(ws)
+        return out
     _check(load().nsa_gemm_bf16(_p(a), _p(b), _p(out), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)),
                                 c_int(b.stride(0)), c_int(out.stride(0)), c_int(int(a_mn)), c_int(int(b_mn)),
                                 c_int(int(out.dtype == torch.float32)), c_int(int(accumulate)), c_int(max_ctas),
@@ -230,6 +271,8 @@ def gemm(a: Tensor, b: Tensor, a_mn: bool, b_mn: bool, out: Optional[Tensor] = N
 def gemm_select(which: str = "default") -> None:
     """Kernel used by plain GEMMs from now on: "pair" (two CTAs per 256 x 256 tile), "single"
     (one CTA per 128 x 256 tile) or "default" (pair unless NSA_B200_GEMM=single)."""
+    global _gemm_which
+    _gemm_which = which
     load().nsa_gemm_select(c_int({"default": 0, "single": 1, "pair": 2}[which]))
 
 

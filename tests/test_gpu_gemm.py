@@ -50,6 +50,35 @@ def test_both_gemm_kernels_agree_with_fp32(native, which):
         native.gemm_select("default")
 
 
+@pytest.mark.parametrize("split_k", [2, 3, 4])
+@pytest.mark.parametrize("a_mn,b_mn", [(True, True), (False, False)])
+def test_gemm_split_k_through_tma_reduce(native, split_k, a_mn, b_mn):
+    """The reduction cut into parts that meet in fp32 through TMA reduce-add stores (weight-gradient
+    shapes: few tiles, long K): bf16 and fp32 outputs, with and without accumulation, ragged edges."""
+    M, N, K = 520, 776, 4104
+    a, b = _mk(M, N, K, a_mn, b_mn)
+    ref = _ref(a, b, a_mn, b_mn)
+    tol = 1e-2 * ref.abs().max().item() + 1e-2
+    c = native.gemm(a, b, a_mn, b_mn, split_k=split_k)
+    assert (c.float() - ref).abs().max().item() <= tol
+    c32 = torch.ones(M, N, device="cuda")
+    native.gemm(a, b, a_mn, b_mn, out=c32, accumulate=True, split_k=split_k)
+    assert (c32 - (ref + 1)).abs().max().item() <= tol
+    c32 = torch.full((M, N), 7.0, device="cuda")
+    native.gemm(a, b, a_mn, b_mn, out=c32, split_k=split_k)
+    assert (c32 - ref).abs().max().item() <= tol
+    if split_k == 2:                       # two parts into a zeroed C: the same bits whichever lands first
+        assert torch.equal(c, native.gemm(a, b, a_mn, b_mn, split_k=2))
+
+
+def test_split_k_is_chosen_for_the_mlp_weight_gradients(native):
+    assert native.split_k_choice(5632, 2048, 65536) == 2 and native.split_k_choice(65536, 8512, 2048) == 1
+    a, b = _mk(5632, 2048, 16384, True, True)
+    c = native.gemm(a, b, True, True)                  # picks split_k = 2 by itself
+    ref = _ref(a, b, True, True)
+    assert (c.float() - ref).abs().max().item() <= 1e-2 * ref.abs().max().item() + 1e-2
+
+
 def test_gemm_is_deterministic(native):
     a, b = _mk(3000, 2048, 1536, False, False)
     c1 = native.gemm(a, b, False, False)
