@@ -2503,6 +2503,112 @@ __global__ void __launch_bounds__(256) attn_delta_kernel(const bf16* __restrict_
 }
 
 // Union of the selection blocks chosen by the R tokens of each query tile.
+// --------------------------------------------------------------------------------------
+// Inverse of the selection map: for every (batch, kv head, block) the ascending list of tokens that
+// selected the block (what the key-stationary dK/dV pass walks).  Counting, scanning and filling,
+// with no sort and no atomics on global memory, so the lists are the same on every run:
+//   1. one warp per (b*h, chunk of INV_CHUNK tokens) builds the chunk's histogram over blocks;
+//   2. per list, an exclusive scan of the histograms along the chunks gives each chunk's offset
+//      inside the list, and the total gives the list's length;
+//   3. one thread block scans the lengths into list starts (and the CTA counts per list);
+//   4. the warps of step 1 walk their tokens again in the same order and write them.
+// Inside a warp, lanes hold consecutive tokens; lanes that name the same block are ranked by lane
+// (match.any), so tokens stay ascending.  An entry is dropped if it is negative, out of range or
+// repeats an earlier entry of the same token.
+// --------------------------------------------------------------------------------------
+constexpr int INV_CHUNK = 1024;
+
+__device__ __forceinline__ bool inv_entry_ok(const int* row, int j, int nS) {
+  const int v = row[j];
+  if (v < 0 || v >= nS) return false;
+  for (int i = 0; i < j; ++i)
+    if (row[i] == v) return false;
+  return true;
+}
+
+// mode 0: hist[(bh * chunks + chunk) * nS + blk] = entries of the chunk; mode 1: fill tok_list.
+__global__ void __launch_bounds__(32) nsa_inverse_walk_kernel(const int* __restrict__ idx, int* __restrict__ hist,
+                                                              const int* __restrict__ chunk_off,
+                                                              const int* __restrict__ list_start, int* __restrict__ tok_list,
+                                                              int T, int n, int nS, int chunks, int mode) {
+  extern __shared__ int bins[];                   // nS running counts of this chunk
+  const int chunk = blockIdx.x, lane = threadIdx.x;
+  const long bh = blockIdx.y;
+  for (int i = lane; i < nS; i += 32) bins[i] = 0;
+  __syncwarp();
+  const long slot = (bh * chunks + chunk) * nS;
+  const int t_end = min(T, (chunk + 1) * INV_CHUNK);
+  for (int t0 = chunk * INV_CHUNK; t0 < t_end; t0 += 32) {
+    const int t = t0 + lane;
+    const int* row = idx + (bh * T + (t < T ? t : 0)) * n;
+    for (int j = 0; j < n; ++j) {
+      const bool ok = t < t_end && inv_entry_ok(row, j, nS);
+      const int blk = ok ? row[j] : -1 - lane;    // lanes without an entry match nobody
+      const unsigned peers = __match_any_sync(0xffffffffu, blk);
+      if (ok) {
+        const int rank = __popc(peers & ((1u << lane) - 1u));
+        const int before = bins[blk];
+        if (mode == 1) tok_list[list_start[bh * nS + blk] + chunk_off[slot + blk] + before + rank] = t;
+        __syncwarp(peers);
+        if (rank == 0) bins[blk] = before + __popc(peers);
+      }
+      __syncwarp();
+    }
+  }
+  if (mode == 0)
+    for (int i = lane; i < nS; i += 32) hist[slot + i] = bins[i];
+}
+
+// one thread per list: offsets of the chunks inside the list (in place over hist) and the length
+__global__ void __launch_bounds__(256) nsa_inverse_offsets_kernel(int* __restrict__ hist, int* __restrict__ count, long lists,
+                                                                 int nS, int chunks) {
+  const long l = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (l >= lists) return;
+  const long bh = l / nS;
+  const int blk = static_cast<int>(l - bh * nS);
+  int run = 0;
+  for (int c = 0; c < chunks; ++c) {
+    int* p = hist + (bh * chunks + c) * nS + blk;
+    const int v = *p;
+    *p = run;
+    run += v;
+  }
+  count[l] = run;
+}
+
+// single CTA: list_start[l] = sum of count[< l]; item_start[l] = sum of ceil(ceil(count / R) / vpc)
+__global__ void __launch_bounds__(1024) nsa_inverse_scan_kernel(const int* __restrict__ count, int* __restrict__ list_start,
+                                                               int* __restrict__ item_start, long lists, int R, int vpc) {
+  __shared__ int sa[1024], sb[1024];
+  __shared__ int base_a, base_b;
+  if (threadIdx.x == 0) { base_a = 0; base_b = 0; }
+  __syncthreads();
+  for (long l0 = 0; l0 < lists; l0 += 1024) {
+    const long l = l0 + threadIdx.x;
+    const int c = l < lists ? count[l] : 0;
+    const int it = ((c + R - 1) / R + vpc - 1) / vpc;
+    sa[threadIdx.x] = c;
+    sb[threadIdx.x] = it;
+    __syncthreads();
+    for (int o = 1; o < 1024; o <<= 1) {           // inclusive scan, Hillis-Steele
+      const int va = threadIdx.x >= o ? sa[threadIdx.x - o] : 0;
+      const int vb = threadIdx.x >= o ? sb[threadIdx.x - o] : 0;
+      __syncthreads();
+      sa[threadIdx.x] += va;
+      sb[threadIdx.x] += vb;
+      __syncthreads();
+    }
+    if (l < lists) {
+      list_start[l] = base_a + sa[threadIdx.x] - c;
+      item_start[l] = base_b + sb[threadIdx.x] - it;
+    }
+    __syncthreads();
+    if (threadIdx.x == 1023) { base_a += sa[1023]; base_b += sb[1023]; }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) { list_start[lists] = base_a; item_start[lists] = base_b; }
+}
+
 // idx: [B, Hkv, T, top_n] int32 block ids (-1 = none).  Outputs per (b, h, tile): ascending
 // block list, per-entry token bit masks, and the entry count.  One CTA per tile.
 __global__ void __launch_bounds__(128) nsa_union_kernel(const int* __restrict__ idx, int* __restrict__ tile_blocks,
@@ -2806,4 +2912,24 @@ extern "C" int nsa_union_blocks(const int* idx, int* tile_blocks, unsigned long 
   nsa::count_launch();
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : nsa::fail_cuda(e, "nsa_union_blocks launch");
+}
+
+// Inverse selection map (see nsa_inverse_walk_kernel).  idx: [B*Hkv, T, n] int32.  Outputs: tok_list
+// (capacity B*Hkv*T*n), list_start and item_start (lists + 1 entries, lists = B*Hkv*nS).  Scratch:
+// hist with B*Hkv*chunks*nS ints (chunks = ceil(T / 1024)) and count with `lists` ints.
+extern "C" int nsa_inverse_blocks(const int* idx, int* tok_list, int* list_start, int* item_start, int* hist, int* count,
+                                  int BH, int T, int n, int nS, int R, int visits_per_cta, cudaStream_t st) {
+  if (BH <= 0 || T <= 0 || n <= 0 || nS <= 0 || R <= 0 || visits_per_cta <= 0)
+    return nsa::fail(NSA_ERR_SHAPE, "nsa_inverse_blocks: empty problem");
+  if (nS * 4 > 48 * 1024) return nsa::fail(NSA_ERR_SHAPE, "nsa_inverse_blocks: more than 12288 selection blocks");
+  const int chunks = (T + INV_CHUNK - 1) / INV_CHUNK;
+  const long lists = static_cast<long>(BH) * nS;
+  const dim3 grid(chunks, BH);
+  nsa_inverse_walk_kernel<<<grid, 32, nS * 4, st>>>(idx, hist, nullptr, nullptr, nullptr, T, n, nS, chunks, 0);
+  nsa_inverse_offsets_kernel<<<(unsigned)((lists + 255) / 256), 256, 0, st>>>(hist, count, lists, nS, chunks);
+  nsa_inverse_scan_kernel<<<1, 1024, 0, st>>>(count, list_start, item_start, lists, R, visits_per_cta);
+  nsa_inverse_walk_kernel<<<grid, 32, nS * 4, st>>>(idx, nullptr, hist, list_start, tok_list, T, n, nS, chunks, 1);
+  nsa::count_launch(4);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : nsa::fail_cuda(e, "nsa_inverse_blocks launch");
 }

@@ -1053,6 +1053,27 @@ def union_blocks(idx: Tensor, G: int, nS: int):
 
 
 def inverse_blocks(idx: Tensor, nS: int, R: int, visits_per_cta: int):
+    """Inverse of the selection map (count, scan, fill kernels of ``csrc/attention.cu``; no sort, the
+    same lists on every run).  Same results as :func:`_inverse_blocks_torch`."""
+    B, Hkv, T, n = idx.shape
+    if not idx.is_cuda or nS > 12288:
+        return _inverse_blocks_torch(idx, nS, R, visits_per_cta)
+    dev = idx.device
+    idx = idx.to(torch.int32).contiguous()
+    lists = B * Hkv * nS
+    chunks = -(-T // 1024)
+    tok = _empty(B * Hkv * T * n, dtype=torch.int32, device=dev)
+    list_start = _empty(lists + 1, dtype=torch.int32, device=dev)
+    item_start = _empty(lists + 1, dtype=torch.int32, device=dev)
+    hist = _empty(B * Hkv * chunks * nS, dtype=torch.int32, device=dev)
+    count = _empty(lists, dtype=torch.int32, device=dev)
+    _check(load().nsa_inverse_blocks(_p(idx), _p(tok), _p(list_start), _p(item_start), _p(hist), _p(count), c_int(B * Hkv),
+                                     c_int(T), c_int(n), c_int(nS), c_int(R), c_int(visits_per_cta), _stream()))
+    bound = (B * Hkv * T * n) // (R * visits_per_cta) + lists
+    return tok, list_start, item_start, nS, bound
+
+
+def _inverse_blocks_torch(idx: Tensor, nS: int, R: int, visits_per_cta: int):
     """Inverse of the selection map.  idx (B, Hkv, T, top_n) -> (tok_list, list_start, item_start,
     nS, item_bound): for every (b, h, block) the ascending tokens that selected the block, laid out
     back to back; ``list_start`` / ``item_start`` are the exclusive prefixes of the list lengths and

@@ -228,3 +228,19 @@ def test_two_branch_nsa_over_given_block_lists(native):
     g2 = torch.rand(B, T, Hq, device="cuda").bfloat16()
     run_pair(lambda q, k, v: native.nsa_attention_indexed(q, k, v, idx, g1, g2, 64, 128),
              lambda q, k, v: torch_impl.nsa_attention_indexed(q, k, v, idx, g1.float(), g2.float(), 64, 128), (q, k, v))
+
+
+@pytest.mark.parametrize("T,nS,n", [(3000, 47, 16), (64, 1, 4), (5000, 2100, 8)])
+def test_inverse_selection_map_kernels_match_the_sort_based_form(native, T, nS, n):
+    """count -> scan -> fill against the stable-sort construction, with unused (-1), out-of-range and
+    repeated entries in the lists."""
+    B, Hkv, R, vpc = 2, 2, 8, 4
+    idx = torch.randint(-1, nS + 1, (B, Hkv, T, n), device="cuda", dtype=torch.int32)      # nS itself is out of range
+    idx[..., 1] = idx[..., 0]                                                              # a repeat in every list
+    tok, ls, its, _, bound = native.inverse_blocks(idx, nS, R, vpc)
+    tok_r, ls_r, its_r, _, bound_r = native._inverse_blocks_torch(idx, nS, R, vpc)
+    assert torch.equal(ls, ls_r) and torch.equal(its, its_r) and bound == bound_r
+    total = int(ls_r[-1])
+    assert torch.equal(tok[:total], tok_r[:total])
+    tok2, ls2, _, _, _ = native.inverse_blocks(idx, nS, R, vpc)                            # and the same bits again
+    assert torch.equal(tok2[:total], tok[:total]) and torch.equal(ls2, ls)
