@@ -636,8 +636,15 @@ attn_fwd_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if (p.causal) check = check || ((sb + 63) * p.kp_stride + p.kp_off > t);
         if (p.window > 0) check = check || (sb * p.kp_stride + p.kp_off <= t - p.window);
         if (!check) {
+          // four independent chains: one serial chain of 64 dependent maxima is about 250 cycles of
+          // pure latency on the critical path of every visit
+          float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-          for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
+          for (int i = 0; i < 64; i += 4) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) m4[q] = fmaxf(m4[q], __uint_as_float(sv[i + q]));
+          }
+          mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
         } else {
 #pragma unroll
           for (int i = 0; i < 64; ++i)
@@ -656,13 +663,15 @@ attn_fwd_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 #pragma unroll
         for (int i = 0; i < 32; ++i) pk[i] = 0u;
       } else if (!check) {
+        float s4[4] = {0.f, 0.f, 0.f, 0.f};               // independent partial sums (see the maxima above)
 #pragma unroll
         for (int i = 0; i < 64; i += 2) {
           const float a = exp2f(fmaf(__uint_as_float(sv[i]), sc, -m_ref));
           const float c = exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -m_ref));
-          psum += a + c;
+          s4[(i >> 1) & 3] += a + c;
           pk[i / 2] = tc5::pack_bf16(a, c);
         }
+        psum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
       } else {
 #pragma unroll
         for (int i = 0; i < 64; i += 2) {
@@ -1165,8 +1174,15 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if (p.causal) check = check || ((sb + 63) * p.kp_stride + p.kp_off > t);
         if (p.window > 0) check = check || (sb * p.kp_stride + p.kp_off <= t - p.window);
         if (!check) {
+          // four independent chains: one serial chain of 64 dependent maxima is about 250 cycles of
+          // pure latency on the critical path of every visit
+          float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-          for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
+          for (int i = 0; i < 64; i += 4) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) m4[q] = fmaxf(m4[q], __uint_as_float(sv[i + q]));
+          }
+          mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
         } else {
 #pragma unroll
           for (int i = 0; i < 64; ++i)
@@ -1185,13 +1201,15 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 #pragma unroll
         for (int i = 0; i < 32; ++i) pk[i] = 0u;
       } else if (!check) {
+        float s4[4] = {0.f, 0.f, 0.f, 0.f};               // independent partial sums (see the maxima above)
 #pragma unroll
         for (int i = 0; i < 64; i += 2) {
           const float a = exp2f(fmaf(__uint_as_float(sv[i]), sc, -m_ref));
           const float c = exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -m_ref));
-          psum += a + c;
+          s4[(i >> 1) & 3] += a + c;
           pk[i / 2] = tc5::pack_bf16(a, c);
         }
+        psum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
       } else {
 #pragma unroll
         for (int i = 0; i < 64; i += 2) {
@@ -2512,21 +2530,14 @@ __global__ void __launch_bounds__(256) attn_delta_kernel(const bf16* __restrict_
 //      inside the list, and the total gives the list's length;
 //   3. one thread block scans the lengths into list starts (and the CTA counts per list);
 //   4. the warps of step 1 walk their tokens again in the same order and write them.
-// Inside a warp, lanes hold consecutive tokens; lanes that name the same block are ranked by lane
-// (match.any), so tokens stay ascending.  An entry is dropped if it is negative, out of range or
-// repeats an earlier entry of the same token.
+// An entry is dropped if it is negative, out of range or repeats an earlier entry of the same token.
 // --------------------------------------------------------------------------------------
-constexpr int INV_CHUNK = 1024;
-
-__device__ __forceinline__ bool inv_entry_ok(const int* row, int j, int nS) {
-  const int v = row[j];
-  if (v < 0 || v >= nS) return false;
-  for (int i = 0; i < j; ++i)
-    if (row[i] == v) return false;
-  return true;
-}
+constexpr int INV_CHUNK = 256;
 
 // mode 0: hist[(bh * chunks + chunk) * nS + blk] = entries of the chunk; mode 1: fill tok_list.
+// The warp takes the chunk's tokens one after the other, lane j looking at entry j of the token's
+// list (n <= 32): a token's valid entries name distinct blocks, so the lanes touch distinct counters,
+// and tokens reach every list in ascending order.
 __global__ void __launch_bounds__(32) nsa_inverse_walk_kernel(const int* __restrict__ idx, int* __restrict__ hist,
                                                               const int* __restrict__ chunk_off,
                                                               const int* __restrict__ list_start, int* __restrict__ tok_list,
@@ -2538,22 +2549,19 @@ __global__ void __launch_bounds__(32) nsa_inverse_walk_kernel(const int* __restr
   __syncwarp();
   const long slot = (bh * chunks + chunk) * nS;
   const int t_end = min(T, (chunk + 1) * INV_CHUNK);
-  for (int t0 = chunk * INV_CHUNK; t0 < t_end; t0 += 32) {
-    const int t = t0 + lane;
-    const int* row = idx + (bh * T + (t < T ? t : 0)) * n;
-    for (int j = 0; j < n; ++j) {
-      const bool ok = t < t_end && inv_entry_ok(row, j, nS);
-      const int blk = ok ? row[j] : -1 - lane;    // lanes without an entry match nobody
-      const unsigned peers = __match_any_sync(0xffffffffu, blk);
-      if (ok) {
-        const int rank = __popc(peers & ((1u << lane) - 1u));
-        const int before = bins[blk];
-        if (mode == 1) tok_list[list_start[bh * nS + blk] + chunk_off[slot + blk] + before + rank] = t;
-        __syncwarp(peers);
-        if (rank == 0) bins[blk] = before + __popc(peers);
-      }
-      __syncwarp();
+  int v_next = (lane < n && chunk * INV_CHUNK < t_end) ? idx[(bh * T + chunk * INV_CHUNK) * n + lane] : -1;
+  for (int t = chunk * INV_CHUNK; t < t_end; ++t) {
+    const int v = v_next;
+    if (t + 1 < t_end && lane < n) v_next = idx[(bh * T + t + 1) * n + lane];      // next token's entry, ahead of use
+    const bool in_range = lane < n && v >= 0 && v < nS;
+    const unsigned same = __match_any_sync(0xffffffffu, in_range ? v : -1 - lane);
+    const bool first = (same & ((1u << lane) - 1u)) == 0u;                          // not a repeat of an earlier entry
+    if (in_range && first) {
+      const int before = bins[v];
+      if (mode == 1) tok_list[list_start[bh * nS + v] + chunk_off[slot + v] + before] = t;
+      bins[v] = before + 1;
     }
+    __syncwarp();
   }
   if (mode == 0)
     for (int i = lane; i < nS; i += 32) hist[slot + i] = bins[i];
@@ -2916,12 +2924,12 @@ extern "C" int nsa_union_blocks(const int* idx, int* tile_blocks, unsigned long 
 
 // Inverse selection map (see nsa_inverse_walk_kernel).  idx: [B*Hkv, T, n] int32.  Outputs: tok_list
 // (capacity B*Hkv*T*n), list_start and item_start (lists + 1 entries, lists = B*Hkv*nS).  Scratch:
-// hist with B*Hkv*chunks*nS ints (chunks = ceil(T / 1024)) and count with `lists` ints.
+// hist with B*Hkv*chunks*nS ints (chunks = ceil(T / 256)) and count with `lists` ints.
 extern "C" int nsa_inverse_blocks(const int* idx, int* tok_list, int* list_start, int* item_start, int* hist, int* count,
                                   int BH, int T, int n, int nS, int R, int visits_per_cta, cudaStream_t st) {
   if (BH <= 0 || T <= 0 || n <= 0 || nS <= 0 || R <= 0 || visits_per_cta <= 0)
     return nsa::fail(NSA_ERR_SHAPE, "nsa_inverse_blocks: empty problem");
-  if (nS * 4 > 48 * 1024) return nsa::fail(NSA_ERR_SHAPE, "nsa_inverse_blocks: more than 12288 selection blocks");
+  if (nS * 4 > 48 * 1024 || n > 32) return nsa::fail(NSA_ERR_SHAPE, "nsa_inverse_blocks: at most 12288 selection blocks and 32 entries per token");
   const int chunks = (T + INV_CHUNK - 1) / INV_CHUNK;
   const long lists = static_cast<long>(BH) * nS;
   const dim3 grid(chunks, BH);

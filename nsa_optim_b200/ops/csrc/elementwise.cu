@@ -847,7 +847,7 @@ __global__ void __launch_bounds__(256) rope_kernel(const bf16* __restrict__ x, c
 // Causal depthwise conv1d, width W <= 4, channel-last (B, T, C), optional bias and SiLU.
 // Each thread owns 8 channels and walks TCHUNK consecutive time steps with a register window.
 // ------------------------------------------------------------------------------------
-constexpr int CONV_TCHUNK = 128;
+constexpr int CONV_TCHUNK = 32;
 template <int W>
 __global__ void __launch_bounds__(128) conv1d_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
                                                          const bf16* __restrict__ bias, bf16* __restrict__ y,
@@ -932,7 +932,7 @@ __global__ void __launch_bounds__(128) conv1d_bwd_kernel(const bf16* __restrict_
   }
   // raw rows of x and dy are fetched PF steps ahead: with about 150 registers per thread few warps
   // fit on an SM, so the loads in flight per thread decide the achieved bandwidth
-  constexpr int PF = 6;
+  constexpr int PF = 3;
   uint4 xq[PF], yq[PF];
 #pragma unroll
   for (int i = 0; i < PF; ++i) {

@@ -1056,12 +1056,12 @@ def inverse_blocks(idx: Tensor, nS: int, R: int, visits_per_cta: int):
     """Inverse of the selection map (count, scan, fill kernels of ``csrc/attention.cu``; no sort, the
     same lists on every run).  Same results as :func:`_inverse_blocks_torch`."""
     B, Hkv, T, n = idx.shape
-    if not idx.is_cuda or nS > 12288:
+    if not idx.is_cuda or nS > 12288 or n > 32:
         return _inverse_blocks_torch(idx, nS, R, visits_per_cta)
     dev = idx.device
     idx = idx.to(torch.int32).contiguous()
     lists = B * Hkv * nS
-    chunks = -(-T // 1024)
+    chunks = -(-T // 256)
     tok = _empty(B * Hkv * T * n, dtype=torch.int32, device=dev)
     list_start = _empty(lists + 1, dtype=torch.int32, device=dev)
     item_start = _empty(lists + 1, dtype=torch.int32, device=dev)
