@@ -416,23 +416,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 }
 
 // --------------------------------------------------------------------------------------
-// Forward, warp-specialised, Q and P in tensor memory (head_dim 128, output mode).  As the kernel
-// below, except that Q is copied once into TMEM and each group writes its probabilities over
-// the S columns they came from, so both MMAs take their A operand from TMEM and shared memory
-// carries only the K/V stream.
-// Forward, warp-specialised (head_dim 128, output mode).  Visits are 64-key blocks as in the
-// dQ kernel.  Warp 8 streams K/V through a 4-stage ring, warp 9 issues S = Q K^T and O += P V.
+// Forward, warp-specialised, Q and P in tensor memory (head_dim 128, output mode).  Visits are
+// 64-key blocks as in the dQ kernel.  Warp 8 streams K/V through a 5-stage ring, warp 9 issues
+// S = Q K^T and warp 10 issues O += P V.  Q is copied once into TMEM and each softmax group writes
+// its probabilities into TMEM columns of its own, so both MMAs take their A operand from TMEM and
+// shared memory carries only the K/V stream.  P has its own columns (not those of S): a group
+// releases its S buffer as soon as the scores are in registers, so S of its next visit is
+// computed while this visit is exponentiated and P V runs behind the softmax, not in its chain.
 // The 8 softmax warps form two groups of 128 threads (one thread per query row): group g takes
 // the visits with v mod 2 = g and runs its own online softmax over them, with its own running
 // maximum / sum, its own S buffer, P buffer and O accumulator in TMEM, so the groups never
 // exchange anything per visit; the two partial results are merged once at the end:
 //   m = max(m0, m1), O = (2^(m0-m) O0 + 2^(m1-m) O1) / (2^(m0-m) l0 + 2^(m1-m) l1).
-// tcgen05 MMAs complete in issue order, and S of visit v is issued after P V of visit v-2, so a
-// group that has received S_v may rescale its O accumulator in place.
+// A group waits for P V of its previous visit (p_empty) before it rescales its O accumulator in
+// place or overwrites P.
 // --------------------------------------------------------------------------------------
 constexpr int FWT_STAGES = 5;
 
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(352, 1)
 attn_fwd_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
   constexpr int D = 128;
@@ -449,7 +450,8 @@ attn_fwd_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   uint64_t* s_full = kv_empty + FWT_STAGES;       // [2]
   uint64_t* s_empty = s_full + 2;                // [2]
   uint64_t* p_full = s_empty + 2;                // [2]
-  uint64_t* qt_full = p_full + 2;                // softmax -> MMA: Q is in tensor memory
+  uint64_t* p_empty = p_full + 2;                // [2] MMA -> softmax: P V of the group's previous visit is done
+  uint64_t* qt_full = p_empty + 2;               // softmax -> MMA: Q is in tensor memory
   uint64_t* acc_done = qt_full + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -487,8 +489,9 @@ attn_fwd_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     for (int i = 0; i < FWT_STAGES; ++i) { tc5::mbar_init(kv_full + i, 1); tc5::mbar_init(kv_empty + i, 1); }
     for (int i = 0; i < 2; ++i) {
       tc5::mbar_init(s_full + i, 1);
-      tc5::mbar_init(s_empty + i, 1);
+      tc5::mbar_init(s_empty + i, 128);
       tc5::mbar_init(p_full + i, 128);
+      tc5::mbar_init(p_empty + i, 1);
     }
     tc5::mbar_init(qt_full, 256);
     tc5::mbar_init(acc_done, 1);
@@ -499,8 +502,8 @@ attn_fwd_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   __syncthreads();
   tc5::fence_after_sync();
   const uint32_t tmem = *tmem_slot;
-  // columns: S of group g at g*64; O of group g at 128 + g*128
-  constexpr uint32_t cO = 128, cQ = 384;
+  // columns: S of group g at g*64; O of group g at 128 + g*128; Q at 384; P of group g at 448 + g*32
+  constexpr uint32_t cO = 128, cQ = 384, cP = 448;
 
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
@@ -543,41 +546,62 @@ attn_fwd_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       }
     }
   } else if (warp == 9) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0 && n_vis > 0) {
+    // ------------------------------------------------------------------ MMA issuer 1: S = Q K^T
+    // Issuing one tcgen05.mma costs the issuing thread 70 to 100 cycles here (operands of 64 keys
+    // give the tensor pipe only 32 to 64 cycles of work each), so one thread issuing both products
+    // is the critical path of a visit.  The two products go to two warps; every dependency
+    // between them already runs through an mbarrier (p_full, s_empty, kv_empty).  Each issuing warp
+    // stays converged (all lanes wait, one elected lane issues).
+    if (n_vis > 0) {
+      const bool lead = tc5::elect_one();
       constexpr uint32_t id_s = tc5::make_idesc_bf16(128, 64, 0, 0);
-      constexpr uint32_t id_o = tc5::make_idesc_bf16(128, D, 0, 1);
       const uint64_t bK0 = tc5::desc_kmajor(tc5::smem_u32(sKV));
-      const uint64_t bVmn0 = tc5::desc_mnmajor(tc5::smem_u32(sKV) + 2 * HALF, HALF);
-      bool ok = tc5::mbar_wait(qt_full, 0, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL);
+      bool ok = __all_sync(0xffffffffu, tc5::mbar_wait(qt_full, 0, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL));
       if (ok) tc5::fence_after_sync();
-      for (int v = 0; v <= n_vis && ok; ++v) {
-        if (v < n_vis) {
-          const int st = v % FWT_STAGES, g = v & 1;
-          if (!tc5::mbar_wait(kv_full + st, (v / FWT_STAGES) & 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL)) { ok = false; break; }
-          if (!tc5::mbar_wait(s_empty + g, ((v >> 1) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
-          tc5::fence_after_sync();
-          const uint64_t bK = bK0 + static_cast<uint64_t>((st * 4 * HALF) >> 4);
+      for (int v = 0; v < n_vis && ok; ++v) {
+        const int st = v % FWT_STAGES, g = v & 1;
+        ok = __all_sync(0xffffffffu, tc5::mbar_wait(kv_full + st, (v / FWT_STAGES) & 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL) &&
+                                     tc5::mbar_wait(s_empty + g, ((v >> 1) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY));
+        if (!ok) break;
+        tc5::fence_after_sync();
+        const uint64_t bK = bK0 + static_cast<uint64_t>((st * 4 * HALF) >> 4);
+        if (lead) {
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk)
             tc5::mma_ts(tmem + g * 64, tmem + cQ + kk * 8, bK + static_cast<uint64_t>(((kk >> 2) * HALF + (kk & 3) * 32) >> 4), id_s,
                         kk > 0 ? 1u : 0u);
           tc5::mma_commit(s_full + g);
         }
-        if (v >= 1) {
-          const int u = v - 1, st = u % FWT_STAGES, g = u & 1;
-          if (!tc5::mbar_wait(p_full + g, (u >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
-          tc5::fence_after_sync();
-          const uint64_t bV = bVmn0 + static_cast<uint64_t>((st * 4 * HALF) >> 4);
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)          // O_g += P V: P sits in the first 32 columns of the group's S
-            tc5::mma_ts(tmem + cO + g * 128, tmem + g * 64 + kk * 8, bV + static_cast<uint64_t>((kk * 2048) >> 4), id_o,
-                        (u > 1 || kk > 0) ? 1u : 0u);
-          tc5::mma_commit(kv_empty + st);
-          tc5::mma_commit(s_empty + g);            // S / P columns of the group are free again
-        }
+        __syncwarp();
       }
-      if (ok) tc5::mma_commit(acc_done);
+    }
+  } else if (warp == 10) {
+    // ------------------------------------------------------------------ MMA issuer 2: O += P V
+    if (n_vis > 0) {
+      const bool lead = tc5::elect_one();
+      constexpr uint32_t id_o = tc5::make_idesc_bf16(128, D, 0, 1);
+      const uint64_t bVmn0 = tc5::desc_mnmajor(tc5::smem_u32(sKV) + 2 * HALF, HALF);
+      bool ok = true;
+      for (int u = 0; u < n_vis; ++u) {
+        const int st = u % FWT_STAGES, g = u & 1;
+        // V of this stage: the copy that completes kv_full brings K and V together
+        ok = __all_sync(0xffffffffu, tc5::mbar_wait(kv_full + st, (u / FWT_STAGES) & 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL) &&
+                                     tc5::mbar_wait(p_full + g, (u >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL));
+        if (!ok) break;
+        tc5::fence_after_sync();
+        const uint64_t bV = bVmn0 + static_cast<uint64_t>((st * 4 * HALF) >> 4);
+        if (lead) {
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)          // O_g += P V
+            tc5::mma_ts(tmem + cO + g * 128, tmem + cP + g * 32 + kk * 8, bV + static_cast<uint64_t>((kk * 2048) >> 4), id_o,
+                        (u > 1 || kk > 0) ? 1u : 0u);
+          // a commit covers the MMAs of this thread; S of this visit completed before P could be written
+          tc5::mma_commit(kv_empty + st);
+          tc5::mma_commit(p_empty + g);            // the group's P columns are free, its O accumulator is at rest
+        }
+        __syncwarp();
+      }
+      if (ok && lead) tc5::mma_commit(acc_done);
     }
   } else {
     // ------------------------------------------------------------------ softmax groups
@@ -629,6 +653,8 @@ attn_fwd_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       tc5::fence_after_sync();
       uint32_t sv[64];
       tmem_ld64(tmem + lane_off + grp * 64, sv);
+      tc5::fence_before_sync();
+      tc5::mbar_arrive(s_empty + grp);           // S of the group's next visit may be computed while this one is exponentiated
       bool check = false;
       float mx = -INFINITY;
       if (row_sel) {
@@ -682,7 +708,12 @@ attn_fwd_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
       }
       l_sum = l_sum * alpha + psum;
-      // O_g is quiescent here: P V of this group's previous visit completed before S of this visit
+      // P V of the group's previous visit must be done before P is overwritten or O rescaled
+      if (!__all_sync(0xffffffffu, tc5::mbar_wait(p_empty + grp, (n_mine & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY))) {
+        ok = false;
+        break;
+      }
+      tc5::fence_after_sync();
       if (n_mine > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll
         for (int q4 = 0; q4 < D / 32; ++q4) {
@@ -695,7 +726,7 @@ attn_fwd_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
         tc5::tmem_st_wait();
       }
-      tc5::tmem_st_x32(tmem + lane_off + grp * 64, pk);          // P over the first half of this row's S columns
+      tc5::tmem_st_x32(tmem + lane_off + cP + grp * 32, pk);
       tc5::tmem_st_wait();
       tc5::fence_before_sync();
       tc5::mbar_arrive(p_full + grp);
@@ -2735,7 +2766,7 @@ extern "C" int nsa_attn_fwd(const void* q, const void* k, const void* v, void* o
     const int smem_ts = (4 + 4 * FWT_STAGES) * HALF + 1024 + 1024 + 256;
     static bool cfg = false;
     if (!cfg) { if ((rc = set_smem(attn_fwd_ts_kernel, smem_ts))) return rc; cfg = true; }
-    attn_fwd_ts_kernel<<<grid, 320, smem_ts, st>>>(tq, tk, tv, p);
+    attn_fwd_ts_kernel<<<grid, 352, smem_ts, st>>>(tq, tk, tv, p);
   } else if (D == 128 && !legacy) {
     const int smem_ws = (4 + 4 * FW_STAGES + 4) * HALF + 1024 + 1024 + 256;
     static bool cfg = false;
