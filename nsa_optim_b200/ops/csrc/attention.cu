@@ -903,24 +903,29 @@ attn_importance_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
       }
     }
   } else if (warp == 9) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0 && n_vis > 0) {
+    // ------------------------------------------------------------------ MMA issuer (converged warp, elected lane issues)
+    if (n_vis > 0) {
+      const bool lead = tc5::elect_one();
       constexpr uint32_t id_s = tc5::make_idesc_bf16(128, 64, 0, 0);
       const uint64_t bK0 = tc5::desc_kmajor(tc5::smem_u32(sKV));
-      bool ok = tc5::mbar_wait(qt_full, 0, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL);
+      bool ok = __all_sync(0xffffffffu, tc5::mbar_wait(qt_full, 0, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL));
       if (ok) tc5::fence_after_sync();
       for (int v = 0; v < n_vis && ok; ++v) {
         const int st = v % IMP_STAGES, g = v & 1;
-        if (!tc5::mbar_wait(kv_full + st, (v / IMP_STAGES) & 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL)) { ok = false; break; }
-        if (!tc5::mbar_wait(s_empty + g, ((v >> 1) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+        ok = __all_sync(0xffffffffu, tc5::mbar_wait(kv_full + st, (v / IMP_STAGES) & 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL) &&
+                                     tc5::mbar_wait(s_empty + g, ((v >> 1) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY));
+        if (!ok) break;
         tc5::fence_after_sync();
         const uint64_t bK = bK0 + static_cast<uint64_t>((st * 2 * HALF) >> 4);
+        if (lead) {
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
-          tc5::mma_ts(tmem + g * 64, tmem + cQ + kk * 8, bK + static_cast<uint64_t>(((kk >> 2) * HALF + (kk & 3) * 32) >> 4), id_s,
-                      kk > 0 ? 1u : 0u);
-        tc5::mma_commit(s_full + g);
-        tc5::mma_commit(kv_empty + st);            // the K stage is free once S is complete
+          for (int kk = 0; kk < D / 16; ++kk)
+            tc5::mma_ts(tmem + g * 64, tmem + cQ + kk * 8, bK + static_cast<uint64_t>(((kk >> 2) * HALF + (kk & 3) * 32) >> 4), id_s,
+                        kk > 0 ? 1u : 0u);
+          tc5::mma_commit(s_full + g);
+          tc5::mma_commit(kv_empty + st);          // the K stage is free once S is complete
+        }
+        __syncwarp();
       }
     }
   } else {
@@ -1569,15 +1574,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 // tcgen05.mma; dS is written back into the S columns it was computed from (each thread into the
 // first half of its own column range) and is the A operand of dQ += dS K.  Shared memory then
 // carries only the K/V stream.  Same roles as the dK/dV kernel below:
-// warps 0-7 turn S and dP into dS, warp 8 streams 64-key K/V blocks through a 4-stage ring,
-// warp 9 issues S = Q K^T, dP = dO V^T (double-buffered in TMEM) and dQ += dS K (resident in
-// TMEM).  Visits are 64-key blocks: the contiguous range allowed by causality / window, or the
+// warps 0-7 turn S and dP into dS, warp 8 streams 64-key K/V blocks through a 5-stage ring,
+// warps 9, 10 and 11 issue S = Q K^T, dP = dO V^T (double-buffered in TMEM) and dQ += dS K
+// (resident in TMEM).  Visits are 64-key blocks: the contiguous range allowed by causality / window, or the
 // entries of the tile's union list (selected mode, with the per-token bit masks).
 // Needs D = 128.
 // --------------------------------------------------------------------------------------
 constexpr int DQT_STAGES = 5;
 
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(384, 1)
 attn_bwd_dq_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                    const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                    const AttnParams p, const float scale) {
@@ -1634,7 +1639,7 @@ attn_bwd_dq_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     *abort_flag = 0;
     tc5::mbar_init(q_full, 1);
     for (int i = 0; i < DQT_STAGES; ++i) { tc5::mbar_init(kv_full + i, 1); tc5::mbar_init(kv_empty + i, 1); }
-    for (int i = 0; i < 2; ++i) { tc5::mbar_init(s_full + i, 1); tc5::mbar_init(s_empty + i, 1); }
+    for (int i = 0; i < 2; ++i) { tc5::mbar_init(s_full + i, 2); tc5::mbar_init(s_empty + i, 1); }
     tc5::mbar_init(ds_full, 256);
     tc5::mbar_init(ds_full + 1, 256);
     tc5::mbar_init(qt_full, 256);
@@ -1693,51 +1698,64 @@ attn_bwd_dq_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         }
       }
     }
-  } else if (warp == 9) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0 && n_vis > 0) {
+  } else if (warp == 9 || warp == 10) {
+    // ------------------------------------------------------------------ MMA issuers 1 and 2: S = Q K^T, dP = dO V^T
+    // Three issuing warps, each converged with one elected lane issuing (see the forward kernel):
+    // warp 9 issues S, warp 10 dP, warp 11 dQ += dS K.  s_full counts one commit of each of the
+    // first two.  The address field (bits 0-13, address >> 4) of a shared-memory descriptor is
+    // advanced by adding the byte offset >> 4.
+    if (n_vis > 0) {
+      const bool lead = tc5::elect_one();
+      const bool is_dp = warp == 10;
       constexpr uint32_t id_s = tc5::make_idesc_bf16(128, 64, 0, 0);
-      constexpr uint32_t id_q = tc5::make_idesc_bf16(128, D, 0, 1);
-      // Every shared-memory descriptor is built once.  The address field (bits 0-13, address >> 4) of
-      // a descriptor can be advanced by adding the byte offset >> 4, so the per-visit work of this
-      // thread is one add per operand and the MMA itself: with 64-key MMAs of about 32 cycles the
-      // issuing thread's instruction count, not the tensor pipe, sets the pace otherwise.
-      const uint64_t bK0 = tc5::desc_kmajor(tc5::smem_u32(sKV));             // stage 0, K, k-step 0
-      const uint64_t bKmn0 = tc5::desc_mnmajor(tc5::smem_u32(sKV), HALF);    // same tile as an MN-major operand
-      bool ok = tc5::mbar_wait(qt_full, 0, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL);
+      const uint64_t b0 = tc5::desc_kmajor(tc5::smem_u32(sKV) + (is_dp ? 2 * HALF : 0));   // stage 0, K or V, k-step 0
+      const uint32_t acol = is_dp ? cDO : cQ, dcol = is_dp ? 64u : 0u;
+      bool ok = __all_sync(0xffffffffu, tc5::mbar_wait(qt_full, 0, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL));
       if (ok) tc5::fence_after_sync();
-      for (int v = 0; v <= n_vis && ok; ++v) {
-        if (v < n_vis) {
-          const int st = v % DQT_STAGES, buf = v & 1;
-          if (!tc5::mbar_wait(kv_full + st, (v / DQT_STAGES) & 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL)) { ok = false; break; }
-          if (!tc5::mbar_wait(s_empty + buf, ((v >> 1) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
-          tc5::fence_after_sync();
-          const uint64_t bK = bK0 + static_cast<uint64_t>((st * 4 * HALF) >> 4);
-          const uint64_t bV = bK + static_cast<uint64_t>((2 * HALF) >> 4);
+      for (int v = 0; v < n_vis && ok; ++v) {
+        const int st = v % DQT_STAGES, buf = v & 1;
+        ok = __all_sync(0xffffffffu, tc5::mbar_wait(kv_full + st, (v / DQT_STAGES) & 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL) &&
+                                     tc5::mbar_wait(s_empty + buf, ((v >> 1) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY));
+        if (!ok) break;
+        tc5::fence_after_sync();
+        const uint64_t bB = b0 + static_cast<uint64_t>((st * 4 * HALF) >> 4);
+        if (lead) {
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk)      // a k-step of 16 bf16 is 8 TMEM columns of the A operand
-            tc5::mma_ts(tmem + buf * 128, tmem + cQ + kk * 8, bK + static_cast<uint64_t>(((kk >> 2) * HALF + (kk & 3) * 32) >> 4),
-                        id_s, kk > 0 ? 1u : 0u);
-#pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk)
-            tc5::mma_ts(tmem + buf * 128 + 64, tmem + cDO + kk * 8, bV + static_cast<uint64_t>(((kk >> 2) * HALF + (kk & 3) * 32) >> 4),
+            tc5::mma_ts(tmem + buf * 128 + dcol, tmem + acol + kk * 8, bB + static_cast<uint64_t>(((kk >> 2) * HALF + (kk & 3) * 32) >> 4),
                         id_s, kk > 0 ? 1u : 0u);
           tc5::mma_commit(s_full + buf);
         }
-        if (v >= 1) {
-          const int u = v - 1, st = u % DQT_STAGES, buf = u & 1;
-          if (!tc5::mbar_wait(ds_full + buf, (u >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
-          tc5::fence_after_sync();
-          const uint64_t bKmn = bKmn0 + static_cast<uint64_t>((st * 4 * HALF) >> 4);
+        __syncwarp();
+      }
+    }
+  } else if (warp == 11) {
+    // ------------------------------------------------------------------ MMA issuer 3: dQ += dS K
+    if (n_vis > 0) {
+      const bool lead = tc5::elect_one();
+      constexpr uint32_t id_q = tc5::make_idesc_bf16(128, D, 0, 1);
+      const uint64_t bKmn0 = tc5::desc_mnmajor(tc5::smem_u32(sKV), HALF);    // the K tile as an MN-major operand
+      bool ok = true;
+      for (int u = 0; u < n_vis; ++u) {
+        const int st = u % DQT_STAGES, buf = u & 1;
+        ok = __all_sync(0xffffffffu, tc5::mbar_wait(kv_full + st, (u / DQT_STAGES) & 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL) &&
+                                     tc5::mbar_wait(ds_full + buf, (u >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL));
+        if (!ok) break;
+        tc5::fence_after_sync();
+        const uint64_t bKmn = bKmn0 + static_cast<uint64_t>((st * 4 * HALF) >> 4);
+        if (lead) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)          // dQ += dS K: keys 0-31 sit in columns 0-15, keys 32-63 in columns 32-47
             tc5::mma_ts(tmem + cDQ, tmem + buf * 128 + (kk >> 1) * 32 + (kk & 1) * 8, bKmn + static_cast<uint64_t>((kk * 2048) >> 4),
                         id_q, (u > 0 || kk > 0) ? 1u : 0u);
+          // S and dP of this visit completed before dS could be written, so the commits of this warp
+          // alone release the stage and the buffer
           tc5::mma_commit(kv_empty + st);
           tc5::mma_commit(s_empty + buf);          // the S / dP / dS columns of this buffer are free again
         }
+        __syncwarp();
       }
-      if (ok) tc5::mma_commit(acc_done);
+      if (ok && lead) tc5::mma_commit(acc_done);
     }
   } else {
     // ------------------------------------------------------------------ softmax warps
@@ -1856,9 +1874,9 @@ attn_bwd_dq_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
 // --------------------------------------------------------------------------------------
 // Backward for dQ, query-tile stationary, pipelined.  Same roles as the dK/dV kernel below:
-// warps 0-7 turn S and dP into dS, warp 8 streams 64-key K/V blocks through a 4-stage ring,
-// warp 9 issues S = Q K^T, dP = dO V^T (double-buffered in TMEM) and dQ += dS K (resident in
-// TMEM).  Visits are 64-key blocks: the contiguous range allowed by causality / window, or the
+// warps 0-7 turn S and dP into dS, warp 8 streams 64-key K/V blocks through a 5-stage ring,
+// warps 9, 10 and 11 issue S = Q K^T, dP = dO V^T (double-buffered in TMEM) and dQ += dS K
+// (resident in TMEM).  Visits are 64-key blocks: the contiguous range allowed by causality / window, or the
 // entries of the tile's union list (selected mode, with the per-token bit masks).
 // Needs D = 128.
 // --------------------------------------------------------------------------------------
@@ -2144,7 +2162,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 // dV^T (D x 64) += dO^T P and dK^T (D x 64) += Q^T dS stay in TMEM for the whole walk, so global
 // memory sees one fp32 reduction per CTA instead of one per (query tile, key tile) pair.
 // Roles: warps 0-7 softmax (thread (r, ch) = row r, 32 key columns), warp 8 TMA producer,
-// warp 9 MMA issuer.  Q/dO are double-buffered in shared memory and S/dP in TMEM: while the
+// warps 9-11 MMA issuers.  Q/dO are double-buffered in shared memory and S/dP in TMEM: while the
 // softmax warps work on visit v the tensor pipe runs S/dP of visit v+1 and dV/dK of visit v-1.
 // Needs D = 128 (the accumulators put D on the 128 TMEM lanes).
 // --------------------------------------------------------------------------------------
@@ -2156,7 +2174,7 @@ struct KvWalk {
   int n_lists, nS;
 };
 
-constexpr int KV_THREADS = 320;
+constexpr int KV_THREADS = 384;
 
 __global__ void __launch_bounds__(KV_THREADS, 1)
 attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
@@ -2229,13 +2247,13 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     tc5::mbar_init(kv_full, 1);
     for (int i = 0; i < 2; ++i) {
       tc5::mbar_init(q_full + i, 1);
-      tc5::mbar_init(q_empty + i, 1);
+      tc5::mbar_init(q_empty + i, 2);
       tc5::mbar_init(s_full + i, 1);
       tc5::mbar_init(s_empty + i, 256);
     }
     tc5::mbar_init(p_full, 256);
-    tc5::mbar_init(p_empty, 1);
-    tc5::mbar_init(acc_done, 1);
+    tc5::mbar_init(p_empty, 2);
+    tc5::mbar_init(acc_done, 2);
     tc5::fence_barrier_init();
   }
   if (warp == 9) { tc5::tmem_alloc(tmem_slot, 512); tc5::tmem_relinquish(); }
@@ -2307,60 +2325,68 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       }
     }
   } else if (warp == 9) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------------ MMA issuer 1: S = Q K^T, dP = dO V^T
+    // Three issuing warps, each converged with one elected lane issuing (see the forward kernel):
+    // warp 9 issues S and dP, warp 10 dV^T += dO^T P, warp 11 dK^T += Q^T dS.  q_empty, p_empty and
+    // acc_done count one commit of each of the last two.  (A thirteenth warp would put four warps on
+    // one scheduler and cap every thread at 128 registers.)
+    {
+      const bool lead = tc5::elect_one();
       constexpr uint32_t id_s = tc5::make_idesc_bf16(128, 64, 0, 0);
-      constexpr uint32_t id_t = tc5::make_idesc_bf16(128, 64, 1, 1);
-      // descriptors are built once; a buffer switch is an add on the address field (see the dQ kernel)
-      uint64_t bK[D / 16], bV[D / 16], bP[BM / 16], bDS[BM / 16];
-#pragma unroll
-      for (int kk = 0; kk < D / 16; ++kk) {
-        const uint32_t b_off = (kk >> 2) * HALF + (kk & 3) * 32;
-        bK[kk] = tc5::desc_kmajor(tc5::smem_u32(sK) + b_off);
-        bV[kk] = tc5::desc_kmajor(tc5::smem_u32(sV) + b_off);
-      }
-#pragma unroll
-      for (int kk = 0; kk < BM / 16; ++kk) {
-        bP[kk] = tc5::desc_mnmajor(tc5::smem_u32(sP) + kk * 2048, 2 * HALF);
-        bDS[kk] = tc5::desc_mnmajor(tc5::smem_u32(sDS) + kk * 2048, 2 * HALF);
-      }
       const uint64_t aQ0 = tc5::desc_kmajor(tc5::smem_u32(sQ)), aDO0 = tc5::desc_kmajor(tc5::smem_u32(sDO));
-      const uint64_t aQmn0 = tc5::desc_mnmajor(tc5::smem_u32(sQ), 2 * HALF), aDOmn0 = tc5::desc_mnmajor(tc5::smem_u32(sDO), 2 * HALF);
-      bool ok = tc5::mbar_wait(kv_full, 0, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL);
-      for (int v = 0; v <= n_vis && ok; ++v) {
-        if (v < n_vis) {
-          const int buf = v & 1;
-          const uint32_t ph = (v >> 1) & 1;
-          if (!tc5::mbar_wait(q_full + buf, ph, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL)) { ok = false; break; }
-          if (!tc5::mbar_wait(s_empty + buf, ph ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
-          tc5::fence_after_sync();
-          const uint64_t aQ = aQ0 + static_cast<uint64_t>((buf * QT) >> 4), aDO = aDO0 + static_cast<uint64_t>((buf * QT) >> 4);
+      const uint64_t bK0 = tc5::desc_kmajor(tc5::smem_u32(sK)), bV0 = tc5::desc_kmajor(tc5::smem_u32(sV));
+      bool ok = __all_sync(0xffffffffu, tc5::mbar_wait(kv_full, 0, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL));
+      for (int v = 0; v < n_vis && ok; ++v) {
+        const int buf = v & 1;
+        const uint32_t ph = (v >> 1) & 1;
+        ok = __all_sync(0xffffffffu, tc5::mbar_wait(q_full + buf, ph, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL) &&
+                                     tc5::mbar_wait(s_empty + buf, ph ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY));
+        if (!ok) break;
+        tc5::fence_after_sync();
+        const uint64_t aQ = aQ0 + static_cast<uint64_t>((buf * QT) >> 4), aDO = aDO0 + static_cast<uint64_t>((buf * QT) >> 4);
+        if (lead) {
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk)
-            tc5::mma_ss(tmem + buf * 128, aQ + static_cast<uint64_t>(((kk >> 2) * 2 * HALF + (kk & 3) * 32) >> 4), bK[kk], id_s,
-                        kk > 0 ? 1u : 0u);
+            tc5::mma_ss(tmem + buf * 128, aQ + static_cast<uint64_t>(((kk >> 2) * 2 * HALF + (kk & 3) * 32) >> 4),
+                        bK0 + static_cast<uint64_t>(((kk >> 2) * HALF + (kk & 3) * 32) >> 4), id_s, kk > 0 ? 1u : 0u);
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk)
-            tc5::mma_ss(tmem + buf * 128 + 64, aDO + static_cast<uint64_t>(((kk >> 2) * 2 * HALF + (kk & 3) * 32) >> 4), bV[kk], id_s,
-                        kk > 0 ? 1u : 0u);
+            tc5::mma_ss(tmem + buf * 128 + 64, aDO + static_cast<uint64_t>(((kk >> 2) * 2 * HALF + (kk & 3) * 32) >> 4),
+                        bV0 + static_cast<uint64_t>(((kk >> 2) * HALF + (kk & 3) * 32) >> 4), id_s, kk > 0 ? 1u : 0u);
           tc5::mma_commit(s_full + buf);
         }
-        if (v >= 1) {
-          const int u = v - 1, buf = u & 1;
-          if (!tc5::mbar_wait(p_full, u & 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL)) { ok = false; break; }
-          tc5::fence_after_sync();
-          const uint64_t aQmn = aQmn0 + static_cast<uint64_t>((buf * QT) >> 4), aDOmn = aDOmn0 + static_cast<uint64_t>((buf * QT) >> 4);
+        __syncwarp();
+      }
+    }
+  } else if (warp == 10 || warp == 11) {
+    // ------------------------------------------------------------------ MMA issuers 2 and 3: dV^T += dO^T P, dK^T += Q^T dS
+    {
+      const bool lead = tc5::elect_one();
+      const bool is_dk = warp == 11;
+      constexpr uint32_t id_t = tc5::make_idesc_bf16(128, 64, 1, 1);
+      const uint64_t a0 = tc5::desc_mnmajor(tc5::smem_u32(is_dk ? sQ : sDO), 2 * HALF);
+      const uint64_t b0 = tc5::desc_mnmajor(tc5::smem_u32(is_dk ? sDS : sP), 2 * HALF);
+      const uint32_t dcol = is_dk ? cDK : cDV;
+      bool ok = true;
+      for (int u = 0; u < n_vis; ++u) {
+        const int buf = u & 1;
+        ok = __all_sync(0xffffffffu, tc5::mbar_wait(p_full, u & 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL));
+        if (!ok) break;
+        tc5::fence_after_sync();
+        const uint64_t aA = a0 + static_cast<uint64_t>((buf * QT) >> 4);
+        if (lead) {
 #pragma unroll
-          for (int kk = 0; kk < BM / 16; ++kk)     // dV^T += dO^T P
-            tc5::mma_ss(tmem + cDV, aDOmn + static_cast<uint64_t>((kk * 2048) >> 4), bP[kk], id_t, (u > 0 || kk > 0) ? 1u : 0u);
-#pragma unroll
-          for (int kk = 0; kk < BM / 16; ++kk)     // dK^T += Q^T dS
-            tc5::mma_ss(tmem + cDK, aQmn + static_cast<uint64_t>((kk * 2048) >> 4), bDS[kk], id_t, (u > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < BM / 16; ++kk)
+            tc5::mma_ss(tmem + dcol, aA + static_cast<uint64_t>((kk * 2048) >> 4), b0 + static_cast<uint64_t>((kk * 2048) >> 4), id_t,
+                        (u > 0 || kk > 0) ? 1u : 0u);
+          // S and dP of this visit completed before P and dS could be written, so the commits of these
+          // two warps alone release the Q / dO buffer and the P / dS tiles
           tc5::mma_commit(q_empty + buf);
           tc5::mma_commit(p_empty);
         }
+        __syncwarp();
       }
-      if (ok) tc5::mma_commit(acc_done);
+      if (ok && lead) tc5::mma_commit(acc_done);
     }
   } else {
     // ------------------------------------------------------------------ softmax warps
@@ -2895,7 +2921,7 @@ extern "C" int nsa_attn_bwd_split(const void* q, const void* k, const void* v, c
       const int smem = (8 + 4 * DQT_STAGES) * HALF + 1024 + 256;
       static bool cfg = false;
       if (!cfg) { if ((rc = set_smem(attn_bwd_dq_ts_kernel, smem))) return rc; cfg = true; }
-      attn_bwd_dq_ts_kernel<<<grid, 320, smem, st>>>(tq, tdo, tk, tv, p, scale);
+      attn_bwd_dq_ts_kernel<<<grid, 384, smem, st>>>(tq, tdo, tk, tv, p, scale);
     } else {
       const int smem = (8 + 4 * DQ_STAGES + 2) * HALF + 1024 + 256;
       static bool cfg = false;
