@@ -973,13 +973,22 @@ attn_importance_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
 #pragma unroll
       for (int i = 0; i < 17; ++i) bins[i] = 0.f;
       if (row_ok) {
+        // the visibility test is decided once per visit: a test per element costs a branch per element
         const bool check = (sb + 63 >= p.S) || ((sb + 63) * p.kp_stride + p.kp_off > t);
+        if (!check) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) {
-          const bool vis = !check || key_visible(p, sb + i, t);
-          const float pr = vis ? exp2f(fmaf(__uint_as_float(sv[i]), sc, -Lrow)) : 0.f;
-          bins[i / 4] += pr;
-          bins[(i + 1) / 4] += pr;
+          for (int i = 0; i < 64; ++i) {
+            const float pr = exp2f(fmaf(__uint_as_float(sv[i]), sc, -Lrow));
+            bins[i / 4] += pr;
+            bins[(i + 1) / 4] += pr;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            const float pr = key_visible(p, sb + i, t) ? exp2f(fmaf(__uint_as_float(sv[i]), sc, -Lrow)) : 0.f;
+            bins[i / 4] += pr;
+            bins[(i + 1) / 4] += pr;
+          }
         }
       }
       for (int o = p.G >> 1; o > 0; o >>= 1)
@@ -1823,14 +1832,23 @@ attn_bwd_dq_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         bool check = sb + 31 >= p.S;
         if (p.causal) check = check || ((sb + 31) * p.kp_stride + p.kp_off > t);
         if (p.window > 0) check = check || (sb * p.kp_stride + p.kp_off <= t - p.window);
+        // the visibility test is decided once per visit: a test per element costs a branch per element
+        if (!check) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const bool v0_ = !check || key_visible(p, sb + i, t);
-          const bool v1_ = !check || key_visible(p, sb + i + 1, t);
-          const float p0 = v0_ ? exp2f(fmaf(__uint_as_float(sv[i]), sc, -Lrow)) : 0.f;
-          const float p1 = v1_ ? exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -Lrow)) : 0.f;
-          ds[i / 2] = tc5::pack_bf16(p0 * fmaf(__uint_as_float(dv[i]), scale, nds),
-                                     p1 * fmaf(__uint_as_float(dv[i + 1]), scale, nds));
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = exp2f(fmaf(__uint_as_float(sv[i]), sc, -Lrow));
+            const float p1 = exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -Lrow));
+            ds[i / 2] = tc5::pack_bf16(p0 * fmaf(__uint_as_float(dv[i]), scale, nds),
+                                       p1 * fmaf(__uint_as_float(dv[i + 1]), scale, nds));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = key_visible(p, sb + i, t) ? exp2f(fmaf(__uint_as_float(sv[i]), sc, -Lrow)) : 0.f;
+            const float p1 = key_visible(p, sb + i + 1, t) ? exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -Lrow)) : 0.f;
+            ds[i / 2] = tc5::pack_bf16(p0 * fmaf(__uint_as_float(dv[i]), scale, nds),
+                                       p1 * fmaf(__uint_as_float(dv[i + 1]), scale, nds));
+          }
         }
       }
       // dS replaces the first half of this thread's own S columns
@@ -2095,14 +2113,23 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         bool check = sb + 31 >= p.S;
         if (p.causal) check = check || ((sb + 31) * p.kp_stride + p.kp_off > t);
         if (p.window > 0) check = check || (sb * p.kp_stride + p.kp_off <= t - p.window);
+        // the visibility test is decided once per visit: a test per element costs a branch per element
+        if (!check) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const bool v0_ = !check || key_visible(p, sb + i, t);
-          const bool v1_ = !check || key_visible(p, sb + i + 1, t);
-          const float p0 = v0_ ? exp2f(fmaf(__uint_as_float(sv[i]), sc, -Lrow)) : 0.f;
-          const float p1 = v1_ ? exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -Lrow)) : 0.f;
-          ds[i / 2] = tc5::pack_bf16(p0 * fmaf(__uint_as_float(dv[i]), scale, nds),
-                                     p1 * fmaf(__uint_as_float(dv[i + 1]), scale, nds));
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = exp2f(fmaf(__uint_as_float(sv[i]), sc, -Lrow));
+            const float p1 = exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -Lrow));
+            ds[i / 2] = tc5::pack_bf16(p0 * fmaf(__uint_as_float(dv[i]), scale, nds),
+                                       p1 * fmaf(__uint_as_float(dv[i + 1]), scale, nds));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = key_visible(p, sb + i, t) ? exp2f(fmaf(__uint_as_float(sv[i]), sc, -Lrow)) : 0.f;
+            const float p1 = key_visible(p, sb + i + 1, t) ? exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -Lrow)) : 0.f;
+            ds[i / 2] = tc5::pack_bf16(p0 * fmaf(__uint_as_float(dv[i]), scale, nds),
+                                       p1 * fmaf(__uint_as_float(dv[i + 1]), scale, nds));
+          }
         }
       }
       if (!__all_sync(0xffffffffu, tc5::mbar_wait(ds_empty, (v & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_EMPTY))) {
@@ -2446,15 +2473,25 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         bool check = sb + 31 >= p.S;
         if (p.causal) check = check || ((sb + 31) * p.kp_stride + p.kp_off > t);
         if (p.window > 0) check = check || (sb * p.kp_stride + p.kp_off <= t - p.window);
+        // the visibility test is decided once per visit: a test per element costs a branch per element
+        if (!check) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const bool v0_ = !check || key_visible(p, sb + i, t);
-          const bool v1_ = !check || key_visible(p, sb + i + 1, t);
-          const float p0 = v0_ ? exp2f(fmaf(__uint_as_float(sv[i]), sc, -Lrow)) : 0.f;
-          const float p1 = v1_ ? exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -Lrow)) : 0.f;
-          pp[i / 2] = tc5::pack_bf16(p0, p1);
-          ds[i / 2] = tc5::pack_bf16(p0 * fmaf(__uint_as_float(dv[i]), scale, nds),
-                                     p1 * fmaf(__uint_as_float(dv[i + 1]), scale, nds));
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = exp2f(fmaf(__uint_as_float(sv[i]), sc, -Lrow));
+            const float p1 = exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -Lrow));
+            pp[i / 2] = tc5::pack_bf16(p0, p1);
+            ds[i / 2] = tc5::pack_bf16(p0 * fmaf(__uint_as_float(dv[i]), scale, nds),
+                                       p1 * fmaf(__uint_as_float(dv[i + 1]), scale, nds));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = key_visible(p, sb + i, t) ? exp2f(fmaf(__uint_as_float(sv[i]), sc, -Lrow)) : 0.f;
+            const float p1 = key_visible(p, sb + i + 1, t) ? exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -Lrow)) : 0.f;
+            pp[i / 2] = tc5::pack_bf16(p0, p1);
+            ds[i / 2] = tc5::pack_bf16(p0 * fmaf(__uint_as_float(dv[i]), scale, nds),
+                                       p1 * fmaf(__uint_as_float(dv[i + 1]), scale, nds));
+          }
         }
       }
       if (!__all_sync(0xffffffffu, tc5::mbar_wait(p_empty, (v & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_EMPTY))) {
