@@ -187,19 +187,24 @@ gdn_seq_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 #pragma unroll
     for (int j = 0; j < 32; ++j) upk[j] = upk_next[j];
     const float g = g_next;                        // decay applied to the state that enters chunk c + 1
-    if (r == 0) {
-      if (tc5::mbar_wait(&full[s], (c >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL)) {
+    if (warp == 0) {
+      // The issuing warp stays converged and one elected lane issues: descriptors then live in
+      // uniform registers and an MMA costs the issuing thread a few cycles instead of 70 to 100,
+      // which matters in a loop that is one dependent chain.
+      const bool lead = tc5::elect_one();
+      if (__all_sync(0xffffffffu, tc5::mbar_wait(&full[s], (c >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL))) {
         tc5::fence_after_sync();
-        const uint32_t a1 = tc5::smem_u32(st), sb = tc5::smem_u32(Sb);
+        const uint64_t a1 = tc5::desc_kmajor(tc5::smem_u32(st)), sb = tc5::desc_mnmajor(tc5::smem_u32(Sb), BOX);
+        if (lead) {
 #pragma unroll
-        for (int kk = 0; kk < KD / 16; ++kk) {
-          const uint64_t ad = tc5::desc_kmajor(a1 + (kk >> 2) * 2 * BOX + (kk & 3) * 32);
-          const uint64_t bd = tc5::desc_mnmajor(sb + kk * 2048, BOX);
-          tc5::mma_ss(tmem, ad, bd, idesc1, kk > 0 ? 1u : 0u);
+          for (int kk = 0; kk < KD / 16; ++kk)
+            tc5::mma_ss(tmem, a1 + static_cast<uint64_t>(((kk >> 2) * 2 * BOX + (kk & 3) * 32) >> 4),
+                        sb + static_cast<uint64_t>((kk * 2048) >> 4), idesc1, kk > 0 ? 1u : 0u);
+          tc5::mma_commit(m1);
+          if (c + 1 < NC) issue_loads(c + 1);
         }
-        tc5::mma_commit(m1);
-        if (c + 1 < NC) issue_loads(c + 1);
       }
+      __syncwarp();
     }
     // next chunk's u row (rows 0..63 only) and the decay after it, in flight while this chunk computes
     if (c + 1 < NC && r < CH) load_row_global(p.u + (row0 + CH + r) * V + vt * VT, upk_next);
@@ -228,16 +233,17 @@ gdn_seq_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     tc5::fence_proxy_async();
     tc5::fence_before_sync();
     __syncthreads();
-    if (r == 0) {
+    if (warp == 0) {
+      const bool lead = tc5::elect_one();
       tc5::fence_after_sync();
-      const uint32_t kt = tc5::smem_u32(st + 4 * BOX), vb = tc5::smem_u32(Vb);
+      const uint64_t kt = tc5::desc_mnmajor(tc5::smem_u32(st + 4 * BOX), BOX), vb = tc5::desc_mnmajor(tc5::smem_u32(Vb), BOX);
+      if (lead) {
 #pragma unroll
-      for (int kk = 0; kk < CH / 16; ++kk) {
-        const uint64_t ad = tc5::desc_mnmajor(kt + kk * 2048, BOX);
-        const uint64_t bd = tc5::desc_mnmajor(vb + kk * 2048, BOX);
-        tc5::mma_ss(tmem + 64, ad, bd, idesc2, 1u);
+        for (int kk = 0; kk < CH / 16; ++kk)
+          tc5::mma_ss(tmem + 64, kt + static_cast<uint64_t>((kk * 2048) >> 4), vb + static_cast<uint64_t>((kk * 2048) >> 4), idesc2, 1u);
+        tc5::mma_commit(m2);
       }
-      tc5::mma_commit(m2);
+      __syncwarp();
     }
     if (!tc5::mbar_wait(m2, c & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; }
     if (__syncthreads_or(!ok)) { ok = false; break; }
@@ -407,20 +413,26 @@ gdn_seq_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     tc5::fence_proxy_async();
     tc5::fence_before_sync();
     __syncthreads();
-    if (r == 0) {
-      if (tc5::mbar_wait(&full[s], (it >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL)) {
+    if (warp == 0) {
+      // converged issuing warp, one elected lane issues (see the forward kernel)
+      const bool lead = tc5::elect_one();
+      if (__all_sync(0xffffffffu, tc5::mbar_wait(&full[s], (it >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL))) {
         tc5::fence_after_sync();
-        const uint32_t a = tc5::smem_u32(st), dsb = tc5::smem_u32(dSb), av = tc5::smem_u32(AV);
+        const uint64_t a = tc5::desc_kmajor(tc5::smem_u32(st)), dsbm = tc5::desc_mnmajor(tc5::smem_u32(dSb), BOX);
+        const uint64_t dsbk = tc5::desc_kmajor(tc5::smem_u32(dSb)), av = tc5::desc_kmajor(tc5::smem_u32(AV));
+        if (lead) {
 #pragma unroll
-        for (int kk = 0; kk < KD / 16; ++kk)      // Da = [k_tail ; w] * dS
-          tc5::mma_ss(tmem + cDa, tc5::desc_kmajor(a + (kk >> 2) * 2 * BOX + (kk & 3) * 32),
-                      tc5::desc_mnmajor(dsb + kk * 2048, BOX), id_a, kk > 0 ? 1u : 0u);
+          for (int kk = 0; kk < KD / 16; ++kk)      // Da = [k_tail ; w] * dS
+            tc5::mma_ss(tmem + cDa, a + static_cast<uint64_t>(((kk >> 2) * 2 * BOX + (kk & 3) * 32) >> 4),
+                        dsbm + static_cast<uint64_t>((kk * 2048) >> 4), id_a, kk > 0 ? 1u : 0u);
 #pragma unroll
-        for (int kk = 0; kk < VT / 16; ++kk)      // Dc = [v_new ; do] * dS^T
-          tc5::mma_ss(tmem + cDc, tc5::desc_kmajor(av + kk * 32), tc5::desc_kmajor(dsb + kk * 32), id_c, kk > 0 ? 1u : 0u);
-        tc5::mma_commit(m1);
-        if (it + 1 < NC) issue_loads(c - 1, it + 1);
+          for (int kk = 0; kk < VT / 16; ++kk)      // Dc = [v_new ; do] * dS^T
+            tc5::mma_ss(tmem + cDc, av + static_cast<uint64_t>((kk * 32) >> 4), dsbk + static_cast<uint64_t>((kk * 32) >> 4), id_c, kk > 0 ? 1u : 0u);
+          tc5::mma_commit(m1);
+          if (it + 1 < NC) issue_loads(c - 1, it + 1);
+        }
       }
+      __syncwarp();
     }
     if (!tc5::mbar_wait(m1, it & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; }
     if (__syncthreads_or(!ok)) { ok = false; break; }
@@ -462,22 +474,26 @@ gdn_seq_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     tc5::fence_proxy_async();
     tc5::fence_before_sync();
     __syncthreads();
-    if (r == 0) {
-      p.dgamma_part[(static_cast<long>(vt) * p.BH + bh) * NC + c] = red[0] + red[1] + red[2] + red[3];
+    if (r == 0) p.dgamma_part[(static_cast<long>(vt) * p.BH + bh) * NC + c] = red[0] + red[1] + red[2] + red[3];
+    if (warp == 0) {
+      const bool lead = tc5::elect_one();
       tc5::fence_after_sync();
-      const uint32_t a = tc5::smem_u32(st), ad = tc5::smem_u32(AD), sp = tc5::smem_u32(st + 6 * BOX);
+      const uint64_t adk = tc5::desc_kmajor(tc5::smem_u32(AD)), spk = tc5::desc_kmajor(tc5::smem_u32(st + 6 * BOX));
+      const uint64_t qdm = tc5::desc_mnmajor(tc5::smem_u32(st + 4 * BOX), BOX), dom = tc5::desc_mnmajor(tc5::smem_u32(AD + BOX), BOX);
+      const uint64_t wm = tc5::desc_mnmajor(tc5::smem_u32(st + BOX), 2 * BOX), adm = tc5::desc_mnmajor(tc5::smem_u32(AD), BOX);
+      if (lead) {
 #pragma unroll
-      for (int kk = 0; kk < VT / 16; ++kk)        // Db = [dv_tot ; do] * S_prev^T
-        tc5::mma_ss(tmem + cDb, tc5::desc_kmajor(ad + kk * 32), tc5::desc_kmajor(sp + kk * 32), id_c, kk > 0 ? 1u : 0u);
+        for (int kk = 0; kk < VT / 16; ++kk)        // Db = [dv_tot ; do] * S_prev^T
+          tc5::mma_ss(tmem + cDb, adk + static_cast<uint64_t>((kk * 32) >> 4), spk + static_cast<uint64_t>((kk * 32) >> 4), id_c, kk > 0 ? 1u : 0u);
 #pragma unroll
-      for (int kk = 0; kk < CH / 16; ++kk)        // dS += q_dec^T * do      (do = rows 64..127 of AD)
-        tc5::mma_ss(tmem + cDs, tc5::desc_mnmajor(a + 4 * BOX + kk * 2048, BOX),
-                    tc5::desc_mnmajor(ad + BOX + kk * 2048, BOX), id_d, 1u);
+        for (int kk = 0; kk < CH / 16; ++kk)        // dS += q_dec^T * do      (do = rows 64..127 of AD)
+          tc5::mma_ss(tmem + cDs, qdm + static_cast<uint64_t>((kk * 2048) >> 4), dom + static_cast<uint64_t>((kk * 2048) >> 4), id_d, 1u);
 #pragma unroll
-      for (int kk = 0; kk < CH / 16; ++kk)        // dS -= w^T * dv_tot      (w = second half of each k-block)
-        tc5::mma_ss(tmem + cDs, tc5::desc_mnmajor(a + BOX + kk * 2048, 2 * BOX),
-                    tc5::desc_mnmajor(ad + kk * 2048, BOX), id_dn, 1u);
-      tc5::mma_commit(m2);
+        for (int kk = 0; kk < CH / 16; ++kk)        // dS -= w^T * dv_tot      (w = second half of each k-block)
+          tc5::mma_ss(tmem + cDs, wm + static_cast<uint64_t>((kk * 2048) >> 4), adm + static_cast<uint64_t>((kk * 2048) >> 4), id_dn, 1u);
+        tc5::mma_commit(m2);
+      }
+      __syncwarp();
     }
     if (!tc5::mbar_wait(m2, it & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; }
     if (__syncthreads_or(!ok)) { ok = false; break; }

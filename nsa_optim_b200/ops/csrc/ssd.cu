@@ -163,14 +163,20 @@ ssd_chunk_state_kernel(const __grid_constant__ CUtensorMap tm_bc, const __grid_c
   tc5::fence_proxy_async();
   tc5::fence_before_sync();
   if (__syncthreads_or(!ok)) ok = false;
-  if (ok && r == 0) {
+  if (ok && warp == 0) {
+    // the whole warp stays converged and one elected lane issues: descriptors then live in uniform
+    // registers and an MMA costs the issuing thread a few cycles instead of 70 to 100
+    const bool lead = tc5::elect_one();
     tc5::fence_after_sync();
     constexpr uint32_t idesc = tc5::make_idesc_bf16(128, PD, 1, 1);
-    const uint32_t a0 = tc5::smem_u32(sBC), v0 = tc5::smem_u32(sV);
+    const uint64_t a0 = tc5::desc_mnmajor(tc5::smem_u32(sBC), BOXB), v0 = tc5::desc_mnmajor(tc5::smem_u32(sV), BOXB);
+    if (lead) {
 #pragma unroll
-    for (int kk = 0; kk < L / 16; ++kk)
-      tc5::mma_ss(tmem, tc5::desc_mnmajor(a0 + kk * 2048, BOXB), tc5::desc_mnmajor(v0 + kk * 2048, BOXB), idesc, kk > 0 ? 1u : 0u);
-    tc5::mma_commit(done);
+      for (int kk = 0; kk < L / 16; ++kk)
+        tc5::mma_ss(tmem, a0 + static_cast<uint64_t>((kk * 2048) >> 4), v0 + static_cast<uint64_t>((kk * 2048) >> 4), idesc, kk > 0 ? 1u : 0u);
+      tc5::mma_commit(done);
+    }
+    __syncwarp();
   }
   if (ok && !tc5::mbar_wait(done, 0, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) ok = false;
   if (!__syncthreads_or(!ok)) {
@@ -193,7 +199,7 @@ ssd_chunk_state_kernel(const __grid_constant__ CUtensorMap tm_bc, const __grid_c
 __global__ void __launch_bounds__(128, 1)
 ssd_chunk_out_kernel(const __grid_constant__ CUtensorMap tm_c, const __grid_constant__ CUtensorMap tm_b,
                      const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_h,
-                     const SsdParams p) {
+                     const __grid_constant__ CUtensorMap tm_y, const SsdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sC = smem;                  // [2 k-blocks][128][64]
@@ -242,21 +248,27 @@ ssd_chunk_out_kernel(const __grid_constant__ CUtensorMap tm_c, const __grid_cons
   constexpr uint32_t id_s = tc5::make_idesc_bf16(128, 128, 0, 0);
   constexpr uint32_t id_y = tc5::make_idesc_bf16(128, PD, 0, 1);
   bool ok = true;
-  if (r == 0) {
-    if (tc5::mbar_wait(full, 0, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL)) {
+  if (warp == 0) {
+    // converged warp, elected lane issues (see ssd_chunk_state_kernel)
+    const bool lead = tc5::elect_one();
+    if (__all_sync(0xffffffffu, tc5::mbar_wait(full, 0, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL))) {
       tc5::fence_after_sync();
-      const uint32_t cc = tc5::smem_u32(sC), bb = tc5::smem_u32(sB), hh = tc5::smem_u32(sH);
+      const uint64_t cc = tc5::desc_kmajor(tc5::smem_u32(sC)), bb = tc5::desc_kmajor(tc5::smem_u32(sB));
+      const uint64_t hh = tc5::desc_mnmajor(tc5::smem_u32(sH), BOXB);
+      if (lead) {
 #pragma unroll
-      for (int kk = 0; kk < NS / 16; ++kk) {
-        const uint32_t off = (kk >> 2) * BOXB + (kk & 3) * 32;
-        tc5::mma_ss(tmem + cS, tc5::desc_kmajor(cc + off), tc5::desc_kmajor(bb + off), id_s, kk > 0 ? 1u : 0u);
+        for (int kk = 0; kk < NS / 16; ++kk) {
+          const uint64_t off = static_cast<uint64_t>(((kk >> 2) * BOXB + (kk & 3) * 32) >> 4);
+          tc5::mma_ss(tmem + cS, cc + off, bb + off, id_s, kk > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < NS / 16; ++kk)
+          tc5::mma_ss(tmem + cYi, cc + static_cast<uint64_t>(((kk >> 2) * BOXB + (kk & 3) * 32) >> 4),
+                      hh + static_cast<uint64_t>((kk * 2048) >> 4), id_y, kk > 0 ? 1u : 0u);
+        tc5::mma_commit(m1);
       }
-#pragma unroll
-      for (int kk = 0; kk < NS / 16; ++kk)
-        tc5::mma_ss(tmem + cYi, tc5::desc_kmajor(cc + (kk >> 2) * BOXB + (kk & 3) * 32),
-                    tc5::desc_mnmajor(hh + kk * 2048, BOXB), id_y, kk > 0 ? 1u : 0u);
-      tc5::mma_commit(m1);
     }
+    __syncwarp();
   }
   if (!tc5::mbar_wait(m1, 0, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) ok = false;
   if (__syncthreads_or(!ok)) ok = false;
@@ -270,9 +282,13 @@ ssd_chunk_out_kernel(const __grid_constant__ CUtensorMap tm_c, const __grid_cons
       uint32_t pk[32];
 #pragma unroll
       for (int j = 0; j < 64; j += 2) {
+        // operands fetched and the weight computed for every j, then selected: a conditional around
+        // the loads costs a branch per element
         const int j0 = half * 64 + j;
-        const float p0 = j0 <= r ? s[j] * exp2f(ci - cum[j0] * LOG2E) * dts[j0] : 0.f;
-        const float p1 = j0 + 1 <= r ? s[j + 1] * exp2f(ci - cum[j0 + 1] * LOG2E) * dts[j0 + 1] : 0.f;
+        const float2 cj = *reinterpret_cast<const float2*>(cum + j0), dj = *reinterpret_cast<const float2*>(dts + j0);
+        const float w0 = exp2f(fminf(ci - cj.x * LOG2E, 0.f)) * dj.x, w1 = exp2f(fminf(ci - cj.y * LOG2E, 0.f)) * dj.y;
+        const float p0 = j0 <= r ? s[j] * w0 : 0.f;
+        const float p1 = j0 + 1 <= r ? s[j + 1] * w1 : 0.f;
         pk[j / 2] = tc5::pack_bf16(p0, p1);
       }
       st_row64(sP + half * BOXB, r, pk);
@@ -281,39 +297,44 @@ ssd_chunk_out_kernel(const __grid_constant__ CUtensorMap tm_c, const __grid_cons
   tc5::fence_proxy_async();
   tc5::fence_before_sync();
   __syncthreads();
-  if (ok && r == 0) {
+  if (ok && warp == 0) {
+    const bool lead = tc5::elect_one();
     tc5::fence_after_sync();
-    const uint32_t pp = tc5::smem_u32(sP), xx = tc5::smem_u32(sX);
+    const uint64_t pp = tc5::desc_kmajor(tc5::smem_u32(sP)), xx = tc5::desc_mnmajor(tc5::smem_u32(sX), BOXB);
+    if (lead) {
 #pragma unroll
-    for (int kk = 0; kk < L / 16; ++kk)
-      tc5::mma_ss(tmem + cYo, tc5::desc_kmajor(pp + (kk >> 2) * BOXB + (kk & 3) * 32),
-                  tc5::desc_mnmajor(xx + kk * 2048, BOXB), id_y, kk > 0 ? 1u : 0u);
-    tc5::mma_commit(m2);
+      for (int kk = 0; kk < L / 16; ++kk)
+        tc5::mma_ss(tmem + cYo, pp + static_cast<uint64_t>(((kk >> 2) * BOXB + (kk & 3) * 32) >> 4),
+                    xx + static_cast<uint64_t>((kk * 2048) >> 4), id_y, kk > 0 ? 1u : 0u);
+      tc5::mma_commit(m2);
+    }
+    __syncwarp();
   }
   if (ok && !tc5::mbar_wait(m2, 0, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) ok = false;
   if (!__syncthreads_or(!ok)) {
     tc5::fence_after_sync();
+    // y leaves through shared memory and one TMA store (a thread owns a token row, so direct stores
+    // would write 16 bytes per thread into 32 different rows per instruction); x comes from its tile
     float yo[64], yi[64];
     tld64(tmem + lane_off + cYo, yo);
     tld64(tmem + lane_off + cYi, yi);
-    if (row_ok) {
-      const float e = exp2f(cm * LOG2E);
-      const float dsk = p.Dskip ? p.Dskip[h] : 0.f;
-      const bf16* xr = p.x_raw + (static_cast<long>(b) * p.T + t) * p.ldx + h * PD;
-      uint4* dst = reinterpret_cast<uint4*>(p.y + ((static_cast<long>(b) * p.T + t) * p.H + h) * PD);
+    const float e = exp2f(cm * LOG2E);
+    const float dsk = p.Dskip ? p.Dskip[h] : 0.f;
+    uint32_t o[32];
+    {
+      float xf[64];
+      ld_row64(sX, r, xf);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const uint4 xv = reinterpret_cast<const uint4*>(xr)[j];
-        const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&xv);
-        uint32_t o[4];
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const float2 xf = __bfloat1622float2(xh[k]);
-          const int i0 = 8 * j + 2 * k;
-          o[k] = tc5::pack_bf16(yo[i0] + e * yi[i0] + dsk * xf.x, yo[i0 + 1] + e * yi[i0 + 1] + dsk * xf.y);
-        }
-        dst[j] = make_uint4(o[0], o[1], o[2], o[3]);
-      }
+      for (int i = 0; i < 64; i += 2)
+        o[i / 2] = tc5::pack_bf16(yo[i] + e * yi[i] + dsk * xf[i], yo[i + 1] + e * yi[i + 1] + dsk * xf[i + 1]);
+    }
+    st_row64(sP, r, o);                 // the P tile is free once the second MMA is complete
+    tc5::fence_proxy_async();
+    __syncthreads();
+    if (r == 0) {                       // rows past T are clipped by the copy engine
+      tc5::tma_store_4d(&tm_y, sP, 0, h, t0, b);
+      tc5::tma_store_commit();
+      tc5::tma_store_wait_read<0>();
     }
   }
   tc5::fence_before_sync();
@@ -334,7 +355,8 @@ __global__ void __launch_bounds__(128, 1)
 ssd_chunk_grad_kernel(const __grid_constant__ CUtensorMap tm_c, const __grid_constant__ CUtensorMap tm_b,
                       const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_dy,
                       const __grid_constant__ CUtensorMap tm_h, const __grid_constant__ CUtensorMap tm_dh,
-                      const SsdParams p) {
+                      const __grid_constant__ CUtensorMap tm_dx, const __grid_constant__ CUtensorMap tm_dbh,
+                      const __grid_constant__ CUtensorMap tm_dch, const SsdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sC = smem;                  // 2 boxes
@@ -396,28 +418,34 @@ ssd_chunk_grad_kernel(const __grid_constant__ CUtensorMap tm_c, const __grid_con
   constexpr uint32_t id_kn128 = tc5::make_idesc_bf16(128, NS, 0, 1);  // K-major A, MN-major B -> [128 x 128]
   constexpr uint32_t id_tn128 = tc5::make_idesc_bf16(128, NS, 1, 1);  // MN-major A, MN-major B -> [128 x 128]
   bool ok = true;
-  if (r == 0) {
-    if (tc5::mbar_wait(full, 0, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL)) {
+  if (warp == 0) {
+    // converged warp, elected lane issues (see ssd_chunk_state_kernel)
+    const bool lead = tc5::elect_one();
+    if (__all_sync(0xffffffffu, tc5::mbar_wait(full, 0, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL))) {
       tc5::fence_after_sync();
-      const uint32_t cc = tc5::smem_u32(sC), bb = tc5::smem_u32(sB), xx = tc5::smem_u32(sX), dy = tc5::smem_u32(sDY);
-      const uint32_t hh = tc5::smem_u32(sH), dh = tc5::smem_u32(sDH);
+      const uint64_t cc = tc5::desc_kmajor(tc5::smem_u32(sC)), bb = tc5::desc_kmajor(tc5::smem_u32(sB));
+      const uint64_t xx = tc5::desc_kmajor(tc5::smem_u32(sX)), dy = tc5::desc_kmajor(tc5::smem_u32(sDY));
+      const uint64_t hh = tc5::desc_kmajor(tc5::smem_u32(sH)), dhm = tc5::desc_mnmajor(tc5::smem_u32(sDH), BOXB);
+      if (lead) {
 #pragma unroll
-      for (int kk = 0; kk < NS / 16; ++kk) {             // S = C B^T
-        const uint32_t off = (kk >> 2) * BOXB + (kk & 3) * 32;
-        tc5::mma_ss(tmem + cS, tc5::desc_kmajor(cc + off), tc5::desc_kmajor(bb + off), id_s, kk > 0 ? 1u : 0u);
+        for (int kk = 0; kk < NS / 16; ++kk) {             // S = C B^T
+          const uint64_t off = static_cast<uint64_t>(((kk >> 2) * BOXB + (kk & 3) * 32) >> 4);
+          tc5::mma_ss(tmem + cS, cc + off, bb + off, id_s, kk > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < PD / 16; ++kk)               // R = dy x^T
+          tc5::mma_ss(tmem + cR, dy + static_cast<uint64_t>((kk * 32) >> 4), xx + static_cast<uint64_t>((kk * 32) >> 4), id_s, kk > 0 ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < NS / 16; ++kk)               // dXi = B dHn   (row scale s_j applied later)
+          tc5::mma_ss(tmem + cDXI, bb + static_cast<uint64_t>(((kk >> 2) * BOXB + (kk & 3) * 32) >> 4),
+                      dhm + static_cast<uint64_t>((kk * 2048) >> 4), id_kn64, kk > 0 ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < PD / 16; ++kk)               // dCi = dy H^T  (row scale exp(cum_i) applied later)
+          tc5::mma_ss(tmem + cDCI, dy + static_cast<uint64_t>((kk * 32) >> 4), hh + static_cast<uint64_t>((kk * 32) >> 4), id_s, kk > 0 ? 1u : 0u);
+        tc5::mma_commit(m1);
       }
-#pragma unroll
-      for (int kk = 0; kk < PD / 16; ++kk)               // R = dy x^T
-        tc5::mma_ss(tmem + cR, tc5::desc_kmajor(dy + kk * 32), tc5::desc_kmajor(xx + kk * 32), id_s, kk > 0 ? 1u : 0u);
-#pragma unroll
-      for (int kk = 0; kk < NS / 16; ++kk)               // dXi = B dHn   (row scale s_j applied later)
-        tc5::mma_ss(tmem + cDXI, tc5::desc_kmajor(bb + (kk >> 2) * BOXB + (kk & 3) * 32),
-                    tc5::desc_mnmajor(dh + kk * 2048, BOXB), id_kn64, kk > 0 ? 1u : 0u);
-#pragma unroll
-      for (int kk = 0; kk < PD / 16; ++kk)               // dCi = dy H^T  (row scale exp(cum_i) applied later)
-        tc5::mma_ss(tmem + cDCI, tc5::desc_kmajor(dy + kk * 32), tc5::desc_kmajor(hh + kk * 32), id_s, kk > 0 ? 1u : 0u);
-      tc5::mma_commit(m1);
     }
+    __syncwarp();
   }
   // x rows scaled by s_j (operand of the state-path part of dB) while the MMAs run
   bool landed = tc5::mbar_wait(full, 0, abort_flag, p.status, STATUS_TIMEOUT_SMEM_FULL);
@@ -443,9 +471,12 @@ ssd_chunk_grad_kernel(const __grid_constant__ CUtensorMap tm_c, const __grid_con
       uint32_t pp[32], ds[32];
 #pragma unroll
       for (int j = 0; j < 64; j += 2) {
+        // operands fetched and the weight computed for every j, then selected (no branch per element)
         const int j0 = half * 64 + j;
-        const float w0 = j0 <= r ? exp2f(ci - cum[j0] * LOG2E) * dts[j0] : 0.f;
-        const float w1 = j0 + 1 <= r ? exp2f(ci - cum[j0 + 1] * LOG2E) * dts[j0 + 1] : 0.f;
+        const float2 cj = *reinterpret_cast<const float2*>(cum + j0), dj = *reinterpret_cast<const float2*>(dts + j0);
+        const float e0 = exp2f(fminf(ci - cj.x * LOG2E, 0.f)) * dj.x, e1 = exp2f(fminf(ci - cj.y * LOG2E, 0.f)) * dj.y;
+        const float w0 = j0 <= r ? e0 : 0.f;
+        const float w1 = j0 + 1 <= r ? e1 : 0.f;
         pp[j / 2] = tc5::pack_bf16(s[j] * w0, s[j + 1] * w1);
         ds[j / 2] = tc5::pack_bf16(rr[j] * w0, rr[j + 1] * w1);
         const float2 pr = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pp[j / 2]));
@@ -458,58 +489,62 @@ ssd_chunk_grad_kernel(const __grid_constant__ CUtensorMap tm_c, const __grid_con
   tc5::fence_proxy_async();
   tc5::fence_before_sync();
   __syncthreads();
-  if (ok && r == 0) {
+  if (ok && warp == 0) {
+    const bool lead = tc5::elect_one();
     tc5::fence_after_sync();
-    const uint32_t cc = tc5::smem_u32(sC), bb = tc5::smem_u32(sB), dy = tc5::smem_u32(sDY), dh = tc5::smem_u32(sDH);
-    const uint32_t pp = tc5::smem_u32(sP), ds = tc5::smem_u32(sDS), xs = tc5::smem_u32(sXS);
+    const uint64_t ccm = tc5::desc_mnmajor(tc5::smem_u32(sC), BOXB), bbm = tc5::desc_mnmajor(tc5::smem_u32(sB), BOXB);
+    const uint64_t dym = tc5::desc_mnmajor(tc5::smem_u32(sDY), BOXB), dh = tc5::desc_kmajor(tc5::smem_u32(sDH));
+    const uint64_t ppm = tc5::desc_mnmajor(tc5::smem_u32(sP), BOXB), ds = tc5::desc_kmajor(tc5::smem_u32(sDS));
+    const uint64_t dsm = tc5::desc_mnmajor(tc5::smem_u32(sDS), BOXB), xs = tc5::desc_kmajor(tc5::smem_u32(sXS));
+    if (lead) {
 #pragma unroll
-    for (int kk = 0; kk < L / 16; ++kk)                  // dX = P^T dy
-      tc5::mma_ss(tmem + cDX, tc5::desc_mnmajor(pp + kk * 2048, BOXB), tc5::desc_mnmajor(dy + kk * 2048, BOXB), id_tn64, kk > 0 ? 1u : 0u);
+      for (int kk = 0; kk < L / 16; ++kk)                  // dX = P^T dy
+        tc5::mma_ss(tmem + cDX, ppm + static_cast<uint64_t>((kk * 2048) >> 4), dym + static_cast<uint64_t>((kk * 2048) >> 4), id_tn64, kk > 0 ? 1u : 0u);
 #pragma unroll
-    for (int kk = 0; kk < L / 16; ++kk)                  // dC = dS B
-      tc5::mma_ss(tmem + cS, tc5::desc_kmajor(ds + (kk >> 2) * BOXB + (kk & 3) * 32),
-                  tc5::desc_mnmajor(bb + kk * 2048, BOXB), id_kn128, kk > 0 ? 1u : 0u);
+      for (int kk = 0; kk < L / 16; ++kk)                  // dC = dS B
+        tc5::mma_ss(tmem + cS, ds + static_cast<uint64_t>(((kk >> 2) * BOXB + (kk & 3) * 32) >> 4),
+                    bbm + static_cast<uint64_t>((kk * 2048) >> 4), id_kn128, kk > 0 ? 1u : 0u);
 #pragma unroll
-    for (int kk = 0; kk < L / 16; ++kk)                  // dB = dS^T C
-      tc5::mma_ss(tmem + cR, tc5::desc_mnmajor(ds + kk * 2048, BOXB), tc5::desc_mnmajor(cc + kk * 2048, BOXB), id_tn128, kk > 0 ? 1u : 0u);
+      for (int kk = 0; kk < L / 16; ++kk)                  // dB = dS^T C
+        tc5::mma_ss(tmem + cR, dsm + static_cast<uint64_t>((kk * 2048) >> 4), ccm + static_cast<uint64_t>((kk * 2048) >> 4), id_tn128, kk > 0 ? 1u : 0u);
 #pragma unroll
-    for (int kk = 0; kk < PD / 16; ++kk)                 // dB += (s x) dHn^T
-      tc5::mma_ss(tmem + cR, tc5::desc_kmajor(xs + kk * 32), tc5::desc_kmajor(dh + kk * 32), id_s, 1u);
-    tc5::mma_commit(m2);
+      for (int kk = 0; kk < PD / 16; ++kk)                 // dB += (s x) dHn^T
+        tc5::mma_ss(tmem + cR, xs + static_cast<uint64_t>((kk * 32) >> 4), dh + static_cast<uint64_t>((kk * 32) >> 4), id_s, 1u);
+      tc5::mma_commit(m2);
+    }
+    __syncwarp();
   }
   if (ok && !tc5::mbar_wait(m2, 0, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) ok = false;
   if (!__syncthreads_or(!ok)) {
     tc5::fence_after_sync();
+    // Outputs leave through shared memory and TMA stores: a thread owns a token row, so direct
+    // stores would write 16 bytes per thread into 32 different rows per instruction.  The operand
+    // tiles are free once the second group of MMAs is complete: dx goes to the x-scaled tile, dC
+    // to the P tile, dB to the dS tile.  x and dy are read back from their own tiles.
     const long tok = static_cast<long>(b) * p.T + t;
     const float e = exp2f(cm * LOG2E);
+    const bool heads = p.dB_heads != nullptr;
     {
       float dxa[64], dxi[64];
       tld64(tmem + lane_off + cDX, dxa);
       tld64(tmem + lane_off + cDXI, dxi);
-      if (row_ok) {
-        const float dsk = p.Dskip ? p.Dskip[h] : 0.f;
-        const bf16* xr = p.x_raw + tok * p.ldx + h * PD;
-        const bf16* dyr = p.dy_raw + (tok * p.H + h) * PD;
-        uint4* dst = reinterpret_cast<uint4*>(p.dx + (tok * p.H + h) * PD);
-        float kacc = 0.f, racc = 0.f;
+      const float dsk = p.Dskip ? p.Dskip[h] : 0.f;
+      float kacc = 0.f, racc = 0.f;
+      uint32_t o[32];
+      {
+        float xf[64], df[64];
+        ld_row64(sX, r, xf);
+        ld_row64(sDY, r, df);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint4 xv = reinterpret_cast<const uint4*>(xr)[j];
-          const uint4 dv = reinterpret_cast<const uint4*>(dyr)[j];
-          const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&xv);
-          const __nv_bfloat162* dh2 = reinterpret_cast<const __nv_bfloat162*>(&dv);
-          uint32_t o[4];
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const float2 xf = __bfloat1622float2(xh[k]), df = __bfloat1622float2(dh2[k]);
-            const int i0 = 8 * j + 2 * k;
-            const float g0 = dxa[i0] + s_row * dxi[i0], g1 = dxa[i0 + 1] + s_row * dxi[i0 + 1];
-            kacc += xf.x * g0 + xf.y * g1;
-            racc += xf.x * df.x + xf.y * df.y;
-            o[k] = tc5::pack_bf16(g0 + dsk * df.x, g1 + dsk * df.y);
-          }
-          dst[j] = make_uint4(o[0], o[1], o[2], o[3]);
+        for (int i = 0; i < 64; i += 2) {
+          const float g0 = dxa[i] + s_row * dxi[i], g1 = dxa[i + 1] + s_row * dxi[i + 1];
+          kacc += xf[i] * g0 + xf[i + 1] * g1;
+          racc += xf[i] * df[i] + xf[i + 1] * df[i + 1];
+          o[i / 2] = tc5::pack_bf16(g0 + dsk * df[i], g1 + dsk * df[i + 1]);
         }
+      }
+      st_row64(sXS, r, o);
+      if (row_ok) {
         p.k_out[tok * p.H + h] = kacc;
         if (p.r_out) p.r_out[tok * p.H + h] = racc;
       }
@@ -527,23 +562,15 @@ ssd_chunk_grad_kernel(const __grid_constant__ CUtensorMap tm_c, const __grid_con
 #pragma unroll
         for (int j = 0; j < 64; ++j) q_inter += cv[j] * dci[j];
       }
-      if (row_ok && p.dB_heads != nullptr) {
-        uint4* pc = reinterpret_cast<uint4*>(p.dC_heads + (tok * p.H + h) * NS + half * 64);
-        uint4* pb = reinterpret_cast<uint4*>(p.dB_heads + (tok * p.H + h) * NS + half * 64);
+      if (heads) {
+        uint32_t vc[32], vb[32];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          uint4 vc, vb;
-          vc.x = tc5::pack_bf16(dc[8 * j] + e * dci[8 * j], dc[8 * j + 1] + e * dci[8 * j + 1]);
-          vc.y = tc5::pack_bf16(dc[8 * j + 2] + e * dci[8 * j + 2], dc[8 * j + 3] + e * dci[8 * j + 3]);
-          vc.z = tc5::pack_bf16(dc[8 * j + 4] + e * dci[8 * j + 4], dc[8 * j + 5] + e * dci[8 * j + 5]);
-          vc.w = tc5::pack_bf16(dc[8 * j + 6] + e * dci[8 * j + 6], dc[8 * j + 7] + e * dci[8 * j + 7]);
-          vb.x = tc5::pack_bf16(db[8 * j], db[8 * j + 1]);
-          vb.y = tc5::pack_bf16(db[8 * j + 2], db[8 * j + 3]);
-          vb.z = tc5::pack_bf16(db[8 * j + 4], db[8 * j + 5]);
-          vb.w = tc5::pack_bf16(db[8 * j + 6], db[8 * j + 7]);
-          pc[j] = vc;
-          pb[j] = vb;
+        for (int j = 0; j < 32; ++j) {
+          vc[j] = tc5::pack_bf16(dc[2 * j] + e * dci[2 * j], dc[2 * j + 1] + e * dci[2 * j + 1]);
+          vb[j] = tc5::pack_bf16(db[2 * j], db[2 * j + 1]);
         }
+        st_row64(sP + half * BOXB, r, vc);
+        st_row64(sDS + half * BOXB, r, vb);
       } else if (row_ok) {
         float4* pc = reinterpret_cast<float4*>(p.dC_acc + tok * NS + half * 64);
         float4* pb = reinterpret_cast<float4*>(p.dB_acc + tok * NS + half * 64);
@@ -554,6 +581,19 @@ ssd_chunk_grad_kernel(const __grid_constant__ CUtensorMap tm_c, const __grid_con
           atomicAdd(pb + j, make_float4(db[4 * j], db[4 * j + 1], db[4 * j + 2], db[4 * j + 3]));
         }
       }
+    }
+    tc5::fence_proxy_async();
+    __syncthreads();
+    if (r == 0) {                       // rows past T are clipped by the copy engine
+      tc5::tma_store_4d(&tm_dx, sXS, 0, h, t0, b);
+      if (heads) {
+        tc5::tma_store_4d(&tm_dch, sP, 0, h, t0, b);
+        tc5::tma_store_4d(&tm_dch, sP + BOXB, 64, h, t0, b);
+        tc5::tma_store_4d(&tm_dbh, sDS, 0, h, t0, b);
+        tc5::tma_store_4d(&tm_dbh, sDS + BOXB, 64, h, t0, b);
+      }
+      tc5::tma_store_commit();
+      tc5::tma_store_wait_read<0>();    // shared memory must outlive the copies' reads
     }
     if (row_ok) p.q_out[tok * p.H + h] = q_intra + e * q_inter;
   }
@@ -603,6 +643,13 @@ int map_bc(CUtensorMap* m, const void* base, int B, int T, long ld) {
 int map_v(CUtensorMap* m, const void* base, int B, int T, int H, long ld) {
   uint64_t dims[4] = {(uint64_t)PD, (uint64_t)H, (uint64_t)T, (uint64_t)B};
   uint64_t strides[3] = {(uint64_t)PD * 2, (uint64_t)ld * 2, (uint64_t)T * ld * 2};
+  uint32_t box[4] = {64, 1, (uint32_t)L, 1};
+  return nsa::make_tmap_bf16(m, base, 4, dims, strides, box, 1);
+}
+int map_heads(CUtensorMap* m, const void* base, int B, int T, int H, bool real) {
+  if (!real) return map_v(m, base, B, T, H, static_cast<long>(H) * PD);
+  uint64_t dims[4] = {(uint64_t)NS, (uint64_t)H, (uint64_t)T, (uint64_t)B};
+  uint64_t strides[3] = {(uint64_t)NS * 2, (uint64_t)H * NS * 2, (uint64_t)T * H * NS * 2};
   uint32_t box[4] = {64, 1, (uint32_t)L, 1};
   return nsa::make_tmap_bf16(m, base, 4, dims, strides, box, 1);
 }
@@ -672,7 +719,7 @@ extern "C" int nsa_ssd_chunk_out(const void* Cm, long ld_c, const void* Bm, long
   int rc = check_dims(N, P, ld_c | ld_b, ld_x);
   if (rc) return rc;
   const int nc = (T + L - 1) / L;
-  CUtensorMap tc, tb, tx, th;
+  CUtensorMap tc, tb, tx, th, ty;
   if ((rc = map_bc(&tc, Cm, B, T, ld_c))) return rc;
   if ((rc = map_bc(&tb, Bm, B, T, ld_b))) return rc;
   if ((rc = map_v(&tx, x, B, T, H, ld_x))) return rc;
@@ -683,7 +730,8 @@ extern "C" int nsa_ssd_chunk_out(const void* Cm, long ld_c, const void* Bm, long
   const int smem = 8 * BOXB + 1024 + 2048;
   static bool cfg = false;
   if (!cfg) { if ((rc = smem_attr(ssd_chunk_out_kernel, smem))) return rc; cfg = true; }
-  ssd_chunk_out_kernel<<<dim3(nc, H, B), 128, smem, st>>>(tc, tb, tx, th, p);
+  if ((rc = map_v(&ty, y, B, T, H, static_cast<long>(H) * PD))) return rc;
+  ssd_chunk_out_kernel<<<dim3(nc, H, B), 128, smem, st>>>(tc, tb, tx, th, ty, p);
   nsa::count_launch();
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : nsa::fail_cuda(e, "nsa_ssd_chunk_out launch");
@@ -699,13 +747,17 @@ static int ssd_chunk_grad_impl(const void* Cm, long ld_c, const void* Bm, long l
   if (rc) return rc;
   const int nc = (T + L - 1) / L;
   const long rows = static_cast<long>(B) * nc * H * NS;
-  CUtensorMap tc, tb, tx, tdy, th, tdh;
+  CUtensorMap tc, tb, tx, tdy, th, tdh, tdx, tdbh, tdch;
   if ((rc = map_bc(&tc, Cm, B, T, ld_c))) return rc;
   if ((rc = map_bc(&tb, Bm, B, T, ld_b))) return rc;
   if ((rc = map_v(&tx, x, B, T, H, ld_x))) return rc;
   if ((rc = map_v(&tdy, dy, B, T, H, static_cast<long>(H) * PD))) return rc;
   if ((rc = map_state(&th, Hprev_bf16, rows))) return rc;
   if ((rc = map_state(&tdh, dHn_bf16, rows))) return rc;
+  if ((rc = map_v(&tdx, dx, B, T, H, static_cast<long>(H) * PD))) return rc;
+  // per-head dB / dC [B, T, H, N]; without them the maps point at dx and are never used
+  if ((rc = map_heads(&tdbh, dB_heads ? dB_heads : dx, B, T, H, dB_heads != nullptr))) return rc;
+  if ((rc = map_heads(&tdch, dC_heads ? dC_heads : dx, B, T, H, dC_heads != nullptr))) return rc;
   SsdParams p{};
   p.dt = dt; p.A = A; p.Dskip = Dskip; p.B = B; p.T = T; p.H = H; p.nc = nc;
   p.x_raw = (const bf16*)x; p.ldx = ld_x; p.y_in = (const bf16*)y; p.dy_raw = (const bf16*)dy; p.dx = (bf16*)dx;
@@ -714,7 +766,7 @@ static int ssd_chunk_grad_impl(const void* Cm, long ld_c, const void* Bm, long l
   const int smem = 13 * BOXB + 1024 + 2048;
   static bool cfg = false;
   if (!cfg) { if ((rc = smem_attr(ssd_chunk_grad_kernel, smem))) return rc; cfg = true; }
-  ssd_chunk_grad_kernel<<<dim3(nc, H, B), 128, smem, st>>>(tc, tb, tx, tdy, th, tdh, p);
+  ssd_chunk_grad_kernel<<<dim3(nc, H, B), 128, smem, st>>>(tc, tb, tx, tdy, th, tdh, tdx, tdbh, tdch, p);
   nsa::count_launch();
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : nsa::fail_cuda(e, "nsa_ssd_chunk_grad launch");
