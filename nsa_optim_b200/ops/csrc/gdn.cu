@@ -101,16 +101,19 @@ struct FwdParams {
 };
 
 constexpr int FWD_STAGE = 2 * 2 * BOX /*[w;qd] two k-blocks*/ + 2 * BOX /*k_tail*/;   // 48 KB
-constexpr int FWD_SMEM = 2 * FWD_STAGE + 2 * BOX /*Sb*/ + BOX /*Vb*/ + 1024 + 128;
+constexpr int FWD_SMEM = 2 * FWD_STAGE + 2 * BOX /*Sb*/ + BOX /*Vb*/ + 2 * BOX /*Ob*/ + 1024 + 128;
 
 __global__ void __launch_bounds__(128, 1)
 gdn_seq_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_qd,
-                   const __grid_constant__ CUtensorMap tm_kt, const FwdParams p) {
+                   const __grid_constant__ CUtensorMap tm_kt, const __grid_constant__ CUtensorMap tm_vn,
+                   const __grid_constant__ CUtensorMap tm_oi, const __grid_constant__ CUtensorMap tm_sa,
+                   const FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* Sb = smem + 2 * FWD_STAGE;           // [KD rows][64] bf16, B operand of MMA1
   uint8_t* Vb = Sb + 2 * BOX;                   // [64 rows][64] bf16, B operand of MMA2
-  uint64_t* bars = reinterpret_cast<uint64_t*>(Vb + BOX);
+  uint8_t* Ob = Vb + BOX;                       // [2 column halves][64 rows][32] fp32: o_inter on its way out
+  uint64_t* bars = reinterpret_cast<uint64_t*>(Ob + 2 * BOX);
   uint64_t* full = bars;        // [2]
   uint64_t* m1 = bars + 2;
   uint64_t* m2 = bars + 3;
@@ -154,6 +157,14 @@ gdn_seq_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   }
   tc5::fence_before_sync();
   __syncthreads();
+  // Outputs leave as TMA stores from the swizzled tiles they are in anyway (a thread owns a row, so
+  // direct stores would be 32 separate 16-byte writes per instruction; they were a third of the
+  // chunk loop).  One thread issues and waits; at most one store group stays pending across a point
+  // where a tile is overwritten.  Chunk 0 enters with the zero state that Sb holds now.
+  if (r == 0) {
+    tc5::tma_store_2d(&tm_sa, Sb, vt * VT, bh * NC * KD);
+    tc5::tma_store_commit();
+  }
 
   auto issue_loads = [&](int c) {
     const int s = c & 1;
@@ -209,6 +220,7 @@ gdn_seq_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     // next chunk's u row (rows 0..63 only) and the decay after it, in flight while this chunk computes
     if (c + 1 < NC && r < CH) load_row_global(p.u + (row0 + CH + r) * V + vt * VT, upk_next);
     if (c + 2 < NC) g_next = p.gamma[bh * NC + c + 2];
+    if (r == 0) tc5::tma_store_wait_read<1>();     // the previous chunk's v_new / o_inter tiles have been read
     if (!tc5::mbar_wait(m1, c & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; }
     if (__syncthreads_or(!ok)) { ok = false; break; }
     tc5::fence_after_sync();
@@ -223,16 +235,25 @@ gdn_seq_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         uint32_t pk[32];
         pack_row(d1, pk);
         write_row_swz(Vb, r, pk);
-        store_row_global(p.v_new + (row0 + r) * V + vt * VT, pk);
       } else {
-        float4* dst = reinterpret_cast<float4*>(p.o_inter + (row0 + r - CH) * V + vt * VT);
+        const int rr = r - CH;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) dst[j] = make_float4(d1[4 * j], d1[4 * j + 1], d1[4 * j + 2], d1[4 * j + 3]);
+        for (int half = 0; half < 2; ++half)
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<float4*>(Ob + half * BOX + rr * 128 + ((j ^ (rr & 7)) << 4)) =
+                make_float4(d1[half * 32 + 4 * j], d1[half * 32 + 4 * j + 1], d1[half * 32 + 4 * j + 2], d1[half * 32 + 4 * j + 3]);
       }
     }
     tc5::fence_proxy_async();
     tc5::fence_before_sync();
     __syncthreads();
+    if (r == 0) {
+      tc5::tma_store_2d(&tm_vn, Vb, vt * VT, static_cast<int>(row0));
+      tc5::tma_store_2d(&tm_oi, Ob, vt * VT, static_cast<int>(row0));
+      tc5::tma_store_2d(&tm_oi, Ob + BOX, vt * VT + 32, static_cast<int>(row0));
+      tc5::tma_store_commit();
+    }
     if (warp == 0) {
       const bool lead = tc5::elect_one();
       tc5::fence_after_sync();
@@ -245,6 +266,7 @@ gdn_seq_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       }
       __syncwarp();
     }
+    if (r == 0) tc5::tma_store_wait_read<1>();     // the previous state tile has been read
     if (!tc5::mbar_wait(m2, c & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; }
     if (__syncthreads_or(!ok)) { ok = false; break; }
     tc5::fence_after_sync();
@@ -254,7 +276,6 @@ gdn_seq_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       uint32_t pk[32];
       pack_row(sv, pk);
       write_row_swz(Sb, r, pk);
-      store_row_global(p.S_all + (static_cast<long>(bh * NC + c + 1) * KD + r) * V + vt * VT, pk);
 #pragma unroll
       for (int j = 0; j < 64; ++j) sv[j] *= g;
       tmem_st_row64(tS, sv);
@@ -262,14 +283,12 @@ gdn_seq_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     }
     tc5::fence_before_sync();
     __syncthreads();
+    if (r == 0 && c + 1 < NC) {
+      tc5::tma_store_2d(&tm_sa, Sb, vt * VT, (bh * NC + c + 1) * KD);
+      tc5::tma_store_commit();
+    }
   }
-  // chunk 0 enters with a zero state
-  {
-    uint32_t z[32];
-#pragma unroll
-    for (int j = 0; j < 32; ++j) z[j] = 0u;
-    store_row_global(p.S_all + (static_cast<long>(bh * NC) * KD + r) * V + vt * VT, z);
-  }
+  if (r == 0) tc5::tma_store_wait_read<0>();
   if (!ok && r == 0) {
     // a load for the next chunk may still be in flight: give it a bounded chance to land
     const long long t0 = clock64();
@@ -300,18 +319,25 @@ struct BwdParams {
 
 // stage: k-block kb of [k_tail ; w] (2 x 16 KB), q_dec (2 x 8 KB), S_prev [KD][64] (16 KB)
 constexpr int BWD_STAGE = 2 * 2 * BOX + 2 * BOX + 2 * BOX;                 // 64 KB
-constexpr int BWD_SMEM = 2 * BWD_STAGE + 2 * BOX /*[dv_tot;do]*/ + 2 * BOX /*[v_new;do]*/ + 2 * BOX /*dSb*/ + 1024 + 128;
+constexpr int BWD_SMEM = 2 * BWD_STAGE + 2 * BOX /*[dv_tot;do]*/ + 2 * BOX /*[v_new;do]*/ + 2 * BOX /*dSb*/ +
+                         2 * BOX /*dk_tail out*/ + 4 * BOX /*dw, dq_dec out*/ + 1024 + 128;
 
 __global__ void __launch_bounds__(128, 1)
 gdn_seq_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_qd,
                    const __grid_constant__ CUtensorMap tm_kt, const __grid_constant__ CUtensorMap tm_S,
+                   const __grid_constant__ CUtensorMap tm_du, const __grid_constant__ CUtensorMap tm_dkt,
+                   const __grid_constant__ CUtensorMap tm_dw, const __grid_constant__ CUtensorMap tm_dqd,
                    const BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* AD = smem + 2 * BWD_STAGE;     // [dv_tot (64 rows) ; do (64 rows)] x 64 cols
   uint8_t* AV = AD + 2 * BOX;             // [v_new ; do]
   uint8_t* dSb = AV + 2 * BOX;            // [KD rows][64] bf16 mirror of dS
-  uint64_t* bars = reinterpret_cast<uint64_t*>(dSb + 2 * BOX);
+  // Outputs leave as TMA stores from swizzled tiles (see the forward kernel): du straight from AD,
+  // the dk_tail partial from Kst, the -dw and dq_dec partials from Wst.
+  uint8_t* Kst = dSb + 2 * BOX;           // [2 k-blocks][64 rows][64]
+  uint8_t* Wst = Kst + 2 * BOX;           // [2 k-blocks][128 rows][64]: rows 0..63 -dw, rows 64..127 dq_dec
+  uint64_t* bars = reinterpret_cast<uint64_t*>(Wst + 4 * BOX);
   uint64_t* full = bars;
   uint64_t* m1 = bars + 2;
   uint64_t* m2 = bars + 3;
@@ -375,7 +401,7 @@ gdn_seq_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   constexpr uint32_t id_c = tc5::make_idesc_bf16(128, KD, 0, 0);        // [v_new;do] x dS^T  and  [dv_tot;do] x S^T
   constexpr uint32_t id_d = tc5::make_idesc_bf16(128, VT, 1, 1);        // q_dec^T x do
   constexpr uint32_t id_dn = tc5::make_idesc_bf16(128, VT, 1, 1, 1);    // (-w)^T x dv_tot
-  const long part_stride = static_cast<long>(p.BH) * NC * CH * KD;
+  const long part_rows = static_cast<long>(p.BH) * NC * CH;      // rows of one V tile's partials
   bool ok = true;
   // The chunk loop is one dependent chain: the rows that come straight from global memory (v_new and
   // dv_new for rows 0..63, do for rows 64..127) and the decay are fetched one chunk ahead, so their
@@ -434,6 +460,7 @@ gdn_seq_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       }
       __syncwarp();
     }
+    if (r == 0) tc5::tma_store_wait_read<1>();     // the previous chunk's du / dk_tail tiles have been read
     if (!tc5::mbar_wait(m1, it & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; }
     if (__syncthreads_or(!ok)) { ok = false; break; }
     tc5::fence_after_sync();
@@ -456,16 +483,14 @@ gdn_seq_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       uint32_t pk[32];
       pack_row(da, pk);
       write_row_swz(AD, r, pk);
-      store_row_global(p.du + (row0 + r) * V + vt * VT, pk);
       // dk_tail partial: row r of Dc, KD columns
-      bf16* dst = p.dkt_part + vt * part_stride + (row0 + r) * KD;
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         float dc[64];
         tmem_ld_row64(tmem + lane_off + cDc + h * 64, dc);
         uint32_t pk2[32];
         pack_row(dc, pk2);
-        store_row_global(dst + h * 64, pk2);
+        write_row_swz(Kst + h * BOX, r, pk2);
       }
     }
     // block reduction of the dgamma partial
@@ -474,7 +499,13 @@ gdn_seq_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     tc5::fence_proxy_async();
     tc5::fence_before_sync();
     __syncthreads();
-    if (r == 0) p.dgamma_part[(static_cast<long>(vt) * p.BH + bh) * NC + c] = red[0] + red[1] + red[2] + red[3];
+    if (r == 0) {
+      p.dgamma_part[(static_cast<long>(vt) * p.BH + bh) * NC + c] = red[0] + red[1] + red[2] + red[3];
+      tc5::tma_store_2d(&tm_du, AD, vt * VT, static_cast<int>(row0));
+      tc5::tma_store_2d(&tm_dkt, Kst, 0, static_cast<int>(vt * part_rows + row0));
+      tc5::tma_store_2d(&tm_dkt, Kst + BOX, 64, static_cast<int>(vt * part_rows + row0));
+      tc5::tma_store_commit();
+    }
     if (warp == 0) {
       const bool lead = tc5::elect_one();
       tc5::fence_after_sync();
@@ -495,12 +526,12 @@ gdn_seq_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       }
       __syncwarp();
     }
+    if (r == 0) tc5::tma_store_wait_read<1>();     // the previous chunk's dw / dq_dec tiles have been read
     if (!tc5::mbar_wait(m2, it & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; }
     if (__syncthreads_or(!ok)) { ok = false; break; }
     tc5::fence_after_sync();
     {
       // rows 0..63: -dw partial; rows 64..127: dq_dec partial
-      bf16* dst = (r < CH ? p.dw_part : p.dqd_part) + vt * part_stride + (row0 + (r & 63)) * KD;
       const float sign = r < CH ? -1.f : 1.f;
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
@@ -510,7 +541,7 @@ gdn_seq_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         for (int j = 0; j < 64; ++j) db[j] *= sign;
         uint32_t pk[32];
         pack_row(db, pk);
-        store_row_global(dst + h * 64, pk);
+        write_row_swz(Wst + h * 2 * BOX, r, pk);
       }
       float ds[64];
       tmem_ld_row64(tmem + lane_off + cDs, ds);
@@ -521,7 +552,17 @@ gdn_seq_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     tc5::fence_proxy_async();
     tc5::fence_before_sync();
     __syncthreads();
+    if (r == 0) {
+      const int prow = static_cast<int>(vt * part_rows + row0);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        tc5::tma_store_2d(&tm_dw, Wst + h * 2 * BOX, h * 64, prow);
+        tc5::tma_store_2d(&tm_dqd, Wst + h * 2 * BOX + BOX, h * 64, prow);
+      }
+      tc5::tma_store_commit();
+    }
   }
+  if (r == 0) tc5::tma_store_wait_read<0>();
   if (!ok && r == 0) {
     const long long t0 = clock64();
     for (int s = 0; s < 2; ++s)
@@ -552,6 +593,10 @@ extern "C" int nsa_gdn_seq_fwd(const void* w, const void* qd, const void* kt, co
   if ((rc = make_rows_map(&tw, w, rows, KD, 64))) return rc;
   if ((rc = make_rows_map(&tq, qd, rows, KD, 64))) return rc;
   if ((rc = make_rows_map(&tk, kt, rows, KD, 64))) return rc;
+  CUtensorMap tvn, toi, tsa;
+  if ((rc = make_rows_map(&tvn, v_new, rows, V, CH))) return rc;
+  if ((rc = nsa::make_tmap_2d_f32(&toi, o_inter, V, rows, V, 32, CH))) return rc;
+  if ((rc = make_rows_map(&tsa, S_all, static_cast<long>(BH) * NC * KD, V, KD))) return rc;
   FwdParams p{(const bf16*)u, gamma, (bf16*)v_new, o_inter, (bf16*)S_all, NC, V, nsa::status_ptr()};
   static bool configured = false;
   if (!configured) {
@@ -559,7 +604,7 @@ extern "C" int nsa_gdn_seq_fwd(const void* w, const void* qd, const void* kt, co
     if (e != cudaSuccess) return nsa::fail_cuda(e, "gdn fwd smem attribute");
     configured = true;
   }
-  gdn_seq_fwd_kernel<<<dim3(V / VT, BH), 128, FWD_SMEM, st>>>(tw, tq, tk, p);
+  gdn_seq_fwd_kernel<<<dim3(V / VT, BH), 128, FWD_SMEM, st>>>(tw, tq, tk, tvn, toi, tsa, p);
   nsa::count_launch();
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : nsa::fail_cuda(e, "nsa_gdn_seq_fwd launch");
@@ -578,6 +623,12 @@ extern "C" int nsa_gdn_seq_bwd(const void* w, const void* qd, const void* kt, co
   if ((rc = make_rows_map(&tq, qd, rows, KD, 64))) return rc;
   if ((rc = make_rows_map(&tk, kt, rows, KD, 64))) return rc;
   if ((rc = make_rows_map(&ts, S_all, static_cast<long>(BH) * NC * KD, V, KD))) return rc;
+  CUtensorMap tdu, tdkt, tdw, tdqd;
+  const long prows = rows * (V / VT);
+  if ((rc = make_rows_map(&tdu, du, rows, V, CH))) return rc;
+  if ((rc = make_rows_map(&tdkt, dkt_part, prows, KD, CH))) return rc;
+  if ((rc = make_rows_map(&tdw, dw_part, prows, KD, CH))) return rc;
+  if ((rc = make_rows_map(&tdqd, dqd_part, prows, KD, CH))) return rc;
   BwdParams p{(const bf16*)v_new, (const bf16*)dv_new, (const bf16*)d_o, gamma, (bf16*)du, (bf16*)dw_part,
               (bf16*)dqd_part, (bf16*)dkt_part, dgamma_part, NC, V, BH, nsa::status_ptr()};
   static bool configured = false;
@@ -586,7 +637,7 @@ extern "C" int nsa_gdn_seq_bwd(const void* w, const void* qd, const void* kt, co
     if (e != cudaSuccess) return nsa::fail_cuda(e, "gdn bwd smem attribute");
     configured = true;
   }
-  gdn_seq_bwd_kernel<<<dim3(V / VT, BH), 128, BWD_SMEM, st>>>(tw, tq, tk, ts, p);
+  gdn_seq_bwd_kernel<<<dim3(V / VT, BH), 128, BWD_SMEM, st>>>(tw, tq, tk, ts, tdu, tdkt, tdw, tdqd, p);
   nsa::count_launch();
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : nsa::fail_cuda(e, "nsa_gdn_seq_bwd launch");
