@@ -123,6 +123,27 @@ __device__ __forceinline__ bool key_visible(const AttnParams& p, int s, int t) {
   return v;
 }
 
+// Scores of keys sb .. sb+N-1 that query position t may not see become -inf, so that the loops
+// after it need no test per element (exp2 of -inf is 0).  The visible keys of a row form one index
+// range [lo, hi), computed once: a test per element inside the loops costs a branch per element.
+template <int N>
+__device__ __forceinline__ void mask_scores(const AttnParams& p, uint32_t (&sv)[N], int sb, int t) {
+  int hi = min(N, p.S - sb), lo = 0;
+  if (p.causal) {                       // (sb + i) stride + off <= t
+    const int num = t - p.kp_off;
+    const int last = num >= 0 ? num / p.kp_stride : -1;
+    hi = min(hi, last - sb + 1);
+  }
+  if (p.window > 0) {                   // (sb + i) stride + off > t - window
+    const int w = t - p.window - p.kp_off + 1;
+    const int first = w <= 0 ? 0 : (w + p.kp_stride - 1) / p.kp_stride;
+    lo = max(0, first - sb);
+  }
+#pragma unroll
+  for (int i = 0; i < N; ++i)
+    if (i < lo || i >= hi) sv[i] = 0xff800000u;
+}
+
 __device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&v)[64]) {
   uint32_t a[32], b[32];
   tc5::tmem_ld_x32(taddr, a);
@@ -483,6 +504,11 @@ attn_fwd_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     n_vis = last < first ? 0 : static_cast<int>(last / 64) + 1 - kb0;
   }
 
+  if (warp == 8 && lane == 0) {        // descriptor fetch off the first copy's critical path
+    tc5::prefetch_tensormap(&tm_q);
+    tc5::prefetch_tensormap(&tm_k);
+    tc5::prefetch_tensormap(&tm_v);
+  }
   if (tid == 0) {
     *abort_flag = 0;
     tc5::mbar_init(q_full, 1);
@@ -661,21 +687,16 @@ attn_fwd_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         check = sb + 63 >= p.S;
         if (p.causal) check = check || ((sb + 63) * p.kp_stride + p.kp_off > t);
         if (p.window > 0) check = check || (sb * p.kp_stride + p.kp_off <= t - p.window);
-        if (!check) {
-          // four independent chains: one serial chain of 64 dependent maxima is about 250 cycles of
-          // pure latency on the critical path of every visit
-          float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        if (check) mask_scores<64>(p, sv, sb, t);
+        // four independent chains: one serial chain of 64 dependent maxima is about 250 cycles of
+        // pure latency on the critical path of every visit
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-          for (int i = 0; i < 64; i += 4) {
+        for (int i = 0; i < 64; i += 4) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) m4[q] = fmaxf(m4[q], __uint_as_float(sv[i + q]));
-          }
-          mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 64; ++i)
-            if (key_visible(p, sb + i, t)) mx = fmaxf(mx, __uint_as_float(sv[i]));
+          for (int q = 0; q < 4; ++q) m4[q] = fmaxf(m4[q], __uint_as_float(sv[i + q]));
         }
+        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       }
       mx *= sc;
       float alpha = 1.f;
@@ -688,24 +709,16 @@ attn_fwd_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (!row_sel || m_ref == -INFINITY) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) pk[i] = 0u;
-      } else if (!check) {
+      } else {
         float s4[4] = {0.f, 0.f, 0.f, 0.f};               // independent partial sums (see the maxima above)
 #pragma unroll
-        for (int i = 0; i < 64; i += 2) {
+        for (int i = 0; i < 64; i += 2) {                 // masked scores are -inf: their probability is 0
           const float a = exp2f(fmaf(__uint_as_float(sv[i]), sc, -m_ref));
           const float c = exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -m_ref));
           s4[(i >> 1) & 3] += a + c;
           pk[i / 2] = tc5::pack_bf16(a, c);
         }
         psum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
-      } else {
-#pragma unroll
-        for (int i = 0; i < 64; i += 2) {
-          const float a = key_visible(p, sb + i, t) ? exp2f(fmaf(__uint_as_float(sv[i]), sc, -m_ref)) : 0.f;
-          const float c = key_visible(p, sb + i + 1, t) ? exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -m_ref)) : 0.f;
-          psum += a + c;
-          pk[i / 2] = tc5::pack_bf16(a, c);
-        }
       }
       l_sum = l_sum * alpha + psum;
       // P V of the group's previous visit must be done before P is overwritten or O rescaled
@@ -844,6 +857,10 @@ attn_importance_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     n_vis = last < first ? 0 : static_cast<int>(last / 64) + 1 - kb0;
   }
 
+  if (warp == 8 && lane == 0) {        // descriptor fetch off the first copy's critical path
+    tc5::prefetch_tensormap(&tm_q);
+    tc5::prefetch_tensormap(&tm_k);
+  }
   if (tid == 0) {
     *abort_flag = 0;
     tc5::mbar_init(q_full, 1);
@@ -938,6 +955,7 @@ attn_importance_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     const long rowi = (static_cast<long>(b) * p.T + (row_ok ? t : 0)) * p.Hq + h * p.G + gh;
     const float sc = p.scale_log2;
     const float Lrow = row_ok ? p.L_in[rowi] : 0.f;
+    const float negL = Lrow == -INFINITY ? -INFINITY : -Lrow;     // a row that sees no key: -inf - inf, not -inf + inf
     bool ok = true;
     if (n_vis > 0) {
       // Q: shared memory (swizzled [128 rows][64] k-blocks) -> TMEM; thread (r, grp) copies k-block grp of its row
@@ -973,22 +991,13 @@ attn_importance_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
 #pragma unroll
       for (int i = 0; i < 17; ++i) bins[i] = 0.f;
       if (row_ok) {
-        // the visibility test is decided once per visit: a test per element costs a branch per element
         const bool check = (sb + 63 >= p.S) || ((sb + 63) * p.kp_stride + p.kp_off > t);
-        if (!check) {
+        if (check) mask_scores<64>(p, sv, sb, t);
 #pragma unroll
-          for (int i = 0; i < 64; ++i) {
-            const float pr = exp2f(fmaf(__uint_as_float(sv[i]), sc, -Lrow));
-            bins[i / 4] += pr;
-            bins[(i + 1) / 4] += pr;
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 64; ++i) {
-            const float pr = key_visible(p, sb + i, t) ? exp2f(fmaf(__uint_as_float(sv[i]), sc, -Lrow)) : 0.f;
-            bins[i / 4] += pr;
-            bins[(i + 1) / 4] += pr;
-          }
+        for (int i = 0; i < 64; ++i) {                    // masked scores are -inf: their probability is 0
+          const float pr = exp2f(fmaf(__uint_as_float(sv[i]), sc, negL));
+          bins[i / 4] += pr;
+          bins[(i + 1) / 4] += pr;
         }
       }
       for (int o = p.G >> 1; o > 0; o >>= 1)
@@ -1218,21 +1227,16 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         check = sb + 63 >= p.S;
         if (p.causal) check = check || ((sb + 63) * p.kp_stride + p.kp_off > t);
         if (p.window > 0) check = check || (sb * p.kp_stride + p.kp_off <= t - p.window);
-        if (!check) {
-          // four independent chains: one serial chain of 64 dependent maxima is about 250 cycles of
-          // pure latency on the critical path of every visit
-          float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        if (check) mask_scores<64>(p, sv, sb, t);
+        // four independent chains: one serial chain of 64 dependent maxima is about 250 cycles of
+        // pure latency on the critical path of every visit
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-          for (int i = 0; i < 64; i += 4) {
+        for (int i = 0; i < 64; i += 4) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) m4[q] = fmaxf(m4[q], __uint_as_float(sv[i + q]));
-          }
-          mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 64; ++i)
-            if (key_visible(p, sb + i, t)) mx = fmaxf(mx, __uint_as_float(sv[i]));
+          for (int q = 0; q < 4; ++q) m4[q] = fmaxf(m4[q], __uint_as_float(sv[i + q]));
         }
+        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       }
       mx *= sc;
       float alpha = 1.f;
@@ -1245,24 +1249,16 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (!row_sel || m_ref == -INFINITY) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) pk[i] = 0u;
-      } else if (!check) {
+      } else {
         float s4[4] = {0.f, 0.f, 0.f, 0.f};               // independent partial sums (see the maxima above)
 #pragma unroll
-        for (int i = 0; i < 64; i += 2) {
+        for (int i = 0; i < 64; i += 2) {                 // masked scores are -inf: their probability is 0
           const float a = exp2f(fmaf(__uint_as_float(sv[i]), sc, -m_ref));
           const float c = exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -m_ref));
           s4[(i >> 1) & 3] += a + c;
           pk[i / 2] = tc5::pack_bf16(a, c);
         }
         psum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
-      } else {
-#pragma unroll
-        for (int i = 0; i < 64; i += 2) {
-          const float a = key_visible(p, sb + i, t) ? exp2f(fmaf(__uint_as_float(sv[i]), sc, -m_ref)) : 0.f;
-          const float c = key_visible(p, sb + i + 1, t) ? exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -m_ref)) : 0.f;
-          psum += a + c;
-          pk[i / 2] = tc5::pack_bf16(a, c);
-        }
       }
       l_sum = l_sum * alpha + psum;
       // O_g is quiescent here: P V of this group's previous visit completed before S of this visit
@@ -1644,6 +1640,12 @@ attn_bwd_dq_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     n_vis = last < first ? 0 : static_cast<int>(last / 64) + 1 - kb0;
   }
 
+  if (warp == 8 && lane == 0) {        // descriptor fetch off the first copy's critical path
+    tc5::prefetch_tensormap(&tm_q);
+    tc5::prefetch_tensormap(&tm_do);
+    tc5::prefetch_tensormap(&tm_k);
+    tc5::prefetch_tensormap(&tm_v);
+  }
   if (tid == 0) {
     *abort_flag = 0;
     tc5::mbar_init(q_full, 1);
@@ -1775,6 +1777,7 @@ attn_bwd_dq_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const long rowi = (static_cast<long>(b) * p.T + (row_ok ? t : 0)) * p.Hq + h * p.G + g;
     const float Lrow = row_ok ? p.L[rowi] : 0.f;
+    const float negL = Lrow == -INFINITY ? -INFINITY : -Lrow;     // a row that sees no key: -inf - inf, not -inf + inf
     const float drow = row_ok ? p.delta[rowi] : 0.f;
     const float nds = -drow * scale;
     const float sc = p.scale_log2;
@@ -1832,23 +1835,13 @@ attn_bwd_dq_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         bool check = sb + 31 >= p.S;
         if (p.causal) check = check || ((sb + 31) * p.kp_stride + p.kp_off > t);
         if (p.window > 0) check = check || (sb * p.kp_stride + p.kp_off <= t - p.window);
-        // the visibility test is decided once per visit: a test per element costs a branch per element
-        if (!check) {
+        if (check) mask_scores<32>(p, sv, sb, t);
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float p0 = exp2f(fmaf(__uint_as_float(sv[i]), sc, -Lrow));
-            const float p1 = exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -Lrow));
-            ds[i / 2] = tc5::pack_bf16(p0 * fmaf(__uint_as_float(dv[i]), scale, nds),
-                                       p1 * fmaf(__uint_as_float(dv[i + 1]), scale, nds));
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float p0 = key_visible(p, sb + i, t) ? exp2f(fmaf(__uint_as_float(sv[i]), sc, -Lrow)) : 0.f;
-            const float p1 = key_visible(p, sb + i + 1, t) ? exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -Lrow)) : 0.f;
-            ds[i / 2] = tc5::pack_bf16(p0 * fmaf(__uint_as_float(dv[i]), scale, nds),
-                                       p1 * fmaf(__uint_as_float(dv[i + 1]), scale, nds));
-          }
+        for (int i = 0; i < 32; i += 2) {                 // masked scores are -inf: their probability is 0
+          const float p0 = exp2f(fmaf(__uint_as_float(sv[i]), sc, negL));
+          const float p1 = exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, negL));
+          ds[i / 2] = tc5::pack_bf16(p0 * fmaf(__uint_as_float(dv[i]), scale, nds),
+                                     p1 * fmaf(__uint_as_float(dv[i + 1]), scale, nds));
         }
       }
       // dS replaces the first half of this thread's own S columns
@@ -2075,6 +2068,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const long rowi = (static_cast<long>(b) * p.T + (row_ok ? t : 0)) * p.Hq + h * p.G + g;
     const float Lrow = row_ok ? p.L[rowi] : 0.f;
+    const float negL = Lrow == -INFINITY ? -INFINITY : -Lrow;     // a row that sees no key: -inf - inf, not -inf + inf
     const float drow = row_ok ? p.delta[rowi] : 0.f;
     const float nds = -drow * scale;
     const float sc = p.scale_log2;
@@ -2113,23 +2107,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         bool check = sb + 31 >= p.S;
         if (p.causal) check = check || ((sb + 31) * p.kp_stride + p.kp_off > t);
         if (p.window > 0) check = check || (sb * p.kp_stride + p.kp_off <= t - p.window);
-        // the visibility test is decided once per visit: a test per element costs a branch per element
-        if (!check) {
+        if (check) mask_scores<32>(p, sv, sb, t);
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float p0 = exp2f(fmaf(__uint_as_float(sv[i]), sc, -Lrow));
-            const float p1 = exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -Lrow));
-            ds[i / 2] = tc5::pack_bf16(p0 * fmaf(__uint_as_float(dv[i]), scale, nds),
-                                       p1 * fmaf(__uint_as_float(dv[i + 1]), scale, nds));
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float p0 = key_visible(p, sb + i, t) ? exp2f(fmaf(__uint_as_float(sv[i]), sc, -Lrow)) : 0.f;
-            const float p1 = key_visible(p, sb + i + 1, t) ? exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -Lrow)) : 0.f;
-            ds[i / 2] = tc5::pack_bf16(p0 * fmaf(__uint_as_float(dv[i]), scale, nds),
-                                       p1 * fmaf(__uint_as_float(dv[i + 1]), scale, nds));
-          }
+        for (int i = 0; i < 32; i += 2) {                 // masked scores are -inf: their probability is 0
+          const float p0 = exp2f(fmaf(__uint_as_float(sv[i]), sc, negL));
+          const float p1 = exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, negL));
+          ds[i / 2] = tc5::pack_bf16(p0 * fmaf(__uint_as_float(dv[i]), scale, nds),
+                                     p1 * fmaf(__uint_as_float(dv[i + 1]), scale, nds));
         }
       }
       if (!__all_sync(0xffffffffu, tc5::mbar_wait(ds_empty, (v & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_EMPTY))) {
@@ -2445,6 +2429,7 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       const int buf = v & 1;
       const int t = t_cur;
       const float Lrow = L_cur, nds = -d_cur * scale;
+      const float negL = Lrow == -INFINITY ? -INFINITY : -Lrow;   // a row that sees no key: -inf - inf, not -inf + inf
       {
         float Ln = 0.f, dn = 0.f;
         if (t_nxt >= 0) {
@@ -2473,25 +2458,14 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         bool check = sb + 31 >= p.S;
         if (p.causal) check = check || ((sb + 31) * p.kp_stride + p.kp_off > t);
         if (p.window > 0) check = check || (sb * p.kp_stride + p.kp_off <= t - p.window);
-        // the visibility test is decided once per visit: a test per element costs a branch per element
-        if (!check) {
+        if (check) mask_scores<32>(p, sv, sb, t);
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float p0 = exp2f(fmaf(__uint_as_float(sv[i]), sc, -Lrow));
-            const float p1 = exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -Lrow));
-            pp[i / 2] = tc5::pack_bf16(p0, p1);
-            ds[i / 2] = tc5::pack_bf16(p0 * fmaf(__uint_as_float(dv[i]), scale, nds),
-                                       p1 * fmaf(__uint_as_float(dv[i + 1]), scale, nds));
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float p0 = key_visible(p, sb + i, t) ? exp2f(fmaf(__uint_as_float(sv[i]), sc, -Lrow)) : 0.f;
-            const float p1 = key_visible(p, sb + i + 1, t) ? exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -Lrow)) : 0.f;
-            pp[i / 2] = tc5::pack_bf16(p0, p1);
-            ds[i / 2] = tc5::pack_bf16(p0 * fmaf(__uint_as_float(dv[i]), scale, nds),
-                                       p1 * fmaf(__uint_as_float(dv[i + 1]), scale, nds));
-          }
+        for (int i = 0; i < 32; i += 2) {                 // masked scores are -inf: their probability is 0
+          const float p0 = exp2f(fmaf(__uint_as_float(sv[i]), sc, negL));
+          const float p1 = exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, negL));
+          pp[i / 2] = tc5::pack_bf16(p0, p1);
+          ds[i / 2] = tc5::pack_bf16(p0 * fmaf(__uint_as_float(dv[i]), scale, nds),
+                                     p1 * fmaf(__uint_as_float(dv[i + 1]), scale, nds));
         }
       }
       if (!__all_sync(0xffffffffu, tc5::mbar_wait(p_empty, (v & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_SMEM_EMPTY))) {
