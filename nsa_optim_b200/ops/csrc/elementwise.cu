@@ -845,165 +845,234 @@ __global__ void __launch_bounds__(256) rope_kernel(const bf16* __restrict__ x, c
 
 // ------------------------------------------------------------------------------------
 // Causal depthwise conv1d, width W <= 4, channel-last (B, T, C), optional bias and SiLU.
-// Each thread owns 8 channels and walks TCHUNK consecutive time steps with a register window.
+// A CTA owns CT_C channels and walks CT_SEG consecutive tiles of CT_T time steps.  The rows of a
+// tile reach shared memory through cp.async, the next tile's rows while the current tile is
+// computed, so global loads are always in flight and never on a thread's dependency chain; the
+// taps read shared memory.  Thread (rg, c8): 8 channels c8*8.., rows rg, rg+16, ... of the tile.
 // ------------------------------------------------------------------------------------
-constexpr int CONV_TCHUNK = 32;
+constexpr int CT_T = 64, CT_C = 128, CT_SEG = 8, CT_THREADS = 256, CT_RG = CT_THREADS / (CT_C / 8);
+constexpr int CONV_TCHUNK = CT_T * CT_SEG;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool pred) {   // zero fill when !pred
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  const int n = pred ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gmem), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 template <int W>
-__global__ void __launch_bounds__(128) conv1d_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
-                                                         const bf16* __restrict__ bias, bf16* __restrict__ y,
-                                                         int T, int C, long ldx, int act) {
-  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
-  if (c >= C) return;
-  const int t0 = blockIdx.y * CONV_TCHUNK;
+__global__ void __launch_bounds__(CT_THREADS) conv1d_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
+                                                                const bf16* __restrict__ bias, bf16* __restrict__ y,
+                                                                int T, int C, long ldx, int act) {
+  constexpr int XR = CT_T + W - 1;
+  __shared__ __align__(16) bf16 sx[2][XR * CT_C];                // x rows t0-(W-1) .. t0+CT_T-1 of a tile
+  const int c8 = threadIdx.x % (CT_C / 8), rg = threadIdx.x / (CT_C / 8);
+  const int c = blockIdx.x * CT_C + c8 * 8;
   const long b = blockIdx.z;
+  const bool c_ok = c < C;
+  const int seg0 = blockIdx.y * CT_SEG;
+  const int n_tiles = min(CT_SEG, (T + CT_T - 1) / CT_T - seg0);
+  auto load_tile = [&](int n, int buf) {
+    const int t0 = (seg0 + n) * CT_T;
+    for (int i = rg; i < XR; i += CT_RG) {
+      const int t = t0 - (W - 1) + i;
+      const bool ok = c_ok && t >= 0 && t < T;
+      cp_async16(sx[buf] + i * CT_C + c8 * 8, ok ? x + (b * T + t) * ldx + c : x, ok);
+    }
+    cp_async_commit();
+  };
+  load_tile(0, 0);
   float wv[W][8], bv[8];
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
-    bv[k] = bias ? __bfloat162float(bias[c + k]) : 0.f;
+    bv[k] = (bias && c_ok) ? __bfloat162float(bias[c + k]) : 0.f;
 #pragma unroll
-    for (int j = 0; j < W; ++j) wv[j][k] = __bfloat162float(w[(c + k) * W + j]);
+    for (int j = 0; j < W; ++j) wv[j][k] = c_ok ? __bfloat162float(w[(c + k) * W + j]) : 0.f;
   }
-  float win[W][8];
+  for (int n = 0; n < n_tiles; ++n) {
+    const int buf = n & 1;
+    if (n + 1 < n_tiles) { load_tile(n + 1, buf ^ 1); cp_async_wait<1>(); }
+    else cp_async_wait<0>();
+    __syncthreads();
+    const int t0 = (seg0 + n) * CT_T;
+    if (c_ok) {
+      for (int i = rg; i < CT_T; i += CT_RG) {
+        const int t = t0 + i;
+        if (t >= T) break;
+        float o[8];
 #pragma unroll
-  for (int j = 0; j < W - 1; ++j) {
-    const int t = t0 - (W - 1) + j;
-    if (t >= 0) load8(x + (b * T + t) * ldx + c, win[j + 1]);
-    else {
+        for (int k = 0; k < 8; ++k) o[k] = bv[k];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) win[j + 1][k] = 0.f;
+        for (int j = 0; j < W; ++j) {
+          float xv[8];
+          unpack8(*reinterpret_cast<const uint4*>(sx[buf] + (i + j) * CT_C + c8 * 8), xv);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) o[k] += wv[j][k] * xv[k];
+        }
+        if (act) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) o[k] = silu_f(o[k]);
+        }
+        store8(y + (b * T + t) * C + c, o);
+      }
     }
-  }
-  for (int tt = 0; tt < CONV_TCHUNK; ++tt) {
-    const int t = t0 + tt;
-    if (t >= T) break;
-#pragma unroll
-    for (int j = 0; j < W - 1; ++j)
-#pragma unroll
-      for (int k = 0; k < 8; ++k) win[j][k] = win[j + 1][k];
-    load8(x + (b * T + t) * ldx + c, win[W - 1]);
-    float o[8];
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      float acc = bv[k];
-#pragma unroll
-      for (int j = 0; j < W; ++j) acc += wv[j][k] * win[j][k];
-      o[k] = act ? silu_f(acc) : acc;
-    }
-    store8(y + (b * T + t) * C + c, o);
+    __syncthreads();                                // the buffer is refilled two tiles on
   }
 }
 
-// Backward: dx[t] = sum_j w[j] * dpre[t + (W-1) - j];  partial dw[j], db per (time chunk, batch).
-// partial layout: [chunk][ (W+1) ][C]   (row W = bias gradient), chunk = blockIdx.z*gridDim.y + blockIdx.y
+// Backward: dpre[t] = dy[t] (times SiLU'(pre[t]), pre recomputed from x), dx[s] = sum_j w[j] dpre[s + (W-1) - j],
+// dw[j] = sum_t dpre[t] x[t - (W-1) + j], db = sum_t dpre[t].  A tile needs dpre on CT_T + W - 1
+// rows, hence x on CT_T + 2 (W - 1) rows.  Weight and bias gradients stay in registers over the
+// CTA's tiles and leave as one partial sum per (time segment, batch): partial layout
+// [chunk][W + 1][C] (row W = bias gradient), chunk = blockIdx.z * gridDim.y + blockIdx.y; each time
+// step is counted by one tile only, and every sum runs in a fixed order.
 template <int W>
-__global__ void __launch_bounds__(128) conv1d_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
-                                                         const bf16* __restrict__ bias, const bf16* __restrict__ dy,
-                                                         bf16* __restrict__ dx, float* __restrict__ partial,
-                                                         int T, int C, long ldx, int act) {
-  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
-  if (c >= C) return;
-  const int t0 = blockIdx.y * CONV_TCHUNK;
+__global__ void __launch_bounds__(CT_THREADS) conv1d_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
+                                                                const bf16* __restrict__ bias, const bf16* __restrict__ dy,
+                                                                bf16* __restrict__ dx, float* __restrict__ partial,
+                                                                int T, int C, long ldx, int act) {
+  constexpr int XR = CT_T + 2 * (W - 1), DR = CT_T + W - 1;
+  extern __shared__ __align__(16) uint8_t conv_smem[];
+  bf16* sx0 = reinterpret_cast<bf16*>(conv_smem);                // [2][XR][CT_C]  x rows t0-(W-1) ..
+  bf16* sdy0 = sx0 + 2 * XR * CT_C;                              // [2][DR][CT_C]  dy rows t0 ..
+  float* sdp = reinterpret_cast<float*>(sdy0 + 2 * DR * CT_C);   // [DR][CT_C]     dpre rows t0 ..
+  float* sred = reinterpret_cast<float*>(conv_smem);             // [warps][W + 1][CT_C], over the x tiles once they are dead
+  const int c8 = threadIdx.x % (CT_C / 8), rg = threadIdx.x / (CT_C / 8);
+  const int c = blockIdx.x * CT_C + c8 * 8;
   const long b = blockIdx.z;
+  const bool c_ok = c < C;
+  const int seg0 = blockIdx.y * CT_SEG;
+  const int n_tiles = min(CT_SEG, (T + CT_T - 1) / CT_T - seg0);
+  auto load_tile = [&](int n, int buf) {
+    const int t0 = (seg0 + n) * CT_T;
+    bf16* sx = sx0 + buf * XR * CT_C;
+    bf16* sdy = sdy0 + buf * DR * CT_C;
+    for (int i = rg; i < XR; i += CT_RG) {
+      const int t = t0 - (W - 1) + i;
+      const bool ok = c_ok && t >= 0 && t < T;
+      cp_async16(sx + i * CT_C + c8 * 8, ok ? x + (b * T + t) * ldx + c : x, ok);
+    }
+    for (int i = rg; i < DR; i += CT_RG) {
+      const int t = t0 + i;
+      const bool ok = c_ok && t < T;
+      cp_async16(sdy + i * CT_C + c8 * 8, ok ? dy + (b * T + t) * C + c : dy, ok);
+    }
+    cp_async_commit();
+  };
+  load_tile(0, 0);
   float wv[W][8], bv[8];
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
-    bv[k] = bias ? __bfloat162float(bias[c + k]) : 0.f;
+    bv[k] = (bias && c_ok) ? __bfloat162float(bias[c + k]) : 0.f;
 #pragma unroll
-    for (int j = 0; j < W; ++j) wv[j][k] = __bfloat162float(w[(c + k) * W + j]);
+    for (int j = 0; j < W; ++j) wv[j][k] = c_ok ? __bfloat162float(w[(c + k) * W + j]) : 0.f;
   }
-  // dpre over [t0, t0 + TCHUNK + W - 1) is needed for dx on [t0, t0+TCHUNK); recompute pre-activations.
-  float xw[W][8];       // x window ending at the current time step
-  float dq[W][8];       // dpre[t], dpre[t-1], ... ring: dq[0] = newest
   float dwacc[W][8], dbacc[8];
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
     dbacc[k] = 0.f;
 #pragma unroll
-    for (int j = 0; j < W; ++j) { dwacc[j][k] = 0.f; dq[j][k] = 0.f; }
+    for (int j = 0; j < W; ++j) dwacc[j][k] = 0.f;
   }
+  for (int n = 0; n < n_tiles; ++n) {
+    const int buf = n & 1;
+    const bf16* sx = sx0 + buf * XR * CT_C;
+    const bf16* sdy = sdy0 + buf * DR * CT_C;
+    if (n + 1 < n_tiles) { load_tile(n + 1, buf ^ 1); cp_async_wait<1>(); }
+    else cp_async_wait<0>();
+    __syncthreads();
+    const int t0 = (seg0 + n) * CT_T;
+    // ---- dpre (rows past T hold dy = 0, so their dpre is 0)
+    for (int i = rg; i < DR; i += CT_RG) {
+      float dv[8], dp[8];
+      unpack8(*reinterpret_cast<const uint4*>(sdy + i * CT_C + c8 * 8), dv);
+      if (act) {
+        float pre[8];
 #pragma unroll
-  for (int j = 0; j < W - 1; ++j) {
-    const int t = t0 - (W - 1) + j;
-    if (t >= 0 && t < T) load8(x + (b * T + t) * ldx + c, xw[j + 1]);
-    else {
+        for (int k = 0; k < 8; ++k) pre[k] = bv[k];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) xw[j + 1][k] = 0.f;
-    }
-  }
-  // raw rows of x and dy are fetched PF steps ahead: with about 150 registers per thread few warps
-  // fit on an SM, so the loads in flight per thread decide the achieved bandwidth
-  constexpr int PF = 3;
-  uint4 xq[PF], yq[PF];
+        for (int j = 0; j < W; ++j) {
+          float xv[8];
+          unpack8(*reinterpret_cast<const uint4*>(sx + (i + j) * CT_C + c8 * 8), xv);
 #pragma unroll
-  for (int i = 0; i < PF; ++i) {
-    const int t = t0 + i;
-    if (t < T) {
-      xq[i] = *reinterpret_cast<const uint4*>(x + (b * T + t) * ldx + c);
-      yq[i] = *reinterpret_cast<const uint4*>(dy + (b * T + t) * C + c);
-    } else { xq[i] = make_uint4(0, 0, 0, 0); yq[i] = make_uint4(0, 0, 0, 0); }
-  }
-  for (int tt = 0; tt < CONV_TCHUNK + W - 1; ++tt) {
-    const int t = t0 + tt;
-#pragma unroll
-    for (int j = 0; j < W - 1; ++j)
-#pragma unroll
-      for (int k = 0; k < 8; ++k) xw[j][k] = xw[j + 1][k];
-#pragma unroll
-    for (int j = W - 1; j > 0; --j)
-#pragma unroll
-      for (int k = 0; k < 8; ++k) dq[j][k] = dq[j - 1][k];
-    const uint4 xr = xq[0], yr = yq[0];
-#pragma unroll
-    for (int i = 0; i < PF - 1; ++i) { xq[i] = xq[i + 1]; yq[i] = yq[i + 1]; }
-    {
-      const int tn = t + PF;
-      if (tt + PF < CONV_TCHUNK + W - 1 && tn < T) {
-        xq[PF - 1] = *reinterpret_cast<const uint4*>(x + (b * T + tn) * ldx + c);
-        yq[PF - 1] = *reinterpret_cast<const uint4*>(dy + (b * T + tn) * C + c);
-      }
-    }
-    if (t < T) {
-      unpack8(xr, xw[W - 1]);
-      float dv[8];
-      unpack8(yr, dv);
-#pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        float pre = bv[k];
-#pragma unroll
-        for (int j = 0; j < W; ++j) pre += wv[j][k] * xw[j][k];
-        const float dp = act ? dv[k] * dsilu_f(pre) : dv[k];
-        dq[0][k] = dp;
-        if (tt < CONV_TCHUNK) {          // each time step's weight gradient is counted by one chunk only
-          dbacc[k] += dp;
-#pragma unroll
-          for (int j = 0; j < W; ++j) dwacc[j][k] += dp * xw[j][k];
+          for (int k = 0; k < 8; ++k) pre[k] += wv[j][k] * xv[k];
         }
-      }
-    } else {
 #pragma unroll
-      for (int k = 0; k < 8; ++k) { dq[0][k] = 0.f; xw[W - 1][k] = 0.f; }
+        for (int k = 0; k < 8; ++k) dp[k] = dv[k] * dsilu_f(pre[k]);
+      } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) dp[k] = dv[k];
+      }
+      float4* d4 = reinterpret_cast<float4*>(sdp + i * CT_C + c8 * 8);
+      d4[0] = make_float4(dp[0], dp[1], dp[2], dp[3]);
+      d4[1] = make_float4(dp[4], dp[5], dp[6], dp[7]);
     }
-    // dx at time s = t - (W-1): sum_j w[j] * dpre[s + (W-1) - j] = sum_j w[j] * dq[j]
-    const int s = t - (W - 1);
-    if (s >= t0 && s < t0 + CONV_TCHUNK && s < T) {
+    __syncthreads();
+    // ---- dx, and this thread's share of dw / db (its rows only)
+    for (int i = rg; i < CT_T; i += CT_RG) {
+      const int t = t0 + i;
+      if (t >= T) break;
       float o[8];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        float acc = 0.f;
+      for (int k = 0; k < 8; ++k) o[k] = 0.f;
 #pragma unroll
-        for (int j = 0; j < W; ++j) acc += wv[j][k] * dq[j][k];
-        o[k] = acc;
+      for (int j = 0; j < W; ++j) {
+        const float4* d4 = reinterpret_cast<const float4*>(sdp + (i + (W - 1) - j) * CT_C + c8 * 8);
+        const float4 a = d4[0], e = d4[1];
+        const float dq[8] = {a.x, a.y, a.z, a.w, e.x, e.y, e.z, e.w};
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o[k] += wv[j][k] * dq[k];
       }
-      store8(dx + (b * T + s) * C + c, o);
+      if (c_ok) store8(dx + (b * T + t) * C + c, o);
+      const float4* p4 = reinterpret_cast<const float4*>(sdp + i * CT_C + c8 * 8);
+      const float4 a = p4[0], e = p4[1];
+      const float dp[8] = {a.x, a.y, a.z, a.w, e.x, e.y, e.z, e.w};
+#pragma unroll
+      for (int k = 0; k < 8; ++k) dbacc[k] += dp[k];
+#pragma unroll
+      for (int j = 0; j < W; ++j) {
+        float xv[8];
+        unpack8(*reinterpret_cast<const uint4*>(sx + (i + j) * CT_C + c8 * 8), xv);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) dwacc[j][k] += dp[k] * xv[k];
+      }
     }
+    __syncthreads();                                // sdp and this buffer are rewritten next
   }
-  const long chunk = static_cast<long>(blockIdx.z) * gridDim.y + blockIdx.y;
-  float* pp = partial + chunk * (W + 1) * C;
+  // ---- the two row groups of a warp meet by shuffle, the warps through shared memory, in a fixed order
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
+    dbacc[k] += __shfl_xor_sync(0xffffffffu, dbacc[k], 16);
 #pragma unroll
-    for (int j = 0; j < W; ++j) pp[static_cast<long>(j) * C + c + k] = dwacc[j][k];
-    pp[static_cast<long>(W) * C + c + k] = dbacc[k];
+    for (int j = 0; j < W; ++j) dwacc[j][k] += __shfl_xor_sync(0xffffffffu, dwacc[j][k], 16);
+  }
+  const int warp = threadIdx.x >> 5;
+  if ((threadIdx.x & 31) < 16) {
+#pragma unroll
+    for (int j = 0; j <= W; ++j) {
+      float4* d4 = reinterpret_cast<float4*>(sred + (warp * (W + 1) + j) * CT_C + c8 * 8);
+      if (j < W) {
+        d4[0] = make_float4(dwacc[j][0], dwacc[j][1], dwacc[j][2], dwacc[j][3]);
+        d4[1] = make_float4(dwacc[j][4], dwacc[j][5], dwacc[j][6], dwacc[j][7]);
+      } else {
+        d4[0] = make_float4(dbacc[0], dbacc[1], dbacc[2], dbacc[3]);
+        d4[1] = make_float4(dbacc[4], dbacc[5], dbacc[6], dbacc[7]);
+      }
+    }
+  }
+  __syncthreads();
+  const long chunk = static_cast<long>(blockIdx.z) * gridDim.y + blockIdx.y;
+  float* pp = partial + chunk * (W + 1) * C;
+  for (int e = threadIdx.x; e < (W + 1) * CT_C; e += CT_THREADS) {
+    const int j = e / CT_C, cc = e - j * CT_C;
+    const int cg = blockIdx.x * CT_C + cc;
+    if (cg >= C) continue;
+    float acc = 0.f;
+#pragma unroll
+    for (int wi = 0; wi < CT_THREADS / 32; ++wi) acc += sred[(wi * (W + 1) + j) * CT_C + cc];
+    pp[static_cast<long>(j) * C + cg] = acc;
   }
 }
 
@@ -1427,8 +1496,8 @@ extern "C" int nsa_rope(const void* x, const float* cos_t, const float* sin_t, v
 extern "C" int nsa_conv1d_fwd(const void* x, const void* w, const void* bias, void* y, int B, int T, int C, long ldx,
                               int width, int act, cudaStream_t st) {
   if (C % 8 || ldx % 8 || width != 4) return nsa::fail(NSA_ERR_SHAPE, "conv1d: channels multiple of 8 and width 4 required");
-  dim3 grid((C / 8 + 127) / 128, (T + CONV_TCHUNK - 1) / CONV_TCHUNK, B);
-  conv1d_fwd_kernel<4><<<grid, 128, 0, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)bias, (bf16*)y, T, C, ldx, act);
+  dim3 grid((C + CT_C - 1) / CT_C, (T + CONV_TCHUNK - 1) / CONV_TCHUNK, B);
+  conv1d_fwd_kernel<4><<<grid, CT_THREADS, 0, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)bias, (bf16*)y, T, C, ldx, act);
   nsa::count_launch();
   return 0;
 }
@@ -1437,9 +1506,17 @@ extern "C" long nsa_conv1d_bwd_parts(int B, int T) { return static_cast<long>(B)
 extern "C" int nsa_conv1d_bwd(const void* x, const void* w, const void* bias, const void* dy, void* dx, float* partial,
                               float* dwdb_f32, int B, int T, int C, long ldx, int width, int act, cudaStream_t st) {
   if (C % 8 || ldx % 8 || width != 4) return nsa::fail(NSA_ERR_SHAPE, "conv1d: channels multiple of 8 and width 4 required");
-  dim3 grid((C / 8 + 127) / 128, (T + CONV_TCHUNK - 1) / CONV_TCHUNK, B);
-  conv1d_bwd_kernel<4><<<grid, 128, 0, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)bias, (const bf16*)dy, (bf16*)dx,
-                                             partial, T, C, ldx, act);
+  dim3 grid((C + CT_C - 1) / CT_C, (T + CONV_TCHUNK - 1) / CONV_TCHUNK, B);
+  constexpr int smem = 2 * (CT_T + 6) * CT_C * 2 + 2 * (CT_T + 3) * CT_C * 2 + (CT_T + 3) * CT_C * 4;
+  static_assert((CT_THREADS / 32) * 5 * CT_C * 4 <= 2 * (CT_T + 6) * CT_C * 2, "conv1d: reduction scratch");
+  static bool cfg = false;
+  if (!cfg) {
+    cudaError_t e = cudaFuncSetAttribute(conv1d_bwd_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return nsa::fail_cuda(e, "conv1d_bwd: shared memory attribute");
+    cfg = true;
+  }
+  conv1d_bwd_kernel<4><<<grid, CT_THREADS, smem, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)bias, (const bf16*)dy, (bf16*)dx,
+                                                       partial, T, C, ldx, act);
   const int parts = static_cast<int>(nsa_conv1d_bwd_parts(B, T));
   reduce_partials_kernel<<<(5 * C + 255) / 256, 256, 0, st>>>(partial, parts, 5 * C, nullptr, dwdb_f32);
   nsa::count_launch(2);
