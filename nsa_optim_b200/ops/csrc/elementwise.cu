@@ -292,6 +292,27 @@ __global__ void reduce_partials_kernel(const float* __restrict__ partial, int pa
   if (out_f32) out_f32[c] = s;
 }
 
+// out[o][i] = sum_p in[o][p][i] over bf16 partial results, summed in fp32 in ascending p (the same
+// bits on every run), 8 elements per thread.
+__global__ void __launch_bounds__(256) sum_parts_bf16_kernel(const bf16* __restrict__ in, bf16* __restrict__ out,
+                                                             int parts, long n8, long outer) {
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8 * outer;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long o = i / n8, e = i - o * n8;
+    const uint4* src = reinterpret_cast<const uint4*>(in) + (o * parts) * n8 + e;
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+    for (int p = 0; p < parts; ++p) {
+      float v[8];
+      unpack8(src[static_cast<long>(p) * n8], v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += v[k];
+    }
+    store8(out + i * 8, acc);
+  }
+}
+
 // ------------------------------------------------------------------------------------
 // L2 norm over the last dimension (d <= 512, warp per row)
 // ------------------------------------------------------------------------------------
@@ -1480,6 +1501,15 @@ extern "C" int nsa_gdn_tmat_bwd(const float* dA, const void* kk, const void* qkr
   if (n_chunks <= 0 || n_chunks > 2147483647L) return nsa::fail(NSA_ERR_SHAPE, "gdn_tmat: bad chunk count");
   gdn_tmat_bwd_kernel<<<(unsigned)n_chunks, 64, 0, st>>>(dA, (const bf16*)kk, (const bf16*)qkr, (const bf16*)dqk, (const bf16*)dTu,
                                                         (const bf16*)dTw, X, gc, beta, (bf16*)dkk, (bf16*)dqkr, dgc, dbeta, scale);
+  nsa::count_launch();
+  return 0;
+}
+
+// in: [outer][parts][n] bf16 contiguous -> out: [outer][n] bf16 (n a multiple of 8).
+extern "C" int nsa_sum_parts_bf16(const void* in, void* out, long outer, int parts, long n, cudaStream_t st) {
+  if (n % 8 || parts <= 0) return nsa::fail(NSA_ERR_SHAPE, "sum_parts: width must be a multiple of 8");
+  const long total = outer * (n / 8);
+  sum_parts_bf16_kernel<<<grid_for(total, 256), 256, 0, st>>>((const bf16*)in, (bf16*)out, parts, n / 8, outer);
   nsa::count_launch();
   return 0;
 }

@@ -844,7 +844,8 @@ class _GDNSeq(torch.autograd.Function):
         _check(load().nsa_gdn_seq_bwd(_p(w), _p(qd), _p(kt), _p(S_all), _p(v_new), _p(dv), _p(do), _p(gamma), _p(du),
                                       _p(parts[0]), _p(parts[1]), _p(parts[2]), _p(dgp), c_int(BH), c_int(NC),
                                       c_int(K), c_int(V), _stream()))
-        red = parts.sum(1, dtype=torch.float32).to(torch.bfloat16)
+        red = _empty(3, BH, NC, C, K, dtype=torch.bfloat16, device=w.device)
+        _check(load().nsa_sum_parts_bf16(_p(parts), _p(red), c_long(3), c_int(nvt), c_long(BH * NC * C * K), _stream()))
         return red[0], red[1], red[2], du, dgp.sum(0)
 
 
