@@ -161,6 +161,50 @@ def bench_attention(backend: str, T: int, iters: int, window: int = 0) -> List[D
             tf = flops_fwd * mult / (ms * 1e-3) / 1e12
             rows.append({"op": f"attention {name} T={T} window={window} 32q/2kv hd128", "backend": backend, "ms": ms,
                          "tflops": tf, "frac_of_peak": tf / pk["bf16_tflops"], "peak": f"{pk['bf16_tflops']} TFLOP/s of {pk['source']}"})
+    if backend == "native" and window == 0:
+        rows += _attention_library_rows(q, k, v, flops_fwd, iters)
+    return rows
+
+
+def _attention_library_rows(q, k, v, flops_fwd: float, iters: int) -> List[Dict]:
+    """The same problem on the installed library kernels (flash_attn, PyTorch SDPA), local tensors
+    only: the bar the native rows are read against, not a path of the framework."""
+    rows = []
+    T = q.shape[1]
+
+    def add(label, fwd, fb):
+        for name, fn, mult in (("fwd", fwd, 1.0), ("fwd+bwd", fb, 3.5)):
+            try:
+                ms = time_ms(fn, iters)
+            except Exception as e:                       # a library that cannot run this shape here
+                rows.append({"op": f"attention {name} T={T} ({label})", "backend": "library", "unavailable": str(e)[:120]})
+                return
+            rows.append({"op": f"attention {name} T={T} ({label})", "backend": "library", "ms": ms,
+                         "tflops": flops_fwd * mult / (ms * 1e-3) / 1e12})
+
+    try:
+        from flash_attn import flash_attn_func
+
+        def fa_fwd():
+            with torch.no_grad():
+                flash_attn_func(q, k, v, causal=True)
+
+        def fa_fb():
+            o = flash_attn_func(q, k, v, causal=True)
+            o.backward(torch.ones_like(o))
+        add("flash_attn", fa_fwd, fa_fb)
+    except ImportError:
+        pass
+    qs, ks, vs = (t.transpose(1, 2) for t in (q, k, v))
+
+    def sd_fwd():
+        with torch.no_grad():
+            torch.nn.functional.scaled_dot_product_attention(qs, ks, vs, is_causal=True, enable_gqa=True)
+
+    def sd_fb():
+        o = torch.nn.functional.scaled_dot_product_attention(qs, ks, vs, is_causal=True, enable_gqa=True)
+        o.backward(torch.ones_like(o))
+    add("torch SDPA", sd_fwd, sd_fb)
     return rows
 
 
