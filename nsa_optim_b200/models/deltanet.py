@@ -64,7 +64,11 @@ class GatedDeltaNetMixer(nn.Module):
     def forward(self, x: Tensor) -> Tensor:
         B, T, _ = x.shape
         H, K, V = self.num_heads, self.head_k_dim, self.head_v_dim
-        q, k, v = self.q_proj(x), self.k_proj(x), self.v_proj(x)
+        ws = [self.q_proj.weight, self.k_proj.weight, self.v_proj.weight, self.b_proj.weight, self.a_proj.weight]
+        if self.use_gate:
+            ws.append(self.g_proj.weight)
+        outs = ops.multi_linear(x, ws)           # one input, its gradient summed inside the GEMM epilogues
+        q, k, v = outs[0], outs[1], outs[2]
         if self.use_short_conv:
             q = ops.causal_conv1d(q, self.q_conv1d.weight.squeeze(1), None, activation=True)
             k = ops.causal_conv1d(k, self.k_conv1d.weight.squeeze(1), None, activation=True)
@@ -74,11 +78,11 @@ class GatedDeltaNetMixer(nn.Module):
         q = ops.l2_norm(q.view(B, T, H, K))
         k = ops.l2_norm(k.view(B, T, H, K))
         v = v.view(B, T, H, V)
-        beta = torch.sigmoid(self.b_proj(x).float())
-        g = -torch.exp(self.A_log.float()) * F.softplus(self.a_proj(x).float() + self.dt_bias.float())
+        beta = torch.sigmoid(outs[3].float())
+        g = -torch.exp(self.A_log.float()) * F.softplus(outs[4].float() + self.dt_bias.float())
         o = ops.gated_delta_rule(q, k, v, g, beta, scale=K ** -0.5, chunk=self.chunk_size)
         if self.use_gate:
-            gate = self.g_proj(x).view(B, T, H, V)
+            gate = outs[5].view(B, T, H, V)
             o = ops.gated_rms_norm(o, gate, self.o_norm.weight, self.norm_eps, norm_before_gate=True)
         else:
             o = self.o_norm(o)

@@ -160,14 +160,17 @@ class AttentionBlock(nn.Module):
     def attend(self, x: Tensor, position_ids=None) -> Tensor:
         """The attention mixer on the normed input: projections, RoPE, attention, output projection."""
         B, T, _ = x.shape
-        q = self.q_proj(x).view(B, T, self.num_heads, self.head_dim)
-        k = self.k_proj(x).view(B, T, self.num_kv_heads, self.head_dim)
-        v = self.v_proj(x).view(B, T, self.num_kv_heads, self.head_dim)
+        ws = [self.q_proj.weight, self.k_proj.weight, self.v_proj.weight]
+        if self.sparse:
+            ws.append(torch.cat([self.gate_cmp.weight, self.gate_slc.weight, self.gate_swa.weight], 0))
+        outs = ops.multi_linear(x, ws)           # one input, its gradient summed inside the GEMM epilogues
+        q = outs[0].view(B, T, self.num_heads, self.head_dim)
+        k = outs[1].view(B, T, self.num_kv_heads, self.head_dim)
+        v = outs[2].view(B, T, self.num_kv_heads, self.head_dim)
         cos, sin = self.rotary_emb(x, position_ids, seq_len=T)
         q, k = apply_rotary_pos_emb(q, k, cos, sin)
         if self.sparse:
-            w = torch.cat([self.gate_cmp.weight, self.gate_slc.weight, self.gate_swa.weight], 0)
-            o = ops.nsa_attention(q, k, v, None, None, None, gate_logits=ops.linear(x, w), **self.nsa)
+            o = ops.nsa_attention(q, k, v, None, None, None, gate_logits=outs[3], **self.nsa)
         else:
             o = ops.attention(q, k, v, causal=True)
         return self.o_proj(o.reshape(B, T, self.num_heads * self.head_dim))

@@ -151,7 +151,8 @@ class MLP(nn.Module):
 
     def forward(self, x: Tensor) -> Tensor:
         with _ctx(self.kernel_type):
-            return self.down_proj(ops.swiglu(self.gate_proj(x), self.up_proj(x)))
+            g, u = ops.multi_linear(x, (self.gate_proj.weight, self.up_proj.weight))
+            return self.down_proj(ops.swiglu(g, u))
 
 
 def create_rms_norm(hidden_size: int, eps: float = 1e-6, kernel_type: KernelType = "liger") -> nn.Module:

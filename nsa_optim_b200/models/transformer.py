@@ -60,9 +60,10 @@ class DenseAttention(nn.Module):
 
     def _qkv(self, x: Tensor, position_ids: Optional[Tensor]):
         B, T, _ = x.shape
-        q = self.q_proj(x).view(B, T, self.num_heads, self.head_dim)
-        k = self.k_proj(x).view(B, T, self.num_kv_heads, self.head_dim)
-        v = self.v_proj(x).view(B, T, self.num_kv_heads, self.head_dim)
+        q, k, v = ops.multi_linear(x, (self.q_proj.weight, self.k_proj.weight, self.v_proj.weight))
+        q = q.view(B, T, self.num_heads, self.head_dim)
+        k = k.view(B, T, self.num_kv_heads, self.head_dim)
+        v = v.view(B, T, self.num_kv_heads, self.head_dim)
         cos, sin = self.rotary_emb(x, position_ids, seq_len=T)
         q, k = apply_rotary_pos_emb(q, k, cos, sin)
         return q, k, v

@@ -106,6 +106,15 @@ def linear(x: Tensor, weight: Tensor) -> Tensor:
     return torch_impl.linear(x, weight)
 
 
+def multi_linear(x: Tensor, weights) -> tuple:
+    """Projections of one input by several weights, (x W_0^T, x W_1^T, ...).  On the native backend
+    the input gradient is accumulated inside the GEMM epilogues instead of by separate additions."""
+    weights = list(weights)
+    if _library(x) is None and _use_native(x, "linear"):
+        return native_module().multi_linear(x, weights)
+    return tuple(linear(x, w) for w in weights)
+
+
 def rms_norm(x: Tensor, weight: Tensor, eps: float = 1e-6) -> Tensor:
     if _library(x) is not None:
         y = _library(x).rms_norm(x, weight, eps)

@@ -785,8 +785,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           }
           tc5::fence_proxy_async();
           __syncwarp();
-          if (lane == 0) {
-            tc5::tma_store_2d(&tmap_c, box, col, row0);   // rows past M and columns past N are clipped
+          if (lane == 0) {                         // rows past M and columns past N are clipped
+            if (tma_store == 3) tc5::tma_reduce_add_2d(&tmap_c, box, col, row0);   // C += tile, added in bf16 by the memory system
+            else tc5::tma_store_2d(&tmap_c, box, col, row0);
             tc5::tma_store_commit();
           }
           ++boxes;
@@ -902,8 +903,10 @@ extern "C" int nsa_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   p.out_fp32 = out_fp32; p.accumulate = accumulate; p.split_k = 1; p.C = C; p.status = nsa::status_ptr();
   cudaError_t e;
   if (pairk) {
-    // bf16 output without accumulation leaves through TMA stores when C allows a tensor map
-    const int tma_store = (!out_fp32 && !accumulate && (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (ldc & 7) == 0) ? 1 : 0;
+    // bf16 output leaves through TMA stores when C allows a tensor map; with `accumulate` the stores
+    // are TMA reduce-adds (each element gets one bf16 add per launch, so launches on one stream
+    // give the same bits every run)
+    const int tma_store = (!out_fp32 && (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (ldc & 7) == 0) ? (accumulate ? 3 : 1) : 0;
     if (tma_store) {
       if ((rc = nsa::make_tmap_2d_bf16(&tc, C, N, M, ldc, 64, 32))) return rc;
     } else {

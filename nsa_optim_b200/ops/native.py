@@ -297,6 +297,61 @@ class _Linear(torch.autograd.Function):
         return dx, dw
 
 
+class _MultiLinear(torch.autograd.Function):
+    """Several projections of one input, y_i = x W_i^T.  The forward is one GEMM per weight; the
+    backward builds dx = sum_i dy_i W_i in place (the first GEMM stores, the others add through the
+    epilogue's TMA reduce-add) instead of leaving len(ws) - 1 full-size additions to autograd."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, run_first, *ws: Tensor):
+        x2 = _as_2d(x)
+        ctx.save_for_backward(x2, *ws)
+        ctx.xshape = x.shape
+        ys = []
+        for i, w in enumerate(ws):
+            y = run_first(x2, w) if (i == 0 and run_first is not None) else gemm(x2, w, False, False)
+            ys.append(y.view(*x.shape[:-1], w.shape[0]))
+        return tuple(ys)
+
+    @staticmethod
+    def backward(ctx, *dys):
+        x2, *ws = ctx.saved_tensors
+        dx = None
+        dws = []
+        for i, (dy, w) in enumerate(zip(dys, ws)):
+            if dy is None:
+                dws.append(None)
+                continue
+            dy2 = _as_2d(dy)
+            if ctx.needs_input_grad[0]:
+                if dx is None:
+                    dx = gemm(dy2, w, False, True)
+                else:
+                    gemm(dy2, w, False, True, out=dx, accumulate=True, split_k=1)
+            dws.append(gemm(dy2, x2, True, True) if ctx.needs_input_grad[2 + i] else None)
+        if dx is not None:
+            dx = dx.view(ctx.xshape)
+        return (dx, None) + tuple(dws)
+
+
+def multi_linear(x: Tensor, ws) -> tuple:
+    """(x W_0^T, x W_1^T, ...) for weights that share the input (see :class:`_MultiLinear`)."""
+    ws = list(ws)
+    if (x.shape[-1] % 8) or any(w.shape[0] % 8 for w in ws) or x.shape[0] == 0:
+        return tuple(linear(x, w) for w in ws)
+    rows = x.numel() // x.shape[-1]
+    if rows <= 128:                        # the single-CTA kernel has no adding epilogue
+        return tuple(linear(x, w) for w in ws)
+    run = None
+    pg = _pending_gather
+    if pg is not None:
+        if pg[0] <= ws[0].data_ptr() < pg[1] and ws[0].is_contiguous():
+            run = pg[2]
+        else:
+            flush_pending_gather()
+    return _MultiLinear.apply(x, run, *ws)
+
+
 # A sharded unit may defer its all-gather to the first matmul that touches one of its weights:
 # (lo, hi) is the address range of the unit's gathered buffer, ``run(x, w)`` launches the GEMM
 # whose kernel also assembles that buffer, ``fallback()`` gathers it without a matmul.

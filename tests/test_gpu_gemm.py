@@ -141,3 +141,42 @@ def test_linear_autograd(native):
     yr.backward(g.float())
     for got, ref in ((y, yr), (x.grad, xr.grad), (w.grad, wr.grad)):
         assert (got.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2
+
+
+def test_gemm_bf16_accumulate_through_tma_reduce(native):
+    """C += A B^T with bf16 C: the pair kernel's epilogue adds its tiles through TMA reduce stores."""
+    torch.manual_seed(3)
+    M, N, K = 1000, 520, 256
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16()
+    c0 = torch.randn(M, N, device="cuda").bfloat16()
+    c = c0.clone()
+    native.gemm(a, b, False, False, out=c, accumulate=True, split_k=1)
+    ref = c0.float() + a.float() @ b.float().t()
+    assert (c.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()
+    c2 = c0.clone()
+    native.gemm(a, b, False, False, out=c2, accumulate=True, split_k=1)
+    assert torch.equal(c, c2)
+
+
+def test_multi_linear_matches_separate_linears(native):
+    torch.manual_seed(4)
+    T, d = 700, 256
+    x = torch.randn(1, T, d, device="cuda").bfloat16().requires_grad_()
+    ws = [torch.randn(n, d, device="cuda").bfloat16().mul(0.05).requires_grad_() for n in (512, 64, 64, 24)]
+    gs = [torch.randn(1, T, w.shape[0], device="cuda").bfloat16() for w in ws]
+    ys = native.multi_linear(x, ws)
+    torch.autograd.backward(ys, gs)
+    dx, dws = x.grad.clone(), [w.grad.clone() for w in ws]
+    x.grad = None
+    for w in ws:
+        w.grad = None
+    ys2 = [native.linear(x, w) for w in ws]
+    torch.autograd.backward(ys2, gs)
+    for y, y2 in zip(ys, ys2):
+        assert torch.equal(y, y2)
+    for dw, w in zip(dws, ws):
+        assert torch.equal(dw, w.grad)
+    ref = sum(g.float().view(T, -1) @ w.float() for g, w in zip(gs, ws)).view(1, T, d)
+    assert (dx.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2
+    assert (x.grad.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2
