@@ -94,14 +94,14 @@ struct FwdParams {
   const bf16* u;        // [BH, NC, 64, V]
   const float* gamma;   // [BH, NC]
   bf16* v_new;          // [BH, NC, 64, V]
-  float* o_inter;       // [BH, NC, 64, V]
+  bf16* o_inter;        // [BH, NC, 64, V]  (rounded once here: it is added to a bf16 product next)
   bf16* S_all;          // [BH, NC, KD, V]  state entering each chunk
   int NC, V;
   KernelStatus* status;
 };
 
 constexpr int FWD_STAGE = 2 * 2 * BOX /*[w;qd] two k-blocks*/ + 2 * BOX /*k_tail*/;   // 48 KB
-constexpr int FWD_SMEM = 2 * FWD_STAGE + 2 * BOX /*Sb*/ + BOX /*Vb*/ + 2 * BOX /*Ob*/ + 1024 + 128;
+constexpr int FWD_SMEM = 2 * FWD_STAGE + 2 * BOX /*Sb*/ + BOX /*Vb*/ + BOX /*Ob*/ + 1024 + 128;
 
 __global__ void __launch_bounds__(128, 1)
 gdn_seq_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_qd,
@@ -112,8 +112,8 @@ gdn_seq_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* Sb = smem + 2 * FWD_STAGE;           // [KD rows][64] bf16, B operand of MMA1
   uint8_t* Vb = Sb + 2 * BOX;                   // [64 rows][64] bf16, B operand of MMA2
-  uint8_t* Ob = Vb + BOX;                       // [2 column halves][64 rows][32] fp32: o_inter on its way out
-  uint64_t* bars = reinterpret_cast<uint64_t*>(Ob + 2 * BOX);
+  uint8_t* Ob = Vb + BOX;                       // [64 rows][64] bf16: o_inter on its way out
+  uint64_t* bars = reinterpret_cast<uint64_t*>(Ob + BOX);
   uint64_t* full = bars;        // [2]
   uint64_t* m1 = bars + 2;
   uint64_t* m2 = bars + 3;
@@ -236,13 +236,9 @@ gdn_seq_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         pack_row(d1, pk);
         write_row_swz(Vb, r, pk);
       } else {
-        const int rr = r - CH;
-#pragma unroll
-        for (int half = 0; half < 2; ++half)
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            *reinterpret_cast<float4*>(Ob + half * BOX + rr * 128 + ((j ^ (rr & 7)) << 4)) =
-                make_float4(d1[half * 32 + 4 * j], d1[half * 32 + 4 * j + 1], d1[half * 32 + 4 * j + 2], d1[half * 32 + 4 * j + 3]);
+        uint32_t pk[32];
+        pack_row(d1, pk);
+        write_row_swz(Ob, r - CH, pk);
       }
     }
     tc5::fence_proxy_async();
@@ -251,7 +247,6 @@ gdn_seq_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     if (r == 0) {
       tc5::tma_store_2d(&tm_vn, Vb, vt * VT, static_cast<int>(row0));
       tc5::tma_store_2d(&tm_oi, Ob, vt * VT, static_cast<int>(row0));
-      tc5::tma_store_2d(&tm_oi, Ob + BOX, vt * VT + 32, static_cast<int>(row0));
       tc5::tma_store_commit();
     }
     if (warp == 0) {
@@ -582,9 +577,9 @@ int make_rows_map(CUtensorMap* m, const void* base, long rows, int cols, int box
 }  // namespace
 
 // w, qd, kt: [BH*NC*64, 128] bf16; u: [BH*NC*64, V] bf16; gamma: [BH*NC] fp32.
-// Outputs: v_new [BH*NC*64, V] bf16, o_inter [BH*NC*64, V] fp32, S_all [BH*NC*128, V] bf16.
+// Outputs: v_new [BH*NC*64, V] bf16, o_inter [BH*NC*64, V] bf16, S_all [BH*NC*128, V] bf16.
 extern "C" int nsa_gdn_seq_fwd(const void* w, const void* qd, const void* kt, const void* u, const float* gamma,
-                               void* v_new, float* o_inter, void* S_all, int BH, int NC, int K, int V,
+                               void* v_new, void* o_inter, void* S_all, int BH, int NC, int K, int V,
                                cudaStream_t st) {
   if (K != KD || V % VT) return nsa::fail(NSA_ERR_SHAPE, "gdn: key width must be 128 and value width a multiple of 64");
   CUtensorMap tw, tq, tk;
@@ -595,9 +590,9 @@ extern "C" int nsa_gdn_seq_fwd(const void* w, const void* qd, const void* kt, co
   if ((rc = make_rows_map(&tk, kt, rows, KD, 64))) return rc;
   CUtensorMap tvn, toi, tsa;
   if ((rc = make_rows_map(&tvn, v_new, rows, V, CH))) return rc;
-  if ((rc = nsa::make_tmap_2d_f32(&toi, o_inter, V, rows, V, 32, CH))) return rc;
+  if ((rc = make_rows_map(&toi, o_inter, rows, V, CH))) return rc;
   if ((rc = make_rows_map(&tsa, S_all, static_cast<long>(BH) * NC * KD, V, KD))) return rc;
-  FwdParams p{(const bf16*)u, gamma, (bf16*)v_new, o_inter, (bf16*)S_all, NC, V, nsa::status_ptr()};
+  FwdParams p{(const bf16*)u, gamma, (bf16*)v_new, (bf16*)o_inter, (bf16*)S_all, NC, V, nsa::status_ptr()};
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gdn_seq_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM);

@@ -112,7 +112,7 @@ int nsa_gate_combine_bwd(const void* o1, const void* o2, const void* o3, const v
 
 /* ---- Gated DeltaNet state recurrence (csrc/gdn.cu) ---- */
 int nsa_gdn_seq_fwd(const void* w, const void* qd, const void* kt, const void* u, const float* gamma, void* v_new,
-    float* o_inter, void* S_all, int BH, int NC, int K, int V, cudaStream_t st);
+    void* o_inter, void* S_all, int BH, int NC, int K, int V, cudaStream_t st);   /* o_inter: bf16 */
 int nsa_gdn_seq_bwd(const void* w, const void* qd, const void* kt, const void* S_all, const void* v_new, const void*
     dv_new, const void* d_o, const float* gamma, void* du, void* dw_part, void* dqd_part, void* dkt_part, float*
     dgamma_part, int BH, int NC, int K, int V, cudaStream_t st);

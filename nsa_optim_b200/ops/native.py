@@ -876,14 +876,14 @@ class _GDNSeq(torch.autograd.Function):
         BH, NC, C, K = w.shape
         V = u.shape[-1]
         v_new = _empty_like(u)
-        o_inter = _empty(BH, NC, C, V, dtype=torch.float32, device=u.device)
+        o_inter = _empty(BH, NC, C, V, dtype=torch.bfloat16, device=u.device)
         S_all = _empty(BH, NC, K, V, dtype=torch.bfloat16, device=u.device)
         _check(load().nsa_gdn_seq_fwd(_p(w), _p(qd), _p(kt), _p(u), _p(gamma), _p(v_new), _p(o_inter), _p(S_all),
                                       c_int(BH), c_int(NC), c_int(K), c_int(V), _stream()))
         ctx.save_for_backward(w, qd, kt, gamma, S_all, v_new)
-        # handed on as bf16 (it is added to a bf16 matmul result next), so its gradient also arrives
-        # as bf16 instead of making an fp32 round trip
-        return v_new, o_inter.to(torch.bfloat16)
+        # o_inter leaves the kernel as bf16 (it is added to a bf16 matmul result next), so its gradient
+        # also arrives as bf16 instead of making an fp32 round trip
+        return v_new, o_inter
 
     @staticmethod
     def backward(ctx, dv_new, do_inter):
