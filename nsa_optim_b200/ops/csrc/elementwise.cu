@@ -313,6 +313,31 @@ __global__ void __launch_bounds__(256) sum_parts_bf16_kernel(const bf16* __restr
   }
 }
 
+// Rows of D bf16 between head-major (B, H, Ts, D) and token-major (B, Tt, H, D) storage, one warp per
+// row: to_token = 1 reads (b, h, t) and writes (b, t, h); to_token = 0 the reverse.  Only t < min(Ts, Tt)
+// is copied; when the destination is head-major and longer, its rows t >= Tt are zeroed.
+__global__ void __launch_bounds__(256) permute_rows_kernel(const bf16* __restrict__ src, bf16* __restrict__ dst, int B, int H,
+                                                           int Th, int Tt, int D, int to_token) {
+  const int d8 = D / 8;
+  const int Tloop = to_token ? Tt : Th;            // rows of the destination per (b, h)
+  const long rows = static_cast<long>(B) * H * Tloop;
+  const int lane = threadIdx.x & 31;
+  for (long row = static_cast<long>(blockIdx.x) * 8 + (threadIdx.x >> 5); row < rows; row += static_cast<long>(gridDim.x) * 8) {
+    long b, h, t;
+    if (to_token) { b = row / (static_cast<long>(Tt) * H); const long r2 = row - b * Tt * H; t = r2 / H; h = r2 - t * H; }
+    else { b = row / (static_cast<long>(H) * Th); const long r2 = row - b * H * Th; h = r2 / Th; t = r2 - h * Th; }
+    const bf16* hp = (to_token ? src : dst) + ((b * H + h) * Th + t) * D;     // head-major address
+    const bf16* tp = (to_token ? dst : src) + ((b * Tt + t) * H + h) * D;     // token-major address
+    if (to_token) {
+      if (t < Th)
+        for (int j = lane; j < d8; j += 32) reinterpret_cast<uint4*>(const_cast<bf16*>(tp))[j] = reinterpret_cast<const uint4*>(hp)[j];
+    } else {
+      for (int j = lane; j < d8; j += 32)
+        reinterpret_cast<uint4*>(const_cast<bf16*>(hp))[j] = t < Tt ? reinterpret_cast<const uint4*>(tp)[j] : make_uint4(0, 0, 0, 0);
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------
 // L2 norm over the last dimension (d <= 512, warp per row)
 // ------------------------------------------------------------------------------------
@@ -1501,6 +1526,16 @@ extern "C" int nsa_gdn_tmat_bwd(const float* dA, const void* kk, const void* qkr
   if (n_chunks <= 0 || n_chunks > 2147483647L) return nsa::fail(NSA_ERR_SHAPE, "gdn_tmat: bad chunk count");
   gdn_tmat_bwd_kernel<<<(unsigned)n_chunks, 64, 0, st>>>(dA, (const bf16*)kk, (const bf16*)qkr, (const bf16*)dqk, (const bf16*)dTu,
                                                         (const bf16*)dTw, X, gc, beta, (bf16*)dkk, (bf16*)dqkr, dgc, dbeta, scale);
+  nsa::count_launch();
+  return 0;
+}
+
+// Head-major (B, H, Th, D) <-> token-major (B, Tt, H, D) copy of bf16 rows (D a multiple of 8); see the kernel.
+extern "C" int nsa_permute_rows(const void* src, void* dst, int B, int H, int Th, int Tt, int D, int to_token, cudaStream_t st) {
+  if (D % 8) return nsa::fail(NSA_ERR_SHAPE, "permute_rows: width must be a multiple of 8");
+  const long rows = static_cast<long>(B) * H * (to_token ? Tt : Th);
+  if (rows <= 0) return 0;
+  permute_rows_kernel<<<grid_for(rows, 8, 16), 256, 0, st>>>((const bf16*)src, (bf16*)dst, B, H, Th, Tt, D, to_token);
   nsa::count_launch();
   return 0;
 }

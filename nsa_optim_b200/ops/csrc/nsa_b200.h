@@ -45,6 +45,9 @@ int nsa_l2norm_bwd(const void* y, const void* dy, const float* rinv, void* dx, l
 int nsa_swiglu_fwd(const void* g, const void* u, void* y, long rows, int cols, long ldg, long ldu, cudaStream_t st);
 int nsa_swiglu_bwd(const void* g, const void* u, const void* dy, void* dg, void* du, long rows, int cols, long ldg,
                    long ldu, long ldo, cudaStream_t st);
+// bf16 rows between head-major (B, H, Th, D) and token-major (B, Tt, H, D); to_token 1: head -> token (t < Th copied),
+// 0: token -> head (rows t >= Tt zeroed).
+int nsa_permute_rows(const void* src, void* dst, int B, int H, int Th, int Tt, int D, int to_token, cudaStream_t st);
 // out[o][i] = sum over p of in[o][p][i]; bf16 in and out, fp32 sums in ascending p; n a multiple of 8.
 int nsa_sum_parts_bf16(const void* in, void* out, long outer, int parts, long n, cudaStream_t st);
 int nsa_rope(const void* x, const float* cos_t, const float* sin_t, void* y, long batch, int T, int H, int D,

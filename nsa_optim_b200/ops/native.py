@@ -977,6 +977,28 @@ class _GDNTmat(torch.autograd.Function):
         return dkk, dqkr, dgc, dbh, None
 
 
+class _HeadToToken(torch.autograd.Function):
+    """(B*H, Tp, D) head-major rows -> (B, T, H, D) token-major (T <= Tp), one coalesced copy each way
+    (``permute_rows_kernel``) instead of a generic strided copy."""
+
+    @staticmethod
+    def forward(ctx, x, B, H, T):
+        Tp, D = x.shape[-2], x.shape[-1]
+        ctx.dims = (B, H, Tp, T, D)
+        x = x.contiguous()
+        y = _empty(B, T, H, D, dtype=x.dtype, device=x.device)
+        _check(load().nsa_permute_rows(_p(x), _p(y), c_int(B), c_int(H), c_int(Tp), c_int(T), c_int(D), c_int(1), _stream()))
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        B, H, Tp, T, D = ctx.dims
+        dy = dy.to(torch.bfloat16).contiguous()
+        dx = _empty(B * H, Tp, D, dtype=dy.dtype, device=dy.device)
+        _check(load().nsa_permute_rows(_p(dy), _p(dx), c_int(B), c_int(H), c_int(Tp), c_int(T), c_int(D), c_int(0), _stream()))
+        return dx, None, None, None
+
+
 def gated_delta_rule(q, k, v, g, beta, scale=None, chunk=64):
     """Chunkwise gated delta rule.  One layout pass brings q, k, v to head-major chunk rows together
     with the decay-scaled operands; K K^T, Q K^T and the applications of the per-chunk matrices are
@@ -1012,6 +1034,8 @@ def gated_delta_rule(q, k, v, g, beta, scale=None, chunk=64):
     v_new, o_inter = _GDNSeq.apply(w, qd, kt, u, gamma)
     # o = o_inter + qk v_new in one batched GEMM with fp32 accumulation
     o = torch.baddbmm(o_inter.view(-1, C, V), qk.view(-1, C, C), v_new.view(-1, C, V))
+    if o.dtype == torch.bfloat16 and V % 8 == 0:
+        return _HeadToToken.apply(o.view(B * H, Tp, V), B, H, T).to(v.dtype)
     o = o.view(B, H, Tp, V).permute(0, 2, 1, 3)[:, :T]
     return o.to(v.dtype)
 
