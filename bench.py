@@ -297,6 +297,7 @@ def main() -> None:
                        "baseline_note": "vs_baseline divides by the reference's only published number (11589 tok/s, 0.5B MDMA, "
                                         "8K context, unnamed 32 GB GPU); it is not the same config"},
             "clocks": clocks, "gpu_launches": launches, "final_loss": final_loss,
+            "loss_finite": bool(final_loss == final_loss and abs(final_loss) != float("inf")),
             "repeats_ms_per_step": [round(x / K, 3) for x in dev_ms], "region_order": "device, e2e, device, e2e",
             "torch_fallback_calls": fallbacks,
             "native_ops": sorted(native.SUPPORTED) if native is not None else [],
