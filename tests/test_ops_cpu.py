@@ -196,3 +196,22 @@ def test_bracket_table_lookup_equals_binary_search():
             want = blo if (x - cb[blo] <= cb[bhi] - x) else bhi
             assert got == want, (signed, float(x), got, want)
         assert worst <= 8, worst            # the scan stays short where the code book is densest
+
+
+def test_multi_linear_equals_separate_linears_on_the_torch_backend():
+    """``ops.multi_linear`` on CPU tensors is the per-weight ``ops.linear`` (values and gradients)."""
+    from nsa_optim_b200 import ops
+    torch.manual_seed(0)
+    x = torch.randn(2, 5, 16, requires_grad=True)
+    ws = [torch.randn(n, 16, requires_grad=True) for n in (8, 24, 3)]
+    ys = ops.multi_linear(x, ws)
+    assert [tuple(y.shape) for y in ys] == [(2, 5, 8), (2, 5, 24), (2, 5, 3)]
+    sum(y.pow(2).sum() for y in ys).backward()
+    gx, gws = x.grad.clone(), [w.grad.clone() for w in ws]
+    x.grad = None
+    for w in ws:
+        w.grad = None
+    sum(ops.linear(x, w).pow(2).sum() for w in ws).backward()
+    assert torch.allclose(gx, x.grad, atol=1e-5)
+    for a, w in zip(gws, ws):
+        assert torch.allclose(a, w.grad, atol=1e-5)
