@@ -141,6 +141,23 @@ def test_causal_conv1d(native, bias):
         close(b.grad, brr.grad, atol=8e-2)
 
 
+def test_causal_conv1d_many_tiles_and_pitched_input(native):
+    """Several time tiles per CTA (double-buffered loads), two time segments, a partial channel tile
+    and an input that is a column slice of a wider matrix."""
+    B, T, C = 1, 700, 200
+    wide = bf(B, T, C + 56)
+    x = wide[..., 24:24 + C].detach().requires_grad_()
+    w = bf(C, 4, scale=0.5).requires_grad_()
+    b = bf(C, scale=0.5).requires_grad_()
+    y = native.causal_conv1d(x, w, b, True)
+    g = bf(B, T, C)
+    y.backward(g)
+    xr, wr, brr = (t.detach().float().requires_grad_() for t in (x, w, b))
+    yr = oracle.causal_conv1d(xr, wr, brr, True)
+    yr.backward(g.float())
+    close(y, yr); close(x.grad, xr.grad); close(w.grad, wr.grad, atol=2e-1); close(b.grad, brr.grad, atol=2e-1)
+
+
 def test_embedding(native):
     w = bf(500, 64).requires_grad_()
     ids = torch.randint(0, 500, (3, 40), device="cuda")
